@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""MoE-layer throughput benchmark (tokens/s) with roofline and CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode4x44|prefill4096]
+    python bench.py --impl reference ...     # the CPU restatement of the reference's path
+
+One "step" is one pass of the MoE block over one batch of synthetic tokens:
+  decode4x44  (default, N=1): the MTP-verify step, T=4 tokens through all 44 MoE layers
+               (layers 2..45), an independent weight set per layer (55 GB resident), so
+               nothing a step touches is L2-resident when it is touched again.
+  prefill4096: T=4096 tokens through one MoE layer, Zipf(1.2)-skewed routing.
+Rank 0 prints ONE JSON line.  `value` is device-timed with inputs resident in HBM; `e2e` is
+the same metric through the host-buffer C-ABI call, host<->device copies inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+import __graft_entry__ as entry
+
+HIDDEN, INTER, EXPERTS, TOP = 2560, 1024, 256, 8
+EXPERT_BYTES = 3 * (INTER * HIDDEN // 2 + INTER * HIDDEN // 16)        # 4,423,680: packed + scales, 3 matrices
+ROUTER_BYTES = EXPERTS * HIDDEN * 2 + EXPERTS * 4                      # 1,311,744
+SEED = 20261125
+LAYERS = 44
+
+
+def peaks():
+    path = os.path.join(entry.ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a region runs (read-only)."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        self.marks = []
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def mark(self):
+        self.marks.append(time.time())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        lo, hi = (self.marks + [0, 1e18])[:2] if len(self.marks) >= 2 else (0, 1e18)
+        picked = [r for t, r in self.rows if lo <= t <= hi] or [r for _, r in self.rows]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in picked:
+            parts = [p.strip() for p in row.split(",")]
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm: the CPU restatement of the reference's MoE forward on the host cores
+# --------------------------------------------------------------------------------------------
+
+class CpuLayer:
+    """Synthetic layer on the host for the oracle: router/bias/activations, and NVFP4 experts that are
+    drawn (N(0,0.02) -> BF16 -> the oracle's own restatement of the offline quantiser) only when
+    a token is routed to them, since the expert weights do not influence routing."""
+
+    def __init__(self, orc, layer: int, rows: int):
+        self.orc = orc
+        rng = np.random.default_rng([SEED, layer])
+        self.router = orc.f32_to_bf16((rng.standard_normal((EXPERTS, HIDDEN)) * 0.02).astype(np.float32))
+        self.bias = (rng.standard_normal(EXPERTS) * 0.01).astype(np.float32)
+        self.x = orc.f32_to_bf16(rng.standard_normal((rows, HIDDEN)).astype(np.float32))
+        n = (EXPERTS + 1) * 3
+        self.packed = np.empty((n, INTER * HIDDEN // 2), np.uint8)      # untouched pages stay virtual
+        self.scales = np.empty((n, INTER * HIDDEN // 16), np.uint8)
+        self.alpha = np.zeros(n, np.float32)
+        self.have = set()
+        self.layer = layer
+        logits = orc.router_logits(self.x, self.router)
+        ids, _, _ = orc.router_top8(logits, self.bias)
+        for e in sorted(set(ids.reshape(-1).tolist()) | {EXPERTS}):
+            self._draw(e)
+        self.distinct = len(self.have) - 1
+
+    def _draw(self, e: int):
+        rng = np.random.default_rng([SEED, self.layer, 1000 + e])
+        for kind in range(3):
+            shape = (INTER, HIDDEN) if kind < 2 else (HIDDEN, INTER)
+            w = self.orc.f32_to_bf16((rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)))
+            p, s, a = self.orc.nvfp4_pack_weight(w)
+            self.packed[e * 3 + kind] = p.reshape(-1)
+            self.scales[e * 3 + kind] = s.reshape(-1)
+            self.alpha[e * 3 + kind] = a
+        self.have.add(e)
+
+    def forward(self):
+        return self.orc.moe_forward(self.x, self.router, self.bias, self.packed, self.scales, self.alpha, HIDDEN,
+                                    INTER)
+
+
+def run_cpu(args, rows: int, sample_layers: int, total_layers: int, steps: int, warmup: int) -> dict:
+    orc = entry.load_oracle()
+    cores = orc.cpu().orc_threads()
+    layers = [CpuLayer(orc, l, rows) for l in range(sample_layers)]
+    for _ in range(warmup):
+        layers[0].forward()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for layer in layers:
+            layer.forward()
+    dt = (time.perf_counter() - t0) / steps
+    step_time = dt * total_layers / sample_layers
+    return {"value": rows / step_time, "ms_per_step": step_time * 1e3, "cores": cores,
+            "sample": f"{sample_layers} of {total_layers} layers x {rows} tokens per step, {steps} steps, scaled by layer count"}
+
+
+def reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows, total_layers = (4, LAYERS) if args.workload == "decode4x44" else (4096, 1)
+    if args.workload == "decode4x44":
+        sample_layers, sample_rows = 2, rows
+    else:
+        sample_layers, sample_rows = 1, 16          # 16 of the 4096 tokens, scaled by token count
+    steps = max(1, min(args.steps, 3))
+    r = run_cpu(args, sample_rows, sample_layers, total_layers, steps, min(args.warmup, 1))
+    value = r["value"] if sample_rows == rows else r["value"]      # tokens/s is per token either way
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 -> bf16",
+        "data": "synthetic", "config": workload_config(args.workload, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": r["cores"], "kind": "port",
+                         "sample": r["sample"]},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(name: str, gpus: int) -> dict:
+    if name == "decode4x44":
+        return {"workload": "decode MTP-verify: T=4 tokens x 44 MoE layers (hidden 2560, 256+1 experts, FFN 1024, top-8)",
+                "tokens_per_step": 4, "layers": LAYERS, "routing": "bias ~N(0,0.01)", "gpus": gpus,
+                "l2": "44 distinct weight sets (55 GB) cycle per step: inputs larger than L2"}
+    return {"workload": "prefill chunk: T=4096 tokens x 1 MoE layer, Zipf(1.2) routing", "tokens_per_step": 4096,
+            "layers": 1, "routing": "zipf 1.2 (capped at 1/8)", "gpus": gpus,
+            "l2": "1.14 GB of weights per step: inputs larger than L2"}
+
+
+# --------------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------------
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode4x44", choices=["decode4x44", "prefill4096"])
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+
+    pkg = entry.load_package()
+    pkg.load_library()
+    from p92moe_b200 import synth
+
+    decode = args.workload == "decode4x44"
+    rows = 4 if decode else 4096
+    n_layers = args.layers or (LAYERS if decode else 1)
+    layers = [synth.make_layer(SEED + rank, l, bias_mode="normal" if decode else "zipf") for l in range(n_layers)]
+    xs = [synth.make_activations(SEED + rank, l, rows) for l in range(n_layers)]
+    outs = [torch.empty_like(x) for x in xs]
+    plan = pkg.MoePlan(max_rows=rows)
+    blocks = [pkg.MoeBlock(L.bank, L.router_weight, L.bias, plan) for L in layers]
+    torch.cuda.synchronize()
+
+    def step():
+        for b, x, o in zip(blocks, xs, outs):
+            b.run_moe_rows(x, o, rows)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.mark()
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    barrier()
+    if sampler:
+        sampler.mark()
+    ms = start.elapsed_time(stop)
+    launches = plan.last_launches * n_layers * steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    ms_per_step = ms / steps
+    value = world * rows / (ms_per_step * 1e-3)
+
+    # ---- end to end through the host-buffer C-ABI call (pinned host tensors) -----------------
+    host_in = [x.cpu().pin_memory() for x in xs]
+    host_out = [torch.empty_like(h).pin_memory() for h in host_in]
+    e2e_steps = max(3, min(steps, 50))
+    for b, hi, ho in zip(blocks, host_in, host_out):
+        b.run_moe_rows_host(hi, ho, rows)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for b, hi, ho in zip(blocks, host_in, host_out):
+            b.run_moe_rows_host(hi, ho, rows)          # synchronises the stream before returning
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t[0])
+    bytes_io = n_layers * rows * HIDDEN * 2
+    e2e = {"value": world * rows / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": bytes_io,
+           "d2h_bytes_per_step": bytes_io, "ms_per_step": e2e_s * 1e3}
+
+    # ---- per-stage device times (event pairs inside the library) and the roofline -------------
+    plan.stage_timing(True)
+    distinct = []
+    timed_steps = max(2, min(steps, 20))
+    for i in range(timed_steps):
+        for b, x, o in zip(blocks, xs, outs):
+            b.run_moe_rows(x, o, rows)
+            if i == 0:
+                distinct.append(int((plan.views(rows)["counts"] > 0).sum()))
+    stage_ms, calls = plan.stage_times()
+    plan.stage_timing(False)
+    stage_us = {k: v / calls * 1e3 for k, v in stage_ms.items()}
+    d_mean = float(np.mean(distinct))
+    # algorithmic bytes of one gate/up launch: packed weights + scales of gate and up for the distinct
+    # routed experts and the shared expert, the quantised activations read, the quantised SwiGLU rows written
+    gu_bytes = (d_mean + 1) * 2 * (EXPERT_BYTES // 3) + rows * (HIDDEN // 2 + HIDDEN // 16) + \
+        9 * rows * (INTER // 2 + INTER // 16)
+    layer_bytes = (d_mean + 1) * EXPERT_BYTES + ROUTER_BYTES + rows * HIDDEN * 2 * 2
+    pk = peaks()
+    gu_gbs = gu_bytes / (stage_us["gate_up_swiglu"] * 1e-6) / 1e9
+    roofline = {"bound": "hbm", "kernel": "gate_up_stream_kernel", "achieved": gu_gbs, "peak": pk["hbm_gbs"],
+                "unit": "GB/s", "frac": gu_gbs / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                "bytes_per_launch": gu_bytes, "us_per_launch": stage_us["gate_up_swiglu"],
+                "layer_bytes": layer_bytes,
+                "layer_frac_of_hbm": layer_bytes * n_layers / (ms_per_step * 1e-3) / 1e9 / pk["hbm_gbs"],
+                "distinct_routed_experts_mean": d_mean, "stage_us": stage_us}
+
+    if rank == 0:
+        clocks = sampler.stop()
+        cpu = None
+        if not args.no_cpu_baseline:
+            r = run_cpu(args, 4 if decode else 16, 2 if decode else 1, n_layers, 1, 1)
+            cpu = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 -> bf16", "data": "synthetic",
+            "config": workload_config(args.workload, world), "clocks": clocks, "e2e": e2e,
+            "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,196 @@
+/* p92b_moe.h — C ABI of the B200 (sm_100a) MoE block for openPangu-2.0-Flash.
+ *
+ * Drop-in boundary: every entry point stands behind one call of the reference
+ * engine's C++ operator API (include/p92/kernels.h, namespace p92::cuda) or of
+ * ProjectionExecutor / Model::Impl on the MoE path; the citation beside each
+ * declaration names the reference interface it replaces (paths relative to the
+ * reference project).
+ *
+ * Conventions (same as the reference's kernel layer):
+ *   - every pointer is a DEVICE pointer unless its name starts with host_;
+ *   - BF16 is a raw uint16_t (include/p92/kernels.h:10);
+ *   - NVFP4 = two E2M1 values per byte, even element in the low nibble, one
+ *     E4M3 scale per 16 elements along K, one FP32 per-tensor scale (alpha);
+ *   - calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL
+ *     is the default stream) and use the CURRENT device;
+ *   - the return value is a cudaError_t: 0 success, cudaErrorInvalidValue for
+ *     bad arguments, cudaErrorMemoryAllocation, cudaErrorNotSupported, or the
+ *     launch error reported right after the launch
+ *     (cuda/nvfp4_grouped.cu:227-233,313,354-367);
+ *   - *_destroy functions accept NULL and never fail
+ *     (cuda/nvfp4_grouped.cu:176-177,324-326);
+ *   - nothing is thread-safe: a plan carries mutable scratch, one host thread
+ *     and one stream at a time per plan (src/executor.cpp:20-23).
+ * Shapes: hidden and intermediate sizes are run-time arguments (multiples of
+ * 64); the router is fixed at 256 experts / top-8 like the reference
+ * (cuda/nvfp4_ops.cu:365-367).
+ */
+#ifndef P92B_MOE_H
+#define P92B_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define P92B_ROUTED_EXPERTS 256
+#define P92B_TOP_K 8
+
+/* Binary-compatible with p92::cuda::Nvfp4ExpertProjection
+ * (include/p92/kernels.h:12-16): three device pointers. */
+typedef struct p92b_expert_projection {
+    const uint8_t* weight;          /* [rows][columns/2] packed E2M1, K-major */
+    const uint8_t* scales_swizzled; /* E4M3, 128x4-tiled (cuda/nvfp4_ops.cu:869-890) */
+    const float* alpha;             /* device pointer to weight_scale_2 */
+} p92b_expert_projection;
+
+typedef struct p92b_bank p92b_bank; /* one layer's expert weights, retiled and owned by the library */
+typedef struct p92b_plan p92b_plan; /* scratch for up to max_rows tokens; replaces Nvfp4GroupedPlan + executor scratch */
+
+/* ---- element-wise / router operators ------------------------------------ */
+
+/* p92::cuda::bf16_gemv_f32 (include/p92/kernels.h:121-126; cuda/nvfp4_ops.cu:161-176,1019-1030).
+ * Router logits for ONE token, the reference's T=1 summation order. */
+int p92b_bf16_gemv_f32(const uint16_t* input, const uint16_t* weight, float* output, int rows,
+                       int columns, void* stream);
+
+/* p92::cuda::bf16_gemm_f32 (include/p92/kernels.h:128-134; cuda/nvfp4_ops.cu:178-207,1032-1046).
+ * Router logits for batch_rows tokens, the reference's T>1 summation order; output [batch_rows][rows]. */
+int p92b_bf16_gemm_f32(const uint16_t* input, const uint16_t* weight, float* output, int batch_rows,
+                       int rows, int columns, void* stream);
+
+/* p92::cuda::router_top8 / router_top8_rows (include/p92/kernels.h:192-206; cuda/nvfp4_ops.cu:357-433,1160-1186). */
+int p92b_router_top8(const float* logits, const float* correction_bias, int32_t* expert_ids,
+                     float* expert_weights, float routed_scale, void* stream);
+int p92b_router_top8_rows(const float* logits, const float* correction_bias, int32_t* expert_ids,
+                          float* expert_weights, int rows, float routed_scale, void* stream);
+
+/* p92::cuda::nvfp4_quantize (include/p92/kernels.h:479-484; cuda/nvfp4_ops.cu:818-841,1304-1315).
+ * `elements` BF16 values -> elements/2 packed bytes + elements/16 linear scales. */
+int p92b_nvfp4_quantize(const uint16_t* input, uint8_t* output, uint8_t* scales, int elements,
+                        float global_scale, void* stream);
+
+/* p92::cuda::nvfp4_swizzled_scale_bytes / nvfp4_swizzle_scales
+ * (include/p92/kernels.h:494-502; cuda/nvfp4_ops.cu:869-890,1332-1353). */
+size_t p92b_nvfp4_swizzled_scale_bytes(int rows, int scale_columns);
+int p92b_nvfp4_swizzle_scales(const uint8_t* linear, uint8_t* swizzled, int rows, int scale_columns,
+                              void* stream);
+
+/* The offline weight quantiser's arithmetic (cuda/nvfp4_pack.cu:141-176,255-256):
+ * per-tensor amax -> *weight_scale_2 = amax/(6*448) (device float) -> packed E2M1 + linear E4M3 scales. */
+int p92b_nvfp4_pack_weight(const uint16_t* input, uint8_t* packed, uint8_t* scales, size_t elements,
+                           float* weight_scale_2, void* stream);
+
+/* p92::cuda::swiglu (include/p92/kernels.h:100-104; cuda/nvfp4_ops.cu:97-105,948-956). */
+int p92b_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* output, int elements, void* stream);
+
+/* p92::cuda::expert_combine / expert_combine_rows (include/p92/kernels.h:55-68; cuda/nvfp4_ops.cu:107-142,958-988). */
+int p92b_expert_combine(const uint16_t* expert_rows, const float* route_weights, uint16_t* output,
+                        int experts, int elements, void* stream);
+int p92b_expert_combine_rows(const uint16_t* expert_rows, const float* route_weights, uint16_t* output,
+                             int batch_rows, int experts, int elements, void* stream);
+
+/* p92::cuda::add_inplace (include/p92/kernels.h:95-98; cuda/nvfp4_ops.cu:92-95). */
+int p92b_add_inplace(uint16_t* destination, const uint16_t* source, int elements, void* stream);
+
+/* ---- permutation into expert-contiguous order --------------------------- */
+
+/* Replaces the ranking loop of prepare_grouped_pointers_kernel
+ * (cuda/nvfp4_grouped.cu:117-132) and the host scan of src/model.cpp:1528-1540:
+ * stable counting sort of the flat index row*8+slot by expert id.
+ *   order[pos] = flat index, position[flat] = pos (either may be NULL),
+ *   counts[experts], offsets[experts+1] (exclusive prefix).
+ * `plan` supplies the scratch and bounds `assignments` to 8*max_rows. */
+int p92b_moe_permute(p92b_plan* plan, const int32_t* expert_ids, int assignments, int32_t* order,
+                     int32_t* position, int32_t* counts, int32_t* offsets, void* stream);
+
+/* ---- expert bank --------------------------------------------------------- */
+
+/* Replaces the expert-table build of Model::Impl::bind_weights (src/model.cpp:772-805)
+ * and the ResidentProjection layout of src/resident.cpp:75-162.
+ * host_entries: HOST array of (local_experts + 1) * 3 entries in the reference's
+ * bank order expert*3 + kind, kind 0/1/2 = gate/up/down (cuda/nvfp4_grouped.cu:133);
+ * the last three entries are the shared expert.  The weights are copied into
+ * the library's own layout; the caller may free its copies afterwards.
+ * first_expert / local_experts select the expert-parallel shard this bank holds
+ * (0 / 256 on one GPU). */
+int p92b_bank_create(p92b_bank** bank, const p92b_expert_projection* host_entries, int first_expert,
+                     int local_experts, int hidden, int intermediate, void* stream);
+void p92b_bank_destroy(p92b_bank* bank);
+size_t p92b_bank_bytes(const p92b_bank* bank);
+
+/* ---- plan + whole block -------------------------------------------------- */
+
+/* Replaces nvfp4_grouped_plan_create/_destroy (include/p92/kernels.h:25-30) and
+ * ProjectionExecutor::reserve (src/executor.cpp:109-140): all scratch is sized
+ * once for max_rows, so no call on the hot path allocates or synchronises. */
+int p92b_plan_create(p92b_plan** plan, int max_rows, int hidden, int intermediate);
+void p92b_plan_destroy(p92b_plan* plan);
+size_t p92b_plan_bytes(const p92b_plan* plan);
+
+/* Replaces Model::Impl::run_moe (src/model.cpp:1677-1729) and run_moe_rows
+ * (src/model.cpp:1486-1573): router logits -> top-8 -> permutation -> NVFP4
+ * gate/up + SwiGLU -> NVFP4 down -> weighted combine (device law,
+ * cuda/nvfp4_ops.cu:124-142) -> + shared expert.  input/output: BF16 [rows][hidden].
+ * rows == 1 uses the T=1 logits order, rows > 1 the T>1 order, as the reference does. */
+int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input,
+                     const uint16_t* router_weight, const float* correction_bias, uint16_t* output,
+                     int rows, float routed_scale, void* stream);
+
+/* Same block, HOST input and output buffers (pinned or pageable): copies the
+ * rows in, runs p92b_moe_forward, copies the result out and synchronises the
+ * stream.  The call a host-resident caller makes. */
+int p92b_moe_forward_host(p92b_plan* plan, const p92b_bank* bank, const uint16_t* host_input,
+                          const uint16_t* router_weight, const float* correction_bias,
+                          uint16_t* host_output, int rows, float routed_scale, void* stream);
+
+/* Stage entry points at the reference's split, so each existing call can be replaced alone.
+ * ProjectionExecutor::project_expert_gate_up (include/p92/executor.h:31-38; src/executor.cpp:39-71):
+ * gate_output / up_output BF16 [rows][8][intermediate] in (row, slot) order. */
+int p92b_project_expert_gate_up(p92b_plan* plan, const p92b_bank* bank, const int32_t* expert_ids,
+                                const uint16_t* input, uint16_t* gate_output, uint16_t* up_output,
+                                int rows, void* stream);
+/* ProjectionExecutor::project_expert_down (include/p92/executor.h:39-45; src/executor.cpp:73-107):
+ * input_rows BF16 [rows*8][intermediate], output_rows BF16 [rows*8][hidden], (row, slot) order. */
+int p92b_project_expert_down(p92b_plan* plan, const p92b_bank* bank, const int32_t* expert_ids,
+                             const uint16_t* input_rows, uint16_t* output_rows, int rows, void* stream);
+
+/* Device views of the last p92b_moe_forward's intermediates, for tests and
+ * tracing (the reference keeps the same buffers as Model::Impl members,
+ * src/model.cpp:872-885).  Valid until the next call on the plan. */
+typedef struct p92b_plan_views {
+    const float* logits;          /* [rows][256] */
+    const int32_t* expert_ids;    /* [rows][8] */
+    const float* expert_weights;  /* [rows][8] */
+    const int32_t* order;         /* [rows*8] */
+    const int32_t* position;      /* [rows*8] */
+    const int32_t* counts;        /* [256] */
+    const int32_t* offsets;       /* [257] */
+    const uint16_t* mixed;        /* [rows*8 + rows][hidden] BF16 down outputs in permuted order, shared rows last */
+    const int32_t* status;        /* device int: 0 ok, else first error code a kernel recorded */
+} p92b_plan_views;
+int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* views);
+
+/* Stage timing for measurement harnesses (the reference brackets its dispatches with CUDA
+ * events the same way, tests/moe_forward_test.cpp:306-326).  While enabled, p92b_moe_forward
+ * records an event pair on `stream` around every stage, synchronises the stream at the end of
+ * the call and accumulates the elapsed times; off by default and free when off.
+ * Stages: 0 router logits, 1 top-8, 2 permutation, 3 activation quantise, 4 gate/up + SwiGLU,
+ * 5 down, 6 combine + shared add.  host_ms[7] receives the sums since enabling, host_calls the
+ * number of forwards accumulated. */
+#define P92B_STAGES 7
+int p92b_plan_stage_timing(p92b_plan* plan, int enable);
+int p92b_plan_stage_times(const p92b_plan* plan, float* host_ms, int* host_calls);
+
+/* Number of kernels the last p92b_moe_forward on this plan launched. */
+int p92b_plan_last_launches(const p92b_plan* plan);
+
+const char* p92b_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* P92B_MOE_H */

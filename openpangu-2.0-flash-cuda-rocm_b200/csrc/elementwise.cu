@@ -1,0 +1,285 @@
+// Element-wise stages of the MoE block: NVFP4 quantisation (activations and the
+// offline weight law), scale swizzle, SwiGLU, weighted combine, shared-expert add.
+// Each kernel keeps the reference's rounding points; citations are on the kernels.
+// All of these are HBM-bound byte work: 16-byte accesses, one pass.
+#include "p92b_common.cuh"
+
+#include <algorithm>
+
+namespace p92b {
+namespace {
+
+// BF16 -> NVFP4, one thread per 16-element block (two 16-byte loads, one 8-byte
+// store).  Arithmetic of cuda/nvfp4_ops.cu:818-841 == cuda/nvfp4_pack.cu:151-176.
+// global_scale comes either by value or from 1 / *weight_scale_2 (weights).
+__global__ void __launch_bounds__(256) quantize_kernel(const std::uint16_t* __restrict__ input,
+                                                       std::uint8_t* __restrict__ output,
+                                                       std::uint8_t* __restrict__ scales, long groups,
+                                                       float global_scale,
+                                                       const float* __restrict__ weight_scale_2) {
+    const long group = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (group >= groups) return;
+    if (weight_scale_2 != nullptr) global_scale = __fdiv_rn(1.0F, *weight_scale_2);   // host IEEE division in the reference (cuda/nvfp4_pack.cu:256)
+    const uint4* src = reinterpret_cast<const uint4*>(input + group * 16);
+    const uint4 a = src[0];
+    const uint4 b = src[1];
+    const std::uint32_t words[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __uint_as_float(words[i] << 16);
+        v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+    }
+    std::uint8_t scale_bits;
+    const uint2 packed = quantize_block16(v, global_scale, &scale_bits);
+    *reinterpret_cast<uint2*>(output + group * 8) = packed;
+    scales[group] = scale_bits;
+}
+
+// cuda/nvfp4_pack.cu:141-149: |x| maximum of a BF16 tensor as float bits (atomicMax on
+// the bit pattern is order preserving for non-negative floats).
+__global__ void __launch_bounds__(256) amax_kernel(const std::uint16_t* __restrict__ input, std::size_t elements,
+                                                   unsigned* maximum) {
+    unsigned local = 0;
+    const std::size_t vectors = elements / 8;
+    const uint4* src = reinterpret_cast<const uint4*>(input);
+    for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vectors;
+         i += static_cast<std::size_t>(gridDim.x) * blockDim.x) {
+        const uint4 v = src[i];
+        const std::uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            local = max(local, (words[k] << 16) & 0x7fffffffU);
+            local = max(local, words[k] & 0x7fff0000U);
+        }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) local = max(local, __shfl_xor_sync(0xffffffffU, local, offset));
+    if ((threadIdx.x & 31) == 0 && local != 0) atomicMax(maximum, local);
+}
+
+// cuda/nvfp4_pack.cu:255: weight_scale_2 = amax / (6 * 448).
+__global__ void weight_scale_kernel(const unsigned* maximum, float* weight_scale_2) {
+    *weight_scale_2 = __fdiv_rn(__uint_as_float(*maximum), 6.0F * 448.0F);
+}
+
+// cuda/nvfp4_ops.cu:869-890: linear [row][K/16] -> 128-row x 4-column tiles.
+__global__ void __launch_bounds__(256) swizzle_kernel(const std::uint8_t* __restrict__ linear,
+                                                      std::uint8_t* __restrict__ swizzled, int rows,
+                                                      int scale_columns, int column_blocks) {
+    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<long>(rows) * scale_columns) return;
+    const int row = static_cast<int>(index / scale_columns);
+    const int column = static_cast<int>(index - static_cast<long>(row) * scale_columns);
+    const int row_block = row >> 7;
+    const int row_in_block = row & 127;
+    const std::size_t destination =
+        (static_cast<std::size_t>(row_block) * column_blocks + (column >> 2)) * 512 + (row_in_block & 31) * 16 +
+        (row_in_block >> 5) * 4 + (column & 3);
+    swizzled[destination] = linear[index];
+}
+
+// Inverse of the above, used when a bank is built from reference-format entries.
+__global__ void __launch_bounds__(256) unswizzle_kernel(const std::uint8_t* __restrict__ swizzled,
+                                                        std::uint8_t* __restrict__ linear, int rows,
+                                                        int scale_columns, int column_blocks) {
+    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<long>(rows) * scale_columns) return;
+    const int row = static_cast<int>(index / scale_columns);
+    const int column = static_cast<int>(index - static_cast<long>(row) * scale_columns);
+    const int row_block = row >> 7;
+    const int row_in_block = row & 127;
+    const std::size_t source =
+        (static_cast<std::size_t>(row_block) * column_blocks + (column >> 2)) * 512 + (row_in_block & 31) * 16 +
+        (row_in_block >> 5) * 4 + (column & 3);
+    linear[index] = swizzled[source];
+}
+
+// cuda/nvfp4_ops.cu:97-105: bf16( g / (1 + expf(-g)) * u ), fast-math like the reference.
+__global__ void __launch_bounds__(256) swiglu_kernel(const std::uint16_t* __restrict__ gate,
+                                                     const std::uint16_t* __restrict__ up,
+                                                     std::uint16_t* __restrict__ output, int elements) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= elements) return;
+    const float value = bf16_bits_to_float(gate[i]);
+    output[i] = float_to_bf16_bits((value / (1.0F + expf(-value))) * bf16_bits_to_float(up[i]));
+}
+
+// cuda/nvfp4_ops.cu:124-142: FP32 fmaf over the slots in rank order, one rounding.
+__global__ void __launch_bounds__(256) combine_rows_kernel(const std::uint16_t* __restrict__ expert_rows,
+                                                           const float* __restrict__ route_weights,
+                                                           std::uint16_t* __restrict__ output, int experts,
+                                                           int elements) {
+    const int element = blockIdx.x * blockDim.x + threadIdx.x;
+    const int row = blockIdx.y;
+    if (element >= elements) return;
+    float value = 0.0F;
+    const std::size_t route_base = static_cast<std::size_t>(row) * experts;
+    for (int slot = 0; slot < experts; ++slot) {
+        value = fmaf(bf16_bits_to_float(expert_rows[(route_base + slot) * elements + element]),
+                     route_weights[route_base + slot], value);
+    }
+    output[static_cast<std::size_t>(row) * elements + element] = float_to_bf16_bits(value);
+}
+
+// cuda/nvfp4_ops.cu:92-95.
+__global__ void __launch_bounds__(256) add_kernel(std::uint16_t* __restrict__ destination,
+                                                  const std::uint16_t* __restrict__ source, int elements) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < elements) {
+        destination[i] = float_to_bf16_bits(bf16_bits_to_float(destination[i]) + bf16_bits_to_float(source[i]));
+    }
+}
+
+// Fused tail of the block: the weighted combine above (gathering each slot's
+// down row from position space), rounded to BF16 exactly where the reference
+// stores `hidden_`, then the shared expert's BF16 down row added and rounded
+// again (src/model.cpp:1505-1508 then :1571-1572).  Eight columns per thread.
+__global__ void __launch_bounds__(256) combine_shared_kernel(const std::uint16_t* __restrict__ mixed,
+                                                             const std::int32_t* __restrict__ position,
+                                                             const float* __restrict__ route_weights,
+                                                             std::uint16_t* __restrict__ output, int rows,
+                                                             int hidden) {
+    const int row = blockIdx.y;
+    const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c8 * 8 >= hidden) return;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0F;
+    uint4 slot_rows[kTop];
+    float w[kTop];
+#pragma unroll
+    for (int slot = 0; slot < kTop; ++slot) {
+        const int pos = position[row * kTop + slot];
+        w[slot] = route_weights[row * kTop + slot];
+        slot_rows[slot] = *reinterpret_cast<const uint4*>(mixed + static_cast<std::size_t>(pos) * hidden + c8 * 8);
+    }
+#pragma unroll
+    for (int slot = 0; slot < kTop; ++slot) {
+        const std::uint32_t words[4] = {slot_rows[slot].x, slot_rows[slot].y, slot_rows[slot].z, slot_rows[slot].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            acc[2 * k] = fmaf(__uint_as_float(words[k] << 16), w[slot], acc[2 * k]);
+            acc[2 * k + 1] = fmaf(__uint_as_float(words[k] & 0xffff0000U), w[slot], acc[2 * k + 1]);
+        }
+    }
+    const uint4 sh = *reinterpret_cast<const uint4*>(
+        mixed + (static_cast<std::size_t>(rows) * kTop + row) * hidden + c8 * 8);
+    const std::uint32_t sw[4] = {sh.x, sh.y, sh.z, sh.w};
+    std::uint32_t out_words[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float lo = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k])) + __uint_as_float(sw[k] << 16);
+        const float hi = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k + 1])) + __uint_as_float(sw[k] & 0xffff0000U);
+        out_words[k] = static_cast<std::uint32_t>(float_to_bf16_bits(lo)) |
+                       (static_cast<std::uint32_t>(float_to_bf16_bits(hi)) << 16);
+    }
+    *reinterpret_cast<uint4*>(output + static_cast<std::size_t>(row) * hidden + c8 * 8) =
+        make_uint4(out_words[0], out_words[1], out_words[2], out_words[3]);
+}
+
+inline unsigned blocks_for(long n, int per_block) { return static_cast<unsigned>((n + per_block - 1) / per_block); }
+
+}  // namespace
+
+cudaError_t launch_quantize(const std::uint16_t* input, std::uint8_t* output, std::uint8_t* scales,
+                            long groups, float global_scale, cudaStream_t stream) {
+    if (input == nullptr || output == nullptr || scales == nullptr || groups <= 0) return cudaErrorInvalidValue;
+    quantize_kernel<<<blocks_for(groups, 256), 256, 0, stream>>>(input, output, scales, groups, global_scale, nullptr);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* position,
+                                  const float* route_weights, std::uint16_t* output, int rows,
+                                  int hidden, cudaStream_t stream) {
+    dim3 grid(blocks_for(hidden / 8, 256), rows);
+    combine_shared_kernel<<<grid, 256, 0, stream>>>(mixed, position, route_weights, output, rows, hidden);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,
+                             cudaStream_t stream) {
+    const long n = static_cast<long>(rows) * scale_columns;
+    unswizzle_kernel<<<blocks_for(n, 256), 256, 0, stream>>>(swizzled, linear, rows, scale_columns,
+                                                            (scale_columns + 3) / 4);
+    return cudaGetLastError();
+}
+
+}  // namespace p92b
+
+using namespace p92b;
+
+extern "C" {
+
+int p92b_nvfp4_quantize(const uint16_t* input, uint8_t* output, uint8_t* scales, int elements,
+                        float global_scale, void* stream) {
+    if (elements <= 0 || elements % 16 != 0) return cudaErrorInvalidValue;
+    return launch_quantize(input, output, scales, elements / 16, global_scale, static_cast<cudaStream_t>(stream));
+}
+
+size_t p92b_nvfp4_swizzled_scale_bytes(int rows, int scale_columns) {
+    if (rows <= 0 || scale_columns <= 0) return 0;
+    const size_t padded_rows = (static_cast<size_t>(rows) + 127) / 128 * 128;
+    const size_t padded_columns = (static_cast<size_t>(scale_columns) + 3) / 4 * 4;
+    return padded_rows * padded_columns;
+}
+
+int p92b_nvfp4_swizzle_scales(const uint8_t* linear, uint8_t* swizzled, int rows, int scale_columns,
+                              void* stream) {
+    if (linear == nullptr || swizzled == nullptr || rows <= 0 || scale_columns <= 0) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t st = cudaMemsetAsync(swizzled, 0, p92b_nvfp4_swizzled_scale_bytes(rows, scale_columns), s);
+    if (st != cudaSuccess) return st;
+    const long n = static_cast<long>(rows) * scale_columns;
+    swizzle_kernel<<<blocks_for(n, 256), 256, 0, s>>>(linear, swizzled, rows, scale_columns, (scale_columns + 3) / 4);
+    return cudaGetLastError();
+}
+
+int p92b_nvfp4_pack_weight(const uint16_t* input, uint8_t* packed, uint8_t* scales, size_t elements,
+                           float* weight_scale_2, void* stream) {
+    if (input == nullptr || packed == nullptr || scales == nullptr || weight_scale_2 == nullptr ||
+        elements == 0 || elements % 16 != 0) {
+        return cudaErrorInvalidValue;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the float slot doubles as the atomicMax cell (bit pattern of a non-negative float)
+    cudaError_t st = cudaMemsetAsync(weight_scale_2, 0, sizeof(float), s);
+    if (st != cudaSuccess) return st;
+    const unsigned blocks = static_cast<unsigned>(std::min<size_t>((elements / 8 + 255) / 256, 148 * 16));
+    amax_kernel<<<blocks, 256, 0, s>>>(input, elements, reinterpret_cast<unsigned*>(weight_scale_2));
+    weight_scale_kernel<<<1, 1, 0, s>>>(reinterpret_cast<const unsigned*>(weight_scale_2), weight_scale_2);
+    const long groups = static_cast<long>(elements / 16);
+    quantize_kernel<<<blocks_for(groups, 256), 256, 0, s>>>(input, packed, scales, groups, 0.0F, weight_scale_2);
+    return cudaGetLastError();
+}
+
+int p92b_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* output, int elements, void* stream) {
+    if (gate == nullptr || up == nullptr || output == nullptr || elements <= 0) return cudaErrorInvalidValue;
+    swiglu_kernel<<<blocks_for(elements, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(gate, up, output, elements);
+    return cudaGetLastError();
+}
+
+int p92b_expert_combine_rows(const uint16_t* expert_rows, const float* route_weights, uint16_t* output,
+                             int batch_rows, int experts, int elements, void* stream) {
+    if (expert_rows == nullptr || route_weights == nullptr || output == nullptr || batch_rows <= 0 ||
+        experts <= 0 || elements <= 0) {
+        return cudaErrorInvalidValue;
+    }
+    dim3 grid(blocks_for(elements, 256), batch_rows);
+    combine_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_rows, route_weights, output,
+                                                                            experts, elements);
+    return cudaGetLastError();
+}
+
+int p92b_expert_combine(const uint16_t* expert_rows, const float* route_weights, uint16_t* output,
+                        int experts, int elements, void* stream) {
+    return p92b_expert_combine_rows(expert_rows, route_weights, output, 1, experts, elements, stream);
+}
+
+int p92b_add_inplace(uint16_t* destination, const uint16_t* source, int elements, void* stream) {
+    if (destination == nullptr || source == nullptr || elements <= 0) return cudaErrorInvalidValue;
+    add_kernel<<<blocks_for(elements, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(destination, source, elements);
+    return cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,420 @@
+// C ABI: expert bank, plan, whole-block forward and the stage entry points.
+// Host-side orchestration only; every kernel lives in the other .cu files.
+#include "p92b_common.cuh"
+
+#include <algorithm>
+#include <new>
+#include <vector>
+
+using namespace p92b;
+
+namespace {
+
+constexpr std::size_t kAlign = 256;
+
+std::size_t align_up(std::size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+// Carves aligned regions out of one allocation.
+struct Carver {
+    std::uint8_t* base = nullptr;
+    std::size_t used = 0;
+    template <class T>
+    T* take(std::size_t count) {
+        T* p = base == nullptr ? nullptr : reinterpret_cast<T*>(base + used);
+        used += align_up(count * sizeof(T));
+        return p;
+    }
+};
+
+struct BankLayout {
+    std::size_t w13, w2, sf13, sf2, sfs13, sfs2, alpha, total;
+};
+
+BankLayout bank_layout(int entries, int hidden, int inter) {
+    BankLayout l {};
+    Carver c;
+    const std::size_t e = static_cast<std::size_t>(entries);
+    l.w13 = c.used; c.take<std::uint8_t>(e * 2 * inter * (hidden / 2));
+    l.w2 = c.used; c.take<std::uint8_t>(e * hidden * (inter / 2));
+    l.sf13 = c.used; c.take<std::uint8_t>(e * 2 * inter * (hidden / 16));
+    l.sf2 = c.used; c.take<std::uint8_t>(e * hidden * (inter / 16));
+    l.sfs13 = c.used; c.take<std::uint8_t>(e * 2 * p92b_nvfp4_swizzled_scale_bytes(inter, hidden / 16));
+    l.sfs2 = c.used; c.take<std::uint8_t>(e * p92b_nvfp4_swizzled_scale_bytes(hidden, inter / 16));
+    l.alpha = c.used; c.take<float>(e * 3);
+    l.total = c.used;
+    return l;
+}
+
+RouteView route_view(const p92b_plan* plan) {
+    RouteView r {};
+    r.counts = plan->counts;
+    r.offsets = plan->offsets;
+    r.row_token = plan->row_token;
+    r.active = plan->active;
+    r.active_count = plan->active_count;
+    return r;
+}
+
+bool shapes_match(const p92b_plan* plan, const p92b_bank* bank) {
+    return plan->hidden == bank->view.hidden && plan->intermediate == bank->view.intermediate;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* p92b_version(void) { return "p92b-moe 0.1 (sm_100a)"; }
+
+int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries, int first_expert,
+                     int local_experts, int hidden, int intermediate, void* stream_) {
+    if (out == nullptr) return cudaErrorInvalidValue;
+    *out = nullptr;
+    if (host_entries == nullptr || first_expert < 0 || local_experts <= 0 ||
+        first_expert + local_experts > kExperts || hidden <= 0 || intermediate <= 0 || hidden % 128 != 0 ||
+        intermediate % 128 != 0) {
+        return cudaErrorInvalidValue;
+    }
+    const int entries = local_experts + 1;
+    for (int i = 0; i < entries * 3; ++i) {
+        if (host_entries[i].weight == nullptr || host_entries[i].scales_swizzled == nullptr ||
+            host_entries[i].alpha == nullptr) {
+            return cudaErrorInvalidValue;
+        }
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    p92b_bank* bank = new (std::nothrow) p92b_bank();
+    if (bank == nullptr) return cudaErrorMemoryAllocation;
+    const BankLayout l = bank_layout(entries, hidden, intermediate);
+    cudaError_t st = cudaMalloc(&bank->storage, l.total);
+    if (st != cudaSuccess) {
+        delete bank;
+        return cudaErrorMemoryAllocation;
+    }
+    bank->bytes = l.total;
+    std::uint8_t* base = static_cast<std::uint8_t*>(bank->storage);
+    std::uint8_t* w13 = base + l.w13;
+    std::uint8_t* w2 = base + l.w2;
+    std::uint8_t* sf13 = base + l.sf13;
+    std::uint8_t* sf2 = base + l.sf2;
+    std::uint8_t* sfs13 = base + l.sfs13;
+    std::uint8_t* sfs2 = base + l.sfs2;
+    float* alpha = reinterpret_cast<float*>(base + l.alpha);
+
+    const std::size_t gu_bytes = static_cast<std::size_t>(intermediate) * (hidden / 2);
+    const std::size_t dn_bytes = static_cast<std::size_t>(hidden) * (intermediate / 2);
+    const std::size_t gu_sf = static_cast<std::size_t>(intermediate) * (hidden / 16);
+    const std::size_t dn_sf = static_cast<std::size_t>(hidden) * (intermediate / 16);
+    const std::size_t gu_sfs = p92b_nvfp4_swizzled_scale_bytes(intermediate, hidden / 16);
+    const std::size_t dn_sfs = p92b_nvfp4_swizzled_scale_bytes(hidden, intermediate / 16);
+#define BANK_TRY(call)            \
+    do {                          \
+        st = (call);              \
+        if (st != cudaSuccess) {  \
+            cudaFree(bank->storage); \
+            delete bank;          \
+            return st;            \
+        }                         \
+    } while (0)
+    for (int e = 0; e < entries; ++e) {
+        for (int kind = 0; kind < 3; ++kind) {
+            const p92b_expert_projection& src = host_entries[e * 3 + kind];
+            if (kind < 2) {
+                BANK_TRY(cudaMemcpyAsync(w13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_bytes, src.weight, gu_bytes,
+                                         cudaMemcpyDeviceToDevice, stream));
+                BANK_TRY(cudaMemcpyAsync(sfs13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_sfs, src.scales_swizzled,
+                                         gu_sfs, cudaMemcpyDeviceToDevice, stream));
+                BANK_TRY(launch_unswizzle(src.scales_swizzled, sf13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_sf,
+                                          intermediate, hidden / 16, stream));
+            } else {
+                BANK_TRY(cudaMemcpyAsync(w2 + static_cast<std::size_t>(e) * dn_bytes, src.weight, dn_bytes,
+                                         cudaMemcpyDeviceToDevice, stream));
+                BANK_TRY(cudaMemcpyAsync(sfs2 + static_cast<std::size_t>(e) * dn_sfs, src.scales_swizzled, dn_sfs,
+                                         cudaMemcpyDeviceToDevice, stream));
+                BANK_TRY(launch_unswizzle(src.scales_swizzled, sf2 + static_cast<std::size_t>(e) * dn_sf, hidden,
+                                          intermediate / 16, stream));
+            }
+            BANK_TRY(cudaMemcpyAsync(alpha + e * 3 + kind, src.alpha, sizeof(float), cudaMemcpyDeviceToDevice, stream));
+        }
+    }
+    BANK_TRY(cudaStreamSynchronize(stream));
+#undef BANK_TRY
+    bank->view.w13 = w13;
+    bank->view.w2 = w2;
+    bank->view.sf13 = sf13;
+    bank->view.sf2 = sf2;
+    bank->view.sfs13 = sfs13;
+    bank->view.sfs2 = sfs2;
+    bank->view.alpha = alpha;
+    bank->view.first_expert = first_expert;
+    bank->view.local_experts = local_experts;
+    bank->view.hidden = hidden;
+    bank->view.intermediate = intermediate;
+    *out = bank;
+    return cudaSuccess;
+}
+
+void p92b_bank_destroy(p92b_bank* bank) {
+    if (bank == nullptr) return;
+    if (bank->storage != nullptr) cudaFree(bank->storage);
+    delete bank;
+}
+
+size_t p92b_bank_bytes(const p92b_bank* bank) { return bank == nullptr ? 0 : bank->bytes; }
+
+int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate) {
+    if (out == nullptr) return cudaErrorInvalidValue;
+    *out = nullptr;
+    if (max_rows <= 0 || max_rows > (1 << 20) || hidden <= 0 || intermediate <= 0 || hidden % 128 != 0 ||
+        intermediate % 128 != 0) {
+        return cudaErrorInvalidValue;
+    }
+    p92b_plan* plan = new (std::nothrow) p92b_plan();
+    if (plan == nullptr) return cudaErrorMemoryAllocation;
+    plan->max_rows = max_rows;
+    plan->hidden = hidden;
+    plan->intermediate = intermediate;
+    int device = 0;
+    cudaError_t st = cudaGetDevice(&device);
+    if (st == cudaSuccess) st = cudaDeviceGetAttribute(&plan->sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (st != cudaSuccess) {
+        delete plan;
+        return st;
+    }
+    const std::size_t rows = static_cast<std::size_t>(max_rows);
+    plan->chunks = static_cast<int>((rows * kTop + 255) / 256);
+    for (int pass = 0; pass < 2; ++pass) {
+        Carver c;
+        c.base = static_cast<std::uint8_t*>(plan->storage);
+        plan->logits = c.take<float>(rows * kExperts);
+        plan->ids = c.take<std::int32_t>(rows * kTop);
+        plan->route_weights = c.take<float>(rows * kTop);
+        plan->order = c.take<std::int32_t>(rows * kTop);
+        plan->position = c.take<std::int32_t>(rows * kTop);
+        plan->counts = c.take<std::int32_t>(kExperts + 1);
+        plan->offsets = c.take<std::int32_t>(kExperts + 2);
+        plan->row_token = c.take<std::int32_t>(rows * (kTop + 1));
+        plan->active = c.take<std::int32_t>(kExperts + 1);
+        plan->active_count = c.take<std::int32_t>(1);
+        plan->chunk_hist = c.take<std::int32_t>(static_cast<std::size_t>(plan->chunks) * kExperts);
+        plan->xq = c.take<std::uint8_t>(rows * (hidden / 2));
+        plan->xs = c.take<std::uint8_t>(rows * (hidden / 16));
+        plan->hq = c.take<std::uint8_t>(rows * (kTop + 1) * (intermediate / 2));
+        plan->hs = c.take<std::uint8_t>(rows * (kTop + 1) * (intermediate / 16));
+        plan->mixed = c.take<std::uint16_t>(rows * (kTop + 1) * hidden);
+        plan->stage_in = c.take<std::uint16_t>(rows * hidden);
+        plan->stage_out = c.take<std::uint16_t>(rows * hidden);
+        plan->status = c.take<std::int32_t>(1);
+        if (pass == 0) {
+            plan->bytes = c.used;
+            st = cudaMalloc(&plan->storage, plan->bytes);
+            if (st != cudaSuccess) {
+                delete plan;
+                return cudaErrorMemoryAllocation;
+            }
+            st = cudaMemset(plan->storage, 0, plan->bytes);
+            if (st != cudaSuccess) {
+                cudaFree(plan->storage);
+                delete plan;
+                return st;
+            }
+        }
+    }
+    *out = plan;
+    return cudaSuccess;
+}
+
+void p92b_plan_destroy(p92b_plan* plan) {
+    if (plan == nullptr) return;
+    for (cudaEvent_t& ev : plan->stage_events) {
+        if (ev != nullptr) cudaEventDestroy(ev);
+    }
+    if (plan->storage != nullptr) cudaFree(plan->storage);
+    delete plan;
+}
+
+size_t p92b_plan_bytes(const p92b_plan* plan) { return plan == nullptr ? 0 : plan->bytes; }
+
+int p92b_plan_stage_timing(p92b_plan* plan, int enable) {
+    if (plan == nullptr) return cudaErrorInvalidValue;
+    if (enable) {
+        for (cudaEvent_t& ev : plan->stage_events) {
+            if (ev == nullptr) {
+                cudaError_t st = cudaEventCreate(&ev);
+                if (st != cudaSuccess) return st;
+            }
+        }
+        for (float& ms : plan->stage_ms) ms = 0.0F;
+        plan->timed_calls = 0;
+    }
+    plan->timing = enable != 0;
+    return cudaSuccess;
+}
+
+int p92b_plan_stage_times(const p92b_plan* plan, float* host_ms, int* host_calls) {
+    if (plan == nullptr || host_ms == nullptr || host_calls == nullptr) return cudaErrorInvalidValue;
+    for (int i = 0; i < P92B_STAGES; ++i) host_ms[i] = plan->stage_ms[i];
+    *host_calls = plan->timed_calls;
+    return cudaSuccess;
+}
+
+int p92b_plan_last_launches(const p92b_plan* plan) { return plan == nullptr ? 0 : plan->last_launches; }
+
+int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* v) {
+    if (plan == nullptr || v == nullptr) return cudaErrorInvalidValue;
+    v->logits = plan->logits;
+    v->expert_ids = plan->ids;
+    v->expert_weights = plan->route_weights;
+    v->order = plan->order;
+    v->position = plan->position;
+    v->counts = plan->counts;
+    v->offsets = plan->offsets;
+    v->mixed = plan->mixed;
+    v->status = plan->status;
+    return cudaSuccess;
+}
+
+int p92b_bf16_gemv_f32(const uint16_t* input, const uint16_t* weight, float* output, int rows, int columns,
+                       void* stream) {
+    return launch_router_logits(input, weight, output, 1, rows, columns, true, static_cast<cudaStream_t>(stream));
+}
+
+int p92b_bf16_gemm_f32(const uint16_t* input, const uint16_t* weight, float* output, int batch_rows, int rows,
+                       int columns, void* stream) {
+    return launch_router_logits(input, weight, output, batch_rows, rows, columns, false,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int p92b_router_top8_rows(const float* logits, const float* correction_bias, int32_t* expert_ids,
+                          float* expert_weights, int rows, float routed_scale, void* stream) {
+    return launch_router_top8(logits, correction_bias, expert_ids, expert_weights, rows, routed_scale,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int p92b_router_top8(const float* logits, const float* correction_bias, int32_t* expert_ids,
+                     float* expert_weights, float routed_scale, void* stream) {
+    return p92b_router_top8_rows(logits, correction_bias, expert_ids, expert_weights, 1, routed_scale, stream);
+}
+
+int p92b_moe_permute(p92b_plan* plan, const int32_t* expert_ids, int assignments, int32_t* order,
+                     int32_t* position, int32_t* counts, int32_t* offsets, void* stream) {
+    if (plan == nullptr) return cudaErrorInvalidValue;
+    return launch_permute(plan, expert_ids, assignments, order, position, counts, offsets, false, 0, kExperts,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input,
+                     const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
+                     float routed_scale, void* stream_) {
+    if (plan == nullptr || bank == nullptr || input == nullptr || router_weight == nullptr ||
+        correction_bias == nullptr || output == nullptr || rows <= 0 || rows > plan->max_rows ||
+        !shapes_match(plan, bank) || bank->view.first_expert != 0 || bank->view.local_experts != kExperts) {
+        return cudaErrorInvalidValue;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int hidden = plan->hidden;
+    plan->last_launches = 0;
+    int stage = 0;
+    auto mark = [&]() -> cudaError_t {
+        if (!plan->timing) return cudaSuccess;
+        return cudaEventRecord(plan->stage_events[stage++], stream);
+    };
+    cudaError_t st = mark();
+    if (st != cudaSuccess) return st;
+    st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream);
+    if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
+    st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream);
+    if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
+    plan->last_launches += 2;
+    st = launch_permute(plan, plan->ids, rows * kTop, plan->order, plan->position, plan->counts, plan->offsets, true, 0,
+                        kExperts, stream);
+    if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
+    st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * hidden / 16, 1.0F, stream);
+    if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
+    const RouteView route = route_view(plan);
+    st = launch_gate_up(plan, bank->view, route, plan->xq, plan->xs, plan->hq, plan->hs, nullptr, nullptr, plan->order,
+                        rows, stream);
+    if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
+    st = launch_down(plan, bank->view, route, plan->hq, plan->hs, plan->mixed, nullptr, nullptr, 0, stream);
+    if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
+    st = launch_combine_shared(plan->mixed, plan->position, plan->route_weights, output, rows, hidden, stream);
+    plan->last_launches += 4;
+    if (st != cudaSuccess) return st;
+    if (plan->timing) {
+        if ((st = mark()) != cudaSuccess) return st;
+        if ((st = cudaStreamSynchronize(stream)) != cudaSuccess) return st;
+        for (int i = 0; i < P92B_STAGES; ++i) {
+            float ms = 0.0F;
+            if ((st = cudaEventElapsedTime(&ms, plan->stage_events[i], plan->stage_events[i + 1])) != cudaSuccess) return st;
+            plan->stage_ms[i] += ms;
+        }
+        plan->timed_calls += 1;
+    }
+    return cudaSuccess;
+}
+
+int p92b_moe_forward_host(p92b_plan* plan, const p92b_bank* bank, const uint16_t* host_input,
+                          const uint16_t* router_weight, const float* correction_bias, uint16_t* host_output,
+                          int rows, float routed_scale, void* stream_) {
+    if (plan == nullptr || host_input == nullptr || host_output == nullptr || rows <= 0 || rows > plan->max_rows) {
+        return cudaErrorInvalidValue;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const std::size_t bytes = static_cast<std::size_t>(rows) * plan->hidden * sizeof(std::uint16_t);
+    cudaError_t st = cudaMemcpyAsync(plan->stage_in, host_input, bytes, cudaMemcpyHostToDevice, stream);
+    if (st != cudaSuccess) return st;
+    st = static_cast<cudaError_t>(p92b_moe_forward(plan, bank, plan->stage_in, router_weight, correction_bias,
+                                                   plan->stage_out, rows, routed_scale, stream_));
+    if (st != cudaSuccess) return st;
+    st = cudaMemcpyAsync(host_output, plan->stage_out, bytes, cudaMemcpyDeviceToHost, stream);
+    if (st != cudaSuccess) return st;
+    return cudaStreamSynchronize(stream);
+}
+
+int p92b_project_expert_gate_up(p92b_plan* plan, const p92b_bank* bank, const int32_t* expert_ids,
+                                const uint16_t* input, uint16_t* gate_output, uint16_t* up_output, int rows,
+                                void* stream_) {
+    if (plan == nullptr || bank == nullptr || expert_ids == nullptr || input == nullptr || gate_output == nullptr ||
+        up_output == nullptr || rows <= 0 || rows > plan->max_rows || !shapes_match(plan, bank)) {
+        return cudaErrorInvalidValue;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    plan->last_launches = 0;
+    cudaError_t st = launch_permute(plan, expert_ids, rows * kTop, plan->order, plan->position, plan->counts,
+                                    plan->offsets, true, 0, kExperts, stream);
+    if (st != cudaSuccess) return st;
+    st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * plan->hidden / 16, 1.0F, stream);
+    if (st != cudaSuccess) return st;
+    st = launch_gate_up(plan, bank->view, route_view(plan), plan->xq, plan->xs, nullptr, nullptr, gate_output,
+                        up_output, plan->order, rows, stream);
+    plan->last_launches += 2;
+    return st;
+}
+
+int p92b_project_expert_down(p92b_plan* plan, const p92b_bank* bank, const int32_t* expert_ids,
+                             const uint16_t* input_rows, uint16_t* output_rows, int rows, void* stream_) {
+    if (plan == nullptr || bank == nullptr || expert_ids == nullptr || input_rows == nullptr ||
+        output_rows == nullptr || rows <= 0 || rows > plan->max_rows || !shapes_match(plan, bank)) {
+        return cudaErrorInvalidValue;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    plan->last_launches = 0;
+    cudaError_t st = launch_permute(plan, expert_ids, rows * kTop, plan->order, plan->position, plan->counts,
+                                    plan->offsets, true, 0, kExperts, stream);
+    if (st != cudaSuccess) return st;
+    // every (row, slot) intermediate row is quantised on its own (src/executor.cpp:85-91), in flat order
+    st = launch_quantize(input_rows, plan->hq, plan->hs, static_cast<long>(rows) * kTop * plan->intermediate / 16, 1.0F,
+                         stream);
+    if (st != cudaSuccess) return st;
+    st = launch_down(plan, bank->view, route_view(plan), plan->hq, plan->hs, output_rows, plan->order, plan->order, 1,
+                     stream);
+    plan->last_launches += 2;
+    return st;
+}
+
+}  // extern "C"

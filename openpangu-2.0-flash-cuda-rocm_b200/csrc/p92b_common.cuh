@@ -1,0 +1,174 @@
+// Shared device helpers and internal structures of the sm_100a MoE library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime_api.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "p92b_moe.h"
+
+namespace p92b {
+
+constexpr int kExperts = P92B_ROUTED_EXPERTS;
+constexpr int kTop = P92B_TOP_K;
+
+// Error words a kernel can record in p92b_plan::status instead of faulting.
+enum : int {
+    kStatusOk = 0,
+    kStatusBadExpertId = 1,   // an expert id outside the bank's range was clamped
+    kStatusWaitExpired = 2,   // a bounded mbarrier wait gave up
+};
+
+__device__ __forceinline__ float bf16_bits_to_float(std::uint16_t bits) {
+    return __uint_as_float(static_cast<std::uint32_t>(bits) << 16);
+}
+
+__device__ __forceinline__ std::uint16_t float_to_bf16_bits(float value) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(value));
+}
+
+__device__ __forceinline__ float decode_e4m3(std::uint8_t bits) {
+    __nv_fp8_e4m3 value;
+    value.__x = bits;
+    return static_cast<float>(value);
+}
+
+// Two E2M1 values (low nibble first) -> packed f16x2, exact.
+__device__ __forceinline__ std::uint32_t e2m1x2_to_f16x2(std::uint32_t byte) {
+    std::uint32_t out;
+    asm("{ .reg .b8 lo, hi; .reg .b16 t;\n"
+        "  cvt.u16.u32 t, %1;\n"
+        "  mov.b16 {lo, hi}, t;\n"
+        "  cvt.rn.f16x2.e2m1x2 %0, lo; }\n"
+        : "=r"(out)
+        : "r"(byte));
+    return out;
+}
+
+// One 16-element NVFP4 block from 16 floats, the arithmetic of the reference
+// quantiser (amax -> E4M3 scale of amax*gs/6 -> values * gs/scale -> E2M1,
+// round-to-nearest-even).  Returns the 8 packed bytes; *scale_bits gets the scale.
+__device__ __forceinline__ uint2 quantize_block16(const float (&v)[16], float global_scale,
+                                                  std::uint8_t* scale_bits) {
+    float maximum = 0.0F;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(v[i]));
+    const __nv_fp8_e4m3 scale(maximum * (global_scale / 6.0F));
+    *scale_bits = scale.__x;
+    const float decoded = static_cast<float>(scale);
+    const float multiplier = decoded == 0.0F ? 0.0F : global_scale / decoded;
+    std::uint32_t words[2] = {0U, 0U};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float2 pair = make_float2(v[2 * i] * multiplier, v[2 * i + 1] * multiplier);
+        const std::uint32_t byte = __nv_fp4x2_e2m1(pair).__x;
+        words[i >> 2] |= byte << ((i & 3) * 8);
+    }
+    return make_uint2(words[0], words[1]);
+}
+
+// Layout of one layer's expert weights inside the library (device memory).
+// Entry e = local expert index, local_experts = the shared expert.
+struct BankView {
+    const std::uint8_t* w13;    // [entries][2][I][H/2]   gate rows then up rows
+    const std::uint8_t* w2;     // [entries][H][I/2]
+    const std::uint8_t* sf13;   // [entries][2][I][H/16]  linear E4M3
+    const std::uint8_t* sf2;    // [entries][H][I/16]     linear E4M3
+    const std::uint8_t* sfs13;  // [entries][2][swizzled I x H/16]
+    const std::uint8_t* sfs2;   // [entries][swizzled H x I/16]
+    const float* alpha;         // [entries][3]
+    int first_expert;
+    int local_experts;
+    int hidden;
+    int intermediate;
+};
+
+// Routing products of one call, all in device memory owned by the plan.
+// "Position" space: routed assignments sorted by expert (stable), followed by
+// one row per token for the shared expert.
+struct RouteView {
+    const std::int32_t* counts;      // [257]  rows per entry (entry 256 = shared = rows)
+    const std::int32_t* offsets;     // [258]  exclusive prefix in position space
+    const std::int32_t* row_token;   // [9*rows] token of each position
+    const std::int32_t* active;      // [257]  entries with rows, shared expert first
+    const std::int32_t* active_count;
+};
+
+}  // namespace p92b
+
+struct p92b_bank {
+    p92b::BankView view {};
+    void* storage = nullptr;
+    std::size_t bytes = 0;
+};
+
+struct p92b_plan {
+    int max_rows = 0;
+    int hidden = 0;
+    int intermediate = 0;
+    int sm_count = 0;
+    int last_launches = 0;
+    void* storage = nullptr;
+    std::size_t bytes = 0;
+    // device scratch (carved out of storage)
+    float* logits = nullptr;              // [max_rows][256]
+    std::int32_t* ids = nullptr;          // [max_rows][8]
+    float* route_weights = nullptr;       // [max_rows][8]
+    std::int32_t* order = nullptr;        // [8*max_rows]
+    std::int32_t* position = nullptr;     // [8*max_rows]
+    std::int32_t* counts = nullptr;       // [257]
+    std::int32_t* offsets = nullptr;      // [258]
+    std::int32_t* row_token = nullptr;    // [9*max_rows]
+    std::int32_t* active = nullptr;       // [257]
+    std::int32_t* active_count = nullptr; // [1]
+    std::int32_t* chunk_hist = nullptr;   // [chunks][256]
+    int chunks = 0;
+    std::uint8_t* xq = nullptr;           // [max_rows][H/2]
+    std::uint8_t* xs = nullptr;           // [max_rows][H/16]
+    std::uint8_t* hq = nullptr;           // [9*max_rows][I/2]   position space
+    std::uint8_t* hs = nullptr;           // [9*max_rows][I/16]
+    std::uint16_t* mixed = nullptr;       // [9*max_rows][H]     position space
+    std::uint16_t* stage_in = nullptr;    // [max_rows][H]  host-call staging
+    std::uint16_t* stage_out = nullptr;   // [max_rows][H]
+    std::int32_t* status = nullptr;       // [1]
+    // optional stage timing (host side)
+    bool timing = false;
+    cudaEvent_t stage_events[P92B_STAGES + 1] = {};
+    float stage_ms[P92B_STAGES] = {};
+    int timed_calls = 0;
+};
+
+namespace p92b {
+
+// kernel launchers (defined across the .cu files)
+cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w, float* out,
+                                 int batch_rows, int rows, int columns, bool gemv_order,
+                                 cudaStream_t stream);
+cudaError_t launch_router_top8(const float* logits, const float* bias, std::int32_t* ids,
+                               float* weights, int rows, float routed_scale, cudaStream_t stream);
+cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignments,
+                           std::int32_t* order, std::int32_t* position, std::int32_t* counts,
+                           std::int32_t* offsets, bool route_lists, int first_expert,
+                           int local_experts, cudaStream_t stream);
+cudaError_t launch_quantize(const std::uint16_t* input, std::uint8_t* output, std::uint8_t* scales,
+                            long groups, float global_scale, cudaStream_t stream);
+cudaError_t launch_gate_up(const p92b_plan* plan, const BankView& bank, const RouteView& route,
+                           const std::uint8_t* xq, const std::uint8_t* xs, std::uint8_t* hq,
+                           std::uint8_t* hs, std::uint16_t* gate_out, std::uint16_t* up_out,
+                           const std::int32_t* order, int rows, cudaStream_t stream);
+cudaError_t launch_down(const p92b_plan* plan, const BankView& bank, const RouteView& route,
+                        const std::uint8_t* hq, const std::uint8_t* hs, std::uint16_t* mixed,
+                        const std::int32_t* in_rows, const std::int32_t* out_rows, int first_active,
+                        cudaStream_t stream);
+cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,
+                             cudaStream_t stream);
+cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* position,
+                                  const float* route_weights, std::uint16_t* output, int rows,
+                                  int hidden, cudaStream_t stream);
+
+}  // namespace p92b

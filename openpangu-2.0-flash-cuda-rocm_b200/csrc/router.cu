@@ -1,0 +1,241 @@
+// Router: BF16 logits in the reference's two FP32 summation orders, and the
+// sigmoid + correction-bias top-8 with renormalised weights.
+//
+// Bit-exactness contract.  Expert ids must equal the reference's, so the logits
+// reproduce its FP32 fmaf chains and reduction trees value for value:
+//   T == 1 (cuda/nvfp4_ops.cu:161-176): thread t of 256 sums columns t, t+256, ...;
+//           warp shuffle-down tree; tree over the 8 warp sums (block_sum, :38-51).
+//   T  > 1 (cuda/nvfp4_ops.cu:178-207): lane l of a warp sums columns l, l+32, ...;
+//           warp shuffle-down tree.
+// The score is written as the reference writes it, 1/(1+expf(-x)), and this
+// file is compiled with --use_fast_math like the reference (CMakeLists.txt:98)
+// so expf and the divisions lower to the same hardware approximations.
+// Selection is pure comparison with ties to the lower id, which is order
+// independent, so the top-8 itself is free to use a warp-per-token layout.
+#include "p92b_common.cuh"
+
+#include <cfloat>
+
+namespace p92b {
+namespace {
+
+// ---- T == 1 order ---------------------------------------------------------
+// One block of 256 threads per expert row; thread t owns columns t + 256 j.
+// The 5 KB row is one fully coalesced pass (ten 512-byte warp requests).
+__global__ void __launch_bounds__(256) logits_gemv_kernel(const std::uint16_t* __restrict__ x,
+                                                          const std::uint16_t* __restrict__ w,
+                                                          float* __restrict__ out, int rows,
+                                                          int columns) {
+    const int row = blockIdx.x;
+    if (row >= rows) return;
+    __shared__ float warp_sums[8];
+    const std::uint16_t* wr = w + static_cast<std::size_t>(row) * columns;
+    float value = 0.0F;
+    for (int c = threadIdx.x; c < columns; c += 256) {
+        value = fmaf(bf16_bits_to_float(x[c]), bf16_bits_to_float(wr[c]), value);
+    }
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_down_sync(0xffffffffU, value, offset);
+    if (lane == 0) warp_sums[warp] = value;
+    __syncthreads();
+    if (warp == 0) {
+        value = lane < 8 ? warp_sums[lane] : 0.0F;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_down_sync(0xffffffffU, value, offset);
+        if (lane == 0) out[row] = value;
+    }
+}
+
+// ---- T > 1 order ----------------------------------------------------------
+// A warp owns a TE x TT tile of (expert, token) outputs; lane l accumulates the
+// columns l, l+32, ... of every output in the tile (the reference's per-lane
+// chain), so one pass over K yields TE*TT fmaf per TE+TT shared-memory reads,
+// and the final shuffle-down tree is the reference's.  K is staged through
+// shared memory in ascending chunks, which keeps each chain's order.
+template <int TE, int TT, int WE, int WT>
+__global__ void __launch_bounds__(WE* WT * 32) logits_rows_kernel(
+    const std::uint16_t* __restrict__ x, const std::uint16_t* __restrict__ w,
+    float* __restrict__ out, int batch_rows, int rows, int columns, int kc) {
+    constexpr int BE = TE * WE;             // experts per block
+    constexpr int BT = TT * WT;             // tokens per block
+    constexpr int THREADS = WE * WT * 32;
+    extern __shared__ __align__(16) std::uint16_t staged[];
+    std::uint16_t* ws = staged;                                 // [BE][kc]
+    std::uint16_t* xs = staged + static_cast<std::size_t>(BE) * kc;   // [BT][kc]
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int we = warp % WE;
+    const int wt = warp / WE;
+    const int e0 = blockIdx.x * BE;
+    const int t0 = blockIdx.y * BT;
+    const int kc8 = kc / 8;
+    float acc[TE][TT];
+#pragma unroll
+    for (int i = 0; i < TE; ++i)
+#pragma unroll
+        for (int j = 0; j < TT; ++j) acc[i][j] = 0.0F;
+
+    for (int k0 = 0; k0 < columns; k0 += kc) {
+        if (k0 != 0) __syncthreads();
+        // 16-byte coalesced staging; rows beyond the edge are zero filled.
+        for (int idx = threadIdx.x; idx < BE * kc8; idx += THREADS) {
+            const int r = idx / kc8;
+            const int c8 = idx - r * kc8;
+            uint4 v = make_uint4(0U, 0U, 0U, 0U);
+            if (e0 + r < rows) {
+                v = *reinterpret_cast<const uint4*>(w + static_cast<std::size_t>(e0 + r) * columns + k0 + c8 * 8);
+            }
+            *reinterpret_cast<uint4*>(ws + static_cast<std::size_t>(r) * kc + c8 * 8) = v;
+        }
+        for (int idx = threadIdx.x; idx < BT * kc8; idx += THREADS) {
+            const int r = idx / kc8;
+            const int c8 = idx - r * kc8;
+            uint4 v = make_uint4(0U, 0U, 0U, 0U);
+            if (t0 + r < batch_rows) {
+                v = *reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(t0 + r) * columns + k0 + c8 * 8);
+            }
+            *reinterpret_cast<uint4*>(xs + static_cast<std::size_t>(r) * kc + c8 * 8) = v;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = 0; j < kc / 32; ++j) {
+            float wv[TE];
+            float xv[TT];
+#pragma unroll
+            for (int i = 0; i < TE; ++i) wv[i] = bf16_bits_to_float(ws[static_cast<std::size_t>(we * TE + i) * kc + j * 32 + lane]);
+#pragma unroll
+            for (int i = 0; i < TT; ++i) xv[i] = bf16_bits_to_float(xs[static_cast<std::size_t>(wt * TT + i) * kc + j * 32 + lane]);
+#pragma unroll
+            for (int i = 0; i < TE; ++i)
+#pragma unroll
+                for (int t = 0; t < TT; ++t) acc[i][t] = fmaf(xv[t], wv[i], acc[i][t]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TE; ++i) {
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            float value = acc[i][t];
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_down_sync(0xffffffffU, value, offset);
+            const int e = e0 + we * TE + i;
+            const int tok = t0 + wt * TT + t;
+            if (lane == 0 && e < rows && tok < batch_rows) out[static_cast<std::size_t>(tok) * rows + e] = value;
+        }
+    }
+}
+
+// ---- top-8 ----------------------------------------------------------------
+// One warp per token; lane l holds experts l, l+32, ..., l+224 in registers.
+// Eight rounds of (local best, warp butterfly arg-max) with the reference's
+// total order: higher corrected score first, equal scores -> lower id
+// (cuda/nvfp4_ops.cu:391-392,411-412).  Weights are the uncorrected sigmoid of
+// the winners, summed in slot order and scaled by routed_scale/total (:420,425-432).
+__global__ void __launch_bounds__(128) router_top8_kernel(const float* __restrict__ logits,
+                                                          const float* __restrict__ bias,
+                                                          std::int32_t* __restrict__ ids,
+                                                          float* __restrict__ weights, int rows,
+                                                          float routed_scale) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float* lg = logits + static_cast<std::size_t>(row) * kExperts;
+    float raw[8];
+    float corrected[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        raw[i] = 1.0F / (1.0F + expf(-lg[e]));
+        corrected[i] = raw[i] + bias[e];
+    }
+    unsigned used = 0U;
+    float chosen_weight = 0.0F;   // lane k keeps slot k's raw weight
+    int chosen_id = 0;
+#pragma unroll
+    for (int slot = 0; slot < 8; ++slot) {
+        float best = -FLT_MAX;
+        int best_id = 256 + lane;
+        float best_raw = 0.0F;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float c = (used >> i) & 1U ? -FLT_MAX : corrected[i];
+            const int e = lane + 32 * i;
+            // ascending id within the lane, so strict '>' keeps the lower id on ties
+            if (c > best || (c == best && e < best_id)) {
+                best = c;
+                best_id = e;
+                best_raw = raw[i];
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffU, best, offset);
+            const int other_id = __shfl_xor_sync(0xffffffffU, best_id, offset);
+            const float other_raw = __shfl_xor_sync(0xffffffffU, best_raw, offset);
+            if (other > best || (other == best && other_id < best_id)) {
+                best = other;
+                best_id = other_id;
+                best_raw = other_raw;
+            }
+        }
+        if ((best_id & 31) == lane) used |= 1U << (best_id >> 5);
+        if (lane == slot) {
+            chosen_weight = best_raw;
+            chosen_id = best_id;
+        }
+    }
+    float total = 0.0F;
+#pragma unroll
+    for (int slot = 0; slot < 8; ++slot) total += __shfl_sync(0xffffffffU, chosen_weight, slot);
+    const float multiplier = routed_scale / total;
+    if (lane < 8) {
+        ids[static_cast<std::size_t>(row) * 8 + lane] = chosen_id;
+        weights[static_cast<std::size_t>(row) * 8 + lane] = chosen_weight * multiplier;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w, float* out,
+                                 int batch_rows, int rows, int columns, bool gemv_order,
+                                 cudaStream_t stream) {
+    if (x == nullptr || w == nullptr || out == nullptr || batch_rows <= 0 || rows <= 0 ||
+        columns <= 0 || columns % 128 != 0) {
+        return cudaErrorInvalidValue;
+    }
+    if (gemv_order) {
+        if (batch_rows != 1) return cudaErrorInvalidValue;
+        logits_gemv_kernel<<<rows, 256, 0, stream>>>(x, w, out, rows, columns);
+    } else if (batch_rows <= 8) {
+        // decode: the whole K extent of 2 expert rows and of every token sits in
+        // shared memory, so all global loads of a block are in flight at once
+        constexpr int TE = 1, TT = 8, WE = 2, WT = 1;
+        const std::size_t smem = static_cast<std::size_t>(TE * WE + TT * WT) * columns * 2;
+        if (smem > 200 * 1024) return cudaErrorInvalidValue;
+        auto kernel = logits_rows_kernel<TE, TT, WE, WT>;
+        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (st != cudaSuccess) return st;
+        dim3 grid((rows + TE * WE - 1) / (TE * WE), 1);
+        kernel<<<grid, WE * WT * 32, smem, stream>>>(x, w, out, batch_rows, rows, columns, columns);
+    } else {
+        constexpr int TE = 8, TT = 8, WE = 2, WT = 4;
+        constexpr int KC = 128;
+        const std::size_t smem = static_cast<std::size_t>(TE * WE + TT * WT) * KC * 2;
+        dim3 grid((rows + TE * WE - 1) / (TE * WE), (batch_rows + TT * WT - 1) / (TT * WT));
+        logits_rows_kernel<TE, TT, WE, WT><<<grid, WE * WT * 32, smem, stream>>>(x, w, out, batch_rows, rows, columns, KC);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_router_top8(const float* logits, const float* bias, std::int32_t* ids,
+                               float* weights, int rows, float routed_scale, cudaStream_t stream) {
+    if (logits == nullptr || bias == nullptr || ids == nullptr || weights == nullptr || rows <= 0) {
+        return cudaErrorInvalidValue;
+    }
+    router_top8_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(logits, bias, ids, weights, rows, routed_scale);
+    return cudaGetLastError();
+}
+
+}  // namespace p92b
