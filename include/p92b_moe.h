@@ -168,7 +168,8 @@ typedef struct p92b_plan_views {
     const int32_t* position;      /* [rows*8] */
     const int32_t* counts;        /* [256] */
     const int32_t* offsets;       /* [257] */
-    const uint16_t* mixed;        /* [rows*8 + rows][hidden] BF16 down outputs in permuted order, shared rows last */
+    const uint16_t* mixed;        /* BF16 down outputs [mixed rows][hidden] */
+    const int32_t* mixed_index;   /* [rows*8 + rows]: row of `mixed` holding assignment (row, slot), then the shared rows */
     const int32_t* status;        /* device int: 0 ok, else first error code a kernel recorded */
 } p92b_plan_views;
 int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* views);
@@ -183,6 +184,11 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* views);
 #define P92B_STAGES 7
 int p92b_plan_stage_timing(p92b_plan* plan, int enable);
 int p92b_plan_stage_times(const p92b_plan* plan, float* host_ms, int* host_calls);
+
+/* Kernel family for the expert products: 0 automatic, 1 weight-streaming SIMT kernels,
+ * 2 tcgen05 block-scaled MMA kernels (TMA + TMEM).  The environment variable P92B_PATH sets the
+ * default of new plans.  Both families implement the same arithmetic contract. */
+int p92b_plan_set_path(p92b_plan* plan, int path);
 
 /* Number of kernels the last p92b_moe_forward on this plan launched. */
 int p92b_plan_last_launches(const p92b_plan* plan);

@@ -54,6 +54,7 @@ class PlanViews(ctypes.Structure):
         ("counts", c_void_p),
         ("offsets", c_void_p),
         ("mixed", c_void_p),
+        ("mixed_index", c_void_p),
         ("status", c_void_p),
     ]
 
@@ -84,6 +85,7 @@ SIGNATURES = {
     "p92b_project_expert_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_project_expert_down": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_plan_get_views": (c_int, [c_void_p, ctypes.POINTER(PlanViews)]),
+    "p92b_plan_set_path": (c_int, [c_void_p, c_int]),
     "p92b_plan_last_launches": (c_int, [c_void_p]),
     "p92b_plan_stage_timing": (c_int, [c_void_p, c_int]),
     "p92b_plan_stage_times": (c_int, [c_void_p, ctypes.POINTER(c_float), ctypes.POINTER(c_int)]),
@@ -274,7 +276,12 @@ class MoePlan:
         grab = _device_copy
 
         a = rows * TOP_K
+        mixed_index = grab(v.mixed_index, (a + rows,), torch.int32)
+        span = int(mixed_index.max()) + 1
+        typestr_rows = torch.as_tensor(_DeviceSpan(v.mixed, (span, self.hidden), "<i2"), device="cuda")
+        mixed = typestr_rows[mixed_index.long()].contiguous().view(torch.bfloat16)
         return {
+            "mixed": mixed,            # [rows*8 + rows, hidden] in (row, slot) order, shared rows last
             "logits": grab(v.logits, (rows, EXPERTS), torch.float32),
             "expert_ids": grab(v.expert_ids, (rows, TOP_K), torch.int32),
             "expert_weights": grab(v.expert_weights, (rows, TOP_K), torch.float32),
@@ -282,9 +289,14 @@ class MoePlan:
             "position": grab(v.position, (a,), torch.int32),
             "counts": grab(v.counts, (EXPERTS,), torch.int32),
             "offsets": grab(v.offsets, (EXPERTS + 1,), torch.int32),
-            "mixed": grab(v.mixed, (a + rows, self.hidden), torch.bfloat16),
+            "mixed_index": mixed_index,
             "status": grab(v.status, (1,), torch.int32),
         }
+
+    PATH_AUTO, PATH_STREAM, PATH_TENSOR_CORE = 0, 1, 2
+
+    def set_path(self, path: int) -> None:
+        _check(load_library().p92b_plan_set_path(self.handle, path), "plan_set_path")
 
     def permute(self, expert_ids, order, position, counts, offsets) -> None:
         _check(load_library().p92b_moe_permute(self.handle, _ptr(expert_ids), expert_ids.numel(), _ptr(order),

@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) add_kernel(std::uint16_t* __restrict__ de
 // stores `hidden_`, then the shared expert's BF16 down row added and rounded
 // again (src/model.cpp:1505-1508 then :1571-1572).  Eight columns per thread.
 __global__ void __launch_bounds__(256) combine_shared_kernel(const std::uint16_t* __restrict__ mixed,
-                                                             const std::int32_t* __restrict__ position,
+                                                             const std::int32_t* __restrict__ mixed_index,
                                                              const float* __restrict__ route_weights,
                                                              std::uint16_t* __restrict__ output, int rows,
                                                              int hidden) {
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(256) combine_shared_kernel(const std::uint16_t
     float w[kTop];
 #pragma unroll
     for (int slot = 0; slot < kTop; ++slot) {
-        const int pos = position[row * kTop + slot];
+        const int pos = mixed_index[row * kTop + slot];
         w[slot] = route_weights[row * kTop + slot];
         slot_rows[slot] = *reinterpret_cast<const uint4*>(mixed + static_cast<std::size_t>(pos) * hidden + c8 * 8);
     }
@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(256) combine_shared_kernel(const std::uint16_t
         }
     }
     const uint4 sh = *reinterpret_cast<const uint4*>(
-        mixed + (static_cast<std::size_t>(rows) * kTop + row) * hidden + c8 * 8);
+        mixed + static_cast<std::size_t>(mixed_index[rows * kTop + row]) * hidden + c8 * 8);
     const std::uint32_t sw[4] = {sh.x, sh.y, sh.z, sh.w};
     std::uint32_t out_words[4];
 #pragma unroll
@@ -189,11 +189,11 @@ cudaError_t launch_quantize(const std::uint16_t* input, std::uint8_t* output, st
     return cudaGetLastError();
 }
 
-cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* position,
+cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* mixed_index,
                                   const float* route_weights, std::uint16_t* output, int rows,
                                   int hidden, cudaStream_t stream) {
     dim3 grid(blocks_for(hidden / 8, 256), rows);
-    combine_shared_kernel<<<grid, 256, 0, stream>>>(mixed, position, route_weights, output, rows, hidden);
+    combine_shared_kernel<<<grid, 256, 0, stream>>>(mixed, mixed_index, route_weights, output, rows, hidden);
     return cudaGetLastError();
 }
 

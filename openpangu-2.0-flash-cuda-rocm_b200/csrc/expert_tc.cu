@@ -1,0 +1,468 @@
+// Tensor-core expert kernels: tcgen05 block-scaled MMA (E2M1 x E2M1, one UE4M3
+// scale per 16 elements along K) with TMA-staged operands and TMEM accumulators.
+//
+// Orientation.  The expert weight is the M side of the MMA (128 weight rows per
+// tile fill the 128 TMEM lanes), the tokens routed to the expert are the N side
+// (N = 16...128 columns).  With one or two tokens per expert (decode) the kernel
+// is a pure weight streamer - TMA pulls 128 x 128-byte weight boxes through a
+// shared-memory ring and the tensor core consumes them at a small N - and with
+// hundreds of tokens per expert (prefill) the same code is a grouped GEMM.
+//
+// One block = 6 warps, persistent over work items (expert, token tile, 128-row tile):
+//   warp 0  producer: one elected lane issues the TMA copies of a K block
+//           (256 elements = 128 bytes per row): weight box(es), token box, and the
+//           three 2 KB scale-factor slabs, all completing on the stage's mbarrier;
+//   warp 1  MMA issuer: owns TMEM; per K block copies the scale slabs SMEM->TMEM
+//           (tcgen05.cp) and issues 4 MMAs of K=64 per weight operand; commits the
+//           stage back to the producer and, after the last K block, the
+//           accumulator to the epilogue;
+//   warps 2-5  epilogue: each reads its 32-lane quarter of the accumulator
+//           (tcgen05.ld), applies the per-tensor scale, rounds to BF16 where the
+//           reference does, and either fuses SwiGLU + re-quantisation to NVFP4
+//           (gate/up) or stores the BF16 down rows.
+// Scale factors stay in the 128x4-tiled layout the reference keeps them in
+// (cuda/nvfp4_ops.cu:869-890): one 512-byte tile is exactly one tcgen05.cp atom.
+//
+// Every mbarrier wait is bounded; on expiry the block records kStatusWaitExpired,
+// stops issuing work, frees its TMEM and returns.
+#include "p92b_common.cuh"
+#include "tc_ptx.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+
+namespace p92b {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kBlockKBytes = 128;                 // one swizzle row: 256 E2M1 values
+constexpr int kSfSlab = 2048;                     // 128 rows x 16 scales of one K block
+constexpr int kThreadsTc = 192;
+
+template <int MODE, int N>
+struct Tc {
+    static constexpr int kA = MODE == 0 ? 2 : 1;
+    static constexpr int kABytes = kTileM * kBlockKBytes;
+    static constexpr int kBBytes = N * kBlockKBytes;
+    static constexpr int kStageBytes = kA * (kABytes + kSfSlab) + kBBytes + kSfSlab;
+    static constexpr int kStagesRaw = (196 * 1024) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kAccumStride = N < 32 ? 32 : N;          // each accumulator starts on a multiple of 32 columns
+    static constexpr int kAccumCols = kA * kAccumStride;
+    static constexpr int kSfCols = (kA + 1) * 16;                 // per buffer: 4 columns per K=64 step
+    static constexpr int kNeedCols = kAccumCols + 2 * kSfCols;
+    static constexpr int kTmemCols = kNeedCols <= 32 ? 32 : kNeedCols <= 64 ? 64 : kNeedCols <= 128 ? 128
+                                     : kNeedCols <= 256 ? 256 : 512;
+    static constexpr int kBarrierBytes = (2 * kStages + 2) * 8 + 16;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;   // + alignment slack
+    static_assert(kNeedCols <= 512, "accumulators and scale factors must fit TMEM");
+};
+
+struct TcParams {
+    BankView bank;
+    RouteView route;
+    const std::int32_t* pp_off;        // [258]
+    const std::int32_t* tile_prefix;   // [active_count + 1]
+    const std::uint8_t* b_sf;          // token-side scales, 128x4 tiled over padded positions
+    std::uint8_t* hq;                  // MODE 0 out: packed SwiGLU rows [PP][I/2]
+    std::uint8_t* hs;                  // MODE 0 out: their scales, 128x4 tiled over padded positions
+    std::uint16_t* out;                // MODE 1 out: BF16 down rows [PP][H]
+    std::int32_t* status;
+    float quant_scale;                 // 1.0, passed at run time so the quantiser's divisions stay run-time operations
+    int k_bytes;                       // K/2: bytes per operand row
+    int m_total;                       // output rows per expert matrix
+    int m_tiles;
+    int debug_level;                   // 0 full kernel; 1..4 stop after set-up / TMA / scale copies / MMA (bring-up aid)
+};
+
+struct Item {
+    int expert;
+    int entry;
+    int count;
+    int m_tile;
+    int pp0;
+    int valid;     // tokens of this tile that exist
+};
+
+template <int N>
+__device__ __forceinline__ bool decode_item(const TcParams& p, int item, Item* it) {
+    const int tt = item / p.m_tiles;
+    it->m_tile = item - tt * p.m_tiles;
+    const int active_count = *p.route.active_count;
+    int lo = 0, hi = active_count;           // find a: tile_prefix[a] <= tt < tile_prefix[a+1]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (p.tile_prefix[mid] <= tt) lo = mid; else hi = mid;
+    }
+    const int n_tile = tt - p.tile_prefix[lo];
+    it->expert = p.route.active[lo];
+    it->entry = it->expert == kExperts ? p.bank.local_experts : it->expert - p.bank.first_expert;
+    it->count = p.route.counts[it->expert];
+    it->pp0 = p.pp_off[it->expert] + n_tile * N;
+    it->valid = min(N, it->count - n_tile * N);
+    return it->entry >= 0 && it->entry <= p.bank.local_experts;
+}
+
+template <int MODE, int N>
+__global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                   const __grid_constant__ CUtensorMap map_b,
+                                                                   const TcParams p) {
+    using C = Tc<MODE, N>;
+    extern __shared__ std::uint8_t smem_raw[];
+    const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    const std::uint32_t bars = base + C::kStages * C::kStageBytes;
+    auto full_bar = [&](int s) { return bars + 8U * s; };
+    auto empty_bar = [&](int s) { return bars + 8U * (C::kStages + s); };
+    const std::uint32_t accum_full = bars + 8U * (2 * C::kStages);
+    const std::uint32_t accum_empty = accum_full + 8U;
+    const std::uint32_t tmem_slot = accum_empty + 8U;
+    volatile std::uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile std::uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+    volatile std::uint32_t* abort_ptr = tmem_slot_ptr + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int k_blocks = p.k_bytes / kBlockKBytes;
+    const int total_items = p.tile_prefix[*p.route.active_count] * p.m_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accum_full, 1);
+        mbar_init(accum_empty, 4);
+        *abort_ptr = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const std::uint32_t tmem_base = *tmem_slot_ptr;
+    const int level = p.debug_level;
+    if (threadIdx.x == 0 && ((bars & 7U) != 0U || (base & 1023U) != 0U)) {
+        atomicCAS(p.status, kStatusOk, 100);
+        *abort_ptr = 1;
+    }
+    __syncthreads();
+    auto give_up = [&]() {
+        *abort_ptr = 1;
+        atomicCAS(p.status, kStatusOk, kStatusWaitExpired);
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (elect_one()) {
+            int stage = 0;
+            std::uint32_t phase = 0;
+            const std::size_t a_sf_matrix = static_cast<std::size_t>(p.m_total / 128) * (p.k_bytes / 32) * 512;
+            const std::uint8_t* a_sf_base = MODE == 0 ? p.bank.sfs13 : p.bank.sfs2;
+            for (int item = blockIdx.x; item < total_items && !*abort_ptr && level != 1; item += gridDim.x) {
+                Item it;
+                if (!decode_item<N>(p, item, &it)) continue;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(); break; }
+                    const std::uint32_t st = base + stage * C::kStageBytes;
+                    mbar_arrive_expect_tx(full_bar(stage), C::kStageBytes);
+#pragma unroll
+                    for (int a = 0; a < C::kA; ++a) {
+                        const int matrix = it.entry * C::kA + a;
+                        tma_load_2d(st + a * C::kABytes, &map_a, full_bar(stage), kb * kBlockKBytes,
+                                    matrix * p.m_total + it.m_tile * kTileM);
+                        const std::uint8_t* sf = a_sf_base + static_cast<std::size_t>(matrix) * a_sf_matrix +
+                                                 (static_cast<std::size_t>(it.m_tile) * (p.k_bytes / 32) + kb * 4) * 512;
+                        if ((reinterpret_cast<std::uintptr_t>(sf) & 15U) != 0U) { atomicCAS(p.status, kStatusOk, 101); *abort_ptr = 1; }
+                        bulk_load(st + C::kA * C::kABytes + C::kBBytes + a * kSfSlab, sf, kSfSlab, full_bar(stage));
+                    }
+                    tma_load_2d(st + C::kA * C::kABytes, &map_b, full_bar(stage), kb * kBlockKBytes, it.pp0);
+                    const std::uint8_t* bsf = p.b_sf +
+                        (static_cast<std::size_t>(it.pp0 >> 7) * (p.k_bytes / 32) + kb * 4) * 512;
+                    if ((reinterpret_cast<std::uintptr_t>(bsf) & 15U) != 0U) { atomicCAS(p.status, kStatusOk, 102); *abort_ptr = 1; }
+                    bulk_load(st + C::kA * C::kABytes + C::kBBytes + C::kA * kSfSlab, bsf, kSfSlab, full_bar(stage));
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- MMA issuer
+        if (elect_one()) {
+            int stage = 0;
+            std::uint32_t phase = 0;
+            std::uint32_t accum_phase = 0;
+            constexpr std::uint32_t idesc = idesc_nvf4(kTileM, N);
+            const std::uint32_t sf_tmem = tmem_base + C::kAccumCols;
+            int sf_buffer = 0;
+            for (int item = blockIdx.x; item < total_items && !*abort_ptr && level != 1; item += gridDim.x) {
+                Item it;
+                if (!decode_item<N>(p, item, &it)) continue;
+                if (!mbar_wait(accum_empty, accum_phase ^ 1U)) { give_up(); break; }
+                tc_fence_after();
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase)) { give_up(); ok = false; break; }
+                    tc_fence_after();
+                    const std::uint32_t st = base + stage * C::kStageBytes;
+                    const std::uint32_t sf_smem = st + C::kA * C::kABytes + C::kBBytes;
+                    const std::uint32_t sfc = sf_tmem + sf_buffer * C::kSfCols;
+                    if (level == 0 || level >= 3) {
+#pragma unroll
+                        for (int o = 0; o < C::kA + 1; ++o) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                tc_copy_sf(sfc + o * 16 + k * 4, desc_scale_atom(sf_smem + o * kSfSlab + k * 512));
+                            }
+                        }
+                    }
+                    const std::uint64_t b_desc = desc_k_major_sw128(st + C::kA * C::kABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                        for (int a = 0; a < C::kA; ++a) {
+                            const std::uint64_t a_desc = desc_k_major_sw128(st + a * C::kABytes);
+                            if (level == 0 || level >= 4) {
+                                mma_nvf4(tmem_base + a * C::kAccumStride, a_desc + 2 * k, b_desc + 2 * k, idesc, sfc + a * 16 + k * 4,
+                                         sfc + C::kA * 16 + k * 4, kb > 0 || k > 0);
+                            }
+                        }
+                    }
+                    tc_commit(empty_bar(stage));
+                    sf_buffer ^= 1;
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
+                }
+                if (!ok) break;
+                tc_commit(accum_full);
+                accum_phase ^= 1U;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31
+        std::uint32_t accum_phase = 0;
+        for (int item = blockIdx.x; item < total_items && !*abort_ptr && level != 1; item += gridDim.x) {
+            Item it;
+            if (!decode_item<N>(p, item, &it)) continue;
+            if (!mbar_wait(accum_full, accum_phase)) { give_up(); break; }
+            accum_phase ^= 1U;
+            tc_fence_after();
+            if (level != 0) it.valid = 0;
+            const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16);
+            const int row = it.m_tile * kTileM + quarter * 32 + lane;          // output row of this lane
+            if constexpr (MODE == 0) {
+                const float alpha_g = p.bank.alpha[it.entry * 3 + 0];
+                const float alpha_u = p.bank.alpha[it.entry * 3 + 1];
+                const int inter = p.m_total;
+                const int sf_cols = inter / 16;
+                const int sf_col = row >> 4;
+#pragma unroll 1
+                for (int c0 = 0; c0 < N; c0 += 16) {
+                    if (c0 >= it.valid) break;
+                    std::uint32_t g[16], u[16];
+                    tmem_load16(lane_base + c0, g);
+                    tmem_load16(lane_base + C::kAccumStride + c0, u);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int n = c0 + j;
+                        if (n >= it.valid) break;                                 // warp uniform
+                        const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[j]) * alpha_g));
+                        const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[j]) * alpha_u));
+                        const float h = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
+                        // 16 consecutive rows (half a warp) form one NVFP4 block of the down product's K
+                        float amax = fabsf(h);
+#pragma unroll
+                        for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffU, amax, off));
+                        const __nv_fp8_e4m3 scale(amax * (p.quant_scale / 6.0F));
+                        const float decoded = static_cast<float>(scale);
+                        const float multiplier = decoded == 0.0F ? 0.0F : p.quant_scale / decoded;
+                        const float q = h * multiplier;
+                        const float q_next = __shfl_xor_sync(0xffffffffU, q, 1);
+                        const std::size_t pp = static_cast<std::size_t>(it.pp0 + n);
+                        if ((lane & 1) == 0) {
+                            p.hq[pp * (inter / 2) + (row >> 1)] =
+                                static_cast<std::uint8_t>(__nv_fp4x2_e2m1(make_float2(q, q_next)).__x);
+                        }
+                        if ((lane & 15) == 0) {
+                            const std::size_t at = ((pp >> 7) * ((sf_cols + 3) / 4) + (sf_col >> 2)) * 512 +
+                                                   (pp & 31) * 16 + ((pp >> 5) & 3) * 4 + (sf_col & 3);
+                            p.hs[at] = scale.__x;
+                        }
+                    }
+                }
+            } else {
+                const float alpha = p.bank.alpha[it.entry * 3 + 2];
+                const int hidden = p.m_total;
+#pragma unroll 1
+                for (int c0 = 0; c0 < N; c0 += 16) {
+                    if (c0 >= it.valid) break;
+                    std::uint32_t d[16];
+                    tmem_load16(lane_base + c0, d);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int n = c0 + j;
+                        if (n >= it.valid) break;
+                        p.out[static_cast<std::size_t>(it.pp0 + n) * hidden + row] =
+                            float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accum_empty);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// Quantises the token rows into the padded position space of the tensor-core
+// kernels: row pp gets the NVFP4 bytes of its token, and the scales go straight
+// into the 128x4-tiled layout (cuda/nvfp4_ops.cu:818-841 and :869-890 in one pass).
+// One warp per (row, slot) assignment or shared row; lane l owns 16-element blocks l, l+32, ...
+__global__ void __launch_bounds__(256) quantize_padded_kernel(const std::uint16_t* __restrict__ x,
+                                                              const std::int32_t* __restrict__ pp_of_flat,
+                                                              std::uint8_t* __restrict__ xq,
+                                                              std::uint8_t* __restrict__ xs, int rows, int hidden,
+                                                              float global_scale) {
+    const int lane = threadIdx.x & 31;
+    const int index = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // 0 .. 9*rows
+    if (index >= rows * (kTop + 1)) return;
+    const int token = index < rows * kTop ? index / kTop : index - rows * kTop;
+    const std::size_t pp = static_cast<std::size_t>(pp_of_flat[index]);
+    const int blocks = hidden / 16;
+    const int col_blocks = (blocks + 3) / 4;
+    for (int b = lane; b < blocks; b += 32) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(token) * hidden + b * 16);
+        const uint4 lo = __ldg(src);
+        const uint4 hi = __ldg(src + 1);
+        const std::uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = __uint_as_float(words[i] << 16);
+            v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+        }
+        std::uint8_t scale_bits;
+        const uint2 packed = quantize_block16(v, global_scale, &scale_bits);
+        *reinterpret_cast<uint2*>(xq + pp * (hidden / 2) + b * 8) = packed;
+        const std::size_t at = ((pp >> 7) * col_blocks + (b >> 2)) * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4 + (b & 3);
+        xs[at] = scale_bits;
+    }
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &query) == cudaSuccess &&
+            query == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiled>(sym);
+        }
+    }
+    return fn;
+}
+
+template <int MODE, int N>
+cudaError_t launch_tc(const p92b_plan* plan, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p,
+                      cudaStream_t stream) {
+    using C = Tc<MODE, N>;
+    auto kernel = expert_tc_kernel<MODE, N>;
+    cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (st != cudaSuccess) return st;
+    kernel<<<plan->sm_count, kThreadsTc, C::kSmemBytes, stream>>>(map_a, map_b, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// Row-major byte matrix [rows][row_bytes] as a 2-D tensor map with a 128-byte x box_rows box and
+// the 128-byte swizzle (what the K-major operand descriptors expect).
+cudaError_t make_operand_map(CUtensorMap* map, const void* base, std::size_t rows, std::size_t row_bytes,
+                             int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockKBytes), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+int tc_tile_rows(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128; }
+// Every entry's rows start on a multiple of 128 padded positions, so a token tile always begins at
+// row 0 of a 128-row scale-factor tile (TMEM lane 0, first scale column).
+int tc_pad_align(int rows) { (void)rows; return 128; }
+
+cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x, int rows, cudaStream_t stream) {
+    const int warps = rows * (kTop + 1);
+    quantize_padded_kernel<<<(warps + 7) / 8, 256, 0, stream>>>(x, plan->pp_of_flat, plan->xq_pp, plan->xs_sw, rows,
+                                                                plan->hidden, 1.0F);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
+                              cudaStream_t stream) {
+    if (!bank->tc_ready || !plan->tc_ready) return cudaErrorNotSupported;
+    TcParams p {};
+    p.bank = bank->view;
+    p.route.counts = plan->counts;
+    p.route.offsets = plan->offsets;
+    p.route.row_token = plan->row_token;
+    p.route.active = plan->active;
+    p.route.active_count = plan->active_count;
+    p.pp_off = plan->pp_off;
+    p.tile_prefix = plan->tile_prefix;
+    p.status = plan->status;
+    p.quant_scale = 1.0F;
+    if (const char* env = std::getenv("P92B_TC_DEBUG")) p.debug_level = std::atoi(env);
+    const int n = tc_tile_rows(rows);
+    const int which = n == 16 ? 0 : n == 32 ? 1 : n == 64 ? 2 : 3;
+    if (!down) {
+        p.b_sf = plan->xs_sw;
+        p.hq = plan->hq_pp;
+        p.hs = plan->hs_sw;
+        p.k_bytes = plan->hidden / 2;
+        p.m_total = plan->intermediate;
+        p.m_tiles = plan->intermediate / kTileM;
+        switch (which) {
+            case 0: return launch_tc<0, 16>(plan, bank->map_w13, plan->map_x[0], p, stream);
+            case 1: return launch_tc<0, 32>(plan, bank->map_w13, plan->map_x[1], p, stream);
+            case 2: return launch_tc<0, 64>(plan, bank->map_w13, plan->map_x[2], p, stream);
+            default: return launch_tc<0, 128>(plan, bank->map_w13, plan->map_x[3], p, stream);
+        }
+    }
+    p.b_sf = plan->hs_sw;
+    p.out = plan->mixed_pp;
+    p.k_bytes = plan->intermediate / 2;
+    p.m_total = plan->hidden;
+    p.m_tiles = plan->hidden / kTileM;
+    switch (which) {
+        case 0: return launch_tc<1, 16>(plan, bank->map_w2, plan->map_h[0], p, stream);
+        case 1: return launch_tc<1, 32>(plan, bank->map_w2, plan->map_h[1], p, stream);
+        case 2: return launch_tc<1, 64>(plan, bank->map_w2, plan->map_h[2], p, stream);
+        default: return launch_tc<1, 128>(plan, bank->map_w2, plan->map_h[3], p, stream);
+    }
+}
+
+}  // namespace p92b

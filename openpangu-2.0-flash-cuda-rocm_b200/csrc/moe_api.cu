@@ -3,6 +3,8 @@
 #include "p92b_common.cuh"
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -149,6 +151,13 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
     bank->view.local_experts = local_experts;
     bank->view.hidden = hidden;
     bank->view.intermediate = intermediate;
+    // TMA maps for the tensor-core kernels; without the driver entry point the bank still serves the
+    // weight-streaming kernels and the tensor-core path reports cudaErrorNotSupported
+    bank->tc_ready =
+        make_operand_map(&bank->map_w13, w13, static_cast<std::size_t>(entries) * 2 * intermediate, hidden / 2, 128) ==
+            cudaSuccess &&
+        make_operand_map(&bank->map_w2, w2, static_cast<std::size_t>(entries) * hidden, intermediate / 2, 128) ==
+            cudaSuccess;
     *out = bank;
     return cudaSuccess;
 }
@@ -182,6 +191,13 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
     }
     const std::size_t rows = static_cast<std::size_t>(max_rows);
     plan->chunks = static_cast<int>((rows * kTop + 255) / 256);
+    {
+        // worst case of the padded position space: every active entry wastes (align - 1) rows
+        const std::size_t align = static_cast<std::size_t>(tc_pad_align(max_rows));
+        const std::size_t active = std::min<std::size_t>(kExperts, rows * kTop) + 1;
+        plan->pp_rows = (rows * (kTop + 1) + active * (align - 1) + 127) / 128 * 128;
+    }
+    if (const char* env = std::getenv("P92B_PATH")) plan->path = std::atoi(env);
     for (int pass = 0; pass < 2; ++pass) {
         Carver c;
         c.base = static_cast<std::uint8_t*>(plan->storage);
@@ -195,12 +211,20 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->row_token = c.take<std::int32_t>(rows * (kTop + 1));
         plan->active = c.take<std::int32_t>(kExperts + 1);
         plan->active_count = c.take<std::int32_t>(1);
+        plan->pp_off = c.take<std::int32_t>(kExperts + 2);
+        plan->tile_prefix = c.take<std::int32_t>(kExperts + 2);
+        plan->pp_of_flat = c.take<std::int32_t>(rows * (kTop + 1));
         plan->chunk_hist = c.take<std::int32_t>(static_cast<std::size_t>(plan->chunks) * kExperts);
         plan->xq = c.take<std::uint8_t>(rows * (hidden / 2));
         plan->xs = c.take<std::uint8_t>(rows * (hidden / 16));
         plan->hq = c.take<std::uint8_t>(rows * (kTop + 1) * (intermediate / 2));
         plan->hs = c.take<std::uint8_t>(rows * (kTop + 1) * (intermediate / 16));
         plan->mixed = c.take<std::uint16_t>(rows * (kTop + 1) * hidden);
+        plan->xq_pp = c.take<std::uint8_t>(plan->pp_rows * (hidden / 2));
+        plan->xs_sw = c.take<std::uint8_t>(plan->pp_rows * (hidden / 16));
+        plan->hq_pp = c.take<std::uint8_t>(plan->pp_rows * (intermediate / 2));
+        plan->hs_sw = c.take<std::uint8_t>(plan->pp_rows * (intermediate / 16));
+        plan->mixed_pp = c.take<std::uint16_t>(plan->pp_rows * hidden);
         plan->stage_in = c.take<std::uint16_t>(rows * hidden);
         plan->stage_out = c.take<std::uint16_t>(rows * hidden);
         plan->status = c.take<std::int32_t>(1);
@@ -219,7 +243,24 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
             }
         }
     }
+    {
+        static const int kBoxRows[4] = {16, 32, 64, 128};
+        bool ok = true;
+        for (int i = 0; i < 4; ++i) {
+            ok = ok && make_operand_map(&plan->map_x[i], plan->xq_pp, plan->pp_rows, hidden / 2, kBoxRows[i]) == cudaSuccess;
+            ok = ok && make_operand_map(&plan->map_h[i], plan->hq_pp, plan->pp_rows, intermediate / 2, kBoxRows[i]) ==
+                           cudaSuccess;
+        }
+        plan->tc_ready = ok;
+    }
     *out = plan;
+    return cudaSuccess;
+}
+
+int p92b_plan_set_path(p92b_plan* plan, int path) {
+    if (plan == nullptr || path < 0 || path > 2) return cudaErrorInvalidValue;
+    if (path == 2 && !plan->tc_ready) return cudaErrorNotSupported;
+    plan->path = path;
     return cudaSuccess;
 }
 
@@ -268,7 +309,8 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* v) {
     v->position = plan->position;
     v->counts = plan->counts;
     v->offsets = plan->offsets;
-    v->mixed = plan->mixed;
+    v->mixed = plan->last_path == 2 ? plan->mixed_pp : plan->mixed;
+    v->mixed_index = plan->pp_of_flat;
     v->status = plan->status;
     return cudaSuccess;
 }
@@ -298,7 +340,7 @@ int p92b_router_top8(const float* logits, const float* correction_bias, int32_t*
 int p92b_moe_permute(p92b_plan* plan, const int32_t* expert_ids, int assignments, int32_t* order,
                      int32_t* position, int32_t* counts, int32_t* offsets, void* stream) {
     if (plan == nullptr) return cudaErrorInvalidValue;
-    return launch_permute(plan, expert_ids, assignments, order, position, counts, offsets, false, 0, kExperts,
+    return launch_permute(plan, expert_ids, assignments, order, position, counts, offsets, false, 0, 0,
                           static_cast<cudaStream_t>(stream));
 }
 
@@ -314,8 +356,18 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
     const int hidden = plan->hidden;
     plan->last_launches = 0;
     int stage = 0;
+    // P92B_DEBUG_SYNC=1: synchronise after every stage so an asynchronous fault is reported by the
+    // stage that caused it (printed to stderr); a debugging aid, never on in measurements
+    static const bool debug_sync = std::getenv("P92B_DEBUG_SYNC") != nullptr;
     auto mark = [&]() -> cudaError_t {
-        if (!plan->timing) return cudaSuccess;
+        if (debug_sync) {
+            const cudaError_t sync = cudaStreamSynchronize(stream);
+            if (sync != cudaSuccess) {
+                std::fprintf(stderr, "p92b_moe_forward: stage before mark %d failed: %s\n", stage, cudaGetErrorString(sync));
+                return sync;
+            }
+        }
+        if (!plan->timing) { ++stage; return cudaSuccess; }
         return cudaEventRecord(plan->stage_events[stage++], stream);
     };
     cudaError_t st = mark();
@@ -327,24 +379,41 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
     if (st != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
     plan->last_launches += 2;
-    st = launch_permute(plan, plan->ids, rows * kTop, plan->order, plan->position, plan->counts, plan->offsets, true, 0,
-                        kExperts, stream);
+    const bool tc = plan->path == 2 || (plan->path == 0 && plan->tc_ready && bank->tc_ready);
+    if (tc && (!plan->tc_ready || !bank->tc_ready)) return cudaErrorNotSupported;
+    plan->last_path = tc ? 2 : 1;
+    st = launch_permute(plan, plan->ids, rows * kTop, plan->order, plan->position, plan->counts, plan->offsets, true,
+                        tc ? tc_pad_align(rows) : 1, tc ? tc_tile_rows(rows) : (1 << 30), stream);
     if (st != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
-    st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * hidden / 16, 1.0F, stream);
-    if (st != cudaSuccess) return st;
-    if ((st = mark()) != cudaSuccess) return st;
-    const RouteView route = route_view(plan);
-    st = launch_gate_up(plan, bank->view, route, plan->xq, plan->xs, plan->hq, plan->hs, nullptr, nullptr, plan->order,
-                        rows, stream);
-    if (st != cudaSuccess) return st;
-    if ((st = mark()) != cudaSuccess) return st;
-    st = launch_down(plan, bank->view, route, plan->hq, plan->hs, plan->mixed, nullptr, nullptr, 0, stream);
-    if (st != cudaSuccess) return st;
-    if ((st = mark()) != cudaSuccess) return st;
-    st = launch_combine_shared(plan->mixed, plan->position, plan->route_weights, output, rows, hidden, stream);
+    if (tc) {
+        st = launch_quantize_padded(plan, input, rows, stream);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        st = launch_experts_tc(plan, bank, rows, false, stream);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        st = launch_experts_tc(plan, bank, rows, true, stream);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        st = launch_combine_shared(plan->mixed_pp, plan->pp_of_flat, plan->route_weights, output, rows, hidden, stream);
+    } else {
+        st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * hidden / 16, 1.0F, stream);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        const RouteView route = route_view(plan);
+        st = launch_gate_up(plan, bank->view, route, plan->xq, plan->xs, plan->hq, plan->hs, nullptr, nullptr,
+                            plan->order, rows, stream);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        st = launch_down(plan, bank->view, route, plan->hq, plan->hs, plan->mixed, nullptr, nullptr, 0, stream);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        st = launch_combine_shared(plan->mixed, plan->pp_of_flat, plan->route_weights, output, rows, hidden, stream);
+    }
     plan->last_launches += 4;
     if (st != cudaSuccess) return st;
+    if (debug_sync && !plan->timing && (st = mark()) != cudaSuccess) return st;
     if (plan->timing) {
         if ((st = mark()) != cudaSuccess) return st;
         if ((st = cudaStreamSynchronize(stream)) != cudaSuccess) return st;
@@ -386,7 +455,7 @@ int p92b_project_expert_gate_up(p92b_plan* plan, const p92b_bank* bank, const in
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     plan->last_launches = 0;
     cudaError_t st = launch_permute(plan, expert_ids, rows * kTop, plan->order, plan->position, plan->counts,
-                                    plan->offsets, true, 0, kExperts, stream);
+                                    plan->offsets, true, 1, 1 << 30, stream);
     if (st != cudaSuccess) return st;
     st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * plan->hidden / 16, 1.0F, stream);
     if (st != cudaSuccess) return st;
@@ -405,7 +474,7 @@ int p92b_project_expert_down(p92b_plan* plan, const p92b_bank* bank, const int32
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     plan->last_launches = 0;
     cudaError_t st = launch_permute(plan, expert_ids, rows * kTop, plan->order, plan->position, plan->counts,
-                                    plan->offsets, true, 0, kExperts, stream);
+                                    plan->offsets, true, 1, 1 << 30, stream);
     if (st != cudaSuccess) return st;
     // every (row, slot) intermediate row is quantised on its own (src/executor.cpp:85-91), in flat order
     st = launch_quantize(input_rows, plan->hq, plan->hs, static_cast<long>(rows) * kTop * plan->intermediate / 16, 1.0F,

@@ -1,6 +1,7 @@
 // Shared device helpers and internal structures of the sm_100a MoE library.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp4.h>
@@ -105,6 +106,10 @@ struct p92b_bank {
     p92b::BankView view {};
     void* storage = nullptr;
     std::size_t bytes = 0;
+    // tensor-core path: TMA maps over the packed weights (rows of K/2 bytes)
+    bool tc_ready = false;
+    CUtensorMap map_w13 {};
+    CUtensorMap map_w2 {};
 };
 
 struct p92b_plan {
@@ -126,6 +131,9 @@ struct p92b_plan {
     std::int32_t* row_token = nullptr;    // [9*max_rows]
     std::int32_t* active = nullptr;       // [257]
     std::int32_t* active_count = nullptr; // [1]
+    std::int32_t* pp_off = nullptr;       // [258] padded offsets (tensor-core path)
+    std::int32_t* tile_prefix = nullptr;  // [258]
+    std::int32_t* pp_of_flat = nullptr;   // [9*max_rows] padded position of (row, slot), shared rows last
     std::int32_t* chunk_hist = nullptr;   // [chunks][256]
     int chunks = 0;
     std::uint8_t* xq = nullptr;           // [max_rows][H/2]
@@ -136,6 +144,19 @@ struct p92b_plan {
     std::uint16_t* stage_in = nullptr;    // [max_rows][H]  host-call staging
     std::uint16_t* stage_out = nullptr;   // [max_rows][H]
     std::int32_t* status = nullptr;       // [1]
+    // tensor-core path: operands in the padded position space (every expert's rows start on a
+    // multiple of 32 or 128), scales in the 128x4-tiled layout
+    int last_path = 1;                    // path the last forward took
+    int path = 0;                         // 0 auto, 1 weight-streaming SIMT kernels, 2 tcgen05 kernels
+    bool tc_ready = false;
+    std::size_t pp_rows = 0;              // rows of the padded buffers
+    std::uint8_t* xq_pp = nullptr;        // [pp_rows][H/2]
+    std::uint8_t* xs_sw = nullptr;        // tiled scales of xq_pp
+    std::uint8_t* hq_pp = nullptr;        // [pp_rows][I/2]
+    std::uint8_t* hs_sw = nullptr;        // tiled scales of hq_pp
+    std::uint16_t* mixed_pp = nullptr;    // [pp_rows][H]
+    CUtensorMap map_x[4] = {};            // token boxes of 16/32/64/128 rows over xq_pp
+    CUtensorMap map_h[4] = {};            // same over hq_pp
     // optional stage timing (host side)
     bool timing = false;
     cudaEvent_t stage_events[P92B_STAGES + 1] = {};
@@ -153,8 +174,8 @@ cudaError_t launch_router_top8(const float* logits, const float* bias, std::int3
                                float* weights, int rows, float routed_scale, cudaStream_t stream);
 cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignments,
                            std::int32_t* order, std::int32_t* position, std::int32_t* counts,
-                           std::int32_t* offsets, bool route_lists, int first_expert,
-                           int local_experts, cudaStream_t stream);
+                           std::int32_t* offsets, bool route_lists, int pad_align, int tile_rows,
+                           cudaStream_t stream);
 cudaError_t launch_quantize(const std::uint16_t* input, std::uint8_t* output, std::uint8_t* scales,
                             long groups, float global_scale, cudaStream_t stream);
 cudaError_t launch_gate_up(const p92b_plan* plan, const BankView& bank, const RouteView& route,
@@ -167,8 +188,16 @@ cudaError_t launch_down(const p92b_plan* plan, const BankView& bank, const Route
                         cudaStream_t stream);
 cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,
                              cudaStream_t stream);
-cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* position,
+cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* mixed_index,
                                   const float* route_weights, std::uint16_t* output, int rows,
                                   int hidden, cudaStream_t stream);
+// tensor-core path (expert_tc.cu)
+cudaError_t make_operand_map(CUtensorMap* map, const void* base, std::size_t rows, std::size_t row_bytes,
+                             int box_rows);
+int tc_tile_rows(int rows);
+int tc_pad_align(int rows);
+cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x, int rows, cudaStream_t stream);
+cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
+                              cudaStream_t stream);
 
 }  // namespace p92b

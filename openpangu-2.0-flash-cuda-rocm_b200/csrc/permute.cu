@@ -44,7 +44,9 @@ __device__ __forceinline__ void warp_scatter(const std::int32_t* __restrict__ id
                                              const std::int32_t* base, std::int32_t* running,
                                              std::int32_t* __restrict__ order,
                                              std::int32_t* __restrict__ position,
-                                             std::int32_t* __restrict__ row_token) {
+                                             std::int32_t* __restrict__ row_token,
+                                             const std::int32_t* offsets, const std::int32_t* pp_off,
+                                             std::int32_t* __restrict__ pp_of_flat) {
     const int lane = threadIdx.x & 31;
     for (int e = lane; e < kExperts; e += 32) running[e] = base[e];
     __syncwarp();
@@ -61,6 +63,7 @@ __device__ __forceinline__ void warp_scatter(const std::int32_t* __restrict__ id
             if (order != nullptr) order[pos] = i;
             if (position != nullptr) position[i] = pos;
             if (row_token != nullptr) row_token[pos] = i / kTop;
+            if (pp_of_flat != nullptr) pp_of_flat[i] = pp_off[e] + pos - offsets[e];
         }
         __syncwarp();
         if (valid && rank == 0) running[e] += __popc(peers);
@@ -87,32 +90,59 @@ __device__ __forceinline__ int block_exclusive_scan_256(int value, std::int32_t*
 }
 
 // Lists written for the expert kernels: counts/offsets extended with the shared
-// expert as entry 256 (rows = tokens, positions after the routed ones), and the
+// expert as entry 256 (rows = tokens, positions after the routed ones), the
 // compact list of entries that have rows, shared expert first (it is the largest
-// group, so the persistent kernels start it first).
+// group, so the persistent kernels start it first), and - for the tensor-core
+// kernels - a padded position space in which every entry's rows start on a
+// multiple of `pad_align`, plus the prefix of token-tile counts over the active list.
+struct RouteLists {
+    std::int32_t* counts;        // [257]
+    std::int32_t* offsets;       // [258]
+    std::int32_t* active;        // [257]
+    std::int32_t* active_count;  // [1]
+    std::int32_t* pp_off;        // [258] padded offsets (null: not wanted)
+    std::int32_t* tile_prefix;   // [258] exclusive prefix of token tiles over the active list, total last
+    int pad_align;
+    int tile_rows;
+    bool enabled;
+};
+
 __device__ __forceinline__ void write_route_lists(int e, int count, int offset, int assignments, int rows,
-                                                  std::int32_t* counts, std::int32_t* offsets,
-                                                  std::int32_t* active, std::int32_t* active_count,
-                                                  bool route_lists, std::int32_t* scan_scratch) {
-    counts[e] = count;
-    offsets[e] = offset;
-    if (e == kExperts - 1) offsets[kExperts] = assignments;
-    if (!route_lists) return;
+                                                  const RouteLists& lists, std::int32_t* scan_scratch) {
+    lists.counts[e] = count;
+    lists.offsets[e] = offset;
+    if (e == kExperts - 1) lists.offsets[kExperts] = assignments;
+    if (!lists.enabled) return;
     const int slot = block_exclusive_scan_256(count > 0 ? 1 : 0, scan_scratch);
-    if (count > 0) active[1 + slot] = e;
+    if (count > 0) lists.active[1 + slot] = e;
     if (e == kExperts - 1) {
-        counts[kExperts] = rows;
-        offsets[kExperts + 1] = assignments + rows;
-        active[0] = kExperts;
-        *active_count = 1 + slot + (count > 0 ? 1 : 0);
+        lists.counts[kExperts] = rows;
+        lists.offsets[kExperts + 1] = assignments + rows;
+        lists.active[0] = kExperts;
+        *lists.active_count = 1 + slot + (count > 0 ? 1 : 0);
+    }
+    if (lists.pp_off == nullptr) return;
+    const int align = lists.pad_align;
+    const int padded = (count + align - 1) / align * align;
+    const int pp = block_exclusive_scan_256(padded, scan_scratch);
+    lists.pp_off[e] = pp;
+    const int tiles = (count + lists.tile_rows - 1) / lists.tile_rows;
+    const int shared_tiles = (rows + lists.tile_rows - 1) / lists.tile_rows;
+    const int before = block_exclusive_scan_256(tiles, scan_scratch);
+    if (count > 0) lists.tile_prefix[1 + slot] = shared_tiles + before;
+    if (e == kExperts - 1) {
+        lists.pp_off[kExperts] = pp + padded;
+        lists.pp_off[kExperts + 1] = pp + padded + (rows + align - 1) / align * align;
+        lists.tile_prefix[0] = 0;
+        lists.tile_prefix[1 + slot + (count > 0 ? 1 : 0)] = shared_tiles + before + tiles;   // total, after the last active
     }
 }
 
 // ---- single-block path (assignments <= 8 * 1024) ---------------------------
 __global__ void __launch_bounds__(256) permute_small_kernel(
     const std::int32_t* __restrict__ ids, int assignments, std::int32_t* order,
-    std::int32_t* position, std::int32_t* counts, std::int32_t* offsets, std::int32_t* row_token,
-    std::int32_t* active, std::int32_t* active_count, bool route_lists, std::int32_t* status) {
+    std::int32_t* position, RouteLists lists, std::int32_t* row_token, std::int32_t* pp_of_flat,
+    std::int32_t* status) {
     __shared__ std::int32_t hist[kWarps][kExperts];
     __shared__ std::int32_t running[kWarps][kExperts];
     __shared__ std::int32_t scan_scratch[kWarps];
@@ -134,12 +164,15 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
 #pragma unroll
     for (int wi = 0; wi < kWarps; ++wi) hist[wi][e] += offset;
     const int rows = assignments / kTop;
-    write_route_lists(e, total, offset, assignments, rows, counts, offsets, active, active_count, route_lists,
-                      scan_scratch);
+    write_route_lists(e, total, offset, assignments, rows, lists, scan_scratch);
     __syncthreads();
-    warp_scatter(ids, begin, end, hist[warp], running[warp], order, position, row_token);
+    warp_scatter(ids, begin, end, hist[warp], running[warp], order, position, row_token, lists.offsets, lists.pp_off,
+                 pp_of_flat);
     if (row_token != nullptr) {
-        for (int t = threadIdx.x; t < rows; t += blockDim.x) row_token[assignments + t] = t;
+        for (int t = threadIdx.x; t < rows; t += blockDim.x) {
+            row_token[assignments + t] = t;
+            if (pp_of_flat != nullptr) pp_of_flat[assignments + t] = lists.pp_off[kExperts] + t;
+        }
     }
 }
 
@@ -161,9 +194,7 @@ __global__ void __launch_bounds__(256) permute_hist_kernel(const std::int32_t* _
 }
 
 __global__ void __launch_bounds__(256) permute_scan_kernel(std::int32_t* __restrict__ chunk_hist, int chunks,
-                                                           int assignments, std::int32_t* counts,
-                                                           std::int32_t* offsets, std::int32_t* active,
-                                                           std::int32_t* active_count, bool route_lists) {
+                                                           int assignments, RouteLists lists) {
     __shared__ std::int32_t scan_scratch[kWarps];
     const int e = threadIdx.x;
     int total = 0;
@@ -175,14 +206,13 @@ __global__ void __launch_bounds__(256) permute_scan_kernel(std::int32_t* __restr
         total += v;
     }
     const int offset = block_exclusive_scan_256(total, scan_scratch);
-    write_route_lists(e, total, offset, assignments, assignments / kTop, counts, offsets, active, active_count,
-                      route_lists, scan_scratch);
+    write_route_lists(e, total, offset, assignments, assignments / kTop, lists, scan_scratch);
 }
 
 __global__ void __launch_bounds__(256) permute_scatter_kernel(
     const std::int32_t* __restrict__ ids, int assignments, const std::int32_t* __restrict__ chunk_hist,
     const std::int32_t* __restrict__ offsets, std::int32_t* order, std::int32_t* position,
-    std::int32_t* row_token) {
+    std::int32_t* row_token, const std::int32_t* __restrict__ pp_off, std::int32_t* pp_of_flat) {
     __shared__ std::int32_t base[kWarps][kExperts];
     __shared__ std::int32_t running[kWarps][kExperts];
     const int warp = threadIdx.x >> 5;
@@ -196,11 +226,14 @@ __global__ void __launch_bounds__(256) permute_scatter_kernel(
         }
     }
     __syncwarp();
-    warp_scatter(ids, begin, end, base[warp], running[warp], order, position, row_token);
+    warp_scatter(ids, begin, end, base[warp], running[warp], order, position, row_token, offsets, pp_off, pp_of_flat);
     if (row_token != nullptr) {
         const int rows = assignments / kTop;
         const int t = blockIdx.x * blockDim.x + threadIdx.x;
-        if (t < rows) row_token[assignments + t] = t;
+        if (t < rows) {
+            row_token[assignments + t] = t;
+            if (pp_of_flat != nullptr) pp_of_flat[assignments + t] = pp_off[kExperts] + t;
+        }
     }
 }
 
@@ -208,18 +241,28 @@ __global__ void __launch_bounds__(256) permute_scatter_kernel(
 
 cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignments,
                            std::int32_t* order, std::int32_t* position, std::int32_t* counts,
-                           std::int32_t* offsets, bool route_lists, int first_expert,
-                           int local_experts, cudaStream_t stream) {
-    (void)first_expert;
-    (void)local_experts;
+                           std::int32_t* offsets, bool route_lists, int pad_align, int tile_rows,
+                           cudaStream_t stream) {
     if (plan == nullptr || ids == nullptr || counts == nullptr || offsets == nullptr || assignments <= 0 ||
         assignments > plan->max_rows * kTop) {
         return cudaErrorInvalidValue;
     }
+    RouteLists lists {};
+    lists.counts = counts;
+    lists.offsets = offsets;
+    lists.active = plan->active;
+    lists.active_count = plan->active_count;
+    lists.enabled = route_lists;
+    lists.pad_align = pad_align > 0 ? pad_align : 1;
+    lists.tile_rows = tile_rows > 0 ? tile_rows : 1;
+    const bool padded = route_lists && pad_align > 0;
+    lists.pp_off = padded ? plan->pp_off : nullptr;
+    lists.tile_prefix = padded ? plan->tile_prefix : nullptr;
     std::int32_t* row_token = route_lists ? plan->row_token : nullptr;
+    std::int32_t* pp_of_flat = padded ? plan->pp_of_flat : nullptr;
     if (assignments <= kWarps * 1024) {
-        permute_small_kernel<<<1, 256, 0, stream>>>(ids, assignments, order, position, counts, offsets, row_token,
-                                                    plan->active, plan->active_count, route_lists, plan->status);
+        permute_small_kernel<<<1, 256, 0, stream>>>(ids, assignments, order, position, lists, row_token, pp_of_flat,
+                                                    plan->status);
         plan->last_launches += 1;
         return cudaGetLastError();
     }
@@ -227,10 +270,9 @@ cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignm
     if (chunks > plan->chunks) return cudaErrorInvalidValue;
     const int blocks = (chunks + kWarps - 1) / kWarps;
     permute_hist_kernel<<<blocks, 256, 0, stream>>>(ids, assignments, plan->chunk_hist, plan->status);
-    permute_scan_kernel<<<1, 256, 0, stream>>>(plan->chunk_hist, chunks, assignments, counts, offsets, plan->active,
-                                               plan->active_count, route_lists);
+    permute_scan_kernel<<<1, 256, 0, stream>>>(plan->chunk_hist, chunks, assignments, lists);
     permute_scatter_kernel<<<blocks, 256, 0, stream>>>(ids, assignments, plan->chunk_hist, offsets, order, position,
-                                                       row_token);
+                                                       row_token, lists.pp_off, pp_of_flat);
     plan->last_launches += 3;
     return cudaGetLastError();
 }

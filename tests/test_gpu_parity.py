@@ -263,14 +263,19 @@ def _oracle_forward(orc, pkg, host, x_bits, **kw):
                            pkg.HIDDEN, pkg.INTERMEDIATE, **kw)
 
 
+PATHS = [pytest.param(1, id="stream"), pytest.param(2, id="tcgen05")]
+
+
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("rows", [1, 2, 4, 5, 17])
-def test_moe_forward_against_cpu_oracle(cuda, pkg, orc, layer0, layer0_host, rows):
+def test_moe_forward_against_cpu_oracle(cuda, pkg, orc, layer0, layer0_host, rows, path):
     torch = cuda
     from p92moe_b200 import synth
 
     x = synth.make_activations(42, rows, rows)
     out = torch.full_like(x, float("nan"))
     plan = pkg.MoePlan(max_rows=max(rows, 4))
+    plan.set_path(path)
     block = pkg.MoeBlock(layer0.bank, layer0.router_weight, layer0.bias, plan)
     block.run_moe_rows(x, out, rows)
     torch.cuda.synchronize()
@@ -293,16 +298,17 @@ def test_moe_forward_against_cpu_oracle(cuda, pkg, orc, layer0, layer0_host, row
         got = orc.bf16_to_f32(u16(out))
         rel, max_abs = _rel(got, orc.bf16_to_f32(want))
         assert rel <= REL_L2 and max_abs <= MAX_ABS, (rel, max_abs)
-        # per-assignment down rows too (position space -> flat order)
-        mixed = orc.bf16_to_f32(u16(views["mixed"]))[: rows * 8][o_pos]
+        # per-assignment down rows too, in (row, slot) order
+        mixed = orc.bf16_to_f32(u16(views["mixed"]))[: rows * 8]
         rel, max_abs = _rel(mixed, orc.bf16_to_f32(extra["mixed"]))
         assert rel <= REL_L2 and max_abs <= MAX_ABS, (rel, max_abs)
     assert plan.last_launches > 0
     plan.close()
 
 
-@pytest.mark.parametrize("rows", [1, 4, 33])
-def test_moe_forward_against_reference_kernels(cuda, pkg, orc, layer0, rows):
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("rows", [1, 4, 33, 70, 200])
+def test_moe_forward_against_reference_kernels(cuda, pkg, orc, layer0, rows, path):
     torch = cuda
     if not orc.have_ref():
         pytest.skip("oracle/_ref was not built")
@@ -311,6 +317,7 @@ def test_moe_forward_against_reference_kernels(cuda, pkg, orc, layer0, rows):
     x = synth.make_activations(43, rows, rows)
     out = torch.empty_like(x)
     plan = pkg.MoePlan(max_rows=rows)
+    plan.set_path(path)
     pkg.MoeBlock(layer0.bank, layer0.router_weight, layer0.bias, plan).run_moe_rows(x, out, rows)
     raw = layer0.raw
     ref_out = torch.empty_like(x)
@@ -331,13 +338,15 @@ def test_moe_forward_against_reference_kernels(cuda, pkg, orc, layer0, rows):
     plan.close()
 
 
-def test_repeated_rows_equal_single_row_bitwise_and_run_is_deterministic(cuda, pkg, orc, layer0):
+@pytest.mark.parametrize("path", PATHS)
+def test_repeated_rows_equal_single_row_bitwise_and_run_is_deterministic(cuda, pkg, orc, layer0, path):
     """tests/moe_forward_test.cpp:280-285 (M=4 verifier output equals M=1 per row) and :356-358."""
     torch = cuda
     from p92moe_b200 import synth
 
     x1 = synth.make_activations(44, 0, 1)
     plan = pkg.MoePlan(max_rows=4)
+    plan.set_path(path)
     block = pkg.MoeBlock(layer0.bank, layer0.router_weight, layer0.bias, plan)
     # the reference's M=4 fixture repeats the M=1 ids; its logits order differs between M=1 and M>1,
     # so the comparison is made on the routed+shared output for identical routing
@@ -422,4 +431,35 @@ def test_forward_rejects_bad_arguments(cuda, pkg, layer0):
     assert err.value.code == 1
     with pytest.raises(pkg.P92Error):
         block.run_moe_rows(x, x.clone(), 0)
+    plan.close()
+
+
+@pytest.mark.parametrize("rows", [3, 64, 129, 1000, 4096])
+def test_tensor_core_path_equals_streaming_path(cuda, pkg, layer0, rows):
+    """The two kernel families implement one arithmetic contract: ids identical, outputs within the
+    block tolerance of each other at every size, including multi-tile experts and skewed routing."""
+    torch = cuda
+    from p92moe_b200 import synth
+
+    x = synth.make_activations(47, rows, rows)
+    bias = layer0.bias.clone()
+    if rows == 1000:
+        bias[5] += 10.0            # every token routes to expert 5: an expert with 1000 rows (8 token tiles)
+    plan = pkg.MoePlan(max_rows=rows)
+    block = pkg.MoeBlock(layer0.bank, layer0.router_weight, bias, plan)
+    outs = []
+    for path in (1, 2):
+        plan.set_path(path)
+        out = torch.full_like(x, float("nan"))
+        block.run_moe_rows(x, out, rows)
+        torch.cuda.synchronize()
+        v = plan.views(rows)
+        assert int(v["status"][0]) == 0
+        outs.append((out, v["expert_ids"].clone()))
+    assert torch.equal(outs[0][1], outs[1][1])
+    a = outs[0][0].float().cpu().numpy()
+    b = outs[1][0].float().cpu().numpy()
+    assert np.isfinite(b).all()
+    rel, max_abs = _rel(b, a)
+    assert rel <= REL_L2 and max_abs <= MAX_ABS, (rel, max_abs)
     plan.close()
