@@ -106,6 +106,35 @@ int p92b_add_inplace(uint16_t* destination, const uint16_t* source, int elements
 int p92b_moe_permute(p92b_plan* plan, const int32_t* expert_ids, int assignments, int32_t* order,
                      int32_t* position, int32_t* counts, int32_t* offsets, void* stream);
 
+/* Same permutation for callers that cannot allocate device memory.  No counterpart in the
+ * reference: this entry point exists only in this library.
+ *
+ * p92b_moe_permute borrows its scratch from a plan, and a plan is a cudaMalloc.  Some hosts of
+ * this code have no allocator to offer: an engine that hands its whole device-memory budget to
+ * its own arena at start-up (the reference sizes its resident banks to the card and allocates
+ * nothing afterwards), a plug-in loaded into a process whose policy forbids further CUDA
+ * allocations, or a serving loop that must never meet the device-wide synchronisation an
+ * allocation or a free can imply.  For them the scratch (per-chunk histograms and one status
+ * word, P92B_STATIC_PERMUTE_SCRATCH_BYTES in all) is a fixed array inside the library image:
+ * every GPU that loads the library holds it until the process exits.
+ *
+ * Limits and rules:
+ *   - assignments <= P92B_STATIC_PERMUTE_MAX_ASSIGNMENTS (8192 rows x 8); larger requests are
+ *     rejected with cudaErrorInvalidValue and a message on stderr, nothing is launched;
+ *   - the call performs no cudaMalloc / cudaFree and uses no allocating library routine;
+ *   - the first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress with that device current) and remembers it; make that first call
+ *     before starting any stream capture on that device;
+ *   - all calls on a device share the one array, which still holds the previous call's contents:
+ *     the entry point clears the status word itself and overwrites every histogram it reads, but
+ *     two calls whose kernels overlap on the GPU (different streams) race and must be serialised
+ *     by the caller;
+ *   - outputs as p92b_moe_permute: order/position may be NULL, counts[256], offsets[257]. */
+#define P92B_STATIC_PERMUTE_MAX_ASSIGNMENTS 65536
+#define P92B_STATIC_PERMUTE_SCRATCH_BYTES (P92B_STATIC_PERMUTE_MAX_ASSIGNMENTS / 256 * 256 * 4 + 256)
+int p92b_moe_permute_static(const int32_t* expert_ids, int assignments, int32_t* order, int32_t* position,
+                            int32_t* counts, int32_t* offsets, void* stream);
+
 /* ---- expert bank --------------------------------------------------------- */
 
 /* Replaces the expert-table build of Model::Impl::bind_weights (src/model.cpp:772-805)

@@ -74,6 +74,7 @@ SIGNATURES = {
     "p92b_expert_combine_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "p92b_add_inplace": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_moe_permute": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "p92b_moe_permute_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "p92b_bank_create": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(ExpertProjection), c_int, c_int, c_int, c_int, c_void_p]),
     "p92b_bank_destroy": (None, [c_void_p]),
     "p92b_bank_bytes": (c_size_t, [c_void_p]),
@@ -198,6 +199,20 @@ def expert_combine_rows(expert_rows, route_weights, output, batch_rows: int, exp
 
 def add_inplace(destination, source, elements: int) -> None:
     _check(load_library().p92b_add_inplace(_ptr(destination), _ptr(source), elements, _stream()), "add_inplace")
+
+
+STATIC_PERMUTE_MAX_ASSIGNMENTS = 65536
+
+
+def moe_permute_static(expert_ids, order, position, counts, offsets) -> None:
+    """Permutation without a plan, for hosts that cannot allocate device memory (engines whose arena
+    already owns the whole card, processes that forbid further CUDA allocations, loops that must not
+    hit an allocation's device-wide synchronisation).  Scratch is a fixed array inside the library,
+    shared by all calls on a device: at most 65536 assignments, calls must not overlap on the GPU,
+    and the first call on a device (which looks up the array's address) belongs before any stream
+    capture."""
+    _check(load_library().p92b_moe_permute_static(_ptr(expert_ids), expert_ids.numel(), _ptr(order), _ptr(position),
+                                                  _ptr(counts), _ptr(offsets), _stream()), "moe_permute_static")
 
 
 class ExpertBank:

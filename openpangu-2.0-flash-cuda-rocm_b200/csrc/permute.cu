@@ -12,6 +12,8 @@
 // lower lanes, and chunk bases come from an exclusive scan over (expert, chunk).
 #include "p92b_common.cuh"
 
+#include <cstdio>
+
 namespace p92b {
 namespace {
 
@@ -278,3 +280,93 @@ cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignm
 }
 
 }  // namespace p92b
+
+// ---------------------------------------------------------------------------
+// Allocation-free permutation (p92b_moe_permute_static).
+//
+// For callers that cannot give the library a plan because they cannot allocate:
+// the engine has already committed all device memory to its own arena, the host
+// process forbids further CUDA allocations, or the call sits in a loop that must
+// not run into the device-wide synchronisation cudaMalloc / cudaFree may cause.
+// The scratch of the multi-block permutation lives in this file-scope device
+// array instead.  Every GPU that loads the library carries its copy of the array
+// (P92B_STATIC_PERMUTE_SCRATCH_BYTES) until the process exits.
+//
+// In host code the array's name is only a stand-in for the symbol, not a device
+// address, so the address is fetched once per device with cudaGetSymbolAddress
+// (that device current) and handed to the kernels as an ordinary pointer.
+// Layout: [chunks][256] int32 chunk histograms, then the status word.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kStaticMaxAssignments = P92B_STATIC_PERMUTE_MAX_ASSIGNMENTS;
+constexpr int kStaticChunks = kStaticMaxAssignments / p92b::kChunk;
+constexpr int kStaticWords = kStaticChunks * p92b::kExperts + 64;
+static_assert(kStaticWords * 4 == P92B_STATIC_PERMUTE_SCRATCH_BYTES, "header and array disagree");
+constexpr int kStaticMaxDevices = 64;
+
+static __device__ __align__(256) std::int32_t g_static_permute_scratch[kStaticWords];
+
+std::int32_t* g_static_scratch_address[kStaticMaxDevices] = {};
+
+// Device address of the array on the current device; looked up on first use.
+cudaError_t static_scratch(std::int32_t** out) {
+    int device = 0;
+    cudaError_t st = cudaGetDevice(&device);
+    if (st != cudaSuccess) return st;
+    if (device < 0 || device >= kStaticMaxDevices) return cudaErrorNotSupported;
+    if (g_static_scratch_address[device] == nullptr) {
+        void* address = nullptr;
+        st = cudaGetSymbolAddress(&address, g_static_permute_scratch);
+        if (st != cudaSuccess) return st;
+        g_static_scratch_address[device] = static_cast<std::int32_t*>(address);
+    }
+    *out = g_static_scratch_address[device];
+    return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int p92b_moe_permute_static(const int32_t* expert_ids, int assignments, int32_t* order,
+                                       int32_t* position, int32_t* counts, int32_t* offsets, void* stream_) {
+    using namespace p92b;
+    if (expert_ids == nullptr || counts == nullptr || offsets == nullptr || assignments <= 0) {
+        return cudaErrorInvalidValue;
+    }
+    if (assignments > kStaticMaxAssignments) {
+        std::fprintf(stderr,
+                     "p92b_moe_permute_static: %d assignments exceed the built-in scratch (limit %d = %d rows x 8); "
+                     "use p92b_moe_permute with a plan\n",
+                     assignments, kStaticMaxAssignments, kStaticMaxAssignments / kTop);
+        return cudaErrorInvalidValue;
+    }
+    std::int32_t* scratch = nullptr;
+    cudaError_t st = static_scratch(&scratch);
+    if (st != cudaSuccess) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    std::int32_t* chunk_hist = scratch;
+    std::int32_t* status = scratch + kStaticChunks * kExperts;
+    // the array still holds the previous call's words: the status word must start at zero,
+    // the histograms are fully rewritten by permute_hist_kernel before anything reads them
+    st = cudaMemsetAsync(status, 0, sizeof(std::int32_t), stream);
+    if (st != cudaSuccess) return st;
+    RouteLists lists {};
+    lists.counts = counts;
+    lists.offsets = offsets;
+    lists.enabled = false;
+    lists.pad_align = 1;
+    lists.tile_rows = 1;
+    if (assignments <= kWarps * 1024) {
+        permute_small_kernel<<<1, 256, 0, stream>>>(expert_ids, assignments, order, position, lists, nullptr, nullptr,
+                                                    status);
+        return cudaGetLastError();
+    }
+    const int chunks = (assignments + kChunk - 1) / kChunk;
+    const int blocks = (chunks + kWarps - 1) / kWarps;
+    permute_hist_kernel<<<blocks, 256, 0, stream>>>(expert_ids, assignments, chunk_hist, status);
+    permute_scan_kernel<<<1, 256, 0, stream>>>(chunk_hist, chunks, assignments, lists);
+    permute_scatter_kernel<<<blocks, 256, 0, stream>>>(expert_ids, assignments, chunk_hist, offsets, order, position,
+                                                       nullptr, nullptr, nullptr);
+    return cudaGetLastError();
+}
+
