@@ -3,6 +3,7 @@
 // Each kernel keeps the reference's rounding points; citations are on the kernels.
 // All of these are HBM-bound byte work: 16-byte accesses, one pass.
 #include "p92b_common.cuh"
+#include "tc_ptx.cuh"
 
 #include <algorithm>
 
@@ -140,6 +141,8 @@ __global__ void __launch_bounds__(256) combine_shared_kernel(const std::uint16_t
                                                              const float* __restrict__ route_weights,
                                                              std::uint16_t* __restrict__ output, int rows,
                                                              int hidden) {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
     const int row = blockIdx.y;
     const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
     if (c8 * 8 >= hidden) return;
@@ -191,10 +194,10 @@ cudaError_t launch_quantize(const std::uint16_t* input, std::uint8_t* output, st
 
 cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* mixed_index,
                                   const float* route_weights, std::uint16_t* output, int rows,
-                                  int hidden, cudaStream_t stream) {
+                                  int hidden, cudaStream_t stream, bool pdl) {
     dim3 grid(blocks_for(hidden / 8, 256), rows);
-    combine_shared_kernel<<<grid, 256, 0, stream>>>(mixed, mixed_index, route_weights, output, rows, hidden);
-    return cudaGetLastError();
+    return launch_kernel(combine_shared_kernel, grid, dim3(256), 0, stream, pdl, mixed, mixed_index, route_weights,
+                         output, rows, hidden);
 }
 
 cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,

@@ -47,16 +47,20 @@ struct Tc {
     static constexpr int kA = MODE == 0 ? 2 : 1;
     static constexpr int kABytes = kTileM * kBlockKBytes;
     static constexpr int kBBytes = N * kBlockKBytes;
-    static constexpr int kStageBytes = kA * (kABytes + kSfSlab) + kBBytes + kSfSlab;
+    static constexpr int kWeightBytes = kA * (kABytes + kSfSlab);          // per stage, independent of the tokens
+    static constexpr int kTokenBytes = kBBytes + kSfSlab;
+    static constexpr int kStageBytes = kWeightBytes + kTokenBytes;
     static constexpr int kStagesRaw = (196 * 1024) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kAccumStride = N < 32 ? 32 : N;          // each accumulator starts on a multiple of 32 columns
     static constexpr int kAccumCols = kA * kAccumStride;
     static constexpr int kSfCols = (kA + 1) * 16;                 // per buffer: 4 columns per K=64 step
-    static constexpr int kNeedCols = kAccumCols + 2 * kSfCols;
+    static constexpr int kAccumBuffers = 2 * kAccumCols + 2 * kSfCols <= 512 ? 2 : 1;
+    static constexpr int kNeedCols = kAccumBuffers * kAccumCols + 2 * kSfCols;
     static constexpr int kTmemCols = kNeedCols <= 32 ? 32 : kNeedCols <= 64 ? 64 : kNeedCols <= 128 ? 128
                                      : kNeedCols <= 256 ? 256 : 512;
-    static constexpr int kBarrierBytes = (2 * kStages + 2) * 8 + 16;
+    static constexpr int kBarriers = 3 * kStages + 2 * kAccumBuffers;
+    static constexpr int kBarrierBytes = kBarriers * 8 + 16;
     static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;   // + alignment slack
     static_assert(kNeedCols <= 512, "accumulators and scale factors must fit TMEM");
 };
@@ -75,7 +79,7 @@ struct TcParams {
     int k_bytes;                       // K/2: bytes per operand row
     int m_total;                       // output rows per expert matrix
     int m_tiles;
-    int debug_level;                   // 0 full kernel; 1..4 stop after set-up / TMA / scale copies / MMA (bring-up aid)
+    int routing_is_upstream;           // 1: the routing lists are written by the kernel just before this one in the stream
 };
 
 struct Item {
@@ -114,11 +118,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
     extern __shared__ std::uint8_t smem_raw[];
     const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     const std::uint32_t bars = base + C::kStages * C::kStageBytes;
-    auto full_bar = [&](int s) { return bars + 8U * s; };
-    auto empty_bar = [&](int s) { return bars + 8U * (C::kStages + s); };
-    const std::uint32_t accum_full = bars + 8U * (2 * C::kStages);
-    const std::uint32_t accum_empty = accum_full + 8U;
-    const std::uint32_t tmem_slot = accum_empty + 8U;
+    // per stage: weights landed, tokens landed, stage free; per accumulator buffer: full, empty
+    auto weight_bar = [&](int s) { return bars + 8U * s; };
+    auto token_bar = [&](int s) { return bars + 8U * (C::kStages + s); };
+    auto empty_bar = [&](int s) { return bars + 8U * (2 * C::kStages + s); };
+    auto accum_full = [&](int b) { return bars + 8U * (3 * C::kStages + b); };
+    auto accum_empty = [&](int b) { return bars + 8U * (3 * C::kStages + C::kAccumBuffers + b); };
+    const std::uint32_t tmem_slot = bars + 8U * C::kBarriers;
     volatile std::uint32_t* tmem_slot_ptr =
         reinterpret_cast<volatile std::uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
     volatile std::uint32_t* abort_ptr = tmem_slot_ptr + 1;
@@ -126,15 +132,17 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int k_blocks = p.k_bytes / kBlockKBytes;
-    const int total_items = p.tile_prefix[*p.route.active_count] * p.m_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
-            mbar_init(full_bar(s), 1);
+            mbar_init(weight_bar(s), 1);
+            mbar_init(token_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(accum_full, 1);
-        mbar_init(accum_empty, 4);
+        for (int b = 0; b < C::kAccumBuffers; ++b) {
+            mbar_init(accum_full(b), 1);
+            mbar_init(accum_empty(b), 4);
+        }
         *abort_ptr = 0;
         fence_mbar_init();
         prefetch_tensormap(&map_a);
@@ -144,16 +152,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         tmem_alloc(tmem_slot, C::kTmemCols);
         tmem_relinquish();
     }
+    // the routing lists come from the kernel just upstream (gate/up) or from one further up (down):
+    // only the former has to wait for its predecessor before it can look at its work list
+    if (p.routing_is_upstream) pdl_wait();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_launch_dependents();
     const std::uint32_t tmem_base = *tmem_slot_ptr;
-    const int level = p.debug_level;
-    if (threadIdx.x == 0 && ((bars & 7U) != 0U || (base & 1023U) != 0U)) {
-        atomicCAS(p.status, kStatusOk, 100);
-        *abort_ptr = 1;
-    }
-    __syncthreads();
+    const int total_items = p.tile_prefix[*p.route.active_count] * p.m_tiles;
     auto give_up = [&]() {
         *abort_ptr = 1;
         atomicCAS(p.status, kStatusOk, kStatusWaitExpired);
@@ -164,62 +171,90 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         if (elect_one()) {
             int stage = 0;
             std::uint32_t phase = 0;
+            bool upstream_done = p.routing_is_upstream != 0;
             const std::size_t a_sf_matrix = static_cast<std::size_t>(p.m_total / 128) * (p.k_bytes / 32) * 512;
             const std::uint8_t* a_sf_base = MODE == 0 ? p.bank.sfs13 : p.bank.sfs2;
-            for (int item = blockIdx.x; item < total_items && !*abort_ptr && level != 1; item += gridDim.x) {
+            for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
                 Item it;
                 if (!decode_item<N>(p, item, &it)) continue;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(); break; }
                     const std::uint32_t st = base + stage * C::kStageBytes;
-                    mbar_arrive_expect_tx(full_bar(stage), C::kStageBytes);
+                    // weights never depend on the upstream kernel: they start streaming at once
+                    mbar_arrive_expect_tx(weight_bar(stage), C::kWeightBytes);
 #pragma unroll
                     for (int a = 0; a < C::kA; ++a) {
                         const int matrix = it.entry * C::kA + a;
-                        tma_load_2d(st + a * C::kABytes, &map_a, full_bar(stage), kb * kBlockKBytes,
+                        tma_load_2d(st + a * C::kABytes, &map_a, weight_bar(stage), kb * kBlockKBytes,
                                     matrix * p.m_total + it.m_tile * kTileM);
                         const std::uint8_t* sf = a_sf_base + static_cast<std::size_t>(matrix) * a_sf_matrix +
                                                  (static_cast<std::size_t>(it.m_tile) * (p.k_bytes / 32) + kb * 4) * 512;
-                        if ((reinterpret_cast<std::uintptr_t>(sf) & 15U) != 0U) { atomicCAS(p.status, kStatusOk, 101); *abort_ptr = 1; }
-                        bulk_load(st + C::kA * C::kABytes + C::kBBytes + a * kSfSlab, sf, kSfSlab, full_bar(stage));
+                        bulk_load(st + C::kA * C::kABytes + C::kBBytes + a * kSfSlab, sf, kSfSlab, weight_bar(stage));
                     }
-                    tma_load_2d(st + C::kA * C::kABytes, &map_b, full_bar(stage), kb * kBlockKBytes, it.pp0);
-                    const std::uint8_t* bsf = p.b_sf +
-                        (static_cast<std::size_t>(it.pp0 >> 7) * (p.k_bytes / 32) + kb * 4) * 512;
-                    if ((reinterpret_cast<std::uintptr_t>(bsf) & 15U) != 0U) { atomicCAS(p.status, kStatusOk, 102); *abort_ptr = 1; }
-                    bulk_load(st + C::kA * C::kABytes + C::kBBytes + C::kA * kSfSlab, bsf, kSfSlab, full_bar(stage));
+                    if (upstream_done) {
+                        mbar_arrive_expect_tx(token_bar(stage), C::kTokenBytes);
+                        tma_load_2d(st + C::kA * C::kABytes, &map_b, token_bar(stage), kb * kBlockKBytes, it.pp0);
+                        const std::uint8_t* bsf = p.b_sf +
+                            (static_cast<std::size_t>(it.pp0 >> 7) * (p.k_bytes / 32) + kb * 4) * 512;
+                        bulk_load(st + C::kA * C::kABytes + C::kBBytes + C::kA * kSfSlab, bsf, kSfSlab, token_bar(stage));
+                    }
+                    const bool ring_full = stage == C::kStages - 1;
+                    const bool last_load = kb == k_blocks - 1 && item + static_cast<int>(gridDim.x) >= total_items;
+                    if (!upstream_done && (ring_full || last_load)) {
+                        // every stage now has its weights in flight; the token rows are written by the
+                        // upstream kernel, so wait for it, then issue the token loads that were held back
+                        pdl_wait();
+                        upstream_done = true;
+                        int it_item = blockIdx.x, it_kb = 0;
+                        for (int s = 0; s <= stage; ++s) {
+                            Item held;
+                            while (!decode_item<N>(p, it_item, &held)) it_item += gridDim.x;
+                            const std::uint32_t hst = base + s * C::kStageBytes;
+                            mbar_arrive_expect_tx(token_bar(s), C::kTokenBytes);
+                            tma_load_2d(hst + C::kA * C::kABytes, &map_b, token_bar(s), it_kb * kBlockKBytes, held.pp0);
+                            const std::uint8_t* hsf = p.b_sf +
+                                (static_cast<std::size_t>(held.pp0 >> 7) * (p.k_bytes / 32) + it_kb * 4) * 512;
+                            bulk_load(hst + C::kA * C::kABytes + C::kBBytes + C::kA * kSfSlab, hsf, kSfSlab, token_bar(s));
+                            if (++it_kb == k_blocks) { it_kb = 0; it_item += gridDim.x; }
+                        }
+                    }
                     if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
                 }
             }
+            if (!upstream_done) pdl_wait();      // no work at all: still order this grid after its predecessor
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer
         if (elect_one()) {
             int stage = 0;
             std::uint32_t phase = 0;
-            std::uint32_t accum_phase = 0;
+            int buffer = 0;
+            std::uint32_t accum_phase[2] = {0U, 0U};
             constexpr std::uint32_t idesc = idesc_nvf4(kTileM, N);
-            const std::uint32_t sf_tmem = tmem_base + C::kAccumCols;
+            const std::uint32_t sf_tmem = tmem_base + C::kAccumBuffers * C::kAccumCols;
             int sf_buffer = 0;
-            for (int item = blockIdx.x; item < total_items && !*abort_ptr && level != 1; item += gridDim.x) {
+            for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
                 Item it;
                 if (!decode_item<N>(p, item, &it)) continue;
-                if (!mbar_wait(accum_empty, accum_phase ^ 1U)) { give_up(); break; }
+                if (!mbar_wait(accum_empty(buffer), accum_phase[buffer] ^ 1U)) { give_up(); break; }
                 tc_fence_after();
+                const std::uint32_t accum = tmem_base + buffer * C::kAccumCols;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase)) { give_up(); ok = false; break; }
+                    if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) {
+                        give_up();
+                        ok = false;
+                        break;
+                    }
                     tc_fence_after();
                     const std::uint32_t st = base + stage * C::kStageBytes;
                     const std::uint32_t sf_smem = st + C::kA * C::kABytes + C::kBBytes;
                     const std::uint32_t sfc = sf_tmem + sf_buffer * C::kSfCols;
-                    if (level == 0 || level >= 3) {
 #pragma unroll
-                        for (int o = 0; o < C::kA + 1; ++o) {
+                    for (int o = 0; o < C::kA + 1; ++o) {
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                tc_copy_sf(sfc + o * 16 + k * 4, desc_scale_atom(sf_smem + o * kSfSlab + k * 512));
-                            }
+                        for (int k = 0; k < 4; ++k) {
+                            tc_copy_sf(sfc + o * 16 + k * 4, desc_scale_atom(sf_smem + o * kSfSlab + k * 512));
                         }
                     }
                     const std::uint64_t b_desc = desc_k_major_sw128(st + C::kA * C::kABytes);
@@ -228,10 +263,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
 #pragma unroll
                         for (int a = 0; a < C::kA; ++a) {
                             const std::uint64_t a_desc = desc_k_major_sw128(st + a * C::kABytes);
-                            if (level == 0 || level >= 4) {
-                                mma_nvf4(tmem_base + a * C::kAccumStride, a_desc + 2 * k, b_desc + 2 * k, idesc, sfc + a * 16 + k * 4,
-                                         sfc + C::kA * 16 + k * 4, kb > 0 || k > 0);
-                            }
+                            mma_nvf4(accum + a * C::kAccumStride, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                     sfc + a * 16 + k * 4, sfc + C::kA * 16 + k * 4, kb > 0 || k > 0);
                         }
                     }
                     tc_commit(empty_bar(stage));
@@ -239,22 +272,24 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                     if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
                 }
                 if (!ok) break;
-                tc_commit(accum_full);
-                accum_phase ^= 1U;
+                tc_commit(accum_full(buffer));
+                accum_phase[buffer] ^= 1U;
+                if (C::kAccumBuffers == 2) buffer ^= 1;
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31
-        std::uint32_t accum_phase = 0;
-        for (int item = blockIdx.x; item < total_items && !*abort_ptr && level != 1; item += gridDim.x) {
+        int buffer = 0;
+        std::uint32_t accum_phase[2] = {0U, 0U};
+        for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
             Item it;
             if (!decode_item<N>(p, item, &it)) continue;
-            if (!mbar_wait(accum_full, accum_phase)) { give_up(); break; }
-            accum_phase ^= 1U;
+            if (!mbar_wait(accum_full(buffer), accum_phase[buffer])) { give_up(); break; }
+            accum_phase[buffer] ^= 1U;
             tc_fence_after();
-            if (level != 0) it.valid = 0;
-            const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16);
+            const std::uint32_t lane_base =
+                tmem_base + buffer * C::kAccumCols + (static_cast<std::uint32_t>(quarter * 32) << 16);
             const int row = it.m_tile * kTileM + quarter * 32 + lane;          // output row of this lane
             if constexpr (MODE == 0) {
                 const float alpha_g = p.bank.alpha[it.entry * 3 + 0];
@@ -317,7 +352,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(accum_empty);
+            if (lane == 0) mbar_arrive(accum_empty(buffer));
+            if (C::kAccumBuffers == 2) buffer ^= 1;
         }
     }
     tc_fence_before();
@@ -337,6 +373,8 @@ __global__ void __launch_bounds__(256) quantize_padded_kernel(const std::uint16_
                                                               std::uint8_t* __restrict__ xq,
                                                               std::uint8_t* __restrict__ xs, int rows, int hidden,
                                                               float global_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int index = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // 0 .. 9*rows
     if (index >= rows * (kTop + 1)) return;
@@ -382,13 +420,16 @@ EncodeTiled encode_tiled() {
 
 template <int MODE, int N>
 cudaError_t launch_tc(const p92b_plan* plan, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, bool pdl) {
     using C = Tc<MODE, N>;
     auto kernel = expert_tc_kernel<MODE, N>;
-    cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (st != cudaSuccess) return st;
-    kernel<<<plan->sm_count, kThreadsTc, C::kSmemBytes, stream>>>(map_a, map_b, p);
-    return cudaGetLastError();
+    static bool configured = false;          // once per process: not a stream operation
+    if (!configured) {
+        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (st != cudaSuccess) return st;
+        configured = true;
+    }
+    return launch_kernel(kernel, dim3(plan->sm_count), dim3(kThreadsTc), C::kSmemBytes, stream, pdl, map_a, map_b, p);
 }
 
 }  // namespace
@@ -414,15 +455,16 @@ int tc_tile_rows(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 
 // row 0 of a 128-row scale-factor tile (TMEM lane 0, first scale column).
 int tc_pad_align(int rows) { (void)rows; return 128; }
 
-cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x, int rows, cudaStream_t stream) {
+cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x, int rows, cudaStream_t stream,
+                                   bool pdl) {
     const int warps = rows * (kTop + 1);
-    quantize_padded_kernel<<<(warps + 7) / 8, 256, 0, stream>>>(x, plan->pp_of_flat, plan->xq_pp, plan->xs_sw, rows,
-                                                                plan->hidden, 1.0F);
-    return cudaGetLastError();
+    return launch_kernel(quantize_padded_kernel, dim3((warps + 7) / 8), dim3(256), 0, stream, pdl, x,
+                         static_cast<const std::int32_t*>(plan->pp_of_flat), plan->xq_pp, plan->xs_sw, rows,
+                         plan->hidden, 1.0F);
 }
 
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, bool pdl) {
     if (!bank->tc_ready || !plan->tc_ready) return cudaErrorNotSupported;
     TcParams p {};
     p.bank = bank->view;
@@ -435,9 +477,9 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
     p.tile_prefix = plan->tile_prefix;
     p.status = plan->status;
     p.quant_scale = 1.0F;
-    if (const char* env = std::getenv("P92B_TC_DEBUG")) p.debug_level = std::atoi(env);
     const int n = tc_tile_rows(rows);
     const int which = n == 16 ? 0 : n == 32 ? 1 : n == 64 ? 2 : 3;
+    p.routing_is_upstream = down ? 0 : 1;
     if (!down) {
         p.b_sf = plan->xs_sw;
         p.hq = plan->hq_pp;
@@ -446,10 +488,10 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
         p.m_total = plan->intermediate;
         p.m_tiles = plan->intermediate / kTileM;
         switch (which) {
-            case 0: return launch_tc<0, 16>(plan, bank->map_w13, plan->map_x[0], p, stream);
-            case 1: return launch_tc<0, 32>(plan, bank->map_w13, plan->map_x[1], p, stream);
-            case 2: return launch_tc<0, 64>(plan, bank->map_w13, plan->map_x[2], p, stream);
-            default: return launch_tc<0, 128>(plan, bank->map_w13, plan->map_x[3], p, stream);
+            case 0: return launch_tc<0, 16>(plan, bank->map_w13, plan->map_x[0], p, stream, pdl);
+            case 1: return launch_tc<0, 32>(plan, bank->map_w13, plan->map_x[1], p, stream, pdl);
+            case 2: return launch_tc<0, 64>(plan, bank->map_w13, plan->map_x[2], p, stream, pdl);
+            default: return launch_tc<0, 128>(plan, bank->map_w13, plan->map_x[3], p, stream, pdl);
         }
     }
     p.b_sf = plan->hs_sw;
@@ -458,10 +500,10 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
     p.m_total = plan->hidden;
     p.m_tiles = plan->hidden / kTileM;
     switch (which) {
-        case 0: return launch_tc<1, 16>(plan, bank->map_w2, plan->map_h[0], p, stream);
-        case 1: return launch_tc<1, 32>(plan, bank->map_w2, plan->map_h[1], p, stream);
-        case 2: return launch_tc<1, 64>(plan, bank->map_w2, plan->map_h[2], p, stream);
-        default: return launch_tc<1, 128>(plan, bank->map_w2, plan->map_h[3], p, stream);
+        case 0: return launch_tc<1, 16>(plan, bank->map_w2, plan->map_h[0], p, stream, pdl);
+        case 1: return launch_tc<1, 32>(plan, bank->map_w2, plan->map_h[1], p, stream, pdl);
+        case 2: return launch_tc<1, 64>(plan, bank->map_w2, plan->map_h[2], p, stream, pdl);
+        default: return launch_tc<1, 128>(plan, bank->map_w2, plan->map_h[3], p, stream, pdl);
     }
 }
 

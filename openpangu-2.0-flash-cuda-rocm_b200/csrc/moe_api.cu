@@ -370,37 +370,56 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
         if (!plan->timing) { ++stage; return cudaSuccess; }
         return cudaEventRecord(plan->stage_events[stage++], stream);
     };
-    cudaError_t st = mark();
-    if (st != cudaSuccess) return st;
-    st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream);
-    if (st != cudaSuccess) return st;
-    if ((st = mark()) != cudaSuccess) return st;
-    st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream);
-    if (st != cudaSuccess) return st;
-    if ((st = mark()) != cudaSuccess) return st;
-    plan->last_launches += 2;
+    // programmatic dependent launch: each kernel's prologue (and, for the down kernel, its weight
+    // prefetch) overlaps the tail of the one before; P92B_NO_PDL=1 switches it off for A/B timing
+    static const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
     const bool tc = plan->path == 2 || (plan->path == 0 && plan->tc_ready && bank->tc_ready);
     if (tc && (!plan->tc_ready || !bank->tc_ready)) return cudaErrorNotSupported;
     plan->last_path = tc ? 2 : 1;
-    st = launch_permute(plan, plan->ids, rows * kTop, plan->order, plan->position, plan->counts, plan->offsets, true,
-                        tc ? tc_pad_align(rows) : 1, tc ? tc_tile_rows(rows) : (1 << 30), stream);
+    const int pad_align = tc ? tc_pad_align(rows) : 1;
+    const int tile_rows = tc ? tc_tile_rows(rows) : (1 << 30);
+    cudaError_t st = mark();
+    if (st != cudaSuccess) return st;
+    st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream, pdl);
     if (st != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
-    if (tc) {
-        st = launch_quantize_padded(plan, input, rows, stream);
+    plan->last_launches += 1;
+    if (tc && rows <= route_fused_max_rows()) {
+        // top-8, permutation and token quantisation as one block (stages 1-3 of the timing table)
+        st = launch_route_fused(plan, correction_bias, routed_scale, input, rows, pad_align, tile_rows, stream, pdl);
         if (st != cudaSuccess) return st;
         if ((st = mark()) != cudaSuccess) return st;
-        st = launch_experts_tc(plan, bank, rows, false, stream);
-        if (st != cudaSuccess) return st;
         if ((st = mark()) != cudaSuccess) return st;
-        st = launch_experts_tc(plan, bank, rows, true, stream);
-        if (st != cudaSuccess) return st;
         if ((st = mark()) != cudaSuccess) return st;
-        st = launch_combine_shared(plan->mixed_pp, plan->pp_of_flat, plan->route_weights, output, rows, hidden, stream);
     } else {
-        st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * hidden / 16, 1.0F, stream);
+        st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream,
+                                pdl);
         if (st != cudaSuccess) return st;
         if ((st = mark()) != cudaSuccess) return st;
+        plan->last_launches += 1;
+        st = launch_permute(plan, plan->ids, rows * kTop, plan->order, plan->position, plan->counts, plan->offsets, true,
+                            pad_align, tile_rows, stream, pdl);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        if (tc) {
+            st = launch_quantize_padded(plan, input, rows, stream, pdl);
+        } else {
+            st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * hidden / 16, 1.0F, stream);
+        }
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        plan->last_launches += 1;
+    }
+    if (tc) {
+        st = launch_experts_tc(plan, bank, rows, false, stream, pdl);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        st = launch_experts_tc(plan, bank, rows, true, stream, pdl);
+        if (st != cudaSuccess) return st;
+        if ((st = mark()) != cudaSuccess) return st;
+        st = launch_combine_shared(plan->mixed_pp, plan->pp_of_flat, plan->route_weights, output, rows, hidden, stream,
+                                   pdl);
+    } else {
         const RouteView route = route_view(plan);
         st = launch_gate_up(plan, bank->view, route, plan->xq, plan->xs, plan->hq, plan->hs, nullptr, nullptr,
                             plan->order, rows, stream);
@@ -411,7 +430,7 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
         if ((st = mark()) != cudaSuccess) return st;
         st = launch_combine_shared(plan->mixed, plan->pp_of_flat, plan->route_weights, output, rows, hidden, stream);
     }
-    plan->last_launches += 4;
+    plan->last_launches += 3;
     if (st != cudaSuccess) return st;
     if (debug_sync && !plan->timing && (st = mark()) != cudaSuccess) return st;
     if (plan->timing) {

@@ -6,8 +6,9 @@
 #include <cuda_fp16.h>
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
-#include <cuda_runtime_api.h>
+#include <cuda_runtime.h>
 
+#include <cfloat>
 #include <cstddef>
 #include <cstdint>
 
@@ -71,6 +72,71 @@ __device__ __forceinline__ uint2 quantize_block16(const float (&v)[16], float gl
         words[i >> 2] |= byte << ((i & 3) * 8);
     }
     return make_uint2(words[0], words[1]);
+}
+
+// Top-8 of one token by one warp: lane l holds experts l, l+32, ..., l+224 in registers.
+// Eight rounds of (local best, warp butterfly arg-max) with the reference's total order: higher
+// corrected score first, equal scores -> lower id (cuda/nvfp4_ops.cu:391-392,411-412).  Weights
+// are the uncorrected sigmoid of the winners, summed in slot order and scaled by
+// routed_scale/total (:420,425-432).  The score is written exactly as the reference writes it and
+// every file using this is compiled with --use_fast_math like the reference, so expf and the
+// divisions lower to the same hardware approximations.  lg/ids/weights point at this token's row.
+__device__ __forceinline__ void warp_top8(const float* __restrict__ lg, const float* __restrict__ bias,
+                                          std::int32_t* __restrict__ ids, float* __restrict__ weights,
+                                          float routed_scale) {
+    const int lane = threadIdx.x & 31;
+    float raw[8];
+    float corrected[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        raw[i] = 1.0F / (1.0F + expf(-lg[e]));
+        corrected[i] = raw[i] + bias[e];
+    }
+    unsigned used = 0U;
+    float chosen_weight = 0.0F;   // lane k keeps slot k's raw weight
+    int chosen_id = 0;
+#pragma unroll
+    for (int slot = 0; slot < 8; ++slot) {
+        float best = -FLT_MAX;
+        int best_id = 256 + lane;
+        float best_raw = 0.0F;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float c = (used >> i) & 1U ? -FLT_MAX : corrected[i];
+            const int e = lane + 32 * i;
+            // ascending id within the lane, so strict '>' keeps the lower id on ties
+            if (c > best || (c == best && e < best_id)) {
+                best = c;
+                best_id = e;
+                best_raw = raw[i];
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffU, best, offset);
+            const int other_id = __shfl_xor_sync(0xffffffffU, best_id, offset);
+            const float other_raw = __shfl_xor_sync(0xffffffffU, best_raw, offset);
+            if (other > best || (other == best && other_id < best_id)) {
+                best = other;
+                best_id = other_id;
+                best_raw = other_raw;
+            }
+        }
+        if ((best_id & 31) == lane) used |= 1U << (best_id >> 5);
+        if (lane == slot) {
+            chosen_weight = best_raw;
+            chosen_id = best_id;
+        }
+    }
+    float total = 0.0F;
+#pragma unroll
+    for (int slot = 0; slot < 8; ++slot) total += __shfl_sync(0xffffffffU, chosen_weight, slot);
+    const float multiplier = routed_scale / total;
+    if (lane < 8) {
+        ids[lane] = chosen_id;
+        weights[lane] = chosen_weight * multiplier;
+    }
 }
 
 // Layout of one layer's expert weights inside the library (device memory).
@@ -166,16 +232,39 @@ struct p92b_plan {
 
 namespace p92b {
 
+// Launch with or without programmatic dependent launch: with `pdl` the kernel may start while the
+// previous kernel in the stream is still draining, and must call ptx::pdl_wait() before it touches
+// anything that kernel writes.
+template <class... KArgs, class... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, std::size_t smem, cudaStream_t stream,
+                          bool pdl, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 // kernel launchers (defined across the .cu files)
 cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w, float* out,
                                  int batch_rows, int rows, int columns, bool gemv_order,
-                                 cudaStream_t stream);
+                                 cudaStream_t stream, bool pdl = false);
 cudaError_t launch_router_top8(const float* logits, const float* bias, std::int32_t* ids,
-                               float* weights, int rows, float routed_scale, cudaStream_t stream);
+                               float* weights, int rows, float routed_scale, cudaStream_t stream,
+                               bool pdl = false);
 cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignments,
                            std::int32_t* order, std::int32_t* position, std::int32_t* counts,
                            std::int32_t* offsets, bool route_lists, int pad_align, int tile_rows,
-                           cudaStream_t stream);
+                           cudaStream_t stream, bool pdl = false);
+int route_fused_max_rows();
+cudaError_t launch_route_fused(p92b_plan* plan, const float* bias, float routed_scale, const std::uint16_t* x,
+                               int rows, int pad_align, int tile_rows, cudaStream_t stream, bool pdl);
 cudaError_t launch_quantize(const std::uint16_t* input, std::uint8_t* output, std::uint8_t* scales,
                             long groups, float global_scale, cudaStream_t stream);
 cudaError_t launch_gate_up(const p92b_plan* plan, const BankView& bank, const RouteView& route,
@@ -190,14 +279,15 @@ cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear,
                              cudaStream_t stream);
 cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* mixed_index,
                                   const float* route_weights, std::uint16_t* output, int rows,
-                                  int hidden, cudaStream_t stream);
+                                  int hidden, cudaStream_t stream, bool pdl = false);
 // tensor-core path (expert_tc.cu)
 cudaError_t make_operand_map(CUtensorMap* map, const void* base, std::size_t rows, std::size_t row_bytes,
                              int box_rows);
 int tc_tile_rows(int rows);
 int tc_pad_align(int rows);
-cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x, int rows, cudaStream_t stream);
+cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x, int rows, cudaStream_t stream,
+                                   bool pdl = false);
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
-                              cudaStream_t stream);
+                              cudaStream_t stream, bool pdl = false);
 
 }  // namespace p92b

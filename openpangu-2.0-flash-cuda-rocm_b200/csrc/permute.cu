@@ -11,10 +11,15 @@
 // ranks inside a 32-wide step come from __match_any_sync + popcount of the
 // lower lanes, and chunk bases come from an exclusive scan over (expert, chunk).
 #include "p92b_common.cuh"
+#include "tc_ptx.cuh"
 
 #include <cstdio>
 
 namespace p92b {
+
+using ptx::pdl_launch_dependents;
+using ptx::pdl_wait;
+
 namespace {
 
 constexpr int kChunk = 256;          // flat indices per warp in the multi-block path
@@ -148,6 +153,8 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
     __shared__ std::int32_t hist[kWarps][kExperts];
     __shared__ std::int32_t running[kWarps][kExperts];
     __shared__ std::int32_t scan_scratch[kWarps];
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5;
     const int per_warp = ((assignments + kWarps - 1) / kWarps + 31) / 32 * 32;
     const int begin = min(assignments, warp * per_warp);
@@ -184,6 +191,8 @@ __global__ void __launch_bounds__(256) permute_hist_kernel(const std::int32_t* _
                                                            std::int32_t* __restrict__ chunk_hist,
                                                            std::int32_t* status) {
     __shared__ std::int32_t hist[kWarps][kExperts];
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int chunk = blockIdx.x * kWarps + warp;
@@ -198,6 +207,8 @@ __global__ void __launch_bounds__(256) permute_hist_kernel(const std::int32_t* _
 __global__ void __launch_bounds__(256) permute_scan_kernel(std::int32_t* __restrict__ chunk_hist, int chunks,
                                                            int assignments, RouteLists lists) {
     __shared__ std::int32_t scan_scratch[kWarps];
+    pdl_launch_dependents();
+    pdl_wait();
     const int e = threadIdx.x;
     int total = 0;
 #pragma unroll 8
@@ -217,6 +228,8 @@ __global__ void __launch_bounds__(256) permute_scatter_kernel(
     std::int32_t* row_token, const std::int32_t* __restrict__ pp_off, std::int32_t* pp_of_flat) {
     __shared__ std::int32_t base[kWarps][kExperts];
     __shared__ std::int32_t running[kWarps][kExperts];
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int chunk = blockIdx.x * kWarps + warp;
@@ -239,12 +252,114 @@ __global__ void __launch_bounds__(256) permute_scatter_kernel(
     }
 }
 
+// ---- decode front end: top-8 + permutation + lists + NVFP4 token rows, one block ------------
+// For up to 8 tokens the three routing stages are a few microseconds of work each, so they run as
+// one 256-thread block instead of three launches: warp w ranks token w; thread e counts expert e
+// (the ranking law of cuda/nvfp4_grouped.cu:117-132 evaluated directly: 64 assignments at most);
+// then every thread quantises 16-element blocks of the token rows (cuda/nvfp4_ops.cu:818-841) and
+// stores them once per destination row of the padded position space, scales in the 128x4 tiling.
+constexpr int kFusedMaxRows = 8;
+
+__global__ void __launch_bounds__(256) route_fused_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias, std::int32_t* __restrict__ ids,
+    float* __restrict__ weights, float routed_scale, int rows, std::int32_t* __restrict__ order,
+    std::int32_t* __restrict__ position, RouteLists lists, std::int32_t* __restrict__ row_token,
+    std::int32_t* __restrict__ pp_of_flat, const std::uint16_t* __restrict__ x, std::uint8_t* __restrict__ xq,
+    std::uint8_t* __restrict__ xs, int hidden, float quant_scale) {
+    __shared__ std::int32_t s_ids[kFusedMaxRows * kTop];
+    __shared__ std::int32_t s_pp[kFusedMaxRows * (kTop + 1)];
+    __shared__ std::int32_t scan_scratch[kWarps];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5;
+    const int assignments = rows * kTop;
+    if (warp < rows) {
+        warp_top8(logits + static_cast<std::size_t>(warp) * kExperts, bias, ids + warp * kTop, weights + warp * kTop,
+                  routed_scale);
+    }
+    __syncthreads();
+    if (threadIdx.x < assignments) s_ids[threadIdx.x] = ids[threadIdx.x];
+    __syncthreads();
+    const int e = threadIdx.x;
+    int count = 0;
+    for (int j = 0; j < assignments; ++j) count += s_ids[j] == e;
+    const int offset = block_exclusive_scan_256(count, scan_scratch);
+    write_route_lists(e, count, offset, assignments, rows, lists, scan_scratch);
+    __syncthreads();
+    if (threadIdx.x < assignments) {
+        const int i = threadIdx.x;
+        const int mine = s_ids[i];
+        int rank = 0;
+        for (int j = 0; j < i; ++j) rank += s_ids[j] == mine;
+        const int pos = lists.offsets[mine] + rank;
+        order[pos] = i;
+        position[i] = pos;
+        row_token[pos] = i / kTop;
+        const int pp = lists.pp_off[mine] + rank;
+        pp_of_flat[i] = pp;
+        s_pp[i] = pp;
+    } else if (threadIdx.x < assignments + rows) {
+        const int t = threadIdx.x - assignments;
+        row_token[assignments + t] = t;
+        const int pp = lists.pp_off[kExperts] + t;
+        pp_of_flat[assignments + t] = pp;
+        s_pp[assignments + t] = pp;
+    }
+    __syncthreads();
+    const int blocks = hidden / 16;
+    const int col_blocks = (blocks + 3) / 4;
+    for (int idx = threadIdx.x; idx < rows * blocks; idx += blockDim.x) {
+        const int token = idx / blocks;
+        const int b = idx - token * blocks;
+        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(token) * hidden + b * 16);
+        const uint4 lo = __ldg(src);
+        const uint4 hi = __ldg(src + 1);
+        const std::uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = __uint_as_float(words[i] << 16);
+            v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+        }
+        std::uint8_t scale_bits;
+        const uint2 packed = quantize_block16(v, quant_scale, &scale_bits);
+#pragma unroll
+        for (int slot = 0; slot <= kTop; ++slot) {
+            const std::size_t pp =
+                static_cast<std::size_t>(s_pp[slot < kTop ? token * kTop + slot : assignments + token]);
+            *reinterpret_cast<uint2*>(xq + pp * (hidden / 2) + b * 8) = packed;
+            xs[((pp >> 7) * col_blocks + (b >> 2)) * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4 + (b & 3)] = scale_bits;
+        }
+    }
+}
+
 }  // namespace
+
+int route_fused_max_rows() { return kFusedMaxRows; }
+
+cudaError_t launch_route_fused(p92b_plan* plan, const float* bias, float routed_scale, const std::uint16_t* x,
+                               int rows, int pad_align, int tile_rows, cudaStream_t stream, bool pdl) {
+    if (rows <= 0 || rows > kFusedMaxRows) return cudaErrorInvalidValue;
+    RouteLists lists {};
+    lists.counts = plan->counts;
+    lists.offsets = plan->offsets;
+    lists.active = plan->active;
+    lists.active_count = plan->active_count;
+    lists.enabled = true;
+    lists.pad_align = pad_align;
+    lists.tile_rows = tile_rows;
+    lists.pp_off = plan->pp_off;
+    lists.tile_prefix = plan->tile_prefix;
+    plan->last_launches += 1;
+    return launch_kernel(route_fused_kernel, dim3(1), dim3(256), 0, stream, pdl, plan->logits, bias, plan->ids,
+                         plan->route_weights, routed_scale, rows, plan->order, plan->position, lists, plan->row_token,
+                         plan->pp_of_flat, x, plan->xq_pp, plan->xs_sw, plan->hidden, 1.0F);
+}
 
 cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignments,
                            std::int32_t* order, std::int32_t* position, std::int32_t* counts,
                            std::int32_t* offsets, bool route_lists, int pad_align, int tile_rows,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, bool pdl) {
     if (plan == nullptr || ids == nullptr || counts == nullptr || offsets == nullptr || assignments <= 0 ||
         assignments > plan->max_rows * kTop) {
         return cudaErrorInvalidValue;
@@ -263,20 +378,24 @@ cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignm
     std::int32_t* row_token = route_lists ? plan->row_token : nullptr;
     std::int32_t* pp_of_flat = padded ? plan->pp_of_flat : nullptr;
     if (assignments <= kWarps * 1024) {
-        permute_small_kernel<<<1, 256, 0, stream>>>(ids, assignments, order, position, lists, row_token, pp_of_flat,
-                                                    plan->status);
         plan->last_launches += 1;
-        return cudaGetLastError();
+        return launch_kernel(permute_small_kernel, dim3(1), dim3(256), 0, stream, pdl, ids, assignments, order, position,
+                             lists, row_token, pp_of_flat, plan->status);
     }
     const int chunks = (assignments + kChunk - 1) / kChunk;
     if (chunks > plan->chunks) return cudaErrorInvalidValue;
     const int blocks = (chunks + kWarps - 1) / kWarps;
-    permute_hist_kernel<<<blocks, 256, 0, stream>>>(ids, assignments, plan->chunk_hist, plan->status);
-    permute_scan_kernel<<<1, 256, 0, stream>>>(plan->chunk_hist, chunks, assignments, lists);
-    permute_scatter_kernel<<<blocks, 256, 0, stream>>>(ids, assignments, plan->chunk_hist, offsets, order, position,
-                                                       row_token, lists.pp_off, pp_of_flat);
     plan->last_launches += 3;
-    return cudaGetLastError();
+    cudaError_t st = launch_kernel(permute_hist_kernel, dim3(blocks), dim3(256), 0, stream, pdl, ids, assignments,
+                                   plan->chunk_hist, plan->status);
+    if (st != cudaSuccess) return st;
+    st = launch_kernel(permute_scan_kernel, dim3(1), dim3(256), 0, stream, pdl, plan->chunk_hist, chunks, assignments,
+                       lists);
+    if (st != cudaSuccess) return st;
+    return launch_kernel(permute_scatter_kernel, dim3(blocks), dim3(256), 0, stream, pdl,
+                         static_cast<const std::int32_t*>(ids), assignments,
+                         static_cast<const std::int32_t*>(plan->chunk_hist), static_cast<const std::int32_t*>(offsets),
+                         order, position, row_token, static_cast<const std::int32_t*>(lists.pp_off), pp_of_flat);
 }
 
 }  // namespace p92b

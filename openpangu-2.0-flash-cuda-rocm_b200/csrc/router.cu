@@ -13,10 +13,15 @@
 // Selection is pure comparison with ties to the lower id, which is order
 // independent, so the top-8 itself is free to use a warp-per-token layout.
 #include "p92b_common.cuh"
+#include "tc_ptx.cuh"
 
 #include <cfloat>
 
 namespace p92b {
+
+using ptx::pdl_launch_dependents;
+using ptx::pdl_wait;
+
 namespace {
 
 // ---- T == 1 order ---------------------------------------------------------
@@ -28,6 +33,8 @@ __global__ void __launch_bounds__(256) logits_gemv_kernel(const std::uint16_t* _
                                                           int columns) {
     const int row = blockIdx.x;
     if (row >= rows) return;
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float warp_sums[8];
     const std::uint16_t* wr = w + static_cast<std::size_t>(row) * columns;
     float value = 0.0F;
@@ -77,9 +84,11 @@ __global__ void __launch_bounds__(WE* WT * 32) logits_rows_kernel(
 #pragma unroll
         for (int j = 0; j < TT; ++j) acc[i][j] = 0.0F;
 
+    pdl_launch_dependents();
     for (int k0 = 0; k0 < columns; k0 += kc) {
         if (k0 != 0) __syncthreads();
-        // 16-byte coalesced staging; rows beyond the edge are zero filled.
+        // 16-byte coalesced staging; rows beyond the edge are zero filled.  The router weight does
+        // not depend on the upstream kernel, the token rows do.
         for (int idx = threadIdx.x; idx < BE * kc8; idx += THREADS) {
             const int r = idx / kc8;
             const int c8 = idx - r * kc8;
@@ -89,6 +98,7 @@ __global__ void __launch_bounds__(WE* WT * 32) logits_rows_kernel(
             }
             *reinterpret_cast<uint4*>(ws + static_cast<std::size_t>(r) * kc + c8 * 8) = v;
         }
+        if (k0 == 0) pdl_wait();
         for (int idx = threadIdx.x; idx < BT * kc8; idx += THREADS) {
             const int r = idx / kc8;
             const int c8 = idx - r * kc8;
@@ -138,104 +148,59 @@ __global__ void __launch_bounds__(128) router_top8_kernel(const float* __restric
                                                           std::int32_t* __restrict__ ids,
                                                           float* __restrict__ weights, int rows,
                                                           float routed_scale) {
-    const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const float* lg = logits + static_cast<std::size_t>(row) * kExperts;
-    float raw[8];
-    float corrected[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int e = lane + 32 * i;
-        raw[i] = 1.0F / (1.0F + expf(-lg[e]));
-        corrected[i] = raw[i] + bias[e];
-    }
-    unsigned used = 0U;
-    float chosen_weight = 0.0F;   // lane k keeps slot k's raw weight
-    int chosen_id = 0;
-#pragma unroll
-    for (int slot = 0; slot < 8; ++slot) {
-        float best = -FLT_MAX;
-        int best_id = 256 + lane;
-        float best_raw = 0.0F;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float c = (used >> i) & 1U ? -FLT_MAX : corrected[i];
-            const int e = lane + 32 * i;
-            // ascending id within the lane, so strict '>' keeps the lower id on ties
-            if (c > best || (c == best && e < best_id)) {
-                best = c;
-                best_id = e;
-                best_raw = raw[i];
-            }
-        }
-#pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            const float other = __shfl_xor_sync(0xffffffffU, best, offset);
-            const int other_id = __shfl_xor_sync(0xffffffffU, best_id, offset);
-            const float other_raw = __shfl_xor_sync(0xffffffffU, best_raw, offset);
-            if (other > best || (other == best && other_id < best_id)) {
-                best = other;
-                best_id = other_id;
-                best_raw = other_raw;
-            }
-        }
-        if ((best_id & 31) == lane) used |= 1U << (best_id >> 5);
-        if (lane == slot) {
-            chosen_weight = best_raw;
-            chosen_id = best_id;
-        }
-    }
-    float total = 0.0F;
-#pragma unroll
-    for (int slot = 0; slot < 8; ++slot) total += __shfl_sync(0xffffffffU, chosen_weight, slot);
-    const float multiplier = routed_scale / total;
-    if (lane < 8) {
-        ids[static_cast<std::size_t>(row) * 8 + lane] = chosen_id;
-        weights[static_cast<std::size_t>(row) * 8 + lane] = chosen_weight * multiplier;
-    }
+    warp_top8(logits + static_cast<std::size_t>(row) * kExperts, bias, ids + static_cast<std::size_t>(row) * 8,
+              weights + static_cast<std::size_t>(row) * 8, routed_scale);
 }
 
 }  // namespace
 
 cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w, float* out,
                                  int batch_rows, int rows, int columns, bool gemv_order,
-                                 cudaStream_t stream) {
+                                 cudaStream_t stream, bool pdl) {
     if (x == nullptr || w == nullptr || out == nullptr || batch_rows <= 0 || rows <= 0 ||
         columns <= 0 || columns % 128 != 0) {
         return cudaErrorInvalidValue;
     }
     if (gemv_order) {
         if (batch_rows != 1) return cudaErrorInvalidValue;
-        logits_gemv_kernel<<<rows, 256, 0, stream>>>(x, w, out, rows, columns);
+        return launch_kernel(logits_gemv_kernel, dim3(rows), dim3(256), 0, stream, pdl, x, w, out, rows, columns);
     } else if (batch_rows <= 8) {
         // decode: the whole K extent of 2 expert rows and of every token sits in
         // shared memory, so all global loads of a block are in flight at once
-        constexpr int TE = 1, TT = 8, WE = 2, WT = 1;
+        constexpr int TE = 1, TT = 8, WE = 4, WT = 1;
         const std::size_t smem = static_cast<std::size_t>(TE * WE + TT * WT) * columns * 2;
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
         auto kernel = logits_rows_kernel<TE, TT, WE, WT>;
-        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (st != cudaSuccess) return st;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (st != cudaSuccess) return st;
+            configured = true;
+        }
         dim3 grid((rows + TE * WE - 1) / (TE * WE), 1);
-        kernel<<<grid, WE * WT * 32, smem, stream>>>(x, w, out, batch_rows, rows, columns, columns);
+        return launch_kernel(kernel, grid, dim3(WE * WT * 32), smem, stream, pdl, x, w, out, batch_rows, rows, columns,
+                             columns);
     } else {
         constexpr int TE = 8, TT = 8, WE = 2, WT = 4;
         constexpr int KC = 128;
         const std::size_t smem = static_cast<std::size_t>(TE * WE + TT * WT) * KC * 2;
         dim3 grid((rows + TE * WE - 1) / (TE * WE), (batch_rows + TT * WT - 1) / (TT * WT));
-        logits_rows_kernel<TE, TT, WE, WT><<<grid, WE * WT * 32, smem, stream>>>(x, w, out, batch_rows, rows, columns, KC);
+        return launch_kernel(logits_rows_kernel<TE, TT, WE, WT>, grid, dim3(WE * WT * 32), smem, stream, pdl, x, w, out,
+                             batch_rows, rows, columns, KC);
     }
-    return cudaGetLastError();
 }
 
 cudaError_t launch_router_top8(const float* logits, const float* bias, std::int32_t* ids,
-                               float* weights, int rows, float routed_scale, cudaStream_t stream) {
+                               float* weights, int rows, float routed_scale, cudaStream_t stream, bool pdl) {
     if (logits == nullptr || bias == nullptr || ids == nullptr || weights == nullptr || rows <= 0) {
         return cudaErrorInvalidValue;
     }
-    router_top8_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(logits, bias, ids, weights, rows, routed_scale);
-    return cudaGetLastError();
+    return launch_kernel(router_top8_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, pdl, logits, bias, ids, weights,
+                         rows, routed_scale);
 }
 
 }  // namespace p92b

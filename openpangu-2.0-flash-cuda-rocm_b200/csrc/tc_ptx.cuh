@@ -25,6 +25,13 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// No-ops unless the kernel was launched with the programmatic-stream-serialization attribute.
+// pdl_wait: blocks until the preceding kernel in the stream has completed and its writes are visible.
+// pdl_launch_dependents: lets the next kernel in the stream start its prologue now.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(std::uint32_t bar, std::uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
