@@ -296,17 +296,23 @@ def main() -> None:
     plan.stage_timing(False)
     stage_us = {k: v / calls * 1e3 for k, v in stage_ms.items()}
     d_mean = float(np.mean(distinct))
-    # algorithmic bytes of one gate/up launch: packed weights + scales of gate and up for the distinct
-    # routed experts and the shared expert, the quantised activations read, the quantised SwiGLU rows written
-    gu_bytes = (d_mean + 1) * 2 * (EXPERT_BYTES // 3) + rows * (HIDDEN // 2 + HIDDEN // 16) + \
-        9 * rows * (INTER // 2 + INTER // 16)
     layer_bytes = (d_mean + 1) * EXPERT_BYTES + ROUTER_BYTES + rows * HIDDEN * 2 * 2
     pk = peaks()
-    gu_gbs = gu_bytes / (stage_us["gate_up_swiglu"] * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gate_up_stream_kernel", "achieved": gu_gbs, "peak": pk["hbm_gbs"],
-                "unit": "GB/s", "frac": gu_gbs / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                "bytes_per_launch": gu_bytes, "us_per_launch": stage_us["gate_up_swiglu"],
-                "layer_bytes": layer_bytes,
+    if decode:
+        # the whole block is one kernel (moe_decode_kernel): its algorithmic bytes are the layer's
+        # (D+1 experts x 3 matrices packed + scales, the router weight, the token rows in and out);
+        # its device time is the event pair recorded around it on the launch stream (stage 0)
+        kernel, k_bytes, k_us = "moe_decode_kernel", layer_bytes, stage_us["router_logits"]
+    else:
+        # dominant kernel of the multi-kernel path: gate/up + SwiGLU + re-quantise
+        kernel = "expert_tc_kernel<0,128>"
+        k_bytes = (d_mean + 1) * 2 * (EXPERT_BYTES // 3) + rows * (HIDDEN // 2 + HIDDEN // 16) + \
+            9 * rows * (INTER // 2 + INTER // 16)
+        k_us = stage_us["gate_up_swiglu"]
+    k_gbs = k_bytes / (k_us * 1e-6) / 1e9
+    roofline = {"bound": "hbm", "kernel": kernel, "achieved": k_gbs, "peak": pk["hbm_gbs"],
+                "unit": "GB/s", "frac": k_gbs / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                "bytes_per_launch": k_bytes, "us_per_launch": k_us, "layer_bytes": layer_bytes,
                 "layer_frac_of_hbm": layer_bytes * n_layers / (ms_per_step * 1e-3) / 1e9 / pk["hbm_gbs"],
                 "distinct_routed_experts_mean": d_mean, "stage_us": stage_us}
 

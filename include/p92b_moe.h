@@ -142,11 +142,16 @@ int p92b_moe_permute_static(const int32_t* expert_ids, int assignments, int32_t*
  * host_entries: HOST array of (local_experts + 1) * 3 entries in the reference's
  * bank order expert*3 + kind, kind 0/1/2 = gate/up/down (cuda/nvfp4_grouped.cu:133);
  * the last three entries are the shared expert.  The weights are copied into
- * the library's own layout; the caller may free its copies afterwards.
+ * the library's own layout - a tile stream in which the bytes of every pipeline stage of the
+ * tensor-core kernels are contiguous ("retiled for TMA") - and the caller may free its copies
+ * afterwards.  flags: P92B_BANK_STREAM_COPY additionally keeps a row-major copy (twice the
+ * memory), which the SIMT kernel family (p92b_plan_set_path 1) and the two un-fused stage
+ * entry points need; without it those return cudaErrorNotSupported.
  * first_expert / local_experts select the expert-parallel shard this bank holds
  * (0 / 256 on one GPU). */
+#define P92B_BANK_STREAM_COPY 1
 int p92b_bank_create(p92b_bank** bank, const p92b_expert_projection* host_entries, int first_expert,
-                     int local_experts, int hidden, int intermediate, void* stream);
+                     int local_experts, int hidden, int intermediate, int flags, void* stream);
 void p92b_bank_destroy(p92b_bank* bank);
 size_t p92b_bank_bytes(const p92b_bank* bank);
 
@@ -200,6 +205,9 @@ typedef struct p92b_plan_views {
     const uint16_t* mixed;        /* BF16 down outputs [mixed rows][hidden] */
     const int32_t* mixed_index;   /* [rows*8 + rows]: row of `mixed` holding assignment (row, slot), then the shared rows */
     const int32_t* status;        /* device int: 0 ok, else first error code a kernel recorded */
+    const unsigned long long* trace; /* [trace_blocks][64] %globaltimer stamps of the last fused decode launch
+                                        (written only when P92B_TRACE is set in the environment) */
+    int trace_blocks;
 } p92b_plan_views;
 int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* views);
 

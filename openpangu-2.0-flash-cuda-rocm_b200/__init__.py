@@ -56,6 +56,8 @@ class PlanViews(ctypes.Structure):
         ("mixed", c_void_p),
         ("mixed_index", c_void_p),
         ("status", c_void_p),
+        ("trace", c_void_p),
+        ("trace_blocks", c_int),
     ]
 
 
@@ -75,7 +77,7 @@ SIGNATURES = {
     "p92b_add_inplace": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_moe_permute": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "p92b_moe_permute_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
-    "p92b_bank_create": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(ExpertProjection), c_int, c_int, c_int, c_int, c_void_p]),
+    "p92b_bank_create": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(ExpertProjection), c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "p92b_bank_destroy": (None, [c_void_p]),
     "p92b_bank_bytes": (c_size_t, [c_void_p]),
     "p92b_plan_create": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_int]),
@@ -221,10 +223,12 @@ class ExpertBank:
     ``entries``: sequence of (weight, scales_swizzled, alpha) CUDA tensors in the
     reference's bank order ``expert * 3 + kind`` (kind 0/1/2 = gate/up/down), the
     shared expert's three entries last.  The tensors may be freed afterwards.
+    ``stream_copy`` also keeps the row-major copy the SIMT kernel family and the un-fused stage
+    entry points read (twice the memory).
     """
 
     def __init__(self, entries: Sequence[tuple], first_expert: int = 0, local_experts: int = EXPERTS,
-                 hidden: int = HIDDEN, intermediate: int = INTERMEDIATE):
+                 hidden: int = HIDDEN, intermediate: int = INTERMEDIATE, stream_copy: bool = False):
         if len(entries) != (local_experts + 1) * 3:
             raise ValueError("invalid expert bank: need (local_experts + 1) * 3 entries")
         array = (ExpertProjection * len(entries))()
@@ -232,7 +236,7 @@ class ExpertBank:
             array[i].weight, array[i].scales_swizzled, array[i].alpha = w.data_ptr(), s.data_ptr(), a.data_ptr()
         handle = c_void_p()
         _check(load_library().p92b_bank_create(ctypes.byref(handle), array, first_expert, local_experts, hidden,
-                                               intermediate, _stream()), "bank_create")
+                                               intermediate, 1 if stream_copy else 0, _stream()), "bank_create")
         self.handle = handle
         self.first_expert, self.local_experts = first_expert, local_experts
         self.hidden, self.intermediate = hidden, intermediate
@@ -306,6 +310,7 @@ class MoePlan:
             "offsets": grab(v.offsets, (EXPERTS + 1,), torch.int32),
             "mixed_index": mixed_index,
             "status": grab(v.status, (1,), torch.int32),
+            "trace": torch.as_tensor(_DeviceSpan(v.trace, (v.trace_blocks, 64), "<i8"), device="cuda").clone(),
         }
 
     PATH_AUTO, PATH_STREAM, PATH_TENSOR_CORE = 0, 1, 2

@@ -1,0 +1,727 @@
+// The whole MoE block for up to 8 tokens (decode, MTP verify) as ONE persistent kernel.
+//
+// At these sizes the block is a 140 MB weight stream (≈21 µs at HBM speed) wrapped in a
+// few microseconds of routing, so kernel boundaries - five dependent launches - cost
+// as much as the stream itself.  Here one block per SM walks the phases, separated
+// by two device-wide counters instead of launches:
+//
+//   P0  every block: its one or two router rows (logits in the reference's exact FP32
+//       order, cuda/nvfp4_ops.cu:161-207) and its slice of the token quantisation
+//       (cuda/nvfp4_ops.cu:818-841, scales written 128x4-tiled);        -> counter 1
+//   P1  every block, redundantly and in shared memory: top-8 of every token
+//       (cuda/nvfp4_ops.cu:357-433), histogram, stable permutation
+//       (cuda/nvfp4_grouped.cu:117-132), active-expert list; block 0 also writes the
+//       routing products to global memory;
+//   P2  gate/up tiles and P3 down tiles through ONE TMA ring and one tcgen05 pipeline
+//       (same operand formats as expert_tc.cu).  The token side of gate/up is simply all
+//       tokens in token order (N=16 columns cost nothing at M=128), so it does not depend
+//       on routing; the epilogue keeps the columns routed to the tile's expert.  A down
+//       tile needs the eight gate/up tiles of its expert: per-expert counters, no barrier,
+//       and its weights are already in flight while the producer waits.  Work is dealt
+//       statically and evenly in units of ring stages (a gate/up tile is 10 stages,
+//       a down tile 2);                                                   -> counter 2
+//   P4  weighted combine in slot order + shared expert (cuda/nvfp4_ops.cu:124-142,92-95).
+//
+// All blocks are co-resident (one per SM, grid = SM count); every wait on a counter or
+// an mbarrier is bounded by wall time and ends in a status word, never a hang.
+#include "p92b_common.cuh"
+#include "tc_ptx.cuh"
+
+namespace p92b {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kMegaThreads = 192;
+constexpr int kMegaMaxRows = 8;
+constexpr int kN = 16;                             // token columns of every MMA
+constexpr int kTile = 128;
+constexpr int kKB = 128;                           // bytes per operand row per K block
+constexpr int kSlab = 2048;
+// stage: two weight boxes, two token boxes, four scale slabs
+// (the first 36,864 bytes are one chunk of the bank's tile stream, copied as a whole)
+constexpr int kOffA0 = 0, kOffA1 = 16384, kOffSfA0 = 32768, kOffSfA1 = 34816;
+constexpr int kOffB0 = 36864, kOffB1 = 38912, kOffSfB0 = 40960, kOffSfB1 = 43008;
+constexpr int kStage = 45056;
+constexpr int kStages = 4;
+constexpr int kWeightTx = kChunkBytes;
+constexpr int kAccumStride = 32;
+constexpr int kAccumCols = 64;                     // per buffer: gate at +0, up at +32
+constexpr int kSfColsPerBuffer = 64;               // SFA0, SFA1, SFB0, SFB1 x 16 columns
+constexpr int kAccumBuffers = 4;                   // the issuer may run four tiles ahead of the epilogue
+constexpr int kTmemCols = 512;
+constexpr int kMaxActive = kMegaMaxRows * kTop + 1;
+
+struct MegaParams {
+    BankView bank;
+    const std::uint16_t* x;
+    const std::uint16_t* router_w;
+    const float* bias;
+    std::uint16_t* out;
+    float* logits;
+    std::int32_t* ids;
+    float* route_weights;
+    std::int32_t* order;
+    std::int32_t* position;
+    std::int32_t* counts;
+    std::int32_t* offsets;
+    std::int32_t* pp_of_flat;
+    std::uint8_t* xq_tok;          // [16][H/2] token-order NVFP4 rows
+    std::uint8_t* xs_tok;          // their scales: one 128-row tile per 4 scale columns
+    std::uint8_t* hq;              // [PP][I/2]
+    std::uint8_t* hs;              // tiled scales of hq
+    std::uint16_t* mixed;          // [PP][H]
+    unsigned* sync;                // [2] monotonic arrival counters
+    std::int32_t* gu_done;         // [257] gate/up tiles finished per active slot
+    std::int32_t* status;
+    unsigned long long* trace;     // optional [grid][64] %globaltimer stamps per block (null: off)
+    unsigned epoch;                // launches of this kernel on the plan before this one
+    float routed_scale;
+    float quant_scale;
+    int rows;
+    int hidden;
+    int inter;
+};
+
+struct Routing {                   // shared-memory copy, identical in every block
+    std::int32_t ids[kMegaMaxRows * kTop];
+    float weights[kMegaMaxRows * kTop];
+    std::int32_t counts[kExperts];
+    std::int32_t offsets[kExperts + 1];
+    std::int32_t pp_off[kExperts + 1];
+    std::int32_t slot_of[kExperts];            // active slot of an expert (1-based; 0 is the shared expert), -1 if unused
+    std::int32_t active[kMaxActive];
+    std::int32_t pp_tok[kMaxActive][kMegaMaxRows];   // padded position of (active slot, token), -1 if not routed
+    std::int32_t n_active;
+    float logits[kMegaMaxRows * kExperts];
+};
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded wait until *counter has reached `target` (wrap-safe).
+__device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned target) {
+    const std::uint64_t start = global_timer_ns();
+    while (static_cast<int>(ld_acquire(counter) - target) < 0) {
+        if (global_timer_ns() - start > 1000000000ULL) return false;
+    }
+    return true;
+}
+
+// Device-wide rendezvous of the co-resident blocks: arrive, then wait for everyone.
+__device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned target) {
+    __shared__ int ok;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        fence_proxy_async_all();
+        atomicAdd(counter, 1U);
+        ok = wait_counter(counter, target) ? 1 : 0;
+        __threadfence();
+        fence_proxy_async_all();
+    }
+    __syncthreads();
+    return ok != 0;
+}
+
+// The static deal of tiles to blocks, computed identically by every role of every block.
+struct Deal {
+    int gu_items, dn_items, grid;
+    int n_gu;                      // gate/up tiles of this block: block, block+grid, ...
+    int dn_begin, dn_count;        // contiguous down tiles
+    int total_cap;                 // first left-over down tile
+    int leftovers;
+    __device__ void init(int n_active, int gu_tiles, int dn_tiles, int grid_, int block) {
+        grid = grid_;
+        gu_items = n_active * gu_tiles;
+        dn_items = n_active * dn_tiles;
+        // gate/up tiles go round-robin: the first `r` blocks hold q+1 of them, the rest q.  Down tiles
+        // fill every block up to the common level (in ring stages: 10 per gate/up tile, 2 per down
+        // tile); what is left over goes round-robin again.  Closed forms, no loop over the grid.
+        const int q = gu_items / grid;
+        const int r = gu_items - q * grid;
+        const int stages = gu_items * 10 + dn_items * 2;
+        const int level = stages / grid;                // rounded down: the remainder is dealt round-robin
+        int cap_hi = (level - 10 * (q + 1)) / 2;
+        int cap_lo = (level - 10 * q) / 2;
+        cap_hi = cap_hi < 0 ? 0 : cap_hi;
+        cap_lo = cap_lo < 0 ? 0 : cap_lo;
+        n_gu = q + (block < r ? 1 : 0);
+        const int mine = block < r ? cap_hi : cap_lo;
+        // down tiles are dealt in expert order, lightly loaded blocks first: those are free after one
+        // gate/up tile and take the experts whose gate/up tiles all ran in the first round, while the
+        // blocks with two gate/up tiles become free when the later experts' rows exist
+        const int prefix = block >= r ? (block - r) * cap_lo : (grid - r) * cap_lo + block * cap_hi;
+        total_cap = r * cap_hi + (grid - r) * cap_lo;
+        dn_begin = prefix < dn_items ? prefix : dn_items;
+        dn_count = dn_items - dn_begin < mine ? dn_items - dn_begin : mine;
+        leftovers = dn_items > total_cap ? dn_items - total_cap : 0;
+    }
+    // i-th tile of this block: returns false past the end.  kind 0 gate/up, 1 down.
+    __device__ bool item(int i, int block, int gu_tiles, int dn_tiles, int* kind, int* slot, int* m_tile) const {
+        if (i < n_gu) {
+            const int g = block + i * grid;
+            *kind = 0; *slot = g / gu_tiles; *m_tile = g - *slot * gu_tiles;
+            return true;
+        }
+        i -= n_gu;
+        int d;
+        if (i < dn_count) {
+            d = dn_begin + i;
+        } else {
+            const int j = block + (i - dn_count) * grid;
+            if (j >= leftovers) return false;
+            d = total_cap + j;
+        }
+        *kind = 1; *slot = d / dn_tiles; *m_tile = d - *slot * dn_tiles;
+        return true;
+    }
+};
+
+__global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                      const __grid_constant__ CUtensorMap map_h,
+                                                                      const MegaParams p) {
+    extern __shared__ std::uint8_t smem_raw[];
+    __shared__ Routing rt;
+    __shared__ __align__(8) std::uint64_t barrier_words[3 * kStages + 2 * kAccumBuffers];
+    __shared__ std::uint32_t tmem_slot_word;
+    __shared__ volatile std::uint32_t abort_word;
+
+    const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    const std::uint32_t bars = smem_u32(barrier_words);
+    auto weight_bar = [&](int s) { return bars + 8U * s; };
+    auto token_bar = [&](int s) { return bars + 8U * (kStages + s); };
+    auto empty_bar = [&](int s) { return bars + 8U * (2 * kStages + s); };
+    auto accum_full = [&](int b) { return bars + 8U * (3 * kStages + b); };
+    auto accum_empty = [&](int b) { return bars + 8U * (3 * kStages + kAccumBuffers + b); };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rows = p.rows;
+    const int hidden = p.hidden;
+    const int inter = p.inter;
+    const int assignments = rows * kTop;
+    const int grid = gridDim.x;
+    const int block = blockIdx.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(weight_bar(s), 1);
+            mbar_init(token_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < kAccumBuffers; ++b) {
+            mbar_init(accum_full(b), 1);
+            mbar_init(accum_empty(b), 4);
+        }
+        abort_word = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&map_x);
+        prefetch_tensormap(&map_h);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_slot_word), kTmemCols);
+        tmem_relinquish();
+    }
+    pdl_wait();                       // the token rows come from the kernel before this one
+    pdl_launch_dependents();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const std::uint32_t tmem_base = tmem_slot_word;
+    auto stamp = [&](int slot) {
+        if (p.trace != nullptr) p.trace[static_cast<std::size_t>(block) * 64 + slot] = global_timer_ns();
+    };
+    if (threadIdx.x == 0) stamp(0);
+    auto give_up = [&](int code) {
+        abort_word = 1;
+        atomicCAS(p.status, kStatusOk, code);
+    };
+
+    // ------------------------------------------------------------------ P0
+    {
+        // Stage this block's router rows and all token rows in shared memory with one round of
+        // 16-byte loads (the ring is idle until the pipeline starts), then work from there.
+        const int my_experts = block + grid < kExperts ? 2 : (block < kExperts ? 1 : 0);
+        std::uint16_t* w_rows = reinterpret_cast<std::uint16_t*>(smem_raw + (base - smem_u32(smem_raw)));
+        std::uint16_t* x_rows = w_rows + 2 * hidden;
+        const int vec_per_row = hidden / 8;
+        for (int i = threadIdx.x; i < (my_experts + rows) * vec_per_row; i += kMegaThreads) {
+            const int r = i / vec_per_row;
+            const int c = i - r * vec_per_row;
+            if (r < my_experts) {
+                reinterpret_cast<uint4*>(w_rows + r * hidden)[c] =
+                    __ldg(reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
+            } else {
+                reinterpret_cast<uint4*>(x_rows + (r - my_experts) * hidden)[c] =
+                    __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r - my_experts) * hidden) + c);
+            }
+        }
+        __syncthreads();
+        if (rows == 1) {
+            // T = 1 order: 256 partial chains (thread t: columns t, t+256, ...), a shuffle-down tree
+            // per 32 of them, then a tree over the eight results (cuda/nvfp4_ops.cu:38-51,161-176)
+            for (int q = warp; q < my_experts; q += kMegaThreads / 32) {
+                const std::uint16_t* wr = w_rows + q * hidden;
+                float value = 0.0F;
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float partial = 0.0F;
+                    for (int c = lane + 32 * v; c < hidden; c += 256) {
+                        partial = fmaf(bf16_bits_to_float(x_rows[c]), bf16_bits_to_float(wr[c]), partial);
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) partial += __shfl_down_sync(0xffffffffU, partial, off);
+                    const float warp_sum = __shfl_sync(0xffffffffU, partial, 0);
+                    if (lane == v) value = warp_sum;
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
+                if (lane == 0) p.logits[block + q * grid] = value;
+            }
+        } else {
+            // T > 1 order: lane l sums columns l, l+32, ...; shuffle-down tree (cuda/nvfp4_ops.cu:178-207)
+            for (int q = warp; q < my_experts * rows; q += kMegaThreads / 32) {
+                const int r = q / rows;
+                const int t = q - r * rows;
+                const std::uint16_t* wr = w_rows + r * hidden;
+                const std::uint16_t* xr = x_rows + t * hidden;
+                float value = 0.0F;
+#pragma unroll 8
+                for (int c = lane; c < hidden; c += 32) {
+                    value = fmaf(bf16_bits_to_float(xr[c]), bf16_bits_to_float(wr[c]), value);
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
+                if (lane == 0) p.logits[static_cast<std::size_t>(t) * kExperts + block + r * grid] = value;
+            }
+        }
+        // token quantisation, one 16-element block per thread across the grid
+        const int blocks16 = hidden / 16;
+        const int g = block * kMegaThreads + threadIdx.x;
+        if (g < rows * blocks16) {
+            const int t = g / blocks16;
+            const int b = g - t * blocks16;
+            const uint4* src = reinterpret_cast<const uint4*>(x_rows + t * hidden + b * 16);
+            const uint4 lo = src[0];
+            const uint4 hi = src[1];
+            const std::uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[2 * i] = __uint_as_float(words[i] << 16);
+                v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+            }
+            std::uint8_t scale_bits;
+            const uint2 packed = quantize_block16(v, p.quant_scale, &scale_bits);
+            *reinterpret_cast<uint2*>(p.xq_tok + static_cast<std::size_t>(t) * (hidden / 2) + b * 8) = packed;
+            p.xs_tok[static_cast<std::size_t>(b >> 2) * 512 + t * 16 + (b & 3)] = scale_bits;
+        }
+        if (block == 0) {
+            for (int i = threadIdx.x; i <= kExperts; i += kMegaThreads) p.gu_done[i] = 0;
+        }
+    }
+    if (threadIdx.x == 0) stamp(1);
+    if (!grid_rendezvous(p.sync + 0, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
+    if (threadIdx.x == 0) stamp(2);
+
+    // ------------------------------------------------------------------ P1
+    if (!abort_word) {
+        // logits were written by other blocks of this launch: read them past L1
+        for (int i = threadIdx.x; i < rows * kExperts; i += kMegaThreads) rt.logits[i] = __ldcg(p.logits + i);
+        __syncthreads();
+        for (int t = warp; t < rows; t += kMegaThreads / 32) {
+            warp_top8(rt.logits + t * kExperts, p.bias, rt.ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
+        }
+        for (int i = threadIdx.x; i < kMaxActive * kMegaMaxRows; i += kMegaThreads) (&rt.pp_tok[0][0])[i] = -1;
+        __syncthreads();
+        for (int e = threadIdx.x; e < kExperts; e += kMegaThreads) {
+            int count = 0;
+            for (int j = 0; j < assignments; ++j) count += rt.ids[j] == e;
+            rt.counts[e] = count;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane l owns experts 8l .. 8l+7: ascending id order is kept by the lane order
+            int c_sum = 0, a_sum = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                c_sum += rt.counts[lane * 8 + k];
+                a_sum += rt.counts[lane * 8 + k] > 0;
+            }
+            int c_incl = c_sum, a_incl = a_sum;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int c_o = __shfl_up_sync(0xffffffffU, c_incl, off);
+                const int a_o = __shfl_up_sync(0xffffffffU, a_incl, off);
+                if (lane >= off) { c_incl += c_o; a_incl += a_o; }
+            }
+            int c_run = c_incl - c_sum, a_run = a_incl - a_sum;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int e = lane * 8 + k;
+                const int count = rt.counts[e];
+                rt.offsets[e] = c_run;
+                rt.pp_off[e] = a_run * kTile;              // every active expert owns one 128-row slab
+                if (count > 0) {
+                    rt.slot_of[e] = 1 + a_run;
+                    rt.active[1 + a_run] = e;
+                    ++a_run;
+                } else {
+                    rt.slot_of[e] = -1;
+                }
+                c_run += count;
+            }
+            if (lane == 31) {
+                rt.offsets[kExperts] = c_run;
+                rt.pp_off[kExperts] = a_run * kTile;       // the shared expert's slab comes last
+                rt.active[0] = kExperts;
+                rt.n_active = a_run + 1;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < assignments) {
+            const int i = threadIdx.x;
+            const int e = rt.ids[i];
+            int rank = 0;
+            for (int j = 0; j < i; ++j) rank += rt.ids[j] == e;
+            const int pos = rt.offsets[e] + rank;
+            const int pp = rt.pp_off[e] + rank;
+            rt.pp_tok[rt.slot_of[e]][i / kTop] = pp;
+            if (block == 0) {
+                p.ids[i] = e;
+                p.route_weights[i] = rt.weights[i];
+                p.order[pos] = i;
+                p.position[i] = pos;
+                p.pp_of_flat[i] = pp;
+            }
+        } else if (threadIdx.x < assignments + rows) {
+            const int t = threadIdx.x - assignments;
+            rt.pp_tok[0][t] = rt.pp_off[kExperts] + t;
+            if (block == 0) p.pp_of_flat[assignments + t] = rt.pp_off[kExperts] + t;
+        }
+        if (block == 0) {
+            for (int e = threadIdx.x; e <= kExperts; e += kMegaThreads) {
+                if (e < kExperts) p.counts[e] = rt.counts[e];
+                p.offsets[e] = rt.offsets[e];
+            }
+        }
+        __syncthreads();
+    }
+
+    if (threadIdx.x == 0) stamp(3);
+    // ------------------------------------------------------------ P2 + P3
+    const int gu_tiles = inter / kTile;          // 8
+    const int dn_tiles = hidden / kTile;         // 20
+    const int gu_kblocks = (hidden / 2) / kKB;   // 10 stages per gate/up tile
+    const int dn_stages = (inter / 2) / kKB / 2; // 2 stages per down tile (two K blocks each)
+    Deal deal;
+    deal.init(rt.n_active, gu_tiles, dn_tiles, grid, block);
+
+    if (warp == 0) {
+        if (elect_one() && !abort_word) {
+            int stage = 0;
+            std::uint32_t phase = 0;
+            int kind, slot, m_tile;
+            for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+                const int expert = rt.active[slot];
+                const int entry = expert == kExperts ? p.bank.local_experts : expert - p.bank.first_expert;
+                const int n_stages = kind == 0 ? gu_kblocks : dn_stages;
+                bool tokens_ready = kind == 0;
+                for (int s = 0; s < n_stages; ++s) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                    const std::uint32_t st = base + stage * kStage;
+                    if (i == 0 && s < 10) stamp(16 + s);
+                    mbar_arrive_expect_tx(weight_bar(stage), kWeightTx);
+                    if (kind == 0) {
+                        bulk_load(st, p.bank.g13 + ((static_cast<std::size_t>(entry) * gu_tiles + m_tile) * gu_kblocks + s) *
+                                                       kChunkBytes,
+                                  kChunkBytes, weight_bar(stage));
+                        mbar_arrive_expect_tx(token_bar(stage), 2 * kSlab);
+                        tma_load_2d(st + kOffB0, &map_x, token_bar(stage), s * kKB, 0);
+                        bulk_load(st + kOffSfB0, p.xs_tok + static_cast<std::size_t>(s * 4) * 512, kSlab, token_bar(stage));
+                    } else {
+                        bulk_load(st, p.bank.g2 + ((static_cast<std::size_t>(entry) * dn_tiles + m_tile) * dn_stages + s) *
+                                                      kChunkBytes,
+                                  kChunkBytes, weight_bar(stage));
+                        if (!tokens_ready) {
+                            // the SwiGLU rows of this expert exist once its eight gate/up tiles are done
+                            if (!wait_counter(reinterpret_cast<const unsigned*>(p.gu_done + slot),
+                                              static_cast<unsigned>(gu_tiles))) {
+                                give_up(kStatusWaitExpired);
+                                break;
+                            }
+                            fence_proxy_async_all();
+                            tokens_ready = true;
+                        }
+                        const int pp0 = rt.pp_off[expert];
+                        mbar_arrive_expect_tx(token_bar(stage), 4 * kSlab);
+                        tma_load_2d(st + kOffB0, &map_h, token_bar(stage), (2 * s) * kKB, pp0);
+                        tma_load_2d(st + kOffB1, &map_h, token_bar(stage), (2 * s + 1) * kKB, pp0);
+                        const std::uint8_t* bsf = p.hs + (static_cast<std::size_t>(pp0 >> 7) * (inter / 64) + (2 * s) * 4) * 512;
+                        bulk_load(st + kOffSfB0, bsf, kSlab, token_bar(stage));
+                        bulk_load(st + kOffSfB1, bsf + 4 * 512, kSlab, token_bar(stage));
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1U; }
+                }
+                if (i + 1 == deal.n_gu) stamp(4);           // all gate/up loads issued
+            }
+            stamp(5);                                        // all loads issued
+        }
+    } else if (warp == 1) {
+        if (elect_one() && !abort_word) {
+            int stage = 0;
+            std::uint32_t phase = 0;
+            int buffer = 0;
+            std::uint32_t accum_phase = 0;              // bit b = phase of buffer b
+            constexpr std::uint32_t idesc = idesc_nvf4(kTile, kN);
+            const std::uint32_t sf_tmem = tmem_base + kAccumBuffers * kAccumCols;
+            int sf_buffer = 0;
+            int kind, slot, m_tile;
+            for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+                if (!mbar_wait(accum_empty(buffer), ((accum_phase >> buffer) & 1U) ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                tc_fence_after();
+                const std::uint32_t accum = tmem_base + buffer * kAccumCols;
+                const int n_stages = kind == 0 ? gu_kblocks : dn_stages;
+                bool ok = true;
+                for (int s = 0; s < n_stages; ++s) {
+                    if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) {
+                        give_up(kStatusWaitExpired);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    if (i == 0 && s < 10) stamp(26 + s);
+                    const std::uint32_t st = base + stage * kStage;
+                    const std::uint32_t sfc = sf_tmem + sf_buffer * kSfColsPerBuffer;
+                    const int slabs = kind == 0 ? 3 : 4;            // SFA0, SFA1, SFB0 (, SFB1)
+                    for (int o = 0; o < slabs; ++o) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            tc_copy_sf(sfc + o * 16 + k * 4,
+                                       desc_scale_atom(st + (o < 2 ? kOffSfA0 + o * kSlab : kOffSfB0 + (o - 2) * kSlab) + k * 512));
+                        }
+                    }
+                    const std::uint64_t a0 = desc_k_major_sw128(st + kOffA0);
+                    const std::uint64_t a1 = desc_k_major_sw128(st + kOffA1);
+                    const std::uint64_t b0 = desc_k_major_sw128(st + kOffB0);
+                    const std::uint64_t b1 = desc_k_major_sw128(st + kOffB1);
+                    if (kind == 0) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            mma_nvf4(accum, a0 + 2 * k, b0 + 2 * k, idesc, sfc + k * 4, sfc + 32 + k * 4, s > 0 || k > 0);
+                            mma_nvf4(accum + kAccumStride, a1 + 2 * k, b0 + 2 * k, idesc, sfc + 16 + k * 4,
+                                     sfc + 32 + k * 4, s > 0 || k > 0);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            mma_nvf4(accum, a0 + 2 * k, b0 + 2 * k, idesc, sfc + k * 4, sfc + 32 + k * 4, s > 0 || k > 0);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            mma_nvf4(accum, a1 + 2 * k, b1 + 2 * k, idesc, sfc + 16 + k * 4, sfc + 48 + k * 4, true);
+                        }
+                    }
+                    tc_commit(empty_bar(stage));
+                    if (i == 0 && s < 10) stamp(36 + s);
+                    sf_buffer ^= 1;
+                    if (++stage == kStages) { stage = 0; phase ^= 1U; }
+                }
+                if (!ok) break;
+                tc_commit(accum_full(buffer));
+                accum_phase ^= 1U << buffer;
+                buffer = (buffer + 1) % kAccumBuffers;
+                if (i == 0) stamp(6);                        // first tile's MMAs issued
+                if (i + 1 == deal.n_gu) stamp(7);            // gate/up MMAs issued
+            }
+            stamp(8);
+        }
+    } else if (!abort_word) {
+        const int quarter = warp & 3;
+        int buffer = 0;
+        std::uint32_t accum_phase = 0;
+        int kind, slot, m_tile;
+        for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+            if (!mbar_wait(accum_full(buffer), (accum_phase >> buffer) & 1U)) { give_up(kStatusWaitExpired); break; }
+            accum_phase ^= 1U << buffer;
+            tc_fence_after();
+            const int expert = rt.active[slot];
+            const int entry = expert == kExperts ? p.bank.local_experts : expert - p.bank.first_expert;
+            const std::uint32_t lane_base = tmem_base + buffer * kAccumCols + (static_cast<std::uint32_t>(quarter * 32) << 16);
+            const int row = m_tile * kTile + quarter * 32 + lane;
+            if (kind == 0) {
+                const float alpha_g = p.bank.alpha[entry * 3 + 0];
+                const float alpha_u = p.bank.alpha[entry * 3 + 1];
+                const int sf_col = row >> 4;
+                std::uint32_t g[16], u[16];
+                tmem_load16(lane_base, g);
+                tmem_load16(lane_base + kAccumStride, u);
+                tmem_load_wait();
+#pragma unroll
+                for (int n = 0; n < kMegaMaxRows; ++n) {
+                    const int pp_signed = n < rows ? rt.pp_tok[slot][n] : -1;        // warp uniform
+                    if (pp_signed < 0) continue;
+                    const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[n]) * alpha_g));
+                    const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[n]) * alpha_u));
+                    const float h = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
+                    float amax = fabsf(h);
+#pragma unroll
+                    for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffU, amax, off));
+                    const __nv_fp8_e4m3 scale(amax * (p.quant_scale / 6.0F));
+                    const float decoded = static_cast<float>(scale);
+                    const float multiplier = decoded == 0.0F ? 0.0F : p.quant_scale / decoded;
+                    const float q = h * multiplier;
+                    const float q_next = __shfl_xor_sync(0xffffffffU, q, 1);
+                    const std::size_t pp = static_cast<std::size_t>(pp_signed);
+                    if ((lane & 1) == 0) {
+                        p.hq[pp * (inter / 2) + (row >> 1)] =
+                            static_cast<std::uint8_t>(__nv_fp4x2_e2m1(make_float2(q, q_next)).__x);
+                    }
+                    if ((lane & 15) == 0) {
+                        p.hs[((pp >> 7) * (inter / 64) + (sf_col >> 2)) * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4 +
+                             (sf_col & 3)] = scale.__x;
+                    }
+                }
+                tc_fence_before();
+                __threadfence();
+                fence_proxy_async_all();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    mbar_arrive(accum_empty(buffer));
+                    mbar_arrive(accum_empty(buffer));
+                    mbar_arrive(accum_empty(buffer));
+                    mbar_arrive(accum_empty(buffer));
+                    atomicAdd(p.gu_done + slot, 1);
+                }
+            } else {
+                const float alpha = p.bank.alpha[entry * 3 + 2];
+                const int count = expert == kExperts ? rows : rt.counts[expert];
+                const int pp0 = rt.pp_off[expert];
+                std::uint32_t d[16];
+                tmem_load16(lane_base, d);
+                tmem_load_wait();
+#pragma unroll
+                for (int n = 0; n < kMegaMaxRows; ++n) {
+                    if (n < count) {
+                        p.mixed[static_cast<std::size_t>(pp0 + n) * hidden + row] =
+                            float_to_bf16_bits(__uint_as_float(d[n]) * alpha);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accum_empty(buffer));
+            }
+            buffer = (buffer + 1) % kAccumBuffers;
+        }
+        if (warp == 2 && lane == 0) stamp(9);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0) stamp(10);
+
+    // ------------------------------------------------------------------ P4
+    if (!grid_rendezvous(p.sync + 1, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
+    if (threadIdx.x == 0) stamp(11);
+    if (abort_word) return;
+    const int vectors = hidden / 8;
+    for (int v = block * kMegaThreads + threadIdx.x; v < rows * vectors; v += grid * kMegaThreads) {
+        const int row = v / vectors;
+        const int c8 = v - row * vectors;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0F;
+#pragma unroll
+        for (int slot = 0; slot < kTop; ++slot) {
+            const int e = rt.ids[row * kTop + slot];
+            const float w = rt.weights[row * kTop + slot];
+            const int pp = rt.pp_tok[rt.slot_of[e]][row];
+            const uint4 r = __ldcg(reinterpret_cast<const uint4*>(p.mixed + static_cast<std::size_t>(pp) * hidden + c8 * 8));
+            const std::uint32_t words[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[2 * k] = fmaf(__uint_as_float(words[k] << 16), w, acc[2 * k]);
+                acc[2 * k + 1] = fmaf(__uint_as_float(words[k] & 0xffff0000U), w, acc[2 * k + 1]);
+            }
+        }
+        const uint4 sh = __ldcg(reinterpret_cast<const uint4*>(
+            p.mixed + static_cast<std::size_t>(rt.pp_tok[0][row]) * hidden + c8 * 8));
+        const std::uint32_t sw[4] = {sh.x, sh.y, sh.z, sh.w};
+        std::uint32_t out_words[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float lo = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k])) + __uint_as_float(sw[k] << 16);
+            const float hi = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k + 1])) + __uint_as_float(sw[k] & 0xffff0000U);
+            out_words[k] = static_cast<std::uint32_t>(float_to_bf16_bits(lo)) |
+                           (static_cast<std::uint32_t>(float_to_bf16_bits(hi)) << 16);
+        }
+        *reinterpret_cast<uint4*>(p.out + static_cast<std::size_t>(row) * hidden + c8 * 8) =
+            make_uint4(out_words[0], out_words[1], out_words[2], out_words[3]);
+    }
+    if (threadIdx.x == 0) stamp(12);
+}
+
+constexpr int kMegaSmem = kStages * kStage + 1024;
+
+}  // namespace
+
+int decode_mega_max_rows() { return kMegaMaxRows; }
+
+cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std::uint16_t* x,
+                               const std::uint16_t* router_w, const float* bias, std::uint16_t* out, int rows,
+                               float routed_scale, cudaStream_t stream, bool pdl) {
+    if (!plan->tc_ready || !bank->tc_ready || rows <= 0 || rows > kMegaMaxRows || plan->hidden != 2560 ||
+        plan->intermediate != 1024) {
+        return cudaErrorNotSupported;
+    }
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t st = cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMegaSmem);
+        if (st != cudaSuccess) return st;
+        configured = true;
+    }
+    MegaParams p {};
+    p.bank = bank->view;
+    p.x = x;
+    p.router_w = router_w;
+    p.bias = bias;
+    p.out = out;
+    p.logits = plan->logits;
+    p.ids = plan->ids;
+    p.route_weights = plan->route_weights;
+    p.order = plan->order;
+    p.position = plan->position;
+    p.counts = plan->counts;
+    p.offsets = plan->offsets;
+    p.pp_of_flat = plan->pp_of_flat;
+    p.xq_tok = plan->xq_tok;
+    p.xs_tok = plan->xs_tok;
+    p.hq = plan->hq_pp;
+    p.hs = plan->hs_sw;
+    p.mixed = plan->mixed_pp;
+    p.sync = plan->mega_sync;
+    p.gu_done = plan->gu_done;
+    p.status = plan->status;
+    p.trace = plan->trace_on ? plan->mega_trace : nullptr;
+    p.epoch = plan->mega_epoch++;
+    p.routed_scale = routed_scale;
+    p.quant_scale = 1.0F;
+    p.rows = rows;
+    p.hidden = plan->hidden;
+    p.inter = plan->intermediate;
+    plan->last_launches += 1;
+    return launch_kernel(moe_decode_kernel, dim3(plan->sm_count), dim3(kMegaThreads), kMegaSmem, stream, pdl,
+                         plan->map_x_tok, plan->map_h[0], p);
+}
+
+}  // namespace p92b

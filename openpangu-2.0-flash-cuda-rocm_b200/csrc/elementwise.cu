@@ -181,6 +181,44 @@ __global__ void __launch_bounds__(256) combine_shared_kernel(const std::uint16_t
         make_uint4(out_words[0], out_words[1], out_words[2], out_words[3]);
 }
 
+// Row-major packed weights + tiled scales of one matrix -> the chunk stream (see BankView).
+// One thread per 16 bytes: first the weight pieces, then the scale bytes.
+__global__ void __launch_bounds__(256) retile_kernel(const std::uint8_t* __restrict__ weight,
+                                                     const std::uint8_t* __restrict__ scales,
+                                                     std::uint8_t* __restrict__ chunks, int rows, int k_bytes,
+                                                     int blocks_per_chunk, int slot) {
+    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int pieces_per_row = k_bytes / 16;
+    const int k_blocks = k_bytes / 128;
+    const int chunks_per_tile = k_blocks / blocks_per_chunk;
+    const long weight_pieces = static_cast<long>(rows) * pieces_per_row;
+    if (index < weight_pieces) {
+        const int row = static_cast<int>(index / pieces_per_row);
+        const int piece = static_cast<int>(index - static_cast<long>(row) * pieces_per_row);
+        const int tile = row >> 7, r = row & 127;
+        const int kb = piece >> 3, j = piece & 7;
+        const int which = blocks_per_chunk == 1 ? slot : (kb & 1);
+        const std::size_t chunk = static_cast<std::size_t>(tile) * chunks_per_tile + kb / blocks_per_chunk;
+        const uint4 v = *reinterpret_cast<const uint4*>(weight + static_cast<std::size_t>(row) * k_bytes + piece * 16);
+        *reinterpret_cast<uint4*>(chunks + chunk * kChunkBytes + which * kChunkBox + r * 128 + ((j ^ (r & 7)) * 16)) = v;
+        return;
+    }
+    const long scale_piece = index - weight_pieces;                     // 16 scale bytes each
+    const long scale_pieces = static_cast<long>(rows / 128) * k_blocks * (kChunkScaleBytes / 16);
+    if (scale_piece >= scale_pieces) return;
+    const int per_block = kChunkScaleBytes / 16;                        // 128 pieces per (tile, K block)
+    const long block_index = scale_piece / per_block;                   // tile * k_blocks + kb
+    const int within = static_cast<int>(scale_piece - block_index * per_block);
+    const int tile = static_cast<int>(block_index / k_blocks);
+    const int kb = static_cast<int>(block_index - static_cast<long>(tile) * k_blocks);
+    const int which = blocks_per_chunk == 1 ? slot : (kb & 1);
+    const std::size_t chunk = static_cast<std::size_t>(tile) * chunks_per_tile + kb / blocks_per_chunk;
+    // source: tile row-block `tile`, scale column blocks 4*kb .. 4*kb+3, 512 bytes each, contiguous
+    const uint4 v = *reinterpret_cast<const uint4*>(
+        scales + (static_cast<std::size_t>(tile) * (k_blocks * 4) + kb * 4) * 512 + within * 16);
+    *reinterpret_cast<uint4*>(chunks + chunk * kChunkBytes + kChunkScaleOffset + which * kChunkScaleBytes + within * 16) = v;
+}
+
 inline unsigned blocks_for(long n, int per_block) { return static_cast<unsigned>((n + per_block - 1) / per_block); }
 
 }  // namespace
@@ -198,6 +236,15 @@ cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t
     dim3 grid(blocks_for(hidden / 8, 256), rows);
     return launch_kernel(combine_shared_kernel, grid, dim3(256), 0, stream, pdl, mixed, mixed_index, route_weights,
                          output, rows, hidden);
+}
+
+cudaError_t launch_retile(const std::uint8_t* weight, const std::uint8_t* scales_swizzled, std::uint8_t* chunks,
+                          int rows, int k_bytes, int blocks_per_chunk, int slot, cudaStream_t stream) {
+    const long threads = static_cast<long>(rows) * (k_bytes / 16) +
+                         static_cast<long>(rows / 128) * (k_bytes / 128) * (kChunkScaleBytes / 16);
+    retile_kernel<<<blocks_for(threads, 256), 256, 0, stream>>>(weight, scales_swizzled, chunks, rows, k_bytes,
+                                                               blocks_per_chunk, slot);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,

@@ -441,7 +441,7 @@ cudaError_t launch_gate_up(const p92b_plan* plan, const BankView& bank, const Ro
                            std::uint8_t* hs, std::uint16_t* gate_out, std::uint16_t* up_out,
                            const std::int32_t* order, int rows, cudaStream_t stream) {
     (void)rows;
-    if (bank.hidden != 2560 || bank.intermediate % kGateUpRows != 0) return cudaErrorNotSupported;
+    if (bank.w13 == nullptr || bank.hidden != 2560 || bank.intermediate % kGateUpRows != 0) return cudaErrorNotSupported;
     const int blocks = persistent_blocks(plan, 2);
     if (gate_out == nullptr) {
         gate_up_stream_kernel<2560, true><<<blocks, kThreads, 0, stream>>>(bank, route, xq, xs, hq, hs, nullptr,
@@ -457,7 +457,7 @@ cudaError_t launch_down(const p92b_plan* plan, const BankView& bank, const Route
                         const std::uint8_t* hq, const std::uint8_t* hs, std::uint16_t* mixed,
                         const std::int32_t* in_rows, const std::int32_t* out_rows, int first_active,
                         cudaStream_t stream) {
-    if (bank.intermediate != 1024 || bank.hidden % kDownRows != 0) return cudaErrorNotSupported;
+    if (bank.w2 == nullptr || bank.intermediate != 1024 || bank.hidden % kDownRows != 0) return cudaErrorNotSupported;
     const int blocks = persistent_blocks(plan, 2);
     down_stream_kernel<1024><<<blocks, kThreads, 0, stream>>>(bank, route, hq, hs, mixed, in_rows, out_rows,
                                                              first_active, plan->status);

@@ -10,8 +10,10 @@
 //
 // One block = 6 warps, persistent over work items (expert, token tile, 128-row tile):
 //   warp 0  producer: one elected lane issues the TMA copies of a K block
-//           (256 elements = 128 bytes per row): weight box(es), token box, and the
-//           three 2 KB scale-factor slabs, all completing on the stage's mbarrier;
+//           (256 elements = 128 bytes per row): the weight side is one untiled bulk copy of
+//           a contiguous chunk of the bank's tile stream (boxes already in the swizzled
+//           shared-memory image, scale slabs behind them), the token side a tiled box
+//           load plus its 2 KB scale slab; weights and tokens complete on separate mbarriers;
 //   warp 1  MMA issuer: owns TMEM; per K block copies the scale slabs SMEM->TMEM
 //           (tcgen05.cp) and issues 4 MMAs of K=64 per weight operand; commits the
 //           stage back to the producer and, after the last K block, the
@@ -48,6 +50,11 @@ struct Tc {
     static constexpr int kABytes = kTileM * kBlockKBytes;
     static constexpr int kBBytes = N * kBlockKBytes;
     static constexpr int kWeightBytes = kA * (kABytes + kSfSlab);          // per stage, independent of the tokens
+    // stage image: weight boxes | their scale slabs | token box | token scale slab; for the gate/up
+    // kernel the first kWeightBytes are exactly one chunk of the bank's tile stream
+    static constexpr int kOffSfA = kA * kABytes;
+    static constexpr int kOffB = kA * (kABytes + kSfSlab);
+    static constexpr int kOffSfB = kOffB + kBBytes;
     static constexpr int kTokenBytes = kBBytes + kSfSlab;
     static constexpr int kStageBytes = kWeightBytes + kTokenBytes;
     static constexpr int kStagesRaw = (196 * 1024) / kStageBytes;
@@ -111,8 +118,7 @@ __device__ __forceinline__ bool decode_item(const TcParams& p, int item, Item* i
 }
 
 template <int MODE, int N>
-__global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                                   const __grid_constant__ CUtensorMap map_b,
+__global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_constant__ CUtensorMap map_b,
                                                                    const TcParams p) {
     using C = Tc<MODE, N>;
     extern __shared__ std::uint8_t smem_raw[];
@@ -145,7 +151,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         }
         *abort_ptr = 0;
         fence_mbar_init();
-        prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
     }
     if (warp == 1) {
@@ -172,8 +177,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
             int stage = 0;
             std::uint32_t phase = 0;
             bool upstream_done = p.routing_is_upstream != 0;
-            const std::size_t a_sf_matrix = static_cast<std::size_t>(p.m_total / 128) * (p.k_bytes / 32) * 512;
-            const std::uint8_t* a_sf_base = MODE == 0 ? p.bank.sfs13 : p.bank.sfs2;
             for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
                 Item it;
                 if (!decode_item<N>(p, item, &it)) continue;
@@ -182,21 +185,26 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                     const std::uint32_t st = base + stage * C::kStageBytes;
                     // weights never depend on the upstream kernel: they start streaming at once
                     mbar_arrive_expect_tx(weight_bar(stage), C::kWeightBytes);
-#pragma unroll
-                    for (int a = 0; a < C::kA; ++a) {
-                        const int matrix = it.entry * C::kA + a;
-                        tma_load_2d(st + a * C::kABytes, &map_a, weight_bar(stage), kb * kBlockKBytes,
-                                    matrix * p.m_total + it.m_tile * kTileM);
-                        const std::uint8_t* sf = a_sf_base + static_cast<std::size_t>(matrix) * a_sf_matrix +
-                                                 (static_cast<std::size_t>(it.m_tile) * (p.k_bytes / 32) + kb * 4) * 512;
-                        bulk_load(st + C::kA * C::kABytes + C::kBBytes + a * kSfSlab, sf, kSfSlab, weight_bar(stage));
+                    if constexpr (MODE == 0) {
+                        // one chunk = gate box, up box and both scale slabs of this (row tile, K block)
+                        const std::uint8_t* chunk = p.bank.g13 +
+                            ((static_cast<std::size_t>(it.entry) * p.m_tiles + it.m_tile) * k_blocks + kb) * kChunkBytes;
+                        bulk_load(st, chunk, kChunkBytes, weight_bar(stage));
+                    } else {
+                        // chunks of the down stream hold two K blocks: take this block's box and slab
+                        const std::uint8_t* chunk = p.bank.g2 +
+                            ((static_cast<std::size_t>(it.entry) * p.m_tiles + it.m_tile) * (k_blocks / 2) + (kb >> 1)) *
+                                kChunkBytes;
+                        bulk_load(st, chunk + (kb & 1) * kChunkBox, kChunkBox, weight_bar(stage));
+                        bulk_load(st + C::kOffSfA, chunk + kChunkScaleOffset + (kb & 1) * kChunkScaleBytes, kSfSlab,
+                                  weight_bar(stage));
                     }
                     if (upstream_done) {
                         mbar_arrive_expect_tx(token_bar(stage), C::kTokenBytes);
-                        tma_load_2d(st + C::kA * C::kABytes, &map_b, token_bar(stage), kb * kBlockKBytes, it.pp0);
+                        tma_load_2d(st + C::kOffB, &map_b, token_bar(stage), kb * kBlockKBytes, it.pp0);
                         const std::uint8_t* bsf = p.b_sf +
                             (static_cast<std::size_t>(it.pp0 >> 7) * (p.k_bytes / 32) + kb * 4) * 512;
-                        bulk_load(st + C::kA * C::kABytes + C::kBBytes + C::kA * kSfSlab, bsf, kSfSlab, token_bar(stage));
+                        bulk_load(st + C::kOffSfB, bsf, kSfSlab, token_bar(stage));
                     }
                     const bool ring_full = stage == C::kStages - 1;
                     const bool last_load = kb == k_blocks - 1 && item + static_cast<int>(gridDim.x) >= total_items;
@@ -211,10 +219,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                             while (!decode_item<N>(p, it_item, &held)) it_item += gridDim.x;
                             const std::uint32_t hst = base + s * C::kStageBytes;
                             mbar_arrive_expect_tx(token_bar(s), C::kTokenBytes);
-                            tma_load_2d(hst + C::kA * C::kABytes, &map_b, token_bar(s), it_kb * kBlockKBytes, held.pp0);
+                            tma_load_2d(hst + C::kOffB, &map_b, token_bar(s), it_kb * kBlockKBytes, held.pp0);
                             const std::uint8_t* hsf = p.b_sf +
                                 (static_cast<std::size_t>(held.pp0 >> 7) * (p.k_bytes / 32) + it_kb * 4) * 512;
-                            bulk_load(hst + C::kA * C::kABytes + C::kBBytes + C::kA * kSfSlab, hsf, kSfSlab, token_bar(s));
+                            bulk_load(hst + C::kOffSfB, hsf, kSfSlab, token_bar(s));
                             if (++it_kb == k_blocks) { it_kb = 0; it_item += gridDim.x; }
                         }
                     }
@@ -248,16 +256,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                     }
                     tc_fence_after();
                     const std::uint32_t st = base + stage * C::kStageBytes;
-                    const std::uint32_t sf_smem = st + C::kA * C::kABytes + C::kBBytes;
                     const std::uint32_t sfc = sf_tmem + sf_buffer * C::kSfCols;
 #pragma unroll
                     for (int o = 0; o < C::kA + 1; ++o) {
+                        const std::uint32_t slab = o < C::kA ? st + C::kOffSfA + o * kSfSlab : st + C::kOffSfB;
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            tc_copy_sf(sfc + o * 16 + k * 4, desc_scale_atom(sf_smem + o * kSfSlab + k * 512));
-                        }
+                        for (int k = 0; k < 4; ++k) tc_copy_sf(sfc + o * 16 + k * 4, desc_scale_atom(slab + k * 512));
                     }
-                    const std::uint64_t b_desc = desc_k_major_sw128(st + C::kA * C::kABytes);
+                    const std::uint64_t b_desc = desc_k_major_sw128(st + C::kOffB);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
 #pragma unroll
@@ -419,8 +425,8 @@ EncodeTiled encode_tiled() {
 }
 
 template <int MODE, int N>
-cudaError_t launch_tc(const p92b_plan* plan, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p,
-                      cudaStream_t stream, bool pdl) {
+cudaError_t launch_tc(const p92b_plan* plan, const CUtensorMap& map_b, const TcParams& p, cudaStream_t stream,
+                      bool pdl) {
     using C = Tc<MODE, N>;
     auto kernel = expert_tc_kernel<MODE, N>;
     static bool configured = false;          // once per process: not a stream operation
@@ -429,7 +435,7 @@ cudaError_t launch_tc(const p92b_plan* plan, const CUtensorMap& map_a, const CUt
         if (st != cudaSuccess) return st;
         configured = true;
     }
-    return launch_kernel(kernel, dim3(plan->sm_count), dim3(kThreadsTc), C::kSmemBytes, stream, pdl, map_a, map_b, p);
+    return launch_kernel(kernel, dim3(plan->sm_count), dim3(kThreadsTc), C::kSmemBytes, stream, pdl, map_b, p);
 }
 
 }  // namespace
@@ -488,10 +494,10 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
         p.m_total = plan->intermediate;
         p.m_tiles = plan->intermediate / kTileM;
         switch (which) {
-            case 0: return launch_tc<0, 16>(plan, bank->map_w13, plan->map_x[0], p, stream, pdl);
-            case 1: return launch_tc<0, 32>(plan, bank->map_w13, plan->map_x[1], p, stream, pdl);
-            case 2: return launch_tc<0, 64>(plan, bank->map_w13, plan->map_x[2], p, stream, pdl);
-            default: return launch_tc<0, 128>(plan, bank->map_w13, plan->map_x[3], p, stream, pdl);
+            case 0: return launch_tc<0, 16>(plan, plan->map_x[0], p, stream, pdl);
+            case 1: return launch_tc<0, 32>(plan, plan->map_x[1], p, stream, pdl);
+            case 2: return launch_tc<0, 64>(plan, plan->map_x[2], p, stream, pdl);
+            default: return launch_tc<0, 128>(plan, plan->map_x[3], p, stream, pdl);
         }
     }
     p.b_sf = plan->hs_sw;
@@ -500,10 +506,10 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
     p.m_total = plan->hidden;
     p.m_tiles = plan->hidden / kTileM;
     switch (which) {
-        case 0: return launch_tc<1, 16>(plan, bank->map_w2, plan->map_h[0], p, stream, pdl);
-        case 1: return launch_tc<1, 32>(plan, bank->map_w2, plan->map_h[1], p, stream, pdl);
-        case 2: return launch_tc<1, 64>(plan, bank->map_w2, plan->map_h[2], p, stream, pdl);
-        default: return launch_tc<1, 128>(plan, bank->map_w2, plan->map_h[3], p, stream, pdl);
+        case 0: return launch_tc<1, 16>(plan, plan->map_h[0], p, stream, pdl);
+        case 1: return launch_tc<1, 32>(plan, plan->map_h[1], p, stream, pdl);
+        case 2: return launch_tc<1, 64>(plan, plan->map_h[2], p, stream, pdl);
+        default: return launch_tc<1, 128>(plan, plan->map_h[3], p, stream, pdl);
     }
 }
 

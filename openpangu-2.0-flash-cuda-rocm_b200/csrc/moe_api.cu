@@ -29,19 +29,21 @@ struct Carver {
 };
 
 struct BankLayout {
-    std::size_t w13, w2, sf13, sf2, sfs13, sfs2, alpha, total;
+    std::size_t g13, g2, w13, w2, sf13, sf2, alpha, total;
 };
 
-BankLayout bank_layout(int entries, int hidden, int inter) {
+BankLayout bank_layout(int entries, int hidden, int inter, bool stream_copy) {
     BankLayout l {};
     Carver c;
     const std::size_t e = static_cast<std::size_t>(entries);
-    l.w13 = c.used; c.take<std::uint8_t>(e * 2 * inter * (hidden / 2));
-    l.w2 = c.used; c.take<std::uint8_t>(e * hidden * (inter / 2));
-    l.sf13 = c.used; c.take<std::uint8_t>(e * 2 * inter * (hidden / 16));
-    l.sf2 = c.used; c.take<std::uint8_t>(e * hidden * (inter / 16));
-    l.sfs13 = c.used; c.take<std::uint8_t>(e * 2 * p92b_nvfp4_swizzled_scale_bytes(inter, hidden / 16));
-    l.sfs2 = c.used; c.take<std::uint8_t>(e * p92b_nvfp4_swizzled_scale_bytes(hidden, inter / 16));
+    l.g13 = c.used; c.take<std::uint8_t>(e * (inter / 128) * (hidden / 256) * kChunkBytes);
+    l.g2 = c.used; c.take<std::uint8_t>(e * (hidden / 128) * (inter / 512) * kChunkBytes);
+    if (stream_copy) {
+        l.w13 = c.used; c.take<std::uint8_t>(e * 2 * inter * (hidden / 2));
+        l.w2 = c.used; c.take<std::uint8_t>(e * hidden * (inter / 2));
+        l.sf13 = c.used; c.take<std::uint8_t>(e * 2 * inter * (hidden / 16));
+        l.sf2 = c.used; c.take<std::uint8_t>(e * hidden * (inter / 16));
+    }
     l.alpha = c.used; c.take<float>(e * 3);
     l.total = c.used;
     return l;
@@ -68,12 +70,12 @@ extern "C" {
 const char* p92b_version(void) { return "p92b-moe 0.1 (sm_100a)"; }
 
 int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries, int first_expert,
-                     int local_experts, int hidden, int intermediate, void* stream_) {
+                     int local_experts, int hidden, int intermediate, int flags, void* stream_) {
     if (out == nullptr) return cudaErrorInvalidValue;
     *out = nullptr;
     if (host_entries == nullptr || first_expert < 0 || local_experts <= 0 ||
-        first_expert + local_experts > kExperts || hidden <= 0 || intermediate <= 0 || hidden % 128 != 0 ||
-        intermediate % 128 != 0) {
+        first_expert + local_experts > kExperts || hidden <= 0 || intermediate <= 0 || hidden % 256 != 0 ||
+        intermediate % 512 != 0 || (flags & ~P92B_BANK_STREAM_COPY) != 0) {
         return cudaErrorInvalidValue;
     }
     const int entries = local_experts + 1;
@@ -83,10 +85,11 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
             return cudaErrorInvalidValue;
         }
     }
+    const bool stream_copy = (flags & P92B_BANK_STREAM_COPY) != 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     p92b_bank* bank = new (std::nothrow) p92b_bank();
     if (bank == nullptr) return cudaErrorMemoryAllocation;
-    const BankLayout l = bank_layout(entries, hidden, intermediate);
+    const BankLayout l = bank_layout(entries, hidden, intermediate, stream_copy);
     cudaError_t st = cudaMalloc(&bank->storage, l.total);
     if (st != cudaSuccess) {
         delete bank;
@@ -94,20 +97,20 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
     }
     bank->bytes = l.total;
     std::uint8_t* base = static_cast<std::uint8_t*>(bank->storage);
-    std::uint8_t* w13 = base + l.w13;
-    std::uint8_t* w2 = base + l.w2;
-    std::uint8_t* sf13 = base + l.sf13;
-    std::uint8_t* sf2 = base + l.sf2;
-    std::uint8_t* sfs13 = base + l.sfs13;
-    std::uint8_t* sfs2 = base + l.sfs2;
+    std::uint8_t* g13 = base + l.g13;
+    std::uint8_t* g2 = base + l.g2;
+    std::uint8_t* w13 = stream_copy ? base + l.w13 : nullptr;
+    std::uint8_t* w2 = stream_copy ? base + l.w2 : nullptr;
+    std::uint8_t* sf13 = stream_copy ? base + l.sf13 : nullptr;
+    std::uint8_t* sf2 = stream_copy ? base + l.sf2 : nullptr;
     float* alpha = reinterpret_cast<float*>(base + l.alpha);
 
     const std::size_t gu_bytes = static_cast<std::size_t>(intermediate) * (hidden / 2);
     const std::size_t dn_bytes = static_cast<std::size_t>(hidden) * (intermediate / 2);
     const std::size_t gu_sf = static_cast<std::size_t>(intermediate) * (hidden / 16);
     const std::size_t dn_sf = static_cast<std::size_t>(hidden) * (intermediate / 16);
-    const std::size_t gu_sfs = p92b_nvfp4_swizzled_scale_bytes(intermediate, hidden / 16);
-    const std::size_t dn_sfs = p92b_nvfp4_swizzled_scale_bytes(hidden, intermediate / 16);
+    const std::size_t g13_entry = static_cast<std::size_t>(intermediate / 128) * (hidden / 256) * kChunkBytes;
+    const std::size_t g2_entry = static_cast<std::size_t>(hidden / 128) * (intermediate / 512) * kChunkBytes;
 #define BANK_TRY(call)            \
     do {                          \
         st = (call);              \
@@ -121,43 +124,42 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
         for (int kind = 0; kind < 3; ++kind) {
             const p92b_expert_projection& src = host_entries[e * 3 + kind];
             if (kind < 2) {
-                BANK_TRY(cudaMemcpyAsync(w13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_bytes, src.weight, gu_bytes,
-                                         cudaMemcpyDeviceToDevice, stream));
-                BANK_TRY(cudaMemcpyAsync(sfs13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_sfs, src.scales_swizzled,
-                                         gu_sfs, cudaMemcpyDeviceToDevice, stream));
-                BANK_TRY(launch_unswizzle(src.scales_swizzled, sf13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_sf,
-                                          intermediate, hidden / 16, stream));
+                BANK_TRY(launch_retile(src.weight, src.scales_swizzled, g13 + static_cast<std::size_t>(e) * g13_entry,
+                                       intermediate, hidden / 2, 1, kind, stream));
+                if (stream_copy) {
+                    BANK_TRY(cudaMemcpyAsync(w13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_bytes, src.weight,
+                                             gu_bytes, cudaMemcpyDeviceToDevice, stream));
+                    BANK_TRY(launch_unswizzle(src.scales_swizzled,
+                                              sf13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_sf, intermediate,
+                                              hidden / 16, stream));
+                }
             } else {
-                BANK_TRY(cudaMemcpyAsync(w2 + static_cast<std::size_t>(e) * dn_bytes, src.weight, dn_bytes,
-                                         cudaMemcpyDeviceToDevice, stream));
-                BANK_TRY(cudaMemcpyAsync(sfs2 + static_cast<std::size_t>(e) * dn_sfs, src.scales_swizzled, dn_sfs,
-                                         cudaMemcpyDeviceToDevice, stream));
-                BANK_TRY(launch_unswizzle(src.scales_swizzled, sf2 + static_cast<std::size_t>(e) * dn_sf, hidden,
-                                          intermediate / 16, stream));
+                BANK_TRY(launch_retile(src.weight, src.scales_swizzled, g2 + static_cast<std::size_t>(e) * g2_entry,
+                                       hidden, intermediate / 2, 2, 0, stream));
+                if (stream_copy) {
+                    BANK_TRY(cudaMemcpyAsync(w2 + static_cast<std::size_t>(e) * dn_bytes, src.weight, dn_bytes,
+                                             cudaMemcpyDeviceToDevice, stream));
+                    BANK_TRY(launch_unswizzle(src.scales_swizzled, sf2 + static_cast<std::size_t>(e) * dn_sf, hidden,
+                                              intermediate / 16, stream));
+                }
             }
             BANK_TRY(cudaMemcpyAsync(alpha + e * 3 + kind, src.alpha, sizeof(float), cudaMemcpyDeviceToDevice, stream));
         }
     }
     BANK_TRY(cudaStreamSynchronize(stream));
 #undef BANK_TRY
+    bank->view.g13 = g13;
+    bank->view.g2 = g2;
     bank->view.w13 = w13;
     bank->view.w2 = w2;
     bank->view.sf13 = sf13;
     bank->view.sf2 = sf2;
-    bank->view.sfs13 = sfs13;
-    bank->view.sfs2 = sfs2;
     bank->view.alpha = alpha;
     bank->view.first_expert = first_expert;
     bank->view.local_experts = local_experts;
     bank->view.hidden = hidden;
     bank->view.intermediate = intermediate;
-    // TMA maps for the tensor-core kernels; without the driver entry point the bank still serves the
-    // weight-streaming kernels and the tensor-core path reports cudaErrorNotSupported
-    bank->tc_ready =
-        make_operand_map(&bank->map_w13, w13, static_cast<std::size_t>(entries) * 2 * intermediate, hidden / 2, 128) ==
-            cudaSuccess &&
-        make_operand_map(&bank->map_w2, w2, static_cast<std::size_t>(entries) * hidden, intermediate / 2, 128) ==
-            cudaSuccess;
+    bank->tc_ready = true;
     *out = bank;
     return cudaSuccess;
 }
@@ -198,6 +200,7 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->pp_rows = (rows * (kTop + 1) + active * (align - 1) + 127) / 128 * 128;
     }
     if (const char* env = std::getenv("P92B_PATH")) plan->path = std::atoi(env);
+    plan->trace_on = std::getenv("P92B_TRACE") != nullptr;
     for (int pass = 0; pass < 2; ++pass) {
         Carver c;
         c.base = static_cast<std::uint8_t*>(plan->storage);
@@ -225,6 +228,11 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->hq_pp = c.take<std::uint8_t>(plan->pp_rows * (intermediate / 2));
         plan->hs_sw = c.take<std::uint8_t>(plan->pp_rows * (intermediate / 16));
         plan->mixed_pp = c.take<std::uint16_t>(plan->pp_rows * hidden);
+        plan->xq_tok = c.take<std::uint8_t>(static_cast<std::size_t>(16) * (hidden / 2));
+        plan->xs_tok = c.take<std::uint8_t>(static_cast<std::size_t>(hidden / 64) * 512);
+        plan->mega_sync = c.take<unsigned>(4);
+        plan->gu_done = c.take<std::int32_t>(kExperts + 4);
+        plan->mega_trace = c.take<unsigned long long>(static_cast<std::size_t>(plan->sm_count) * 64);
         plan->stage_in = c.take<std::uint16_t>(rows * hidden);
         plan->stage_out = c.take<std::uint16_t>(rows * hidden);
         plan->status = c.take<std::int32_t>(1);
@@ -251,6 +259,7 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
             ok = ok && make_operand_map(&plan->map_h[i], plan->hq_pp, plan->pp_rows, intermediate / 2, kBoxRows[i]) ==
                            cudaSuccess;
         }
+        ok = ok && make_operand_map(&plan->map_x_tok, plan->xq_tok, 16, hidden / 2, 16) == cudaSuccess;
         plan->tc_ready = ok;
     }
     *out = plan;
@@ -258,8 +267,8 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
 }
 
 int p92b_plan_set_path(p92b_plan* plan, int path) {
-    if (plan == nullptr || path < 0 || path > 2) return cudaErrorInvalidValue;
-    if (path == 2 && !plan->tc_ready) return cudaErrorNotSupported;
+    if (plan == nullptr || path < 0 || path > 3) return cudaErrorInvalidValue;
+    if (path >= 2 && !plan->tc_ready) return cudaErrorNotSupported;
     plan->path = path;
     return cudaSuccess;
 }
@@ -312,6 +321,8 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* v) {
     v->mixed = plan->last_path == 2 ? plan->mixed_pp : plan->mixed;
     v->mixed_index = plan->pp_of_flat;
     v->status = plan->status;
+    v->trace = plan->mega_trace;
+    v->trace_blocks = plan->sm_count;
     return cudaSuccess;
 }
 
@@ -373,9 +384,31 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
     // programmatic dependent launch: each kernel's prologue (and, for the down kernel, its weight
     // prefetch) overlaps the tail of the one before; P92B_NO_PDL=1 switches it off for A/B timing
     static const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
-    const bool tc = plan->path == 2 || (plan->path == 0 && plan->tc_ready && bank->tc_ready);
+    const bool tc = plan->path >= 2 || (plan->path == 0 && plan->tc_ready && bank->tc_ready);
     if (tc && (!plan->tc_ready || !bank->tc_ready)) return cudaErrorNotSupported;
+    if (plan->path == 3 && rows > decode_mega_max_rows()) return cudaErrorInvalidValue;
     plan->last_path = tc ? 2 : 1;
+    if (tc && plan->path != 2 && rows <= decode_mega_max_rows()) {
+        // the whole block as one persistent kernel; in timing mode its time is reported as stage 0
+        cudaError_t st = mark();
+        if (st != cudaSuccess) return st;
+        st = launch_decode_mega(plan, bank, input, router_weight, correction_bias, output, rows, routed_scale, stream,
+                                pdl);
+        if (st != cudaSuccess) return st;
+        for (int i = 0; i < P92B_STAGES; ++i) {
+            if ((st = mark()) != cudaSuccess) return st;
+        }
+        if (plan->timing) {
+            if ((st = cudaStreamSynchronize(stream)) != cudaSuccess) return st;
+            for (int i = 0; i < P92B_STAGES; ++i) {
+                float ms = 0.0F;
+                if ((st = cudaEventElapsedTime(&ms, plan->stage_events[i], plan->stage_events[i + 1])) != cudaSuccess) return st;
+                plan->stage_ms[i] += ms;
+            }
+            plan->timed_calls += 1;
+        }
+        return cudaSuccess;
+    }
     const int pad_align = tc ? tc_pad_align(rows) : 1;
     const int tile_rows = tc ? tc_tile_rows(rows) : (1 << 30);
     cudaError_t st = mark();

@@ -140,14 +140,30 @@ __device__ __forceinline__ void warp_top8(const float* __restrict__ lg, const fl
 }
 
 // Layout of one layer's expert weights inside the library (device memory).
-// Entry e = local expert index, local_experts = the shared expert.
+// Entry e = local expert index, entry local_experts = the shared expert.
+//
+// The tensor-core kernels read the weights as a pure stream: for every 128-row tile and K block the
+// bytes of one pipeline stage are contiguous in memory, already in the shared-memory image the MMA
+// descriptors expect, so a stage is ONE bulk copy and an expert's tiles are one sequential read.
+//   chunk (36,864 B) = box0 (16 KB) | box1 (16 KB) | scales0 (2 KB) | scales1 (2 KB)
+//   box    = 128 rows x 128 bytes (256 E2M1 values of one K block), 16-byte pieces XOR-swizzled by
+//            (row & 7): the 128-byte swizzle a TMA tile load would have produced
+//   scales = the matching four 512-byte tiles of the 128x4-tiled E4M3 layout
+//   g13: [entry][row tile of I][K block of H]    box0/1 = gate/up rows of the same K block
+//   g2:  [entry][row tile of H][pair of K blocks] box0/1 = K blocks 2s, 2s+1 of the down matrix
+constexpr int kChunkBytes = 36864;
+constexpr int kChunkBox = 16384;
+constexpr int kChunkScaleOffset = 32768;
+constexpr int kChunkScaleBytes = 2048;
+
 struct BankView {
+    const std::uint8_t* g13;
+    const std::uint8_t* g2;
+    // optional row-major copy for the SIMT kernels and the un-fused stage entry points (null if absent)
     const std::uint8_t* w13;    // [entries][2][I][H/2]   gate rows then up rows
     const std::uint8_t* w2;     // [entries][H][I/2]
     const std::uint8_t* sf13;   // [entries][2][I][H/16]  linear E4M3
     const std::uint8_t* sf2;    // [entries][H][I/16]     linear E4M3
-    const std::uint8_t* sfs13;  // [entries][2][swizzled I x H/16]
-    const std::uint8_t* sfs2;   // [entries][swizzled H x I/16]
     const float* alpha;         // [entries][3]
     int first_expert;
     int local_experts;
@@ -172,10 +188,7 @@ struct p92b_bank {
     p92b::BankView view {};
     void* storage = nullptr;
     std::size_t bytes = 0;
-    // tensor-core path: TMA maps over the packed weights (rows of K/2 bytes)
-    bool tc_ready = false;
-    CUtensorMap map_w13 {};
-    CUtensorMap map_w2 {};
+    bool tc_ready = true;       // the tiled stream is always built
 };
 
 struct p92b_plan {
@@ -213,7 +226,7 @@ struct p92b_plan {
     // tensor-core path: operands in the padded position space (every expert's rows start on a
     // multiple of 32 or 128), scales in the 128x4-tiled layout
     int last_path = 1;                    // path the last forward took
-    int path = 0;                         // 0 auto, 1 weight-streaming SIMT kernels, 2 tcgen05 kernels
+    int path = 0;                         // 0 auto, 1 SIMT kernels, 2 tcgen05 kernels, 3 fused tcgen05 decode kernel
     bool tc_ready = false;
     std::size_t pp_rows = 0;              // rows of the padded buffers
     std::uint8_t* xq_pp = nullptr;        // [pp_rows][H/2]
@@ -223,6 +236,15 @@ struct p92b_plan {
     std::uint16_t* mixed_pp = nullptr;    // [pp_rows][H]
     CUtensorMap map_x[4] = {};            // token boxes of 16/32/64/128 rows over xq_pp
     CUtensorMap map_h[4] = {};            // same over hq_pp
+    // fused decode kernel (rows <= 8)
+    std::uint8_t* xq_tok = nullptr;       // [16][H/2] token-order NVFP4 rows
+    std::uint8_t* xs_tok = nullptr;       // [H/64][512] their scales, one 128-row tile per 4 scale columns
+    unsigned* mega_sync = nullptr;        // [2] arrival counters (monotonic across launches)
+    std::int32_t* gu_done = nullptr;      // [257]
+    unsigned mega_epoch = 0;
+    unsigned long long* mega_trace = nullptr;   // [sm_count][64] timer stamps of the last fused launch (P92B_TRACE=1)
+    bool trace_on = false;
+    CUtensorMap map_x_tok {};
     // optional stage timing (host side)
     bool timing = false;
     cudaEvent_t stage_events[P92B_STAGES + 1] = {};
@@ -277,6 +299,10 @@ cudaError_t launch_down(const p92b_plan* plan, const BankView& bank, const Route
                         cudaStream_t stream);
 cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,
                              cudaStream_t stream);
+// Writes one matrix (row-major packed weights + 128x4-tiled scales) into the chunk stream.
+// blocks_per_chunk 1: gate (slot 0) or up (slot 1) of a K block; 2: K blocks 2s, 2s+1 of a down matrix.
+cudaError_t launch_retile(const std::uint8_t* weight, const std::uint8_t* scales_swizzled, std::uint8_t* chunks,
+                          int rows, int k_bytes, int blocks_per_chunk, int slot, cudaStream_t stream);
 cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* mixed_index,
                                   const float* route_weights, std::uint16_t* output, int rows,
                                   int hidden, cudaStream_t stream, bool pdl = false);
@@ -289,5 +315,10 @@ cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x
                                    bool pdl = false);
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
                               cudaStream_t stream, bool pdl = false);
+// fused decode kernel (decode_mega.cu)
+int decode_mega_max_rows();
+cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std::uint16_t* x,
+                               const std::uint16_t* router_w, const float* bias, std::uint16_t* out, int rows,
+                               float routed_scale, cudaStream_t stream, bool pdl);
 
 }  // namespace p92b

@@ -263,15 +263,18 @@ def _oracle_forward(orc, pkg, host, x_bits, **kw):
                            pkg.HIDDEN, pkg.INTERMEDIATE, **kw)
 
 
-PATHS = [pytest.param(1, id="stream"), pytest.param(2, id="tcgen05")]
+PATHS = [pytest.param(1, id="stream"), pytest.param(2, id="tcgen05"), pytest.param(3, id="fused-decode")]
+FUSED_MAX_ROWS = 8      # path 3 is the single persistent decode kernel, up to 8 tokens
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("rows", [1, 2, 4, 5, 17])
+@pytest.mark.parametrize("rows", [1, 2, 4, 5, 8, 17])
 def test_moe_forward_against_cpu_oracle(cuda, pkg, orc, layer0, layer0_host, rows, path):
     torch = cuda
     from p92moe_b200 import synth
 
+    if path == 3 and rows > FUSED_MAX_ROWS:
+        pytest.skip("fused decode kernel serves up to 8 tokens")
     x = synth.make_activations(42, rows, rows)
     out = torch.full_like(x, float("nan"))
     plan = pkg.MoePlan(max_rows=max(rows, 4))
@@ -307,13 +310,15 @@ def test_moe_forward_against_cpu_oracle(cuda, pkg, orc, layer0, layer0_host, row
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("rows", [1, 4, 33, 70, 200])
+@pytest.mark.parametrize("rows", [1, 3, 4, 8, 33, 70, 200])
 def test_moe_forward_against_reference_kernels(cuda, pkg, orc, layer0, rows, path):
     torch = cuda
     if not orc.have_ref():
         pytest.skip("oracle/_ref was not built")
     from p92moe_b200 import synth
 
+    if path == 3 and rows > FUSED_MAX_ROWS:
+        pytest.skip("fused decode kernel serves up to 8 tokens")
     x = synth.make_activations(43, rows, rows)
     out = torch.empty_like(x)
     plan = pkg.MoePlan(max_rows=rows)
@@ -463,3 +468,36 @@ def test_tensor_core_path_equals_streaming_path(cuda, pkg, layer0, rows):
     rel, max_abs = _rel(b, a)
     assert rel <= REL_L2 and max_abs <= MAX_ABS, (rel, max_abs)
     plan.close()
+
+
+def test_fused_decode_kernel_many_calls_and_changing_row_counts(cuda, pkg, layer0):
+    """The persistent decode kernel keeps device-wide counters across launches: alternate row counts
+    and inputs for many calls and compare every result with the multi-kernel tensor-core path."""
+    torch = cuda
+    from p92moe_b200 import synth
+
+    fused = pkg.MoePlan(max_rows=8)
+    fused.set_path(3)
+    split = pkg.MoePlan(max_rows=8)
+    split.set_path(2)
+    a = pkg.MoeBlock(layer0.bank, layer0.router_weight, layer0.bias, fused)
+    b = pkg.MoeBlock(layer0.bank, layer0.router_weight, layer0.bias, split)
+    for call in range(40):
+        rows = [4, 1, 8, 2, 3, 7, 5, 6][call % 8]
+        x = synth.make_activations(300 + call, 0, rows)
+        oa = torch.full_like(x, float("nan"))
+        ob = torch.full_like(x, float("nan"))
+        a.run_moe_rows(x, oa, rows)
+        b.run_moe_rows(x, ob, rows)
+        torch.cuda.synchronize()
+        va = fused.views(rows)
+        vb = split.views(rows)
+        assert int(va["status"][0]) == 0
+        assert torch.equal(va["logits"], vb["logits"])
+        assert torch.equal(va["expert_ids"], vb["expert_ids"])
+        assert torch.equal(va["expert_weights"], vb["expert_weights"])
+        assert torch.equal(va["position"], vb["position"]) and torch.equal(va["counts"], vb["counts"])
+        rel, max_abs = _rel(oa.float().cpu().numpy(), ob.float().cpu().numpy())
+        assert rel <= REL_L2 and max_abs <= MAX_ABS, (call, rows, rel, max_abs)
+    fused.close()
+    split.close()
