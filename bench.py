@@ -302,7 +302,9 @@ def main() -> None:
         # the whole block is one kernel (moe_decode_kernel): its algorithmic bytes are the layer's
         # (D+1 experts x 3 matrices packed + scales, the router weight, the token rows in and out);
         # its device time is the event pair recorded around it on the launch stream (stage 0)
-        kernel, k_bytes, k_us = "moe_decode_kernel", layer_bytes, stage_us["router_logits"]
+        # duration: the timed region launches exactly one kernel per layer back to back, so the
+        # average launch duration is the CUDA-event step time over the layer count
+        kernel, k_bytes, k_us = "moe_decode_kernel", layer_bytes, ms_per_step * 1e3 / n_layers
     else:
         # dominant kernel of the multi-kernel path: gate/up + SwiGLU + re-quantise
         kernel = "expert_tc_kernel<0,128>"

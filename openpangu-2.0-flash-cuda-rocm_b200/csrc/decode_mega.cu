@@ -87,15 +87,22 @@ struct MegaParams {
 struct Routing {                   // shared-memory copy, identical in every block
     std::int32_t ids[kMegaMaxRows * kTop];
     float weights[kMegaMaxRows * kTop];
-    std::int32_t counts[kExperts];
-    std::int32_t offsets[kExperts + 1];
-    std::int32_t pp_off[kExperts + 1];
-    std::int32_t slot_of[kExperts];            // active slot of an expert (1-based; 0 is the shared expert), -1 if unused
-    std::int32_t active[kMaxActive];
+    std::int32_t rank[kMegaMaxRows * kTop];          // earlier assignments with the same expert
+    std::int32_t less[kMegaMaxRows * kTop];          // assignments with a smaller expert id
+    std::int32_t slot_a[kMegaMaxRows * kTop];        // active slot of the assignment's expert (1-based)
+    std::int32_t active[kMaxActive];                 // expert of an active slot; slot 0 is the shared expert
+    std::int32_t slot_rows[kMaxActive];              // rows of an active slot
     std::int32_t pp_tok[kMaxActive][kMegaMaxRows];   // padded position of (active slot, token), -1 if not routed
     std::int32_t n_active;
     float logits[kMegaMaxRows * kExperts];
+    float bias[kExperts];
 };
+
+// Every active slot owns one 128-row slab of the padded position space, in slot order; the shared
+// expert (slot 0) takes the slab after the last routed one.
+__device__ __forceinline__ int slab_of_slot(int slot, int n_active) {
+    return (slot == 0 ? n_active - 1 : slot - 1) * kTile;
+}
 
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     unsigned v;
@@ -229,8 +236,26 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
         tmem_alloc(smem_u32(&tmem_slot_word), kTmemCols);
         tmem_relinquish();
     }
+    // the router rows and the bias do not depend on the kernel upstream: fetch them before waiting for it
+    const int my_experts = block + grid < kExperts ? 2 : (block < kExperts ? 1 : 0);
+    std::uint16_t* w_rows = reinterpret_cast<std::uint16_t*>(smem_raw + (base - smem_u32(smem_raw)));
+    std::uint16_t* x_rows = w_rows + 2 * hidden;
+    const int vec_per_row = hidden / 8;
+    for (int i = threadIdx.x; i < my_experts * vec_per_row; i += kMegaThreads) {
+        const int r = i / vec_per_row;
+        const int c = i - r * vec_per_row;
+        reinterpret_cast<uint4*>(w_rows + r * hidden)[c] =
+            __ldg(reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
+    }
+    for (int e = threadIdx.x; e < kExperts; e += kMegaThreads) rt.bias[e] = __ldg(p.bias + e);
     pdl_wait();                       // the token rows come from the kernel before this one
     pdl_launch_dependents();
+    for (int i = threadIdx.x; i < rows * vec_per_row; i += kMegaThreads) {
+        const int r = i / vec_per_row;
+        const int c = i - r * vec_per_row;
+        reinterpret_cast<uint4*>(x_rows + r * hidden)[c] =
+            __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r) * hidden) + c);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -246,24 +271,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
 
     // ------------------------------------------------------------------ P0
     {
-        // Stage this block's router rows and all token rows in shared memory with one round of
-        // 16-byte loads (the ring is idle until the pipeline starts), then work from there.
-        const int my_experts = block + grid < kExperts ? 2 : (block < kExperts ? 1 : 0);
-        std::uint16_t* w_rows = reinterpret_cast<std::uint16_t*>(smem_raw + (base - smem_u32(smem_raw)));
-        std::uint16_t* x_rows = w_rows + 2 * hidden;
-        const int vec_per_row = hidden / 8;
-        for (int i = threadIdx.x; i < (my_experts + rows) * vec_per_row; i += kMegaThreads) {
-            const int r = i / vec_per_row;
-            const int c = i - r * vec_per_row;
-            if (r < my_experts) {
-                reinterpret_cast<uint4*>(w_rows + r * hidden)[c] =
-                    __ldg(reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
-            } else {
-                reinterpret_cast<uint4*>(x_rows + (r - my_experts) * hidden)[c] =
-                    __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r - my_experts) * hidden) + c);
-            }
-        }
-        __syncthreads();
         if (rows == 1) {
             // T = 1 order: 256 partial chains (thread t: columns t, t+256, ...), a shuffle-down tree
             // per 32 of them, then a tree over the eight results (cuda/nvfp4_ops.cu:38-51,161-176)
@@ -335,86 +342,49 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     if (!abort_word) {
         // logits were written by other blocks of this launch: read them past L1
         for (int i = threadIdx.x; i < rows * kExperts; i += kMegaThreads) rt.logits[i] = __ldcg(p.logits + i);
-        __syncthreads();
-        for (int t = warp; t < rows; t += kMegaThreads / 32) {
-            warp_top8(rt.logits + t * kExperts, p.bias, rt.ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
-        }
         for (int i = threadIdx.x; i < kMaxActive * kMegaMaxRows; i += kMegaThreads) (&rt.pp_tok[0][0])[i] = -1;
         __syncthreads();
-        for (int e = threadIdx.x; e < kExperts; e += kMegaThreads) {
-            int count = 0;
-            for (int j = 0; j < assignments; ++j) count += rt.ids[j] == e;
-            rt.counts[e] = count;
+        for (int t = warp; t < rows; t += kMegaThreads / 32) {
+            warp_top8(rt.logits + t * kExperts, rt.bias, rt.ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
         }
         __syncthreads();
-        if (warp == 0) {
-            // lane l owns experts 8l .. 8l+7: ascending id order is kept by the lane order
-            int c_sum = 0, a_sum = 0;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                c_sum += rt.counts[lane * 8 + k];
-                a_sum += rt.counts[lane * 8 + k] > 0;
+        // The ranking law of cuda/nvfp4_grouped.cu:117-132 evaluated directly on at most 64 assignments:
+        // position = #(smaller expert id) + #(same id, smaller flat index).
+        int my_rank = 0, my_less = 0, my_same = 0;
+        if (threadIdx.x < assignments) {
+            const int e = rt.ids[threadIdx.x];
+            for (int j = 0; j < assignments; ++j) {
+                const int other = rt.ids[j];
+                my_less += other < e;
+                my_same += other == e;
+                my_rank += other == e && j < static_cast<int>(threadIdx.x);
             }
-            int c_incl = c_sum, a_incl = a_sum;
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int c_o = __shfl_up_sync(0xffffffffU, c_incl, off);
-                const int a_o = __shfl_up_sync(0xffffffffU, a_incl, off);
-                if (lane >= off) { c_incl += c_o; a_incl += a_o; }
-            }
-            int c_run = c_incl - c_sum, a_run = a_incl - a_sum;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int e = lane * 8 + k;
-                const int count = rt.counts[e];
-                rt.offsets[e] = c_run;
-                rt.pp_off[e] = a_run * kTile;              // every active expert owns one 128-row slab
-                if (count > 0) {
-                    rt.slot_of[e] = 1 + a_run;
-                    rt.active[1 + a_run] = e;
-                    ++a_run;
-                } else {
-                    rt.slot_of[e] = -1;
-                }
-                c_run += count;
-            }
-            if (lane == 31) {
-                rt.offsets[kExperts] = c_run;
-                rt.pp_off[kExperts] = a_run * kTile;       // the shared expert's slab comes last
-                rt.active[0] = kExperts;
-                rt.n_active = a_run + 1;
-            }
+            rt.rank[threadIdx.x] = my_rank;
+            rt.less[threadIdx.x] = my_less;
         }
         __syncthreads();
         if (threadIdx.x < assignments) {
             const int i = threadIdx.x;
             const int e = rt.ids[i];
-            int rank = 0;
-            for (int j = 0; j < i; ++j) rank += rt.ids[j] == e;
-            const int pos = rt.offsets[e] + rank;
-            const int pp = rt.pp_off[e] + rank;
-            rt.pp_tok[rt.slot_of[e]][i / kTop] = pp;
-            if (block == 0) {
-                p.ids[i] = e;
-                p.route_weights[i] = rt.weights[i];
-                p.order[pos] = i;
-                p.position[i] = pos;
-                p.pp_of_flat[i] = pp;
+            int distinct_less = 0;
+            for (int j = 0; j < assignments; ++j) distinct_less += rt.rank[j] == 0 && rt.ids[j] < e;
+            const int slot = 1 + distinct_less;
+            rt.slot_a[i] = slot;
+            rt.pp_tok[slot][i / kTop] = (slot - 1) * kTile + my_rank;
+            if (my_rank == 0) {
+                rt.active[slot] = e;
+                rt.slot_rows[slot] = my_same;
             }
-        } else if (threadIdx.x < assignments + rows) {
-            const int t = threadIdx.x - assignments;
-            rt.pp_tok[0][t] = rt.pp_off[kExperts] + t;
-            if (block == 0) p.pp_of_flat[assignments + t] = rt.pp_off[kExperts] + t;
-        }
-        if (block == 0) {
-            for (int e = threadIdx.x; e <= kExperts; e += kMegaThreads) {
-                if (e < kExperts) p.counts[e] = rt.counts[e];
-                p.offsets[e] = rt.offsets[e];
-            }
+        } else if (threadIdx.x == assignments) {
+            int distinct = 0;
+            for (int j = 0; j < assignments; ++j) distinct += rt.rank[j] == 0;
+            rt.n_active = distinct + 1;
+            rt.active[0] = kExperts;
+            rt.slot_rows[0] = rows;
+            for (int t = 0; t < rows; ++t) rt.pp_tok[0][t] = distinct * kTile + t;
         }
         __syncthreads();
     }
-
     if (threadIdx.x == 0) stamp(3);
     // ------------------------------------------------------------ P2 + P3
     const int gu_tiles = inter / kTile;          // 8
@@ -460,7 +430,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                             fence_proxy_async_all();
                             tokens_ready = true;
                         }
-                        const int pp0 = rt.pp_off[expert];
+                        const int pp0 = slab_of_slot(slot, rt.n_active);
                         mbar_arrive_expect_tx(token_bar(stage), 4 * kSlab);
                         tma_load_2d(st + kOffB0, &map_h, token_bar(stage), (2 * s) * kKB, pp0);
                         tma_load_2d(st + kOffB1, &map_h, token_bar(stage), (2 * s + 1) * kKB, pp0);
@@ -544,6 +514,29 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
             stamp(8);
         }
     } else if (!abort_word) {
+        if (block == 0) {
+            // The routing products go to global memory for the caller (ids, weights, permutation,
+            // histogram); these four warps would otherwise idle until the first accumulator is ready.
+            const int t = threadIdx.x - 64;
+            if (t < assignments) {
+                const int pos = rt.less[t] + rt.rank[t];
+                p.ids[t] = rt.ids[t];
+                p.route_weights[t] = rt.weights[t];
+                p.order[pos] = t;
+                p.position[t] = pos;
+                p.pp_of_flat[t] = rt.pp_tok[rt.slot_a[t]][t / kTop];
+            }
+            if (t < rows) p.pp_of_flat[assignments + t] = rt.pp_tok[0][t];
+            for (int e = t; e <= kExperts; e += 128) {
+                int count = 0, before = 0;
+                for (int j = 0; j < assignments; ++j) {
+                    count += rt.ids[j] == e;
+                    before += rt.ids[j] < e;
+                }
+                if (e < kExperts) p.counts[e] = count;
+                p.offsets[e] = before;
+            }
+        }
         const int quarter = warp & 3;
         int buffer = 0;
         std::uint32_t accum_phase = 0;
@@ -602,8 +595,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                 }
             } else {
                 const float alpha = p.bank.alpha[entry * 3 + 2];
-                const int count = expert == kExperts ? rows : rt.counts[expert];
-                const int pp0 = rt.pp_off[expert];
+                const int count = rt.slot_rows[slot];
+                const int pp0 = slab_of_slot(slot, rt.n_active);
                 std::uint32_t d[16];
                 tmem_load16(lane_base, d);
                 tmem_load_wait();
@@ -643,9 +636,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
         for (int i = 0; i < 8; ++i) acc[i] = 0.0F;
 #pragma unroll
         for (int slot = 0; slot < kTop; ++slot) {
-            const int e = rt.ids[row * kTop + slot];
             const float w = rt.weights[row * kTop + slot];
-            const int pp = rt.pp_tok[rt.slot_of[e]][row];
+            const int pp = rt.pp_tok[rt.slot_a[row * kTop + slot]][row];
             const uint4 r = __ldcg(reinterpret_cast<const uint4*>(p.mixed + static_cast<std::size_t>(pp) * hidden + c8 * 8));
             const std::uint32_t words[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
