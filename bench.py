@@ -182,6 +182,10 @@ def workload_config(name: str, gpus: int) -> dict:
         return {"workload": "decode MTP-verify: T=4 tokens x 44 MoE layers (hidden 2560, 256+1 experts, FFN 1024, top-8)",
                 "tokens_per_step": 4, "layers": LAYERS, "routing": "bias ~N(0,0.01)", "gpus": gpus,
                 "l2": "44 distinct weight sets (55 GB) cycle per step: inputs larger than L2"}
+    if name == "ep_prefill16384":
+        return {"workload": "expert-parallel prefill: T=16384 tokens x 1 MoE layer, uniform routing (bias 0)",
+                "tokens_per_step": 16384, "layers": 1, "routing": "uniform", "gpus": gpus,
+                "l2": "0.57-1.14 GB of weights per GPU per step: inputs larger than L2"}
     return {"workload": "prefill chunk: T=4096 tokens x 1 MoE layer, Zipf(1.2) routing", "tokens_per_step": 4096,
             "layers": 1, "routing": "zipf 1.2 (capped at 1/8)", "gpus": gpus,
             "l2": "1.14 GB of weights per step: inputs larger than L2"}
@@ -191,13 +195,124 @@ def workload_config(name: str, gpus: int) -> dict:
 # our arm
 # --------------------------------------------------------------------------------------------
 
+def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps) -> None:
+    """N > 1: the same step, expert-parallel.  Every GPU is home to its own tokens (weak scaling:
+    4 tokens per GPU for the decode step, 4096/N... tokens per GPU for the prefill workloads), the 256
+    experts are sharded 256/N per GPU, rows travel by two NCCL all-to-alls per layer."""
+    import torch
+    import torch.distributed as dist
+    from p92moe_b200 import ep
+
+    decode = args.workload == "decode4x44"
+    if decode:
+        rows, n_layers = 4, args.layers or LAYERS
+    elif args.workload == "ep_prefill16384":
+        rows, n_layers = 16384 // world, args.layers or 1
+    else:
+        rows, n_layers = 4096 // world, args.layers or 1
+    first, local = ep.shard_range(rank, world)
+    states, xs = [], []
+    for l in range(n_layers):
+        raw = synth.make_raw_layer(SEED, l)                     # same weights on every rank; keep the shard
+        entries = raw.entries()
+        shard = entries[first * 3:(first + local) * 3] + entries[EXPERTS * 3:]
+        bank = pkg.ExpertBank(shard, first_expert=first, local_experts=local)
+        router, bias = synth.make_router(SEED, l, bias_std=0.0 if args.workload == "ep_prefill16384" else 0.01)
+        states.append(ep.EpRank(rank, world, bank, router, bias, max_local_rows=rows))
+        xs.append(synth.make_activations(SEED + 1000 * (rank + 1), l, rows))
+        del raw, entries, shard
+    outs = [torch.empty_like(x) for x in xs]
+    torch.cuda.synchronize()
+
+    received = []
+
+    def step(record=False):
+        for st, x, o in zip(states, xs, outs):
+            info = ep.forward_nccl(st, x, o, rows)
+            if record:
+                received.append(info["received_rows"])
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.mark()
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    barrier()
+    if sampler:
+        sampler.mark()
+    t = torch.tensor([start.elapsed_time(stop)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t[0]) / steps
+    value = world * rows / (ms_per_step * 1e-3)
+
+    # end to end: pinned host rows in, host rows out, per layer
+    host_in = [x.cpu().pin_memory() for x in xs]
+    host_out = [torch.empty_like(h).pin_memory() for h in host_in]
+    dev_in = [torch.empty_like(x) for x in xs]
+    e2e_steps = max(2, min(steps, 10))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for st, hi, di, o, ho in zip(states, host_in, dev_in, outs, host_out):
+            di.copy_(hi, non_blocking=True)
+            ep.forward_nccl(st, di, o, rows)
+            ho.copy_(o, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    t = torch.tensor([e2e_s], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t[0])
+    bytes_io = n_layers * rows * HIDDEN * 2
+
+    step(record=True)
+    torch.cuda.synchronize()
+    load = torch.tensor([float(np.sum(received))], device="cuda")
+    loads = [torch.zeros_like(load) for _ in range(world)]
+    dist.all_gather(loads, load)
+    loads = [float(v[0]) for v in loads]
+    distinct = float(np.mean([int((st.arrivals.views(1)["counts"] > 0).sum()) for st in states]))
+    layer_bytes = (distinct + 1) * EXPERT_BYTES + ROUTER_BYTES + rows * HIDDEN * 2 * 2
+    pk = peaks()
+    gbs = layer_bytes * n_layers / (ms_per_step * 1e-3) / 1e9
+    if rank == 0:
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak" if decode else "strong", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 -> bf16",
+            "data": "synthetic", "config": dict(workload_config(args.workload, world),
+                                                parallelism=f"ep{world}: {local} experts per GPU, {rows} home tokens per GPU, "
+                                                            "NCCL all-to-all dispatch and combine"),
+            "clocks": sampler.stop(),
+            "e2e": {"value": world * rows / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": bytes_io,
+                    "d2h_bytes_per_step": bytes_io, "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": steps * n_layers * 19,
+            "roofline": {"bound": "hbm", "kernel": "expert_tc_kernel (per-GPU shard)", "achieved": gbs,
+                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                         "peak_source": pk["source"], "bytes_per_launch": layer_bytes,
+                         "distinct_local_experts_mean": distinct},
+            "load_imbalance": {"rows_per_gpu": loads, "max_over_mean": max(loads) / (sum(loads) / world)},
+            "cpu_baseline": None,
+        }
+        print(json.dumps(line))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode4x44", choices=["decode4x44", "prefill4096"])
+    ap.add_argument("--workload", default="decode4x44", choices=["decode4x44", "prefill4096", "ep_prefill16384"])
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -221,6 +336,10 @@ def main() -> None:
     pkg.load_library()
     from p92moe_b200 import synth
 
+    if world > 1:
+        run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps)
+        dist.destroy_process_group()
+        return
     decode = args.workload == "decode4x44"
     rows = 4 if decode else 4096
     n_layers = args.layers or (LAYERS if decode else 1)

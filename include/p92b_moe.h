@@ -191,6 +191,30 @@ int p92b_project_expert_gate_up(p92b_plan* plan, const p92b_bank* bank, const in
 int p92b_project_expert_down(p92b_plan* plan, const p92b_bank* bank, const int32_t* expert_ids,
                              const uint16_t* input_rows, uint16_t* output_rows, int rows, void* stream);
 
+/* ---- expert parallelism -------------------------------------------------- */
+/* No counterpart in the reference (its CUDA backend is single-device, src/executor.cpp:20-23);
+ * these are the device-side halves of the block either side of the two all-to-all exchanges that
+ * the host issues (NCCL).  Experts are sharded contiguously: the bank of GPU g holds experts
+ * [g*256/G, (g+1)*256/G) and the shared expert (p92b_bank_create first_expert/local_experts).
+ *
+ * p92b_ep_route: logits, top-8, stable permutation and quantisation of the local `rows`; writes the
+ * 8*rows quantised rows (p92b_ep_row_bytes each: packed values then linear scales) in permuted
+ * order, which is grouped by destination GPU.  counts[256] (plan views) give the split sizes.
+ * p92b_ep_experts: `total_rows` arrived rows, the runs of sources 0..sources-1 concatenated, each run
+ * ordered by local expert; recv_counts[sources][local_experts] (device) are the run lengths.  Places
+ * them in global stable order per expert, runs gate/up + SwiGLU + down on the local shard, writes the
+ * BF16 down rows [total_rows][hidden] in arrival order.  `plan` must hold max_rows >= total_rows/8.
+ * p92b_ep_combine: on the home GPU, `returned_rows` [8*rows][hidden] in the order p92b_ep_route
+ * produced; computes the shared expert for the local tokens (scratch from `shared_plan`) and the
+ * weighted combine in slot order. */
+size_t p92b_ep_row_bytes(int hidden);
+int p92b_ep_route(p92b_plan* plan, const uint16_t* input, const uint16_t* router_weight,
+                  const float* correction_bias, int rows, float routed_scale, uint8_t* send_rows, void* stream);
+int p92b_ep_experts(p92b_plan* plan, const p92b_bank* bank, const uint8_t* recv_rows, const int32_t* recv_counts,
+                    int sources, int total_rows, uint16_t* out_rows, void* stream);
+int p92b_ep_combine(p92b_plan* home_plan, p92b_plan* shared_plan, const p92b_bank* bank, const uint16_t* input,
+                    const uint16_t* returned_rows, uint16_t* output, int rows, void* stream);
+
 /* Device views of the last p92b_moe_forward's intermediates, for tests and
  * tracing (the reference keeps the same buffers as Model::Impl members,
  * src/model.cpp:872-885).  Valid until the next call on the plan. */

@@ -77,6 +77,10 @@ SIGNATURES = {
     "p92b_add_inplace": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_moe_permute": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "p92b_moe_permute_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "p92b_ep_row_bytes": (c_size_t, [c_int]),
+    "p92b_ep_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p]),
+    "p92b_ep_experts": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "p92b_ep_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_bank_create": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(ExpertProjection), c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "p92b_bank_destroy": (None, [c_void_p]),
     "p92b_bank_bytes": (c_size_t, [c_void_p]),
@@ -313,7 +317,15 @@ class MoePlan:
             "trace": torch.as_tensor(_DeviceSpan(v.trace, (v.trace_blocks, 64), "<i8"), device="cuda").clone(),
         }
 
-    PATH_AUTO, PATH_STREAM, PATH_TENSOR_CORE = 0, 1, 2
+    def device_counts(self):
+        """Zero-copy int32 [256] view of the last call's per-expert row counts (valid until the next call)."""
+        import torch
+
+        v = PlanViews()
+        _check(load_library().p92b_plan_get_views(self.handle, ctypes.byref(v)), "plan_get_views")
+        return torch.as_tensor(_DeviceSpan(v.counts, (EXPERTS,), "<i4"), device="cuda")
+
+    PATH_AUTO, PATH_STREAM, PATH_TENSOR_CORE, PATH_FUSED_DECODE = 0, 1, 2, 3
 
     def set_path(self, path: int) -> None:
         _check(load_library().p92b_plan_set_path(self.handle, path), "plan_set_path")

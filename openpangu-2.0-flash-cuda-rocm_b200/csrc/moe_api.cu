@@ -233,6 +233,10 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->mega_sync = c.take<unsigned>(4);
         plan->gu_done = c.take<std::int32_t>(kExperts + 4);
         plan->mega_trace = c.take<unsigned long long>(static_cast<std::size_t>(plan->sm_count) * 64);
+        plan->ep_words = 16 * (kExperts + 1);
+        plan->ep_src_base = c.take<std::int32_t>(plan->ep_words);
+        plan->ep_src_start = c.take<std::int32_t>(plan->ep_words);
+        plan->ep_zero_counts = c.take<std::int32_t>(kExperts + 1);
         plan->stage_in = c.take<std::uint16_t>(rows * hidden);
         plan->stage_out = c.take<std::uint16_t>(rows * hidden);
         plan->status = c.take<std::int32_t>(1);

@@ -245,6 +245,11 @@ struct p92b_plan {
     unsigned long long* mega_trace = nullptr;   // [sm_count][64] timer stamps of the last fused launch (P92B_TRACE=1)
     bool trace_on = false;
     CUtensorMap map_x_tok {};
+    // expert-parallel scratch: per (source, local expert) padded base and arrival start
+    std::int32_t* ep_src_base = nullptr;
+    std::int32_t* ep_src_start = nullptr;
+    std::int32_t* ep_zero_counts = nullptr;
+    int ep_words = 0;
     // optional stage timing (host side)
     bool timing = false;
     cudaEvent_t stage_events[P92B_STAGES + 1] = {};

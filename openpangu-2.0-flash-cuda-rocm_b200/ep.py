@@ -1,0 +1,146 @@
+"""Expert-parallel MoE block: host orchestration of the two all-to-all exchanges.
+
+256 routed experts are sharded contiguously over G GPUs (128 / 64 / 32 per GPU at G = 2 / 4 / 8);
+router weight, correction bias and the shared expert are replicated; every GPU is home to its own
+tokens.  One process per GPU; the exchanges are NCCL all-to-alls issued through torch.distributed,
+everything else is the C ABI (p92b_ep_route / p92b_ep_experts / p92b_ep_combine).
+
+The reference has no expert parallelism (its CUDA backend is one device and one stream,
+src/executor.cpp:20-23); the contract kept here is its single-device one: per expert, rows are
+ordered by global flat index (home GPU, token, slot), so the permutation restricted to a GPU's
+experts is what one GPU would compute, and the combine is the device law in slot order.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import (EXPERTS, HIDDEN, INTERMEDIATE, ROUTED_SCALE, TOP_K, ExpertBank, MoePlan, _check, _ptr, _stream,
+               load_library)
+
+ROW_BYTES = HIDDEN // 2 + HIDDEN // 16
+
+
+def shard_range(rank: int, world: int, experts: int = EXPERTS) -> tuple:
+    """[first, first + count) of the experts GPU `rank` owns."""
+    if experts % world != 0:
+        raise ValueError("world size must divide the expert count")
+    per = experts // world
+    return rank * per, per
+
+
+def split_sizes(counts: Sequence[int], world: int) -> List[int]:
+    """Rows this GPU sends to each destination, from its per-expert histogram."""
+    per = len(counts) // world
+    return [int(sum(counts[d * per:(d + 1) * per])) for d in range(world)]
+
+
+class EpRank:
+    """One GPU's share: its expert shard, two plans (arrivals; home tokens + shared expert)."""
+
+    def __init__(self, rank: int, world: int, bank: ExpertBank, router_weight, correction_bias,
+                 max_local_rows: int, max_arrival_rows: Optional[int] = None, routed_scale: float = ROUTED_SCALE):
+        self.rank, self.world = rank, world
+        self.first, self.local = shard_range(rank, world)
+        if bank.first_expert != self.first or bank.local_experts != self.local:
+            raise ValueError("bank does not hold this rank's expert shard")
+        self.bank, self.router_weight, self.bias, self.routed_scale = bank, router_weight, correction_bias, routed_scale
+        # worst case every assignment of every GPU lands here
+        arrival_rows = max_arrival_rows if max_arrival_rows is not None else max_local_rows * world
+        self.home = MoePlan(max_rows=max_local_rows)
+        self.shared = MoePlan(max_rows=max_local_rows)
+        self.arrivals = MoePlan(max_rows=arrival_rows)
+        self.max_local_rows = max_local_rows
+        self.send = torch.empty((max_local_rows * TOP_K, ROW_BYTES), dtype=torch.uint8, device="cuda")
+
+    # ---- device halves ---------------------------------------------------------------------
+    def route(self, x, rows: int):
+        """-> (send rows [8*rows, 1440] in destination order, per-expert counts [256] on the device)."""
+        _check(load_library().p92b_ep_route(self.home.handle, _ptr(x), _ptr(self.router_weight), _ptr(self.bias), rows,
+                                            self.routed_scale, _ptr(self.send), _stream()), "ep_route")
+        return self.send[: rows * TOP_K], self.home.device_counts()
+
+    def experts(self, recv_rows, recv_counts, total_rows: int):
+        """recv_counts int32 [world, local] on the device -> BF16 down rows [total_rows, hidden] in arrival order."""
+        out = torch.empty((total_rows, HIDDEN), dtype=torch.bfloat16, device="cuda")
+        _check(load_library().p92b_ep_experts(self.arrivals.handle, self.bank.handle, _ptr(recv_rows) if total_rows else 0,
+                                              _ptr(recv_counts), self.world, total_rows,
+                                              _ptr(out) if total_rows else 0, _stream()), "ep_experts")
+        return out
+
+    def combine(self, x, returned_rows, out, rows: int) -> None:
+        _check(load_library().p92b_ep_combine(self.home.handle, self.shared.handle, self.bank.handle, _ptr(x),
+                                              _ptr(returned_rows), _ptr(out), rows, _stream()), "ep_combine")
+
+
+def exchange_dispatch(send, counts_by_dst, group=None):
+    """Exchange 1.  send: rows in destination order; counts_by_dst int32 [world, local] = rows per
+    (destination, its local expert).  Returns (arrived rows: the runs of sources 0..world-1
+    concatenated, recv_counts [world(source), local], send_sizes, recv_sizes).  Works on any backend
+    (NCCL on GPUs, gloo on CPU tensors); the split sizes cross to the host once."""
+    import torch.distributed as dist
+
+    recv_counts = torch.empty_like(counts_by_dst)
+    dist.all_to_all_single(recv_counts, counts_by_dst, group=group)
+    sizes = torch.stack([counts_by_dst.sum(dim=1), recv_counts.sum(dim=1)]).cpu().tolist()
+    send_sizes, recv_sizes = [int(v) for v in sizes[0]], [int(v) for v in sizes[1]]
+    recv = torch.empty((sum(recv_sizes),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    dist.all_to_all_single(recv, send, output_split_sizes=recv_sizes, input_split_sizes=send_sizes, group=group)
+    return recv, recv_counts, send_sizes, recv_sizes
+
+
+def exchange_return(rows_out, send_sizes, recv_sizes, group=None):
+    """Exchange 2: rows computed for the arrivals go back to their homes, splits reversed; the result
+    is in the order the home GPU sent its rows."""
+    import torch.distributed as dist
+
+    returned = torch.empty((sum(send_sizes),) + tuple(rows_out.shape[1:]), dtype=rows_out.dtype, device=rows_out.device)
+    dist.all_to_all_single(returned, rows_out, output_split_sizes=send_sizes, input_split_sizes=recv_sizes, group=group)
+    return returned
+
+
+def forward_nccl(state: EpRank, x, out, rows: int, group=None) -> dict:
+    """The block on `rows` home tokens of this rank, exchanges over NCCL.  Returns split statistics."""
+    send, counts = state.route(x, rows)
+    counts_by_dst = counts.view(state.world, state.local).contiguous()
+    recv, recv_counts, send_sizes, recv_sizes = exchange_dispatch(send, counts_by_dst, group)
+    down = state.experts(recv, recv_counts, recv.shape[0])
+    returned = exchange_return(down, send_sizes, recv_sizes, group)
+    state.combine(x, returned, out, rows)
+    return {"sent_rows": send_sizes, "received_rows": int(recv.shape[0])}
+
+
+def forward_emulated(states: Sequence[EpRank], xs: Sequence, outs: Sequence, rows: Sequence[int]) -> None:
+    """All ranks in ONE process on one GPU, the exchanges done by tensor slicing: the same device code
+    path as forward_nccl without NCCL, for single-GPU tests of the multi-GPU logic."""
+    world = len(states)
+    sends, counts = [], []
+    for st, x, r in zip(states, xs, rows):
+        s, c = st.route(x, r)
+        sends.append(s.clone())
+        counts.append(c.view(world, st.local).clone())
+    torch.cuda.synchronize()
+    host_counts = [c.cpu() for c in counts]
+    downs = []
+    for d, st in enumerate(states):
+        recv_counts = torch.stack([counts[s][d] for s in range(world)]).contiguous()
+        pieces = []
+        for s in range(world):
+            start = int(host_counts[s][:d].sum())
+            n = int(host_counts[s][d].sum())
+            pieces.append(sends[s][start:start + n])
+        recv = torch.cat(pieces) if pieces else torch.empty((0, ROW_BYTES), dtype=torch.uint8, device="cuda")
+        downs.append(st.experts(recv.contiguous(), recv_counts, recv.shape[0]))
+    torch.cuda.synchronize()
+    for s, st in enumerate(states):
+        pieces = []
+        for d in range(world):
+            # rows rank s sent to d sit in d's arrival buffer after the runs of sources < s
+            before = sum(int(host_counts[t][d].sum()) for t in range(s))
+            n = int(host_counts[s][d].sum())
+            pieces.append(downs[d][before:before + n])
+        returned = torch.cat(pieces).contiguous()
+        st.combine(xs[s], returned, outs[s], rows[s])
+    torch.cuda.synchronize()

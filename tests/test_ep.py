@@ -1,0 +1,118 @@
+"""Expert parallelism.  CPU: the host-side exchange logic over gloo with two processes.  GPU: all
+ranks emulated in one process on one GPU (same device code as the NCCL path) against the
+single-GPU block."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import __graft_entry__ as entry
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _gloo_worker(rank, world, port, result):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    entry.load_package()
+    from p92moe_b200 import ep
+
+    local = 256 // world
+    rng = np.random.default_rng(100 + rank)
+    rows = 5 + rank * 3
+    ids = np.stack([rng.choice(256, 8, replace=False) for _ in range(rows)]).astype(np.int32).reshape(-1)
+    order = np.argsort(ids, kind="stable")                       # the stable permutation by expert id
+    counts = np.bincount(ids, minlength=256).astype(np.int32)
+    # a row is tagged (home rank, flat index, expert) so its journey can be checked
+    send = torch.tensor([[rank, int(i), int(ids[i])] for i in order], dtype=torch.int32)
+    counts_by_dst = torch.from_numpy(counts).view(world, local).contiguous()
+    assert ep.split_sizes(counts.tolist(), world) == counts_by_dst.sum(dim=1).tolist()
+    recv, recv_counts, send_sizes, recv_sizes = ep.exchange_dispatch(send, counts_by_dst)
+    first, n_local = ep.shard_range(rank, world)
+    ok = True
+    # arrivals: runs by source, inside a run experts ascending and flat index ascending per expert
+    at = 0
+    for s in range(world):
+        run = recv[at:at + recv_sizes[s]]
+        at += recv_sizes[s]
+        ok &= bool((run[:, 0] == s).all())
+        ok &= bool(((run[:, 2] >= first) & (run[:, 2] < first + n_local)).all())
+        keys = (run[:, 2].long() * 100000 + run[:, 1].long()).tolist()
+        ok &= keys == sorted(keys)
+        ok &= recv_counts[s].tolist() == np.bincount(run[:, 2].numpy() - first, minlength=n_local).tolist()
+    # per expert, concatenating the sources' runs gives the global stable order (home rank, flat)
+    for e in range(first, first + n_local):
+        rows_e = recv[recv[:, 2] == e]
+        keys = (rows_e[:, 0].long() * 100000 + rows_e[:, 1].long()).tolist()
+        ok &= keys == sorted(keys)
+    back = ep.exchange_return(recv * 2, send_sizes, recv_sizes)
+    ok &= bool(torch.equal(back, send * 2))                      # every row returns to its slot
+    result[rank] = ok
+    dist.destroy_process_group()
+
+
+def test_exchange_logic_over_gloo_two_ranks():
+    world = 2
+    port = _free_port()
+    with mp.Manager() as manager:
+        result = manager.dict()
+        mp.spawn(_gloo_worker, args=(world, port, result), nprocs=world, join=True)
+        assert dict(result) == {0: True, 1: True}
+
+
+def test_shard_ranges():
+    entry.load_package()
+    from p92moe_b200 import ep
+
+    assert [ep.shard_range(r, 8) for r in (0, 7)] == [(0, 32), (224, 32)]
+    assert ep.shard_range(1, 2) == (128, 128) and ep.shard_range(3, 4) == (192, 64)
+    with pytest.raises(ValueError):
+        ep.shard_range(0, 3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,rows", [(2, [5, 3]), (4, [2, 7, 4, 3]), (8, [4] * 8), (2, [130, 70])])
+def test_expert_parallel_block_matches_single_gpu(cuda, pkg, layer0, world, rows):
+    torch = cuda
+    from p92moe_b200 import ep, synth
+
+    raw = layer0.raw
+    entries = raw.entries()
+    xs = [synth.make_activations(500 + r, 0, n) for r, n in enumerate(rows)]
+    states = []
+    for r in range(world):
+        first, local = ep.shard_range(r, world)
+        shard = entries[first * 3:(first + local) * 3] + entries[256 * 3:]
+        bank = pkg.ExpertBank(shard, first_expert=first, local_experts=local)
+        states.append(ep.EpRank(r, world, bank, layer0.router_weight, layer0.bias, max_local_rows=max(rows),
+                                max_arrival_rows=sum(rows)))
+    outs = [torch.full_like(x, float("nan")) for x in xs]
+    ep.forward_emulated(states, xs, outs, rows)
+    # single GPU on all tokens at once
+    x_all = torch.cat(xs).contiguous()
+    total = x_all.shape[0]
+    plan = pkg.MoePlan(max_rows=total)
+    plan.set_path(2)
+    want = torch.empty_like(x_all)
+    pkg.MoeBlock(layer0.bank, layer0.router_weight, layer0.bias, plan).run_moe_rows(x_all, want, total)
+    torch.cuda.synchronize()
+    ids_all = plan.views(total)["expert_ids"]
+    at = 0
+    for r, n in enumerate(rows):
+        v = states[r].home.views(n)
+        assert torch.equal(v["expert_ids"], ids_all[at:at + n])              # routing is per token: identical ids
+        got = outs[r].float().cpu().numpy()
+        ref = want[at:at + n].float().cpu().numpy()
+        assert np.isfinite(got).all()
+        rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+        assert rel <= 1e-2 and np.abs(got - ref).max() <= 2e-2, (r, rel)
+        at += n
