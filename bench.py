@@ -426,7 +426,7 @@ def main() -> None:
         kernel, k_bytes, k_us = "moe_decode_kernel", layer_bytes, ms_per_step * 1e3 / n_layers
     else:
         # dominant kernel of the multi-kernel path: gate/up + SwiGLU + re-quantise
-        kernel = "expert_tc_kernel<0,128>"
+        kernel = "expert_tc_kernel<0,64>"
         k_bytes = (d_mean + 1) * 2 * (EXPERT_BYTES // 3) + rows * (HIDDEN // 2 + HIDDEN // 16) + \
             9 * rows * (INTER // 2 + INTER // 16)
         k_us = stage_us["gate_up_swiglu"]

@@ -265,8 +265,8 @@ int p92b_ep_experts(p92b_plan* plan, const p92b_bank* bank, const uint8_t* recv_
     const int local = bank->view.local_experts;
     if (static_cast<std::size_t>(sources) * (local + 1) > static_cast<std::size_t>(plan->ep_words)) return cudaErrorInvalidValue;
     plan->last_launches = 0;
-    // token tiles of 128 rows: the row count per expert is only known on the device
-    const int tile_rows = 128;
+    // the row count per expert is only known on the device: use the large-batch tile
+    const int tile_rows = tc_tile_rows(1 << 20);
     ep_lists_kernel<<<1, 256, 0, stream>>>(recv_counts, sources, bank->view.first_expert, local, 0, tile_rows,
                                            plan->counts, plan->pp_off, plan->active, plan->active_count,
                                            plan->tile_prefix, plan->ep_src_base, plan->ep_src_start);
@@ -276,8 +276,8 @@ int p92b_ep_experts(p92b_plan* plan, const p92b_bank* bank, const uint8_t* recv_
                                                                   sources, local, total_rows, plan->xq_pp, plan->xs_sw,
                                                                   plan->pp_of_flat, plan->hidden / 2, plan->hidden / 16);
     if ((st = cudaGetLastError()) != cudaSuccess) return st;
-    if ((st = launch_experts_tc(plan, bank, 128, false, stream)) != cudaSuccess) return st;
-    if ((st = launch_experts_tc(plan, bank, 128, true, stream)) != cudaSuccess) return st;
+    if ((st = launch_experts_tc(plan, bank, 1 << 20, false, stream)) != cudaSuccess) return st;
+    if ((st = launch_experts_tc(plan, bank, 1 << 20, true, stream)) != cudaSuccess) return st;
     ep_gather_rows_kernel<<<warps_grid(total_rows), 256, 0, stream>>>(plan->mixed_pp, plan->pp_of_flat, out_rows,
                                                                       total_rows, plan->hidden);
     plan->last_launches = 5;

@@ -42,7 +42,8 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kBlockKBytes = 128;                 // one swizzle row: 256 E2M1 values
 constexpr int kSfSlab = 2048;                     // 128 rows x 16 scales of one K block
-constexpr int kThreadsTc = 192;
+constexpr int kEpilogueWarps = 8;                 // two per TMEM quarter: they split the column chunks
+constexpr int kThreadsTc = 64 + 32 * kEpilogueWarps;
 
 template <int MODE, int N>
 struct Tc {
@@ -147,7 +148,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         }
         for (int b = 0; b < C::kAccumBuffers; ++b) {
             mbar_init(accum_full(b), 1);
-            mbar_init(accum_empty(b), 4);
+            mbar_init(accum_empty(b), kEpilogueWarps);
         }
         *abort_ptr = 0;
         fence_mbar_init();
@@ -247,6 +248,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                 if (!mbar_wait(accum_empty(buffer), accum_phase[buffer] ^ 1U)) { give_up(); break; }
                 tc_fence_after();
                 const std::uint32_t accum = tmem_base + buffer * C::kAccumCols;
+                // a 64-row token tile may start in the middle of a 128-row scale tile: its scales then sit
+                // two TMEM columns further (rows 64..127 are quarters 2 and 3 of the tile)
+                const std::uint32_t b_quarter = static_cast<std::uint32_t>((it.pp0 & 127) >> 5);
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) {
@@ -270,7 +274,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                         for (int a = 0; a < C::kA; ++a) {
                             const std::uint64_t a_desc = desc_k_major_sw128(st + a * C::kABytes);
                             mma_nvf4(accum + a * C::kAccumStride, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                     sfc + a * 16 + k * 4, sfc + C::kA * 16 + k * 4, kb > 0 || k > 0);
+                                     sfc + a * 16 + k * 4, sfc + C::kA * 16 + k * 4 + b_quarter, kb > 0 || k > 0);
                         }
                     }
                     tc_commit(empty_bar(stage));
@@ -285,7 +289,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31
+        // Eight warps: warp w reads TMEM lanes 32*(w & 3) .. +31 (one output row per lane) and the two
+        // warps of a quarter take alternate 16-column chunks.  A chunk is processed without any
+        // data-dependent branch so the sixteen per-column dependency chains interleave; only the
+        // stores are predicated on the column being a real token.
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         int buffer = 0;
         std::uint32_t accum_phase[2] = {0U, 0U};
         for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
@@ -301,48 +310,71 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                 const float alpha_g = p.bank.alpha[it.entry * 3 + 0];
                 const float alpha_u = p.bank.alpha[it.entry * 3 + 1];
                 const int inter = p.m_total;
-                const int sf_cols = inter / 16;
                 const int sf_col = row >> 4;
+                // scale byte of (token pp0 + n, 16-row block sf_col) in the 128x4 tiling; pp0 is a multiple of 64
+                std::uint8_t* hs_base = p.hs + (static_cast<std::size_t>(it.pp0 >> 7) * (inter / 64) + (sf_col >> 2)) * 512 +
+                                        (sf_col & 3);
+                std::uint8_t* hq_base = p.hq + static_cast<std::size_t>(it.pp0) * (inter / 2) + (row >> 1);
+                const int n_base = it.pp0 & 127;
 #pragma unroll 1
-                for (int c0 = 0; c0 < N; c0 += 16) {
-                    if (c0 >= it.valid) break;
+                for (int c0 = half * 16; c0 < N; c0 += 32) {
+                    if (c0 >= it.valid) break;                                    // warp uniform
                     std::uint32_t g[16], u[16];
                     tmem_load16(lane_base + c0, g);
                     tmem_load16(lane_base + C::kAccumStride + c0, u);
                     tmem_load_wait();
+                    float h[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int n = c0 + j;
-                        if (n >= it.valid) break;                                 // warp uniform
                         const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[j]) * alpha_g));
                         const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[j]) * alpha_u));
-                        const float h = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
-                        // 16 consecutive rows (half a warp) form one NVFP4 block of the down product's K
-                        float amax = fabsf(h);
+                        h[j] = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
+                    }
+                    // |h| maximum over the 16 rows of a block: h is BF16-exact, so two columns share one
+                    // bf16x2 register through the four shuffle rounds
+                    std::uint32_t packed[8];
 #pragma unroll
-                        for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffU, amax, off));
+                    for (int k = 0; k < 8; ++k) {
+                        packed[k] = (__float_as_uint(fabsf(h[2 * k])) >> 16) | (__float_as_uint(fabsf(h[2 * k + 1])) & 0xffff0000U);
+                    }
+#pragma unroll
+                    for (int off = 8; off > 0; off >>= 1) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            const std::uint32_t other = __shfl_xor_sync(0xffffffffU, packed[k], off);
+                            __nv_bfloat162 a2 = *reinterpret_cast<__nv_bfloat162*>(&packed[k]);
+                            const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&other);
+                            a2 = __hmax2(a2, b2);
+                            packed[k] = *reinterpret_cast<std::uint32_t*>(&a2);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float amax = __uint_as_float((j & 1) ? (packed[j >> 1] & 0xffff0000U) : (packed[j >> 1] << 16));
                         const __nv_fp8_e4m3 scale(amax * (p.quant_scale / 6.0F));
                         const float decoded = static_cast<float>(scale);
                         const float multiplier = decoded == 0.0F ? 0.0F : p.quant_scale / decoded;
-                        const float q = h * multiplier;
+                        const float q = h[j] * multiplier;
                         const float q_next = __shfl_xor_sync(0xffffffffU, q, 1);
-                        const std::size_t pp = static_cast<std::size_t>(it.pp0 + n);
-                        if ((lane & 1) == 0) {
-                            p.hq[pp * (inter / 2) + (row >> 1)] =
-                                static_cast<std::uint8_t>(__nv_fp4x2_e2m1(make_float2(q, q_next)).__x);
-                        }
-                        if ((lane & 15) == 0) {
-                            const std::size_t at = ((pp >> 7) * ((sf_cols + 3) / 4) + (sf_col >> 2)) * 512 +
-                                                   (pp & 31) * 16 + ((pp >> 5) & 3) * 4 + (sf_col & 3);
-                            p.hs[at] = scale.__x;
+                        const int n = c0 + j;
+                        if (n < it.valid) {
+                            if ((lane & 1) == 0) {
+                                hq_base[static_cast<std::size_t>(n) * (inter / 2)] =
+                                    static_cast<std::uint8_t>(__nv_fp4x2_e2m1(make_float2(q, q_next)).__x);
+                            }
+                            if ((lane & 15) == 0) {
+                                const int tn = n_base + n;
+                                hs_base[(tn & 31) * 16 + (tn >> 5) * 4] = scale.__x;
+                            }
                         }
                     }
                 }
             } else {
                 const float alpha = p.bank.alpha[it.entry * 3 + 2];
                 const int hidden = p.m_total;
+                std::uint16_t* out_base = p.out + static_cast<std::size_t>(it.pp0) * hidden + row;
 #pragma unroll 1
-                for (int c0 = 0; c0 < N; c0 += 16) {
+                for (int c0 = half * 16; c0 < N; c0 += 32) {
                     if (c0 >= it.valid) break;
                     std::uint32_t d[16];
                     tmem_load16(lane_base + c0, d);
@@ -350,9 +382,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int n = c0 + j;
-                        if (n >= it.valid) break;
-                        p.out[static_cast<std::size_t>(it.pp0 + n) * hidden + row] =
-                            float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
+                        if (n < it.valid) {
+                            out_base[static_cast<std::size_t>(n) * hidden] = float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
+                        }
                     }
                 }
             }
@@ -456,7 +488,9 @@ cudaError_t make_operand_map(CUtensorMap* map, const void* base, std::size_t row
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-int tc_tile_rows(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128; }
+// Token tile of the expert kernels.  Above 32 rows it stays at 64 columns: two gate/up accumulator pairs
+// then fit TMEM side by side, so the epilogue of one tile overlaps the MMAs of the next.
+int tc_tile_rows(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : 64; }
 // Every entry's rows start on a multiple of 128 padded positions, so a token tile always begins at
 // row 0 of a 128-row scale-factor tile (TMEM lane 0, first scale column).
 int tc_pad_align(int rows) { (void)rows; return 128; }
@@ -484,7 +518,7 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
     p.status = plan->status;
     p.quant_scale = 1.0F;
     const int n = tc_tile_rows(rows);
-    const int which = n == 16 ? 0 : n == 32 ? 1 : n == 64 ? 2 : 3;
+    const int which = n == 16 ? 0 : n == 32 ? 1 : 2;
     p.routing_is_upstream = down ? 0 : 1;
     if (!down) {
         p.b_sf = plan->xs_sw;
@@ -496,8 +530,7 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
         switch (which) {
             case 0: return launch_tc<0, 16>(plan, plan->map_x[0], p, stream, pdl);
             case 1: return launch_tc<0, 32>(plan, plan->map_x[1], p, stream, pdl);
-            case 2: return launch_tc<0, 64>(plan, plan->map_x[2], p, stream, pdl);
-            default: return launch_tc<0, 128>(plan, plan->map_x[3], p, stream, pdl);
+            default: return launch_tc<0, 64>(plan, plan->map_x[2], p, stream, pdl);
         }
     }
     p.b_sf = plan->hs_sw;
@@ -508,8 +541,7 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
     switch (which) {
         case 0: return launch_tc<1, 16>(plan, plan->map_h[0], p, stream, pdl);
         case 1: return launch_tc<1, 32>(plan, plan->map_h[1], p, stream, pdl);
-        case 2: return launch_tc<1, 64>(plan, plan->map_h[2], p, stream, pdl);
-        default: return launch_tc<1, 128>(plan, plan->map_h[3], p, stream, pdl);
+        default: return launch_tc<1, 64>(plan, plan->map_h[2], p, stream, pdl);
     }
 }
 
