@@ -137,6 +137,110 @@ __global__ void __launch_bounds__(WE* WT * 32) logits_rows_kernel(
     }
 }
 
+// ---- T > 1 order, large batches ----------------------------------------------
+// Same per-lane chains as above, organised for throughput: a block computes 16 experts x 32 tokens,
+// a warp 8 x 8 of them.  K advances in chunks of 256 columns that are stored TRANSPOSED in shared
+// memory - element (row, column l + 32 j) at [row][l][j] - so a lane fetches its eight j-values of
+// a row with one 16-byte read, and the next chunk's global loads are in flight (registers) while the
+// current chunk is multiplied.  The fmaf order of every chain is still j ascending.
+__global__ void __launch_bounds__(256) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
+                                                                const std::uint16_t* __restrict__ w,
+                                                                float* __restrict__ out, int batch_rows, int rows,
+                                                                int columns) {
+    constexpr int TE = 8, TT = 8, WE = 2, WT = 4, KC = 256;
+    constexpr int BE = TE * WE, BT = TT * WT, ROWS = BE + BT;      // 48 staged rows
+    constexpr int PIECES = ROWS * (KC / 8) / 256;                   // 16-byte global pieces per thread per chunk: 6
+    __shared__ __align__(16) std::uint16_t tile[ROWS][32][8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int we = warp % WE, wt = warp / WE;
+    const int e0 = blockIdx.x * BE, t0 = blockIdx.y * BT;
+    float acc[TE][TT];
+#pragma unroll
+    for (int i = 0; i < TE; ++i)
+#pragma unroll
+        for (int j = 0; j < TT; ++j) acc[i][j] = 0.0F;
+
+    uint4 staged[PIECES];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int q = 0; q < PIECES; ++q) {
+            const int idx = threadIdx.x + q * 256;
+            const int r = idx / (KC / 8);
+            const int c8 = idx - r * (KC / 8);
+            const bool is_w = r < BE;
+            const int src_row = is_w ? e0 + r : t0 + (r - BE);
+            const bool ok = is_w ? src_row < rows : src_row < batch_rows;
+            staged[q] = ok ? __ldg(reinterpret_cast<const uint4*>((is_w ? w : x) + static_cast<std::size_t>(src_row) * columns + k0) + c8)
+                           : make_uint4(0U, 0U, 0U, 0U);
+        }
+    };
+    auto store = [&]() {
+#pragma unroll
+        for (int q = 0; q < PIECES; ++q) {
+            const int idx = threadIdx.x + q * 256;
+            const int r = idx / (KC / 8);
+            const int c8 = idx - r * (KC / 8);
+            // columns 8*c8 .. 8*c8+7 of the chunk: lane (8*c8 + i) & 31, j = (8*c8) >> 5
+            const int j = c8 >> 2;
+            const int l0 = (c8 & 3) * 8;
+            const std::uint32_t words[4] = {staged[q].x, staged[q].y, staged[q].z, staged[q].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                tile[r][l0 + 2 * i][j] = static_cast<std::uint16_t>(words[i] & 0xffffU);
+                tile[r][l0 + 2 * i + 1][j] = static_cast<std::uint16_t>(words[i] >> 16);
+            }
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < columns; k0 += KC) {
+        __syncthreads();                        // everyone is done with the previous chunk
+        store();
+        __syncthreads();
+        if (k0 + KC < columns) fetch(k0 + KC);  // in flight during the multiply below
+#pragma unroll
+        for (int hj = 0; hj < 2; ++hj) {        // j = 4*hj .. 4*hj+3
+            uint2 wv[TE], xv[TT];
+#pragma unroll
+            for (int i = 0; i < TE; ++i) wv[i] = *reinterpret_cast<const uint2*>(&tile[we * TE + i][lane][4 * hj]);
+#pragma unroll
+            for (int i = 0; i < TT; ++i) xv[i] = *reinterpret_cast<const uint2*>(&tile[BE + wt * TT + i][lane][4 * hj]);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                float wf[TE], xf[TT];
+#pragma unroll
+                for (int i = 0; i < TE; ++i) {
+                    const std::uint32_t word = jj < 2 ? wv[i].x : wv[i].y;
+                    wf[i] = __uint_as_float((jj & 1) ? (word & 0xffff0000U) : (word << 16));
+                }
+#pragma unroll
+                for (int i = 0; i < TT; ++i) {
+                    const std::uint32_t word = jj < 2 ? xv[i].x : xv[i].y;
+                    xf[i] = __uint_as_float((jj & 1) ? (word & 0xffff0000U) : (word << 16));
+                }
+#pragma unroll
+                for (int i = 0; i < TE; ++i)
+#pragma unroll
+                    for (int t = 0; t < TT; ++t) acc[i][t] = fmaf(xf[t], wf[i], acc[i][t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TE; ++i) {
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            float value = acc[i][t];
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_down_sync(0xffffffffU, value, offset);
+            const int e = e0 + we * TE + i;
+            const int tok = t0 + wt * TT + t;
+            if (lane == 0 && e < rows && tok < batch_rows) out[static_cast<std::size_t>(tok) * rows + e] = value;
+        }
+    }
+}
+
 // ---- top-8 ----------------------------------------------------------------
 // One warp per token; lane l holds experts l, l+32, ..., l+224 in registers.
 // Eight rounds of (local best, warp butterfly arg-max) with the reference's
@@ -184,6 +288,9 @@ cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w,
         dim3 grid((rows + TE * WE - 1) / (TE * WE), 1);
         return launch_kernel(kernel, grid, dim3(WE * WT * 32), smem, stream, pdl, x, w, out, batch_rows, rows, columns,
                              columns);
+    } else if (batch_rows >= 256 && columns % 256 == 0) {
+        dim3 grid((rows + 15) / 16, (batch_rows + 31) / 32);
+        return launch_kernel(logits_rows_large_kernel, grid, dim3(256), 0, stream, pdl, x, w, out, batch_rows, rows, columns);
     } else {
         constexpr int TE = 8, TT = 8, WE = 2, WT = 4;
         constexpr int KC = 128;
