@@ -224,13 +224,17 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     outs = [torch.empty_like(x) for x in xs]
     torch.cuda.synchronize()
 
-    received = []
+    exact = rows > ep.FIXED_MAX_ROWS or os.environ.get("P92B_EP_EXCHANGE", "") == "exact"
 
-    def step(record=False):
+    def forward(st, x, o):
+        if exact:
+            ep.forward_nccl(st, x, o, rows)
+        else:
+            ep.forward_nccl_fixed(st, x, o, rows, 8 * rows)
+
+    def step():
         for st, x, o in zip(states, xs, outs):
-            info = ep.forward_nccl(st, x, o, rows)
-            if record:
-                received.append(info["received_rows"])
+            forward(st, x, o)
 
     def barrier():
         dist.barrier()
@@ -265,7 +269,7 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     for _ in range(e2e_steps):
         for st, hi, di, o, ho in zip(states, host_in, dev_in, outs, host_out):
             di.copy_(hi, non_blocking=True)
-            ep.forward_nccl(st, di, o, rows)
+            forward(st, di, o)
             ho.copy_(o, non_blocking=True)
             torch.cuda.current_stream().synchronize()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
@@ -274,8 +278,9 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     e2e_s = float(t[0])
     bytes_io = n_layers * rows * HIDDEN * 2
 
-    step(record=True)
+    step()
     torch.cuda.synchronize()
+    received = [int(st.arrivals.views(1)["counts"].sum()) for st in states]
     load = torch.tensor([float(np.sum(received))], device="cuda")
     loads = [torch.zeros_like(load) for _ in range(world)]
     dist.all_gather(loads, load)
@@ -291,7 +296,8 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
             "scaling": "weak" if decode else "strong", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 -> bf16",
             "data": "synthetic", "config": dict(workload_config(args.workload, world),
                                                 parallelism=f"ep{world}: {local} experts per GPU, {rows} home tokens per GPU, "
-                                                            "NCCL all-to-all dispatch and combine"),
+                                                            "NCCL all-to-all dispatch and combine, "
+                                                            + ("exact-size splits" if exact else "fixed-capacity blocks, no host sync")),
             "clocks": sampler.stop(),
             "e2e": {"value": world * rows / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": bytes_io,
                     "d2h_bytes_per_step": bytes_io, "ms_per_step": e2e_s * 1e3},

@@ -215,6 +215,21 @@ int p92b_ep_experts(p92b_plan* plan, const p92b_bank* bank, const uint8_t* recv_
 int p92b_ep_combine(p92b_plan* home_plan, p92b_plan* shared_plan, const p92b_bank* bank, const uint16_t* input,
                     const uint16_t* returned_rows, uint16_t* output, int rows, void* stream);
 
+/* The same three halves for small batches with FIXED-CAPACITY exchange blocks, so that no split size
+ * ever crosses to the host and a whole layer stays asynchronous: every (source, destination) pair
+ * owns one block of p92b_ep_fixed_block_bytes = header (the source's row counts for the
+ * destination's experts) + cap_rows row slots; both all-to-alls have equal splits.  cap_rows must be
+ * the same on all GPUs and at least 8 * rows.  send_blocks / recv_blocks: [world][block];
+ * out_slots / returned_slots: BF16 [world][cap_rows][hidden]. */
+size_t p92b_ep_fixed_block_bytes(int hidden, int local_experts, int cap_rows);
+int p92b_ep_route_fixed(p92b_plan* plan, const uint16_t* input, const uint16_t* router_weight,
+                        const float* correction_bias, int rows, float routed_scale, uint8_t* send_blocks, int world,
+                        int cap_rows, void* stream);
+int p92b_ep_experts_fixed(p92b_plan* plan, const p92b_bank* bank, const uint8_t* recv_blocks, int sources, int cap_rows,
+                          uint16_t* out_slots, void* stream);
+int p92b_ep_combine_fixed(p92b_plan* home_plan, p92b_plan* shared_plan, const p92b_bank* bank, const uint16_t* input,
+                          const uint16_t* returned_slots, uint16_t* output, int rows, void* stream);
+
 /* Device views of the last p92b_moe_forward's intermediates, for tests and
  * tracing (the reference keeps the same buffers as Model::Impl members,
  * src/model.cpp:872-885).  Valid until the next call on the plan. */

@@ -54,6 +54,35 @@ class EpRank:
         self.arrivals = MoePlan(max_rows=arrival_rows)
         self.max_local_rows = max_local_rows
         self.send = torch.empty((max_local_rows * TOP_K, ROW_BYTES), dtype=torch.uint8, device="cuda")
+        self._fixed = {}
+
+    # ---- fixed-capacity exchange buffers (small batches) -----------------------------------
+    def fixed_buffers(self, cap_rows: int):
+        """(send blocks, receive blocks, outgoing result slots, returned result slots) for `cap_rows`
+        row slots per (source, destination) pair; allocated once per capacity."""
+        if cap_rows not in self._fixed:
+            if cap_rows * self.world > self.arrivals.max_rows * TOP_K:
+                raise ValueError("arrival plan too small for this capacity")
+            block = load_library().p92b_ep_fixed_block_bytes(HIDDEN, self.local, cap_rows)
+            self._fixed[cap_rows] = (
+                torch.zeros((self.world, block), dtype=torch.uint8, device="cuda"),
+                torch.zeros((self.world, block), dtype=torch.uint8, device="cuda"),
+                torch.zeros((self.world, cap_rows, HIDDEN), dtype=torch.bfloat16, device="cuda"),
+                torch.zeros((self.world, cap_rows, HIDDEN), dtype=torch.bfloat16, device="cuda"))
+        return self._fixed[cap_rows]
+
+    def route_fixed(self, x, rows: int, cap_rows: int, send_blocks) -> None:
+        _check(load_library().p92b_ep_route_fixed(self.home.handle, _ptr(x), _ptr(self.router_weight), _ptr(self.bias),
+                                                  rows, self.routed_scale, _ptr(send_blocks), self.world, cap_rows,
+                                                  _stream()), "ep_route_fixed")
+
+    def experts_fixed(self, recv_blocks, cap_rows: int, out_slots) -> None:
+        _check(load_library().p92b_ep_experts_fixed(self.arrivals.handle, self.bank.handle, _ptr(recv_blocks), self.world,
+                                                    cap_rows, _ptr(out_slots), _stream()), "ep_experts_fixed")
+
+    def combine_fixed(self, x, returned_slots, out, rows: int) -> None:
+        _check(load_library().p92b_ep_combine_fixed(self.home.handle, self.shared.handle, self.bank.handle, _ptr(x),
+                                                    _ptr(returned_slots), _ptr(out), rows, _stream()), "ep_combine_fixed")
 
     # ---- device halves ---------------------------------------------------------------------
     def route(self, x, rows: int):
@@ -110,6 +139,51 @@ def forward_nccl(state: EpRank, x, out, rows: int, group=None) -> dict:
     returned = exchange_return(down, send_sizes, recv_sizes, group)
     state.combine(x, returned, out, rows)
     return {"sent_rows": send_sizes, "received_rows": int(recv.shape[0])}
+
+
+FIXED_MAX_ROWS = 64      # per-GPU batch up to which forward_auto takes the fixed-capacity exchange
+
+
+def forward_nccl_fixed(state: EpRank, x, out, rows: int, cap_rows: int, group=None) -> None:
+    """The block on `rows` home tokens with fixed-capacity exchange blocks: two equal-split all-to-alls
+    and no host synchronisation anywhere in the layer.  cap_rows (>= 8 * rows) must agree on all ranks."""
+    import torch.distributed as dist
+
+    send, recv, slots_out, slots_back = state.fixed_buffers(cap_rows)
+    state.route_fixed(x, rows, cap_rows, send)
+    dist.all_to_all_single(recv, send, group=group)
+    state.experts_fixed(recv, cap_rows, slots_out)
+    dist.all_to_all_single(slots_back, slots_out, group=group)
+    state.combine_fixed(x, slots_back, out, rows)
+
+
+def forward_auto(state: EpRank, x, out, rows: int, max_rows_any_rank: int, group=None) -> None:
+    """Fixed-capacity exchange for small batches (latency-bound, the padding is cheap), exact-size
+    exchange otherwise (bandwidth-bound).  max_rows_any_rank must be the same number on all ranks."""
+    if max_rows_any_rank <= FIXED_MAX_ROWS:
+        forward_nccl_fixed(state, x, out, rows, TOP_K * max_rows_any_rank, group)
+    else:
+        forward_nccl(state, x, out, rows, group)
+
+
+def forward_emulated_fixed(states: Sequence[EpRank], xs: Sequence, outs: Sequence, rows: Sequence[int]) -> None:
+    """forward_nccl_fixed for all ranks in one process: the all-to-all is a transpose of the blocks."""
+    world = len(states)
+    cap = TOP_K * max(rows)
+    bufs = [st.fixed_buffers(cap) for st in states]
+    for st, x, r, b in zip(states, xs, rows, bufs):
+        st.route_fixed(x, r, cap, b[0])
+    for d in range(world):
+        for s in range(world):
+            bufs[d][1][s].copy_(bufs[s][0][d])
+    for st, b in zip(states, bufs):
+        st.experts_fixed(b[1], cap, b[2])
+    for s in range(world):
+        for d in range(world):
+            bufs[s][3][d].copy_(bufs[d][2][s])
+    for st, x, o, r, b in zip(states, xs, outs, rows, bufs):
+        st.combine_fixed(x, b[3], o, r)
+    torch.cuda.synchronize()
 
 
 def forward_emulated(states: Sequence[EpRank], xs: Sequence, outs: Sequence, rows: Sequence[int]) -> None:

@@ -80,8 +80,9 @@ def test_shard_ranges():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world,rows", [(2, [5, 3]), (4, [2, 7, 4, 3]), (8, [4] * 8), (2, [130, 70])])
-def test_expert_parallel_block_matches_single_gpu(cuda, pkg, layer0, world, rows):
+@pytest.mark.parametrize("exchange", ["exact", "fixed"])
+@pytest.mark.parametrize("world,rows", [(2, [5, 3]), (4, [2, 7, 4, 3]), (8, [4] * 8), (2, [130, 70]), (4, [1, 1, 1, 1])])
+def test_expert_parallel_block_matches_single_gpu(cuda, pkg, layer0, world, rows, exchange):
     torch = cuda
     from p92moe_b200 import ep, synth
 
@@ -94,9 +95,12 @@ def test_expert_parallel_block_matches_single_gpu(cuda, pkg, layer0, world, rows
         shard = entries[first * 3:(first + local) * 3] + entries[256 * 3:]
         bank = pkg.ExpertBank(shard, first_expert=first, local_experts=local)
         states.append(ep.EpRank(r, world, bank, layer0.router_weight, layer0.bias, max_local_rows=max(rows),
-                                max_arrival_rows=sum(rows)))
+                                max_arrival_rows=world * max(rows)))
     outs = [torch.full_like(x, float("nan")) for x in xs]
-    ep.forward_emulated(states, xs, outs, rows)
+    if exchange == "exact":
+        ep.forward_emulated(states, xs, outs, rows)
+    else:
+        ep.forward_emulated_fixed(states, xs, outs, rows)
     # single GPU on all tokens at once
     x_all = torch.cat(xs).contiguous()
     total = x_all.shape[0]
