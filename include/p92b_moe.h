@@ -230,6 +230,39 @@ int p92b_ep_experts_fixed(p92b_plan* plan, const p92b_bank* bank, const uint8_t*
 int p92b_ep_combine_fixed(p92b_plan* home_plan, p92b_plan* shared_plan, const p92b_bank* bank, const uint16_t* input,
                           const uint16_t* returned_slots, uint16_t* output, int rows, void* stream);
 
+/* Small batches, fused: the whole expert-parallel block as ONE kernel launch per GPU, both exchanges
+ * done by the kernel with stores into the peers' memory over NVLink (no NCCL call, no host
+ * synchronisation).  Dispatch is an all-gather of the quantised token rows and their expert ids -
+ * with at most 32 tokens in flight every GPU can hold the whole batch and run the single-GPU law on
+ * its own experts - and the down product's epilogue places each result row directly into its home
+ * GPU's window; the home GPU combines in slot order and adds its shared expert.  No counterpart in the
+ * reference (one device, src/executor.cpp:20-23); the per-expert row order and the combine law are the
+ * single-device ones (cuda/nvfp4_grouped.cu:117-132, cuda/nvfp4_ops.cu:124-142).
+ *
+ * A window is this GPU's exchange memory (p92b_ep_window_bytes, allocated with cudaMalloc) plus the
+ * mapped windows of its peers.  Set-up, once: every process creates its window, publishes the 64-byte
+ * inter-process handle (p92b_ep_window_handle) to all others by any means, and connects with the
+ * handles of all ranks in rank order (its own entry is ignored).  world * rows_per_gpu <= 32,
+ * rows_per_gpu <= 8.  All GPUs must call p92b_ep_forward_fused the same number of times on a window,
+ * in the same order (the flags carry the call number); rows may differ per GPU and per call.  One
+ * window serves any number of layers.  The plan must have been created for at least
+ * world * rows_per_gpu rows.  A peer that never arrives ends the kernel after about a second with
+ * status 2 (a bounded wait gave up) in the plan's status word; the window is then out of step and must be
+ * recreated on all GPUs.  P92B_EP_WIDE=1 in the environment forces the 32-token variant of the kernel
+ * (otherwise chosen when world * rows_per_gpu > 16). */
+typedef struct p92b_ep_window p92b_ep_window;
+int p92b_ep_window_create(p92b_ep_window** out, int rank, int world, int rows_per_gpu);
+void p92b_ep_window_destroy(p92b_ep_window* window);
+size_t p92b_ep_window_bytes(void);
+int p92b_ep_window_handle(const p92b_ep_window* window, uint8_t* handle64);
+int p92b_ep_window_connect(p92b_ep_window* window, const uint8_t* handles /* [world][64] */);
+/* The same for windows that live in THIS process (one process driving several GPUs with peer access
+ * enabled, or tests): all_windows[r] is rank r's window. */
+int p92b_ep_window_connect_local(p92b_ep_window* window, p92b_ep_window* const* all_windows);
+int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window, const uint16_t* input,
+                          const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
+                          float routed_scale, void* stream);
+
 /* Device views of the last p92b_moe_forward's intermediates, for tests and
  * tracing (the reference keeps the same buffers as Model::Impl members,
  * src/model.cpp:872-885).  Valid until the next call on the plan. */
@@ -243,7 +276,7 @@ typedef struct p92b_plan_views {
     const int32_t* offsets;       /* [257] */
     const uint16_t* mixed;        /* BF16 down outputs [mixed rows][hidden] */
     const int32_t* mixed_index;   /* [rows*8 + rows]: row of `mixed` holding assignment (row, slot), then the shared rows */
-    const int32_t* status;        /* device int: 0 ok, else first error code a kernel recorded */
+    const int32_t* status;        /* device int: 0 ok, else the first error a kernel recorded: 1 expert id out of range (clamped), 2 a bounded wait gave up */
     const unsigned long long* trace; /* [trace_blocks][64] %globaltimer stamps of the last fused decode launch
                                         (written only when P92B_TRACE is set in the environment) */
     int trace_blocks;

@@ -1,0 +1,922 @@
+// Expert-parallel MoE block for small batches (decode, MTP verify) as ONE persistent kernel per GPU,
+// the two exchanges done by the kernel itself with stores into the peers' memory over NVLink.
+//
+// At a handful of tokens per GPU the exchanges carry a few kilobytes; what they cost is latency: a
+// library all-to-all is a launch of its own, and around it sit the launches that pack and unpack
+// its buffers.  Here the layer is one launch per GPU and the fabric is used the way the sizes ask:
+//
+//   dispatch = all-gather.  Every GPU pushes its (at most 8) quantised token rows and their top-8
+//       expert ids into every peer's window (≈1.5 KB per token and peer), then raises a flag there.
+//       With all tokens of the batch present, a GPU runs the single-GPU law restricted to its own
+//       experts: per expert the rows are ordered by global token index (home GPU, token), which is
+//       the order one GPU would give them (cuda/nvfp4_grouped.cu:117-132).
+//   combine = direct placement.  The down product's epilogue stores each BF16 row straight into the
+//       home GPU's window at [token][slot]; when all tiles of a GPU are done it raises a flag at
+//       every home.  The home GPU then applies the device law in slot order and adds its shared
+//       expert (cuda/nvfp4_ops.cu:124-142,92-95).
+//
+// Inside a GPU the phases are those of the single-GPU decode kernel (decode_mega.cu): router rows
+// and token quantisation spread over the grid, routing lists in shared memory, gate/up and down
+// tiles through one TMA ring and one tcgen05 pipeline, static deal of tiles.  The token side of
+// every MMA is the whole gathered batch (16 or 32 columns).
+//
+// Windows are double-buffered by launch parity; flags carry the launch number, so nothing is ever
+// reset.  A GPU cannot be more than one launch ahead of any peer (it needs the peer's results of
+// launch k to finish launch k), which is what makes two buffers enough.  Every wait - on a peer's
+// flag, a device-wide counter or an mbarrier - is bounded by wall time and ends in a status word.
+#include "p92b_common.cuh"
+#include "tc_ptx.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+namespace p92b {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kEpThreads = 192;
+constexpr int kEpMaxLocalRows = 8;                 // home tokens per GPU
+constexpr int kEpMaxTokens = 32;                   // gathered batch (all GPUs)
+constexpr int kEpMaxWorld = 16;
+constexpr int kTile = 128;
+constexpr int kKB = 128;
+constexpr int kSlab = 2048;
+constexpr int kOffA0 = 0, kOffA1 = 16384, kOffSfA0 = 32768, kOffB0 = 36864;   // SFA1 follows SFA0 by one slab
+constexpr int kStages = 4;
+constexpr int kAccumStride = 32;
+constexpr int kAccumCols = 64;
+constexpr int kSfColsPerBuffer = 64;
+constexpr int kAccumBuffers = 4;
+constexpr int kTmemCols = 512;
+constexpr int kMaxSlots = kExperts + 1;            // local experts (all 256 on a single GPU) + the shared expert
+
+// ---- window layout (identical on every GPU) --------------------------------------------------
+constexpr std::size_t kWinFlagsGather = 0;                                  // u32 [16]
+constexpr std::size_t kWinFlagsReturn = 64;                                 // u32 [16]
+constexpr std::size_t kWinRowsOf = 128;                                     // i32 [2][16]
+constexpr std::size_t kWinXq = 256;                                         // [2][32][1280]
+constexpr std::size_t kXqRow = 1280;
+constexpr std::size_t kWinXqParity = kEpMaxTokens * kXqRow;
+constexpr std::size_t kWinXs = kWinXq + 2 * kWinXqParity;                   // [2][40][512]
+constexpr std::size_t kWinXsParity = 40 * 512;
+constexpr std::size_t kWinIds = kWinXs + 2 * kWinXsParity;                  // i32 [2][256]
+constexpr std::size_t kWinIdsParity = kEpMaxTokens * kTop * 4;
+constexpr std::size_t kWinRet = kWinIds + 2 * kWinIdsParity;                // bf16 [2][64][2560]
+constexpr std::size_t kWinRetParity = static_cast<std::size_t>(kEpMaxLocalRows) * kTop * 2560 * 2;
+constexpr std::size_t kWinBytes = kWinRet + 2 * kWinRetParity;
+static_assert(kWinXs % 16 == 0 && kWinRet % 256 == 0, "window regions must keep their alignment");
+
+struct EpParams {
+    BankView bank;
+    const std::uint16_t* x;
+    const std::uint16_t* router_w;
+    const float* bias;
+    std::uint16_t* out;
+    float* logits;
+    std::int32_t* ids;
+    float* route_weights;
+    std::int32_t* counts;
+    std::uint8_t* xq_tok;          // local staging of this GPU's quantised rows [16][H/2]
+    std::uint8_t* xs_tok;
+    std::uint8_t* hq;
+    std::uint8_t* hs;
+    std::uint16_t* mixed;          // shared-expert rows only
+    unsigned* sync;                // [2] device-wide arrival counters of the plan (+2, +3 of mega_sync)
+    std::int32_t* gu_done;
+    std::int32_t* status;
+    unsigned long long* trace;
+    std::uint8_t* win[kEpMaxWorld];
+    unsigned epoch;                // launches of this kernel on the plan before this one
+    unsigned wepoch;               // launches on the window before this one (same on every GPU)
+    float routed_scale;
+    float quant_scale;
+    int rows;                      // this GPU's home tokens
+    int rank, world, rows_per_gpu;
+    int hidden, inter;
+};
+
+struct Routing {
+    std::int32_t ids[kEpMaxTokens * kTop];           // gathered, [global token][slot]
+    std::uint32_t expert_mask[kMaxSlots];            // local expert -> tokens routed to it; [local] = shared
+    std::uint32_t slot_mask[kMaxSlots];              // active slot -> tokens
+    std::int32_t active[kMaxSlots];                  // active slot -> bank entry; slot 0 is the shared expert
+    std::int32_t rows_of[kEpMaxWorld];
+    std::int32_t n_active;
+    float weights[kEpMaxLocalRows * kTop];           // home tokens only
+    std::int32_t my_ids[kEpMaxLocalRows * kTop];
+    float logits[kEpMaxLocalRows * kExperts];
+    float bias[kExperts];
+};
+
+__device__ __forceinline__ int slab_of_slot(int slot, int n_active) {
+    return (slot == 0 ? n_active - 1 : slot - 1) * kTile;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned target) {
+    const std::uint64_t start = global_timer_ns();
+    while (static_cast<int>(ld_acquire_gpu(counter) - target) < 0) {
+        if (global_timer_ns() - start > 1000000000ULL) return false;
+    }
+    return true;
+}
+// A flag another GPU writes into this GPU's memory.
+__device__ __forceinline__ bool wait_flag(const unsigned* flag, unsigned target) {
+    const std::uint64_t start = global_timer_ns();
+    while (static_cast<int>(ld_acquire_sys(flag) - target) < 0) {
+        if (global_timer_ns() - start > 1000000000ULL) return false;
+    }
+    return true;
+}
+
+// Device-wide rendezvous of the co-resident blocks; the fences are system-wide because the stores
+// it orders may have gone to a peer.
+__device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned target) {
+    __shared__ int ok;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        fence_proxy_async_all();
+        atomicAdd(counter, 1U);
+        ok = wait_counter(counter, target) ? 1 : 0;
+        __threadfence_system();
+        fence_proxy_async_all();
+    }
+    __syncthreads();
+    return ok != 0;
+}
+
+// Static deal of tiles to blocks (same scheme as the single-GPU decode kernel): gate/up tiles
+// round-robin, down tiles fill every block to a common level counted in ring stages.
+struct Deal {
+    int gu_items, dn_items, grid, n_gu, dn_begin, dn_count, total_cap, leftovers;
+    __device__ void init(int n_active, int gu_tiles, int dn_tiles, int grid_, int block) {
+        grid = grid_;
+        gu_items = n_active * gu_tiles;
+        dn_items = n_active * dn_tiles;
+        const int q = gu_items / grid;
+        const int r = gu_items - q * grid;
+        const int stages = gu_items * 10 + dn_items * 2;
+        const int level = stages / grid;
+        int cap_hi = (level - 10 * (q + 1)) / 2;
+        int cap_lo = (level - 10 * q) / 2;
+        cap_hi = cap_hi < 0 ? 0 : cap_hi;
+        cap_lo = cap_lo < 0 ? 0 : cap_lo;
+        n_gu = q + (block < r ? 1 : 0);
+        const int mine = block < r ? cap_hi : cap_lo;
+        const int prefix = block >= r ? (block - r) * cap_lo : (grid - r) * cap_lo + block * cap_hi;
+        total_cap = r * cap_hi + (grid - r) * cap_lo;
+        dn_begin = prefix < dn_items ? prefix : dn_items;
+        dn_count = dn_items - dn_begin < mine ? dn_items - dn_begin : mine;
+        leftovers = dn_items > total_cap ? dn_items - total_cap : 0;
+    }
+    __device__ bool item(int i, int block, int gu_tiles, int dn_tiles, int* kind, int* slot, int* m_tile) const {
+        if (i < n_gu) {
+            const int g = block + i * grid;
+            *kind = 0; *slot = g / gu_tiles; *m_tile = g - *slot * gu_tiles;
+            return true;
+        }
+        i -= n_gu;
+        int d;
+        if (i < dn_count) {
+            d = dn_begin + i;
+        } else {
+            const int j = block + (i - dn_count) * grid;
+            if (j >= leftovers) return false;
+            d = total_cap + j;
+        }
+        *kind = 1; *slot = d / dn_tiles; *m_tile = d - *slot * dn_tiles;
+        return true;
+    }
+};
+
+template <int kN>
+struct StageLayout {
+    static constexpr int kOffB1 = kOffB0 + kN * kKB;
+    static constexpr int kOffSfB0 = kOffB0 + 2 * kN * kKB;
+    static constexpr int kOffSfB1 = kOffSfB0 + kSlab;
+    static constexpr int kStage = kOffSfB0 + 2 * kSlab;
+    static constexpr int kSmem = kStages * kStage + 1024;
+};
+
+template <int kN>
+__global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __grid_constant__ CUtensorMap map_tok,
+                                                                      const __grid_constant__ CUtensorMap map_h,
+                                                                      const EpParams p) {
+    using L = StageLayout<kN>;
+    extern __shared__ std::uint8_t smem_raw[];
+    __shared__ Routing rt;
+    __shared__ __align__(8) std::uint64_t barrier_words[3 * kStages + 2 * kAccumBuffers];
+    __shared__ std::uint32_t tmem_slot_word;
+    __shared__ volatile std::uint32_t abort_word;
+
+    const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    const std::uint32_t bars = smem_u32(barrier_words);
+    auto weight_bar = [&](int s) { return bars + 8U * s; };
+    auto token_bar = [&](int s) { return bars + 8U * (kStages + s); };
+    auto empty_bar = [&](int s) { return bars + 8U * (2 * kStages + s); };
+    auto accum_full = [&](int b) { return bars + 8U * (3 * kStages + b); };
+    auto accum_empty = [&](int b) { return bars + 8U * (3 * kStages + kAccumBuffers + b); };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rows = p.rows;
+    const int hidden = p.hidden;
+    const int inter = p.inter;
+    const int grid = gridDim.x;
+    const int block = blockIdx.x;
+    const int world = p.world;
+    const int rpg = p.rows_per_gpu;
+    const int parity = static_cast<int>(p.wepoch & 1U);
+    const unsigned flag_target = p.wepoch + 1U;
+    std::uint8_t* const my_win = p.win[p.rank];
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(weight_bar(s), 1);
+            mbar_init(token_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < kAccumBuffers; ++b) {
+            mbar_init(accum_full(b), 1);
+            mbar_init(accum_empty(b), 4);
+        }
+        abort_word = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&map_tok);
+        prefetch_tensormap(&map_h);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_slot_word), kTmemCols);
+        tmem_relinquish();
+    }
+    // router rows and bias do not depend on the kernel upstream
+    const int my_experts = block + grid < kExperts ? 2 : (block < kExperts ? 1 : 0);
+    std::uint16_t* w_rows = reinterpret_cast<std::uint16_t*>(smem_raw + (base - smem_u32(smem_raw)));
+    std::uint16_t* x_rows = w_rows + 2 * hidden;
+    const int vec_per_row = hidden / 8;
+    for (int i = threadIdx.x; i < my_experts * vec_per_row; i += kEpThreads) {
+        const int r = i / vec_per_row;
+        const int c = i - r * vec_per_row;
+        reinterpret_cast<uint4*>(w_rows + r * hidden)[c] =
+            __ldg(reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
+    }
+    for (int e = threadIdx.x; e < kExperts; e += kEpThreads) rt.bias[e] = __ldg(p.bias + e);
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int i = threadIdx.x; i < rows * vec_per_row; i += kEpThreads) {
+        const int r = i / vec_per_row;
+        const int c = i - r * vec_per_row;
+        reinterpret_cast<uint4*>(x_rows + r * hidden)[c] =
+            __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r) * hidden) + c);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const std::uint32_t tmem_base = tmem_slot_word;
+    auto stamp = [&](int slot) {
+        if (p.trace != nullptr) p.trace[static_cast<std::size_t>(block) * 64 + slot] = global_timer_ns();
+    };
+    if (threadIdx.x == 0) stamp(0);
+    auto give_up = [&](int code) {
+        abort_word = 1;
+        atomicCAS(p.status, kStatusOk, code);
+    };
+
+    // ------------------------------------------------------------------ P0: home tokens
+    {
+        // More than one token is in flight across the GPUs, so the router uses the batched order
+        // (lane l sums columns l, l+32, ...; shuffle-down tree: cuda/nvfp4_ops.cu:178-207) - unless
+        // this is the only GPU and it has one token, which is the single-token law (:161-176).
+        if (world == 1 && rows == 1) {
+            for (int q = warp; q < my_experts; q += kEpThreads / 32) {
+                const std::uint16_t* wr = w_rows + q * hidden;
+                float value = 0.0F;
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float partial = 0.0F;
+                    for (int c = lane + 32 * v; c < hidden; c += 256) {
+                        partial = fmaf(bf16_bits_to_float(x_rows[c]), bf16_bits_to_float(wr[c]), partial);
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) partial += __shfl_down_sync(0xffffffffU, partial, off);
+                    const float warp_sum = __shfl_sync(0xffffffffU, partial, 0);
+                    if (lane == v) value = warp_sum;
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
+                if (lane == 0) p.logits[block + q * grid] = value;
+            }
+        } else {
+            for (int q = warp; q < my_experts * rows; q += kEpThreads / 32) {
+                const int r = q / rows;
+                const int t = q - r * rows;
+                const std::uint16_t* wr = w_rows + r * hidden;
+                const std::uint16_t* xr = x_rows + t * hidden;
+                float value = 0.0F;
+#pragma unroll 8
+                for (int c = lane; c < hidden; c += 32) {
+                    value = fmaf(bf16_bits_to_float(xr[c]), bf16_bits_to_float(wr[c]), value);
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
+                if (lane == 0) p.logits[static_cast<std::size_t>(t) * kExperts + block + r * grid] = value;
+            }
+        }
+        const int blocks16 = hidden / 16;
+        const int g = block * kEpThreads + threadIdx.x;
+        if (g < rows * blocks16) {
+            const int t = g / blocks16;
+            const int b = g - t * blocks16;
+            const uint4* src = reinterpret_cast<const uint4*>(x_rows + t * hidden + b * 16);
+            const uint4 lo = src[0];
+            const uint4 hi = src[1];
+            const std::uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[2 * i] = __uint_as_float(words[i] << 16);
+                v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+            }
+            std::uint8_t scale_bits;
+            const uint2 packed = quantize_block16(v, p.quant_scale, &scale_bits);
+            *reinterpret_cast<uint2*>(p.xq_tok + static_cast<std::size_t>(t) * (hidden / 2) + b * 8) = packed;
+            p.xs_tok[static_cast<std::size_t>(b >> 2) * 512 + t * 16 + (b & 3)] = scale_bits;
+        }
+        if (block == 0) {
+            for (int i = threadIdx.x; i <= kExperts; i += kEpThreads) p.gu_done[i] = 0;
+        }
+    }
+    if (threadIdx.x == 0) stamp(1);
+    if (!grid_rendezvous(p.sync + 0, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
+    if (threadIdx.x == 0) stamp(2);
+
+    // ------------------------------------------------- dispatch: block d pushes to GPU d
+    if (!abort_word && block < world) {
+        for (int i = threadIdx.x; i < rows * kExperts; i += kEpThreads) rt.logits[i] = __ldcg(p.logits + i);
+        __syncthreads();
+        for (int t = warp; t < rows; t += kEpThreads / 32) {
+            warp_top8(rt.logits + t * kExperts, rt.bias, rt.my_ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
+        }
+        __syncthreads();
+        std::uint8_t* dst = p.win[block];
+        const int first_token = p.rank * rpg;
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(p.xq_tok);
+            uint4* out = reinterpret_cast<uint4*>(dst + kWinXq + parity * kWinXqParity + first_token * kXqRow);
+            for (int i = threadIdx.x; i < rows * static_cast<int>(kXqRow / 16); i += kEpThreads) out[i] = __ldcg(src + i);
+        }
+        {
+            const int chunks = hidden / 64;               // 40 scale tiles, one word per (tile, token)
+            std::uint8_t* xs_out = dst + kWinXs + parity * kWinXsParity;
+            for (int i = threadIdx.x; i < rows * chunks; i += kEpThreads) {
+                const int t = i / chunks;
+                const int c = i - t * chunks;
+                const std::uint32_t word = __ldcg(reinterpret_cast<const std::uint32_t*>(p.xs_tok + c * 512 + t * 16));
+                *reinterpret_cast<std::uint32_t*>(xs_out + c * 512 + (first_token + t) * 16) = word;
+            }
+        }
+        {
+            std::int32_t* ids_out = reinterpret_cast<std::int32_t*>(dst + kWinIds + parity * kWinIdsParity) + first_token * kTop;
+            for (int i = threadIdx.x; i < rows * kTop; i += kEpThreads) ids_out[i] = rt.my_ids[i];
+            if (threadIdx.x == 0) reinterpret_cast<std::int32_t*>(dst + kWinRowsOf)[parity * kEpMaxWorld + p.rank] = rows;
+        }
+        if (block == p.rank) {
+            for (int i = threadIdx.x; i < rows * kTop; i += kEpThreads) {
+                p.ids[i] = rt.my_ids[i];
+                p.route_weights[i] = rt.weights[i];
+            }
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) st_release_sys(reinterpret_cast<unsigned*>(dst + kWinFlagsGather) + p.rank, flag_target);
+    }
+    if (threadIdx.x == 0) stamp(3);
+    if (!abort_word && threadIdx.x < world) {
+        if (!wait_flag(reinterpret_cast<const unsigned*>(my_win + kWinFlagsGather) + threadIdx.x, flag_target)) {
+            give_up(kStatusWaitExpired);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) stamp(4);
+
+    // ------------------------------------------------- routing lists of this GPU's experts
+    const int local = p.bank.local_experts;
+    if (!abort_word) {
+        for (int i = threadIdx.x; i < kMaxSlots; i += kEpThreads) rt.expert_mask[i] = 0;
+        if (threadIdx.x < world) {
+            rt.rows_of[threadIdx.x] =
+                __ldcg(reinterpret_cast<const std::int32_t*>(my_win + kWinRowsOf) + parity * kEpMaxWorld + threadIdx.x);
+        }
+        __syncthreads();
+        const std::int32_t* gathered = reinterpret_cast<const std::int32_t*>(my_win + kWinIds + parity * kWinIdsParity);
+        for (int a = threadIdx.x; a < world * rpg * kTop; a += kEpThreads) {
+            const int g = a / kTop;
+            const int src = g / rpg;
+            std::int32_t e = -1;
+            if (g - src * rpg < rt.rows_of[src]) {
+                e = __ldcg(gathered + a);
+                const int le = e - p.bank.first_expert;
+                if (le >= 0 && le < local) atomicOr(&rt.expert_mask[le], 1U << g);
+            }
+            rt.ids[a] = e;
+        }
+        if (threadIdx.x == 0) rt.expert_mask[local] = ((rows >= 32 ? 0U : (1U << rows)) - 1U) << (p.rank * rpg);
+        __syncthreads();
+        if (warp == 0) {
+            int found = 0;
+            for (int e0 = 0; e0 < local; e0 += 32) {
+                const int e = e0 + lane;
+                const std::uint32_t m = e < local ? rt.expert_mask[e] : 0U;
+                const unsigned vote = __ballot_sync(0xffffffffU, m != 0U);
+                if (m != 0U) {
+                    const int slot = 1 + found + __popc(vote & ((1U << lane) - 1U));
+                    rt.active[slot] = e;
+                    rt.slot_mask[slot] = m;
+                }
+                found += __popc(vote);
+            }
+            if (lane == 0) {
+                rt.active[0] = local;
+                rt.slot_mask[0] = rt.expert_mask[local];
+                rt.n_active = found + 1;
+            }
+        }
+        if (block == 0) {
+            for (int e = threadIdx.x; e < local; e += kEpThreads) p.counts[p.bank.first_expert + e] = __popc(rt.expert_mask[e]);
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) stamp(5);
+
+    // ------------------------------------------------------------ gate/up and down tiles
+    const int gu_tiles = inter / kTile;
+    const int dn_tiles = hidden / kTile;
+    const int gu_kblocks = (hidden / 2) / kKB;
+    const int dn_stages = (inter / 2) / kKB / 2;
+    Deal deal;
+    deal.init(abort_word ? 0 : rt.n_active, gu_tiles, dn_tiles, grid, block);
+    const int token_row0 = parity * kEpMaxTokens;         // first row of this launch's batch in the token map
+    const std::uint8_t* xs_batch = my_win + kWinXs + parity * kWinXsParity;
+
+    if (warp == 0) {
+        if (elect_one() && !abort_word) {
+            int stage = 0;
+            std::uint32_t phase = 0;
+            int kind, slot, m_tile;
+            fence_proxy_async_all();          // the gathered rows were written by ordinary stores (peers', over NVLink)
+            for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+                const int entry = rt.active[slot];
+                const int n_stages = kind == 0 ? gu_kblocks : dn_stages;
+                bool tokens_ready = kind == 0;
+                for (int s = 0; s < n_stages; ++s) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                    const std::uint32_t st = base + stage * L::kStage;
+                    mbar_arrive_expect_tx(weight_bar(stage), kChunkBytes);
+                    if (kind == 0) {
+                        bulk_load(st, p.bank.g13 + ((static_cast<std::size_t>(entry) * gu_tiles + m_tile) * gu_kblocks + s) *
+                                                       kChunkBytes,
+                                  kChunkBytes, weight_bar(stage));
+                        mbar_arrive_expect_tx(token_bar(stage), kN * kKB + kSlab);
+                        tma_load_2d(st + kOffB0, &map_tok, token_bar(stage), s * kKB, token_row0);
+                        bulk_load(st + L::kOffSfB0, xs_batch + static_cast<std::size_t>(s * 4) * 512, kSlab, token_bar(stage));
+                    } else {
+                        bulk_load(st, p.bank.g2 + ((static_cast<std::size_t>(entry) * dn_tiles + m_tile) * dn_stages + s) *
+                                                      kChunkBytes,
+                                  kChunkBytes, weight_bar(stage));
+                        if (!tokens_ready) {
+                            if (!wait_counter(reinterpret_cast<const unsigned*>(p.gu_done + slot),
+                                              static_cast<unsigned>(gu_tiles))) {
+                                give_up(kStatusWaitExpired);
+                                break;
+                            }
+                            fence_proxy_async_all();
+                            tokens_ready = true;
+                        }
+                        const int pp0 = slab_of_slot(slot, rt.n_active);
+                        mbar_arrive_expect_tx(token_bar(stage), 2 * kN * kKB + 2 * kSlab);
+                        tma_load_2d(st + kOffB0, &map_h, token_bar(stage), (2 * s) * kKB, pp0);
+                        tma_load_2d(st + L::kOffB1, &map_h, token_bar(stage), (2 * s + 1) * kKB, pp0);
+                        const std::uint8_t* bsf = p.hs + (static_cast<std::size_t>(pp0 >> 7) * (inter / 64) + (2 * s) * 4) * 512;
+                        bulk_load(st + L::kOffSfB0, bsf, kSlab, token_bar(stage));
+                        bulk_load(st + L::kOffSfB1, bsf + 4 * 512, kSlab, token_bar(stage));
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1U; }
+                }
+            }
+            stamp(6);
+        }
+    } else if (warp == 1) {
+        if (elect_one() && !abort_word) {
+            int stage = 0;
+            std::uint32_t phase = 0;
+            int buffer = 0;
+            std::uint32_t accum_phase = 0;
+            constexpr std::uint32_t idesc = idesc_nvf4(kTile, kN);
+            const std::uint32_t sf_tmem = tmem_base + kAccumBuffers * kAccumCols;
+            int sf_buffer = 0;
+            int kind, slot, m_tile;
+            for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+                if (!mbar_wait(accum_empty(buffer), ((accum_phase >> buffer) & 1U) ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                tc_fence_after();
+                const std::uint32_t accum = tmem_base + buffer * kAccumCols;
+                const int n_stages = kind == 0 ? gu_kblocks : dn_stages;
+                bool ok = true;
+                for (int s = 0; s < n_stages; ++s) {
+                    if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) {
+                        give_up(kStatusWaitExpired);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const std::uint32_t st = base + stage * L::kStage;
+                    const std::uint32_t sfc = sf_tmem + sf_buffer * kSfColsPerBuffer;
+                    const int slabs = kind == 0 ? 3 : 4;
+                    for (int o = 0; o < slabs; ++o) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            tc_copy_sf(sfc + o * 16 + k * 4,
+                                       desc_scale_atom(st + (o < 2 ? kOffSfA0 + o * kSlab : L::kOffSfB0 + (o - 2) * kSlab) + k * 512));
+                        }
+                    }
+                    const std::uint64_t a0 = desc_k_major_sw128(st + kOffA0);
+                    const std::uint64_t a1 = desc_k_major_sw128(st + kOffA1);
+                    const std::uint64_t b0 = desc_k_major_sw128(st + kOffB0);
+                    const std::uint64_t b1 = desc_k_major_sw128(st + L::kOffB1);
+                    if (kind == 0) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            mma_nvf4(accum, a0 + 2 * k, b0 + 2 * k, idesc, sfc + k * 4, sfc + 32 + k * 4, s > 0 || k > 0);
+                            mma_nvf4(accum + kAccumStride, a1 + 2 * k, b0 + 2 * k, idesc, sfc + 16 + k * 4,
+                                     sfc + 32 + k * 4, s > 0 || k > 0);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            mma_nvf4(accum, a0 + 2 * k, b0 + 2 * k, idesc, sfc + k * 4, sfc + 32 + k * 4, s > 0 || k > 0);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            mma_nvf4(accum, a1 + 2 * k, b1 + 2 * k, idesc, sfc + 16 + k * 4, sfc + 48 + k * 4, true);
+                        }
+                    }
+                    tc_commit(empty_bar(stage));
+                    sf_buffer ^= 1;
+                    if (++stage == kStages) { stage = 0; phase ^= 1U; }
+                }
+                if (!ok) break;
+                tc_commit(accum_full(buffer));
+                accum_phase ^= 1U << buffer;
+                buffer = (buffer + 1) % kAccumBuffers;
+            }
+            stamp(7);
+        }
+    } else if (!abort_word) {
+        const int quarter = warp & 3;
+        int buffer = 0;
+        std::uint32_t accum_phase = 0;
+        int kind, slot, m_tile;
+        for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+            if (!mbar_wait(accum_full(buffer), (accum_phase >> buffer) & 1U)) { give_up(kStatusWaitExpired); break; }
+            accum_phase ^= 1U << buffer;
+            tc_fence_after();
+            const int entry = rt.active[slot];
+            const std::uint32_t mask = rt.slot_mask[slot];
+            const int pp0 = slab_of_slot(slot, rt.n_active);
+            const std::uint32_t lane_base = tmem_base + buffer * kAccumCols + (static_cast<std::uint32_t>(quarter * 32) << 16);
+            const int row = m_tile * kTile + quarter * 32 + lane;
+            if (kind == 0) {
+                const float alpha_g = p.bank.alpha[entry * 3 + 0];
+                const float alpha_u = p.bank.alpha[entry * 3 + 1];
+                const int sf_col = row >> 4;
+#pragma unroll
+                for (int c = 0; c < kN / 16; ++c) {
+                    if ((mask >> (16 * c) & 0xffffU) == 0U) continue;                 // warp uniform
+                    std::uint32_t g[16], u[16];
+                    tmem_load16(lane_base + 16 * c, g);
+                    tmem_load16(lane_base + kAccumStride + 16 * c, u);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) {
+                        const int token = 16 * c + n;
+                        if (!(mask >> token & 1U)) continue;                          // warp uniform
+                        const std::size_t pp = static_cast<std::size_t>(pp0 + __popc(mask & ((1U << token) - 1U)));
+                        const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[n]) * alpha_g));
+                        const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[n]) * alpha_u));
+                        const float h = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
+                        float amax = fabsf(h);
+#pragma unroll
+                        for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffU, amax, off));
+                        const __nv_fp8_e4m3 scale(amax * (p.quant_scale / 6.0F));
+                        const float decoded = static_cast<float>(scale);
+                        const float multiplier = decoded == 0.0F ? 0.0F : p.quant_scale / decoded;
+                        const float q = h * multiplier;
+                        const float q_next = __shfl_xor_sync(0xffffffffU, q, 1);
+                        if ((lane & 1) == 0) {
+                            p.hq[pp * (inter / 2) + (row >> 1)] =
+                                static_cast<std::uint8_t>(__nv_fp4x2_e2m1(make_float2(q, q_next)).__x);
+                        }
+                        if ((lane & 15) == 0) {
+                            p.hs[((pp >> 7) * (inter / 64) + (sf_col >> 2)) * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4 +
+                                 (sf_col & 3)] = scale.__x;
+                        }
+                    }
+                }
+                tc_fence_before();
+                __threadfence();
+                fence_proxy_async_all();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    mbar_arrive(accum_empty(buffer));
+                    mbar_arrive(accum_empty(buffer));
+                    mbar_arrive(accum_empty(buffer));
+                    mbar_arrive(accum_empty(buffer));
+                    atomicAdd(p.gu_done + slot, 1);
+                }
+            } else {
+                const float alpha = p.bank.alpha[entry * 3 + 2];
+                const int expert = p.bank.first_expert + entry;
+                std::uint32_t remaining = mask;
+#pragma unroll
+                for (int c = 0; c < kN / 16; ++c) {
+                    if (remaining == 0U) break;                                       // warp uniform
+                    std::uint32_t d[16];
+                    tmem_load16(lane_base + 16 * c, d);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) {
+                        if (remaining == 0U) continue;
+                        // column 16c+n is the (16c+n)-th row of this expert = its (16c+n)-th token
+                        const int token = __ffs(remaining) - 1;
+                        remaining &= remaining - 1U;
+                        const std::uint16_t value = float_to_bf16_bits(__uint_as_float(d[n]) * alpha);
+                        if (slot == 0) {
+                            p.mixed[static_cast<std::size_t>(pp0 + 16 * c + n) * hidden + row] = value;
+                        } else {
+                            const int home = token / rpg;
+                            const int t_local = token - home * rpg;
+                            int k = 0;
+#pragma unroll
+                            for (int kk = 1; kk < kTop; ++kk) k = rt.ids[token * kTop + kk] == expert ? kk : k;
+                            std::uint16_t* ret = reinterpret_cast<std::uint16_t*>(p.win[home] + kWinRet + parity * kWinRetParity);
+                            ret[static_cast<std::size_t>(t_local * kTop + k) * hidden + row] = value;
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accum_empty(buffer));
+            }
+            buffer = (buffer + 1) % kAccumBuffers;
+        }
+        if (warp == 2 && lane == 0) stamp(8);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0) stamp(9);
+
+    // --------------------------------------- all tiles of this GPU done -> tell every home GPU
+    if (!grid_rendezvous(p.sync + 1, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
+    if (threadIdx.x == 0) stamp(10);
+    if (abort_word) return;
+    if (block < world && threadIdx.x == 0) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<unsigned*>(p.win[block] + kWinFlagsReturn) + p.rank, flag_target);
+    }
+    const int vectors = hidden / 8;
+    if (block * kEpThreads >= rows * vectors) return;          // no share of the combine
+    if (threadIdx.x < world) {
+        if (!wait_flag(reinterpret_cast<const unsigned*>(my_win + kWinFlagsReturn) + threadIdx.x, flag_target)) {
+            give_up(kStatusWaitExpired);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) stamp(11);
+    if (abort_word) return;
+
+    // ------------------------------------------------------------------ combine (home tokens)
+    const std::uint16_t* ret = reinterpret_cast<const std::uint16_t*>(my_win + kWinRet + parity * kWinRetParity);
+    const int shared_pp0 = slab_of_slot(0, rt.n_active);
+    for (int v = block * kEpThreads + threadIdx.x; v < rows * vectors; v += grid * kEpThreads) {
+        const int row = v / vectors;
+        const int c8 = v - row * vectors;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0F;
+#pragma unroll
+        for (int slot = 0; slot < kTop; ++slot) {
+            const float w = __ldcg(p.route_weights + row * kTop + slot);
+            const uint4 r = __ldcg(reinterpret_cast<const uint4*>(ret + static_cast<std::size_t>(row * kTop + slot) * hidden + c8 * 8));
+            const std::uint32_t words[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[2 * k] = fmaf(__uint_as_float(words[k] << 16), w, acc[2 * k]);
+                acc[2 * k + 1] = fmaf(__uint_as_float(words[k] & 0xffff0000U), w, acc[2 * k + 1]);
+            }
+        }
+        const uint4 sh = __ldcg(reinterpret_cast<const uint4*>(p.mixed + static_cast<std::size_t>(shared_pp0 + row) * hidden + c8 * 8));
+        const std::uint32_t sw[4] = {sh.x, sh.y, sh.z, sh.w};
+        std::uint32_t out_words[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float lo = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k])) + __uint_as_float(sw[k] << 16);
+            const float hi = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k + 1])) + __uint_as_float(sw[k] & 0xffff0000U);
+            out_words[k] = static_cast<std::uint32_t>(float_to_bf16_bits(lo)) |
+                           (static_cast<std::uint32_t>(float_to_bf16_bits(hi)) << 16);
+        }
+        *reinterpret_cast<uint4*>(p.out + static_cast<std::size_t>(row) * hidden + c8 * 8) =
+            make_uint4(out_words[0], out_words[1], out_words[2], out_words[3]);
+    }
+    if (threadIdx.x == 0) stamp(12);
+}
+
+}  // namespace
+
+}  // namespace p92b
+
+// ---- the window object ---------------------------------------------------------------------------
+struct p92b_ep_window {
+    int rank = 0, world = 1, rows_per_gpu = 0;
+    std::uint8_t* local = nullptr;
+    std::uint8_t* peers[p92b::kEpMaxWorld] = {};
+    bool opened[p92b::kEpMaxWorld] = {};
+    bool connected = false;
+    unsigned epoch = 0;
+    CUtensorMap map_tok[2] = {};
+};
+
+extern "C" {
+
+int p92b_ep_window_create(p92b_ep_window** out, int rank, int world, int rows_per_gpu) {
+    using namespace p92b;
+    if (out == nullptr) return cudaErrorInvalidValue;
+    *out = nullptr;
+    if (world <= 0 || world > kEpMaxWorld || rank < 0 || rank >= world || kExperts % world != 0 || rows_per_gpu <= 0 ||
+        rows_per_gpu > kEpMaxLocalRows || world * rows_per_gpu > kEpMaxTokens) {
+        return cudaErrorInvalidValue;
+    }
+    p92b_ep_window* w = new (std::nothrow) p92b_ep_window();
+    if (w == nullptr) return cudaErrorMemoryAllocation;
+    w->rank = rank;
+    w->world = world;
+    w->rows_per_gpu = rows_per_gpu;
+    cudaError_t st = cudaMalloc(reinterpret_cast<void**>(&w->local), kWinBytes);
+    if (st == cudaSuccess) st = cudaMemset(w->local, 0, kWinBytes);
+    if (st == cudaSuccess) st = cudaDeviceSynchronize();
+    bool ok = st == cudaSuccess;
+    ok = ok && make_operand_map(&w->map_tok[0], w->local + kWinXq, 2 * kEpMaxTokens, kXqRow, 16) == cudaSuccess;
+    ok = ok && make_operand_map(&w->map_tok[1], w->local + kWinXq, 2 * kEpMaxTokens, kXqRow, 32) == cudaSuccess;
+    if (!ok) {
+        if (w->local != nullptr) cudaFree(w->local);
+        delete w;
+        return st != cudaSuccess ? st : cudaErrorNotSupported;
+    }
+    w->peers[rank] = w->local;
+    w->connected = world == 1;
+    *out = w;
+    return cudaSuccess;
+}
+
+size_t p92b_ep_window_bytes(void) { return p92b::kWinBytes; }
+
+int p92b_ep_window_handle(const p92b_ep_window* window, uint8_t* handle64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "inter-process handle size");
+    if (window == nullptr || handle64 == nullptr) return cudaErrorInvalidValue;
+    cudaIpcMemHandle_t handle;
+    const cudaError_t st = cudaIpcGetMemHandle(&handle, window->local);
+    if (st != cudaSuccess) return st;
+    std::memcpy(handle64, &handle, 64);
+    return cudaSuccess;
+}
+
+int p92b_ep_window_connect(p92b_ep_window* window, const uint8_t* handles) {
+    if (window == nullptr || (window->world > 1 && handles == nullptr)) return cudaErrorInvalidValue;
+    if (window->connected) return cudaSuccess;
+    for (int r = 0; r < window->world; ++r) {
+        if (r == window->rank) continue;
+        cudaIpcMemHandle_t handle;
+        std::memcpy(&handle, handles + static_cast<size_t>(r) * 64, 64);
+        void* ptr = nullptr;
+        const cudaError_t st = cudaIpcOpenMemHandle(&ptr, handle, cudaIpcMemLazyEnablePeerAccess);
+        if (st != cudaSuccess) return st;
+        window->peers[r] = static_cast<std::uint8_t*>(ptr);
+        window->opened[r] = true;
+    }
+    window->connected = true;
+    return cudaSuccess;
+}
+
+int p92b_ep_window_connect_local(p92b_ep_window* window, p92b_ep_window* const* all_windows) {
+    if (window == nullptr || all_windows == nullptr) return cudaErrorInvalidValue;
+    for (int r = 0; r < window->world; ++r) {
+        if (all_windows[r] == nullptr || all_windows[r]->world != window->world || all_windows[r]->rank != r ||
+            all_windows[r]->rows_per_gpu != window->rows_per_gpu) {
+            return cudaErrorInvalidValue;
+        }
+    }
+    for (int r = 0; r < window->world; ++r) window->peers[r] = all_windows[r]->local;
+    window->connected = true;
+    return cudaSuccess;
+}
+
+void p92b_ep_window_destroy(p92b_ep_window* window) {
+    if (window == nullptr) return;
+    for (int r = 0; r < window->world; ++r) {
+        if (window->opened[r]) cudaIpcCloseMemHandle(window->peers[r]);
+    }
+    if (window->local != nullptr) cudaFree(window->local);
+    delete window;
+}
+
+int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window, const uint16_t* input,
+                          const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
+                          float routed_scale, void* stream_) {
+    using namespace p92b;
+    if (plan == nullptr || bank == nullptr || window == nullptr || input == nullptr || router_weight == nullptr ||
+        correction_bias == nullptr || output == nullptr || rows <= 0 || rows > window->rows_per_gpu) {
+        return cudaErrorInvalidValue;
+    }
+    if (!window->connected || !plan->tc_ready || !bank->tc_ready || plan->hidden != 2560 || plan->intermediate != 1024 ||
+        bank->view.hidden != 2560 || bank->view.intermediate != 1024 || bank->view.local_experts != kExperts / window->world ||
+        bank->view.first_expert != window->rank * (kExperts / window->world) ||
+        plan->pp_rows < static_cast<std::size_t>(std::min(bank->view.local_experts,
+                                                          window->world * window->rows_per_gpu * kTop) + 1) * kTile) {
+        return cudaErrorNotSupported;     // one 128-row slab per expert that can be active, plus the shared expert's
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const bool wide = window->world * window->rows_per_gpu > 16 || std::getenv("P92B_EP_WIDE") != nullptr;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t st = cudaFuncSetAttribute(moe_decode_ep_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              StageLayout<16>::kSmem);
+        if (st == cudaSuccess) {
+            st = cudaFuncSetAttribute(moe_decode_ep_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      StageLayout<32>::kSmem);
+        }
+        if (st != cudaSuccess) return st;
+        configured = true;
+    }
+    EpParams p {};
+    p.bank = bank->view;
+    p.x = input;
+    p.router_w = router_weight;
+    p.bias = correction_bias;
+    p.out = output;
+    p.logits = plan->logits;
+    p.ids = plan->ids;
+    p.route_weights = plan->route_weights;
+    p.counts = plan->counts;
+    p.xq_tok = plan->xq_tok;
+    p.xs_tok = plan->xs_tok;
+    p.hq = plan->hq_pp;
+    p.hs = plan->hs_sw;
+    p.mixed = plan->mixed_pp;
+    p.sync = plan->mega_sync + 2;
+    p.gu_done = plan->gu_done;
+    p.status = plan->status;
+    p.trace = plan->trace_on ? plan->mega_trace : nullptr;
+    for (int r = 0; r < window->world; ++r) p.win[r] = window->peers[r];
+    p.epoch = plan->ep_epoch++;
+    p.wepoch = window->epoch++;
+    p.routed_scale = routed_scale;
+    p.quant_scale = 1.0F;
+    p.rows = rows;
+    p.rank = window->rank;
+    p.world = window->world;
+    p.rows_per_gpu = window->rows_per_gpu;
+    p.hidden = plan->hidden;
+    p.inter = plan->intermediate;
+    plan->last_launches = 1;
+    plan->last_path = 3;
+    const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
+    if (wide) {
+        return launch_kernel(moe_decode_ep_kernel<32>, dim3(plan->sm_count), dim3(kEpThreads), StageLayout<32>::kSmem, stream,
+                             pdl, window->map_tok[1], plan->map_h[1], p);
+    }
+    return launch_kernel(moe_decode_ep_kernel<16>, dim3(plan->sm_count), dim3(kEpThreads), StageLayout<16>::kSmem, stream,
+                         pdl, window->map_tok[0], plan->map_h[0], p);
+}
+
+}  // extern "C"

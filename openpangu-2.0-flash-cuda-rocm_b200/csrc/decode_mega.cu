@@ -41,7 +41,7 @@ constexpr int kKB = 128;                           // bytes per operand row per 
 constexpr int kSlab = 2048;
 // stage: two weight boxes, two token boxes, four scale slabs
 // (the first 36,864 bytes are one chunk of the bank's tile stream, copied as a whole)
-constexpr int kOffA0 = 0, kOffA1 = 16384, kOffSfA0 = 32768, kOffSfA1 = 34816;
+constexpr int kOffA0 = 0, kOffA1 = 16384, kOffSfA0 = 32768;   // SFA1 follows SFA0 by one slab
 constexpr int kOffB0 = 36864, kOffB1 = 38912, kOffSfB0 = 40960, kOffSfB1 = 43008;
 constexpr int kStage = 45056;
 constexpr int kStages = 4;

@@ -242,6 +242,7 @@ struct p92b_plan {
     unsigned* mega_sync = nullptr;        // [2] arrival counters (monotonic across launches)
     std::int32_t* gu_done = nullptr;      // [257]
     unsigned mega_epoch = 0;
+    unsigned ep_epoch = 0;                // launches of the fused expert-parallel kernel (counters mega_sync[2..3])
     unsigned long long* mega_trace = nullptr;   // [sm_count][64] timer stamps of the last fused launch (P92B_TRACE=1)
     bool trace_on = false;
     CUtensorMap map_x_tok {};

@@ -141,6 +141,59 @@ def forward_nccl(state: EpRank, x, out, rows: int, group=None) -> dict:
     return {"sent_rows": send_sizes, "received_rows": int(recv.shape[0])}
 
 
+FUSED_MAX_ROWS = 8       # home tokens per GPU the fused kernel takes ...
+FUSED_MAX_TOKENS = 32    # ... and tokens in flight over all GPUs
+
+
+class EpWindow:
+    """This GPU's exchange window for the fused small-batch kernel, connected to all peers' windows.
+    Collective over `group` when world > 1 (the 64-byte handles are all-gathered); one window serves all
+    layers.  Every rank must make the same sequence of forward_fused calls on it."""
+
+    def __init__(self, rank: int, world: int, rows_per_gpu: int, group=None, connect: bool = True):
+        lib = load_library()
+        handle = ctypes.c_void_p()
+        _check(lib.p92b_ep_window_create(ctypes.byref(handle), rank, world, rows_per_gpu), "ep_window_create")
+        self.handle, self.rank, self.world, self.rows_per_gpu = handle, rank, world, rows_per_gpu
+        if not connect:
+            return
+        if world > 1:
+            import torch.distributed as dist
+
+            mine = (ctypes.c_uint8 * 64)()
+            _check(lib.p92b_ep_window_handle(handle, mine), "ep_window_handle")
+            device = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+            local = torch.tensor(list(mine), dtype=torch.uint8, device=device)
+            gathered = [torch.empty_like(local) for _ in range(world)]
+            dist.all_gather(gathered, local, group=group)
+            blob = bytes(torch.stack(gathered).cpu().flatten().tolist())
+            everyone = (ctypes.c_uint8 * (64 * world)).from_buffer_copy(blob)
+            _check(lib.p92b_ep_window_connect(handle, everyone), "ep_window_connect")
+        else:
+            _check(lib.p92b_ep_window_connect(handle, None), "ep_window_connect")
+
+    @staticmethod
+    def connect_local(windows: Sequence["EpWindow"]) -> None:
+        """Connect windows that all live in this process (rank order)."""
+        array = (ctypes.c_void_p * len(windows))(*[w.handle.value for w in windows])
+        for w in windows:
+            _check(load_library().p92b_ep_window_connect_local(w.handle, array), "ep_window_connect_local")
+
+    def close(self) -> None:
+        if self.handle:
+            load_library().p92b_ep_window_destroy(self.handle)
+            self.handle = None
+
+
+def forward_fused(window: EpWindow, plan: MoePlan, bank: ExpertBank, router_weight, correction_bias, x, out, rows: int,
+                  routed_scale: float = ROUTED_SCALE) -> None:
+    """The block on this GPU's `rows` home tokens as one kernel launch; the exchanges happen inside it.
+    `plan` needs max_rows >= world * rows_per_gpu; it can be shared by all layers of a rank."""
+    _check(load_library().p92b_ep_forward_fused(plan.handle, bank.handle, window.handle, _ptr(x), _ptr(router_weight),
+                                                _ptr(correction_bias), _ptr(out), rows, routed_scale, _stream()),
+           "ep_forward_fused")
+
+
 FIXED_MAX_ROWS = 64      # per-GPU batch up to which forward_auto takes the fixed-capacity exchange
 
 

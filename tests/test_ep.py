@@ -120,3 +120,73 @@ def test_expert_parallel_block_matches_single_gpu(cuda, pkg, layer0, world, rows
         rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
         assert rel <= 1e-2 and np.abs(got - ref).max() <= 2e-2, (r, rel)
         at += n
+
+
+# ---- fused small-batch kernel: exchanges inside the kernel -----------------------------------------
+
+def _single_gpu_reference(pkg, layer0, x, rows):
+    plan = pkg.MoePlan(max_rows=max(rows, 1))
+    plan.set_path(2)
+    want = x.new_empty(x.shape)
+    pkg.MoeBlock(layer0.bank, layer0.router_weight, layer0.bias, plan).run_moe_rows(x, want, rows)
+    import torch
+    torch.cuda.synchronize()
+    return want, plan.views(rows)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("rows", [1, 2, 4, 5, 8])
+def test_fused_kernel_world_one_matches_block(cuda, pkg, layer0, rows, wide, monkeypatch):
+    """One GPU owning all experts: the fused kernel's gather, routing lists, tiles, direct placement
+    and combine all run (to and from its own window), both token widths, several calls in a row so
+    that both halves of the double-buffered window are used."""
+    torch = cuda
+    from p92moe_b200 import ep, synth
+
+    if wide:
+        monkeypatch.setenv("P92B_EP_WIDE", "1")
+    window = ep.EpWindow(0, 1, 8)
+    plan = pkg.MoePlan(max_rows=32)
+    try:
+        for call in range(3):
+            x = synth.make_activations(700 + call, 0, rows)
+            out = torch.full_like(x, float("nan"))
+            ep.forward_fused(window, plan, layer0.bank, layer0.router_weight, layer0.bias, x, out, rows)
+            torch.cuda.synchronize()
+            v = plan.views(rows)
+            assert int(v["status"][0]) == 0
+            want, ref = _single_gpu_reference(pkg, layer0, x, rows)
+            assert torch.equal(v["expert_ids"], ref["expert_ids"])
+            assert torch.equal(v["expert_weights"], ref["expert_weights"])
+            assert torch.equal(v["counts"][:256], ref["counts"][:256])
+            got, exp = out.float().cpu().numpy(), want.float().cpu().numpy()
+            assert np.isfinite(got).all()
+            rel = np.linalg.norm(got - exp) / np.linalg.norm(exp)
+            assert rel <= 1e-2 and np.abs(got - exp).max() <= 2e-2, (call, rel)
+    finally:
+        window.close()
+
+
+@pytest.mark.gpu
+def test_fused_kernel_gives_up_when_a_peer_never_arrives(cuda, pkg, layer0):
+    """Two windows in this process, only rank 0 launches: its wait for rank 1's flag runs out after
+    about a second, the kernel returns, the status word says so and the context stays usable."""
+    torch = cuda
+    from p92moe_b200 import ep, synth
+
+    windows = [ep.EpWindow(r, 2, 4, connect=False) for r in range(2)]
+    ep.EpWindow.connect_local(windows)
+    entries = layer0.raw.entries()
+    bank = pkg.ExpertBank(entries[:128 * 3] + entries[256 * 3:], first_expert=0, local_experts=128)
+    plan = pkg.MoePlan(max_rows=8)
+    x = synth.make_activations(720, 0, 4)
+    out = torch.zeros_like(x)
+    try:
+        ep.forward_fused(windows[0], plan, bank, layer0.router_weight, layer0.bias, x, out, 4)
+        torch.cuda.synchronize()
+        assert int(plan.views(4)["status"][0]) == 2
+        assert float((x.float() * 2).sum().cpu()) == float(x.float().sum().cpu()) * 2     # the GPU still answers
+    finally:
+        for w in windows:
+            w.close()
