@@ -198,7 +198,8 @@ def workload_config(name: str, gpus: int) -> dict:
 def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps) -> None:
     """N > 1: the same step, expert-parallel.  Every GPU is home to its own tokens (weak scaling:
     4 tokens per GPU for the decode step, 4096/N... tokens per GPU for the prefill workloads), the 256
-    experts are sharded 256/N per GPU, rows travel by two NCCL all-to-alls per layer."""
+    experts are sharded 256/N per GPU.  Small batches take the fused kernel (exchanges by peer stores
+    inside it), larger ones two NCCL all-to-alls per layer; P92B_EP_EXCHANGE=fused|fixed|exact overrides."""
     import torch
     import torch.distributed as dist
     from p92moe_b200 import ep
@@ -211,30 +212,39 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     else:
         rows, n_layers = 4096 // world, args.layers or 1
     first, local = ep.shard_range(rank, world)
-    states, xs = [], []
+    mode = os.environ.get("P92B_EP_EXCHANGE", "")
+    if not mode:
+        mode = "fused" if rows <= ep.FUSED_MAX_ROWS and world * rows <= ep.FUSED_MAX_TOKENS else \
+            "fixed" if rows <= ep.FIXED_MAX_ROWS else "exact"
+    banks, routers, states, xs = [], [], [], []
     for l in range(n_layers):
         raw = synth.make_raw_layer(SEED, l)                     # same weights on every rank; keep the shard
         entries = raw.entries()
         shard = entries[first * 3:(first + local) * 3] + entries[EXPERTS * 3:]
-        bank = pkg.ExpertBank(shard, first_expert=first, local_experts=local)
-        router, bias = synth.make_router(SEED, l, bias_std=0.0 if args.workload == "ep_prefill16384" else 0.01)
-        states.append(ep.EpRank(rank, world, bank, router, bias, max_local_rows=rows))
+        banks.append(pkg.ExpertBank(shard, first_expert=first, local_experts=local))
+        routers.append(synth.make_router(SEED, l, bias_std=0.0 if args.workload == "ep_prefill16384" else 0.01))
+        if mode != "fused":
+            states.append(ep.EpRank(rank, world, banks[-1], routers[-1][0], routers[-1][1], max_local_rows=rows))
         xs.append(synth.make_activations(SEED + 1000 * (rank + 1), l, rows))
         del raw, entries, shard
     outs = [torch.empty_like(x) for x in xs]
+    window = fused_plan = None
+    if mode == "fused":
+        window = ep.EpWindow(rank, world, rows)                 # one window and one plan serve all layers
+        fused_plan = pkg.MoePlan(max_rows=world * rows)
     torch.cuda.synchronize()
 
-    exact = rows > ep.FIXED_MAX_ROWS or os.environ.get("P92B_EP_EXCHANGE", "") == "exact"
-
-    def forward(st, x, o):
-        if exact:
-            ep.forward_nccl(st, x, o, rows)
+    def forward(l, x, o):
+        if mode == "fused":
+            ep.forward_fused(window, fused_plan, banks[l], routers[l][0], routers[l][1], x, o, rows)
+        elif mode == "fixed":
+            ep.forward_nccl_fixed(states[l], x, o, rows, 8 * rows)
         else:
-            ep.forward_nccl_fixed(st, x, o, rows, 8 * rows)
+            ep.forward_nccl(states[l], x, o, rows)
 
     def step():
-        for st, x, o in zip(states, xs, outs):
-            forward(st, x, o)
+        for l in range(n_layers):
+            forward(l, xs[l], outs[l])
 
     def barrier():
         dist.barrier()
@@ -267,9 +277,9 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        for st, hi, di, o, ho in zip(states, host_in, dev_in, outs, host_out):
+        for l, (hi, di, o, ho) in enumerate(zip(host_in, dev_in, outs, host_out)):
             di.copy_(hi, non_blocking=True)
-            forward(st, di, o)
+            forward(l, di, o)
             ho.copy_(o, non_blocking=True)
             torch.cuda.current_stream().synchronize()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
@@ -280,12 +290,14 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
 
     step()
     torch.cuda.synchronize()
-    received = [int(st.arrivals.views(1)["counts"].sum()) for st in states]
-    load = torch.tensor([float(np.sum(received))], device="cuda")
+    count_plans = [fused_plan] if mode == "fused" else [st.arrivals for st in states]
+    local_counts = [pl.views(1)["counts"][first:first + local] for pl in count_plans]
+    received = [int(c.sum()) for c in local_counts]
+    load = torch.tensor([float(np.mean(received))], device="cuda")     # rows arriving per layer
     loads = [torch.zeros_like(load) for _ in range(world)]
     dist.all_gather(loads, load)
     loads = [float(v[0]) for v in loads]
-    distinct = float(np.mean([int((st.arrivals.views(1)["counts"] > 0).sum()) for st in states]))
+    distinct = float(np.mean([int((c > 0).sum()) for c in local_counts]))
     layer_bytes = (distinct + 1) * EXPERT_BYTES + ROUTER_BYTES + rows * HIDDEN * 2 * 2
     pk = peaks()
     gbs = layer_bytes * n_layers / (ms_per_step * 1e-3) / 1e9
@@ -296,17 +308,21 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
             "scaling": "weak" if decode else "strong", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 -> bf16",
             "data": "synthetic", "config": dict(workload_config(args.workload, world),
                                                 parallelism=f"ep{world}: {local} experts per GPU, {rows} home tokens per GPU, "
-                                                            "NCCL all-to-all dispatch and combine, "
-                                                            + ("exact-size splits" if exact else "fixed-capacity blocks, no host sync")),
+                                                            + {"fused": "one kernel per GPU and layer, dispatch (all-gather) and combine by peer stores "
+                                                                        "over NVLink inside the kernel",
+                                                               "fixed": "NCCL all-to-all dispatch and combine, fixed-capacity blocks, "
+                                                                        "no host sync",
+                                                               "exact": "NCCL all-to-all dispatch and combine, exact-size splits"}[mode]),
             "clocks": sampler.stop(),
             "e2e": {"value": world * rows / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": bytes_io,
                     "d2h_bytes_per_step": bytes_io, "ms_per_step": e2e_s * 1e3},
-            "gpu_launches": steps * n_layers * 19,
-            "roofline": {"bound": "hbm", "kernel": "expert_tc_kernel (per-GPU shard)", "achieved": gbs,
+            "gpu_launches": steps * n_layers * {"fused": 1, "fixed": 16, "exact": 16}[mode],
+            "roofline": {"bound": "hbm", "kernel": "moe_decode_ep_kernel (per-GPU shard)" if mode == "fused"
+                         else "expert_tc_kernel (per-GPU shard)", "achieved": gbs,
                          "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
                          "peak_source": pk["source"], "bytes_per_launch": layer_bytes,
                          "distinct_local_experts_mean": distinct},
-            "load_imbalance": {"rows_per_gpu": loads, "max_over_mean": max(loads) / (sum(loads) / world)},
+            "load_imbalance": {"rows_per_gpu_per_layer": loads, "max_over_mean": max(loads) / (sum(loads) / world)},
             "cpu_baseline": None,
         }
         print(json.dumps(line))

@@ -147,17 +147,17 @@ __device__ __forceinline__ bool wait_flag(const unsigned* flag, unsigned target)
     return true;
 }
 
-// Device-wide rendezvous of the co-resident blocks; the fences are system-wide because the stores
-// it orders may have gone to a peer.
+// Device-wide rendezvous of the co-resident blocks: arrive, then wait for everyone.  Nothing the
+// kernel has written before it leaves this GPU, so device-scope fences are enough.
 __device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned target) {
     __shared__ int ok;
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
+        __threadfence();
         fence_proxy_async_all();
         atomicAdd(counter, 1U);
         ok = wait_counter(counter, target) ? 1 : 0;
-        __threadfence_system();
+        __threadfence();
         fence_proxy_async_all();
     }
     __syncthreads();
@@ -371,14 +371,9 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
 
     // ------------------------------------------------- dispatch: block d pushes to GPU d
     if (!abort_word && block < world) {
-        for (int i = threadIdx.x; i < rows * kExperts; i += kEpThreads) rt.logits[i] = __ldcg(p.logits + i);
-        __syncthreads();
-        for (int t = warp; t < rows; t += kEpThreads / 32) {
-            warp_top8(rt.logits + t * kExperts, rt.bias, rt.my_ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
-        }
-        __syncthreads();
         std::uint8_t* dst = p.win[block];
         const int first_token = p.rank * rpg;
+        // the rows do not depend on the routing: their stores travel while the top-8 is computed
         {
             const uint4* src = reinterpret_cast<const uint4*>(p.xq_tok);
             uint4* out = reinterpret_cast<uint4*>(dst + kWinXq + parity * kWinXqParity + first_token * kXqRow);
@@ -394,10 +389,22 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                 *reinterpret_cast<std::uint32_t*>(xs_out + c * 512 + (first_token + t) * 16) = word;
             }
         }
+        for (int i = threadIdx.x; i < rows * kExperts; i += kEpThreads) rt.logits[i] = __ldcg(p.logits + i);
+        __syncthreads();
+        for (int t = warp; t < rows; t += kEpThreads / 32) {
+            warp_top8(rt.logits + t * kExperts, rt.bias, rt.my_ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
+        }
+        __syncthreads();
         {
             std::int32_t* ids_out = reinterpret_cast<std::int32_t*>(dst + kWinIds + parity * kWinIdsParity) + first_token * kTop;
             for (int i = threadIdx.x; i < rows * kTop; i += kEpThreads) ids_out[i] = rt.my_ids[i];
             if (threadIdx.x == 0) reinterpret_cast<std::int32_t*>(dst + kWinRowsOf)[parity * kEpMaxWorld + p.rank] = rows;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            // one fence for the block: the barrier ordered every thread's stores before it
+            __threadfence_system();
+            st_release_sys(reinterpret_cast<unsigned*>(dst + kWinFlagsGather) + p.rank, flag_target);
         }
         if (block == p.rank) {
             for (int i = threadIdx.x; i < rows * kTop; i += kEpThreads) {
@@ -405,9 +412,6 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                 p.route_weights[i] = rt.weights[i];
             }
         }
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0) st_release_sys(reinterpret_cast<unsigned*>(dst + kWinFlagsGather) + p.rank, flag_target);
     }
     if (threadIdx.x == 0) stamp(3);
     if (!abort_word && threadIdx.x < world) {
@@ -697,14 +701,19 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     }
     if (threadIdx.x == 0) stamp(9);
 
-    // --------------------------------------- all tiles of this GPU done -> tell every home GPU
-    if (!grid_rendezvous(p.sync + 1, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
+    // ------------------- all tiles of this GPU done -> the last block to get here tells every home GPU
+    if (threadIdx.x == 0) {
+        __threadfence_system();                               // this block's rows have reached their homes
+        const unsigned before = atomicAdd(p.sync + 1, 1U);
+        if (before + 1U == (p.epoch + 1U) * static_cast<unsigned>(grid)) {
+            __threadfence_system();
+            for (int r = 0; r < world; ++r) {
+                st_release_sys(reinterpret_cast<unsigned*>(p.win[r] + kWinFlagsReturn) + p.rank, flag_target);
+            }
+        }
+    }
     if (threadIdx.x == 0) stamp(10);
     if (abort_word) return;
-    if (block < world && threadIdx.x == 0) {
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<unsigned*>(p.win[block] + kWinFlagsReturn) + p.rank, flag_target);
-    }
     const int vectors = hidden / 8;
     if (block * kEpThreads >= rows * vectors) return;          // no share of the combine
     if (threadIdx.x < world) {
