@@ -20,10 +20,13 @@
 // tiles through one TMA ring and one tcgen05 pipeline, static deal of tiles.  The token side of
 // every MMA is the whole gathered batch (16 or 32 columns).
 //
-// Windows are double-buffered by launch parity; flags carry the launch number, so nothing is ever
-// reset.  A GPU cannot be more than one launch ahead of any peer (it needs the peer's results of
+// Nothing that crosses NVLink is ordered by a fence (a system-scope fence costs about 5 µs here, more
+// than the rest of an exchange).  Every word that travels is 8 bytes, {4 bytes of payload, the launch
+// number}, stored whole; a reader polls the word itself until the launch number is the one it waits
+// for.  So there are no flags and nothing is ever reset; the windows are double-buffered by launch
+// parity, and a GPU cannot be more than one launch ahead of any peer (it needs the peer's results of
 // launch k to finish launch k), which is what makes two buffers enough.  Every wait - on a peer's
-// flag, a device-wide counter or an mbarrier - is bounded by wall time and ends in a status word.
+// word, a device-wide counter or an mbarrier - is bounded by wall time and ends in a status word.
 #include "p92b_common.cuh"
 #include "tc_ptx.cuh"
 
@@ -55,20 +58,24 @@ constexpr int kTmemCols = 512;
 constexpr int kMaxSlots = kExperts + 1;            // local experts (all 256 on a single GPU) + the shared expert
 
 // ---- window layout (identical on every GPU) --------------------------------------------------
-constexpr std::size_t kWinFlagsGather = 0;                                  // u32 [16]
-constexpr std::size_t kWinFlagsReturn = 64;                                 // u32 [16]
-constexpr std::size_t kWinRowsOf = 128;                                     // i32 [2][16]
-constexpr std::size_t kWinXq = 256;                                         // [2][32][1280]
+// arrivals: per parity and global token 368 tagged words = 8 expert ids, 320 words of E2M1 row, 40 of scales
+constexpr int kTokIdWords = kTop, kTokRowWords = 320, kTokScaleWords = 40;
+constexpr int kTokWords = kTokIdWords + kTokRowWords + kTokScaleWords;
+constexpr std::size_t kWinArrive = 0;                                       // u64 [2][32][368]
+constexpr std::size_t kWinArriveParity = static_cast<std::size_t>(kEpMaxTokens) * kTokWords * 8;
+// the same rows untagged, in the layouts the tensor-core pipeline loads (written by this GPU itself)
 constexpr std::size_t kXqRow = 1280;
+constexpr std::size_t kWinXq = kWinArrive + 2 * kWinArriveParity;           // [2][32][1280]
 constexpr std::size_t kWinXqParity = kEpMaxTokens * kXqRow;
 constexpr std::size_t kWinXs = kWinXq + 2 * kWinXqParity;                   // [2][40][512]
 constexpr std::size_t kWinXsParity = 40 * 512;
-constexpr std::size_t kWinIds = kWinXs + 2 * kWinXsParity;                  // i32 [2][256]
-constexpr std::size_t kWinIdsParity = kEpMaxTokens * kTop * 4;
-constexpr std::size_t kWinRet = kWinIds + 2 * kWinIdsParity;                // bf16 [2][64][2560]
-constexpr std::size_t kWinRetParity = static_cast<std::size_t>(kEpMaxLocalRows) * kTop * 2560 * 2;
+// results: per parity, home token and slot (8 routed + the shared expert) 1280 tagged words of two BF16
+constexpr int kRetSlots = kTop + 1;
+constexpr int kRetRowWords = 1280;
+constexpr std::size_t kWinRet = kWinXs + 2 * kWinXsParity;                  // u64 [2][8][9][1280]
+constexpr std::size_t kWinRetParity = static_cast<std::size_t>(kEpMaxLocalRows) * kRetSlots * kRetRowWords * 8;
 constexpr std::size_t kWinBytes = kWinRet + 2 * kWinRetParity;
-static_assert(kWinXs % 16 == 0 && kWinRet % 256 == 0, "window regions must keep their alignment");
+static_assert(kWinXq % 256 == 0 && kWinXs % 16 == 0 && kWinRet % 16 == 0, "window regions must keep their alignment");
 
 struct EpParams {
     BankView bank;
@@ -80,12 +87,9 @@ struct EpParams {
     std::int32_t* ids;
     float* route_weights;
     std::int32_t* counts;
-    std::uint8_t* xq_tok;          // local staging of this GPU's quantised rows [16][H/2]
-    std::uint8_t* xs_tok;
     std::uint8_t* hq;
     std::uint8_t* hs;
-    std::uint16_t* mixed;          // shared-expert rows only
-    unsigned* sync;                // [2] device-wide arrival counters of the plan (+2, +3 of mega_sync)
+    unsigned* sync;                // [2] device-wide arrival counters of the plan
     std::int32_t* gu_done;
     std::int32_t* status;
     unsigned long long* trace;
@@ -104,7 +108,6 @@ struct Routing {
     std::uint32_t expert_mask[kMaxSlots];            // local expert -> tokens routed to it; [local] = shared
     std::uint32_t slot_mask[kMaxSlots];              // active slot -> tokens
     std::int32_t active[kMaxSlots];                  // active slot -> bank entry; slot 0 is the shared expert
-    std::int32_t rows_of[kEpMaxWorld];
     std::int32_t n_active;
     float weights[kEpMaxLocalRows * kTop];           // home tokens only
     std::int32_t my_ids[kEpMaxLocalRows * kTop];
@@ -121,13 +124,45 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// A tagged word: the payload and the launch number it belongs to, stored and loaded as one 8-byte access.
+__device__ __forceinline__ void st_tagged(void* p, std::uint32_t payload, std::uint32_t tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged(const void* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ uint4 ld_tagged_pair(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// Bounded polls: false after about a second.
+__device__ __forceinline__ bool poll_tagged(const void* p, std::uint32_t tag, std::uint32_t* payload) {
+    uint2 v = ld_tagged(p);
+    if (v.y != tag) {
+        const std::uint64_t start = global_timer_ns();
+        do {
+            if (global_timer_ns() - start > 1000000000ULL) return false;
+            v = ld_tagged(p);
+        } while (v.y != tag);
+    }
+    *payload = v.x;
+    return true;
+}
+__device__ __forceinline__ bool poll_tagged_pair(const void* p, std::uint32_t tag, std::uint32_t* first, std::uint32_t* second) {
+    uint4 v = ld_tagged_pair(p);
+    if (v.y != tag || v.w != tag) {
+        const std::uint64_t start = global_timer_ns();
+        do {
+            if (global_timer_ns() - start > 1000000000ULL) return false;
+            v = ld_tagged_pair(p);
+        } while (v.y != tag || v.w != tag);
+    }
+    *first = v.x;
+    *second = v.z;
+    return true;
 }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
@@ -138,15 +173,6 @@ __device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned t
     }
     return true;
 }
-// A flag another GPU writes into this GPU's memory.
-__device__ __forceinline__ bool wait_flag(const unsigned* flag, unsigned target) {
-    const std::uint64_t start = global_timer_ns();
-    while (static_cast<int>(ld_acquire_sys(flag) - target) < 0) {
-        if (global_timer_ns() - start > 1000000000ULL) return false;
-    }
-    return true;
-}
-
 // Device-wide rendezvous of the co-resident blocks: arrive, then wait for everyone.  Nothing the
 // kernel has written before it leaves this GPU, so device-scope fences are enough.
 __device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned target) {
@@ -246,7 +272,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     const int world = p.world;
     const int rpg = p.rows_per_gpu;
     const int parity = static_cast<int>(p.wepoch & 1U);
-    const unsigned flag_target = p.wepoch + 1U;
+    const std::uint32_t tag = p.wepoch + 1U;               // never 0: a fresh window reads as "not yet"
     std::uint8_t* const my_win = p.win[p.rank];
 
     if (threadIdx.x == 0) {
@@ -358,8 +384,20 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
             }
             std::uint8_t scale_bits;
             const uint2 packed = quantize_block16(v, p.quant_scale, &scale_bits);
-            *reinterpret_cast<uint2*>(p.xq_tok + static_cast<std::size_t>(t) * (hidden / 2) + b * 8) = packed;
-            p.xs_tok[static_cast<std::size_t>(b >> 2) * 512 + t * 16 + (b & 3)] = scale_bits;
+            // (whole warps take this branch: 160 blocks per row and 192 threads per block are multiples of 32)
+            std::uint32_t scales4 = scale_bits;
+            scales4 |= __shfl_down_sync(0xffffffffU, static_cast<std::uint32_t>(scale_bits), 1) << 8;
+            scales4 |= __shfl_down_sync(0xffffffffU, static_cast<std::uint32_t>(scale_bits), 2) << 16;
+            scales4 |= __shfl_down_sync(0xffffffffU, static_cast<std::uint32_t>(scale_bits), 3) << 24;
+            // straight into every GPU's window (this one's included): two row words, and from every fourth
+            // thread the word of four scales; they travel while the router finishes
+            for (int d = 0; d < world; ++d) {
+                std::uint64_t* dst = reinterpret_cast<std::uint64_t*>(p.win[d] + kWinArrive + parity * kWinArriveParity) +
+                                     static_cast<std::size_t>(p.rank * rpg + t) * kTokWords + kTokIdWords;
+                st_tagged(dst + 2 * b, packed.x, tag);
+                st_tagged(dst + 2 * b + 1, packed.y, tag);
+                if ((b & 3) == 0) st_tagged(dst + kTokRowWords + (b >> 2), scales4, tag);
+            }
         }
         if (block == 0) {
             for (int i = threadIdx.x; i <= kExperts; i += kEpThreads) p.gu_done[i] = 0;
@@ -369,42 +407,22 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     if (!grid_rendezvous(p.sync + 0, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
     if (threadIdx.x == 0) stamp(2);
 
-    // ------------------------------------------------- dispatch: block d pushes to GPU d
+    // ------------------------------------------------- routing of the home tokens: block d tells GPU d
     if (!abort_word && block < world) {
-        std::uint8_t* dst = p.win[block];
-        const int first_token = p.rank * rpg;
-        // the rows do not depend on the routing: their stores travel while the top-8 is computed
-        {
-            const uint4* src = reinterpret_cast<const uint4*>(p.xq_tok);
-            uint4* out = reinterpret_cast<uint4*>(dst + kWinXq + parity * kWinXqParity + first_token * kXqRow);
-            for (int i = threadIdx.x; i < rows * static_cast<int>(kXqRow / 16); i += kEpThreads) out[i] = __ldcg(src + i);
-        }
-        {
-            const int chunks = hidden / 64;               // 40 scale tiles, one word per (tile, token)
-            std::uint8_t* xs_out = dst + kWinXs + parity * kWinXsParity;
-            for (int i = threadIdx.x; i < rows * chunks; i += kEpThreads) {
-                const int t = i / chunks;
-                const int c = i - t * chunks;
-                const std::uint32_t word = __ldcg(reinterpret_cast<const std::uint32_t*>(p.xs_tok + c * 512 + t * 16));
-                *reinterpret_cast<std::uint32_t*>(xs_out + c * 512 + (first_token + t) * 16) = word;
-            }
-        }
+        std::uint64_t* dst = reinterpret_cast<std::uint64_t*>(p.win[block] + kWinArrive + parity * kWinArriveParity) +
+                             static_cast<std::size_t>(p.rank * rpg) * kTokWords;
         for (int i = threadIdx.x; i < rows * kExperts; i += kEpThreads) rt.logits[i] = __ldcg(p.logits + i);
         __syncthreads();
+        if (threadIdx.x == 0) stamp(13);
         for (int t = warp; t < rows; t += kEpThreads / 32) {
             warp_top8(rt.logits + t * kExperts, rt.bias, rt.my_ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
         }
         __syncthreads();
-        {
-            std::int32_t* ids_out = reinterpret_cast<std::int32_t*>(dst + kWinIds + parity * kWinIdsParity) + first_token * kTop;
-            for (int i = threadIdx.x; i < rows * kTop; i += kEpThreads) ids_out[i] = rt.my_ids[i];
-            if (threadIdx.x == 0) reinterpret_cast<std::int32_t*>(dst + kWinRowsOf)[parity * kEpMaxWorld + p.rank] = rows;
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            // one fence for the block: the barrier ordered every thread's stores before it
-            __threadfence_system();
-            st_release_sys(reinterpret_cast<unsigned*>(dst + kWinFlagsGather) + p.rank, flag_target);
+        if (threadIdx.x == 0) stamp(14);
+        // token slots this GPU does not fill this time say so with id -1
+        for (int i = threadIdx.x; i < rpg * kTop; i += kEpThreads) {
+            const int t = i / kTop;
+            st_tagged(dst + t * kTokWords + (i - t * kTop), static_cast<std::uint32_t>(t < rows ? rt.my_ids[i] : -1), tag);
         }
         if (block == p.rank) {
             for (int i = threadIdx.x; i < rows * kTop; i += kEpThreads) {
@@ -414,37 +432,53 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
         }
     }
     if (threadIdx.x == 0) stamp(3);
-    if (!abort_word && threadIdx.x < world) {
-        if (!wait_flag(reinterpret_cast<const unsigned*>(my_win + kWinFlagsGather) + threadIdx.x, flag_target)) {
-            give_up(kStatusWaitExpired);
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) stamp(4);
 
-    // ------------------------------------------------- routing lists of this GPU's experts
+    // ------------------------------------------------- arrivals: ids (every block), rows (one word per thread)
     const int local = p.bank.local_experts;
+    const int tokens = world * rpg;
+    const std::uint64_t* arrive = reinterpret_cast<const std::uint64_t*>(my_win + kWinArrive + parity * kWinArriveParity);
+    for (int i = threadIdx.x; i < kMaxSlots; i += kEpThreads) rt.expert_mask[i] = 0;
+    __syncthreads();
     if (!abort_word) {
-        for (int i = threadIdx.x; i < kMaxSlots; i += kEpThreads) rt.expert_mask[i] = 0;
-        if (threadIdx.x < world) {
-            rt.rows_of[threadIdx.x] =
-                __ldcg(reinterpret_cast<const std::int32_t*>(my_win + kWinRowsOf) + parity * kEpMaxWorld + threadIdx.x);
-        }
-        __syncthreads();
-        const std::int32_t* gathered = reinterpret_cast<const std::int32_t*>(my_win + kWinIds + parity * kWinIdsParity);
-        for (int a = threadIdx.x; a < world * rpg * kTop; a += kEpThreads) {
+        for (int a = threadIdx.x; a < tokens * kTop; a += kEpThreads) {
             const int g = a / kTop;
-            const int src = g / rpg;
-            std::int32_t e = -1;
-            if (g - src * rpg < rt.rows_of[src]) {
-                e = __ldcg(gathered + a);
-                const int le = e - p.bank.first_expert;
-                if (le >= 0 && le < local) atomicOr(&rt.expert_mask[le], 1U << g);
+            std::uint32_t word = 0;
+            if (!poll_tagged(arrive + static_cast<std::size_t>(g) * kTokWords + (a - g * kTop), tag, &word)) {
+                give_up(kStatusWaitExpired);
+                break;
             }
+            const std::int32_t e = static_cast<std::int32_t>(word);
+            const int le = e - p.bank.first_expert;
+            if (e >= 0 && le >= 0 && le < local) atomicOr(&rt.expert_mask[le], 1U << g);
             rt.ids[a] = e;
         }
-        if (threadIdx.x == 0) rt.expert_mask[local] = ((rows >= 32 ? 0U : (1U << rows)) - 1U) << (p.rank * rpg);
-        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        rt.expert_mask[local] = ((1U << rows) - 1U) << (p.rank * rpg);
+        stamp(4);
+    }
+    __syncthreads();
+    if (!abort_word) {
+        // this thread's share of the batch: tagged word -> the untagged row and scale layouts
+        std::uint8_t* xq_dense = my_win + kWinXq + parity * kWinXqParity;
+        std::uint8_t* xs_dense = my_win + kWinXs + parity * kWinXsParity;
+        const int per_token = kTokRowWords + kTokScaleWords;
+        for (int i = block * kEpThreads + threadIdx.x; i < tokens * per_token; i += grid * kEpThreads) {
+            const int g = i / per_token;
+            const int w = i - g * per_token;
+            if (rt.ids[g * kTop] < 0) continue;                      // slot not filled this time
+            std::uint32_t word = 0;
+            if (!poll_tagged(arrive + static_cast<std::size_t>(g) * kTokWords + kTokIdWords + w, tag, &word)) {
+                give_up(kStatusWaitExpired);
+                break;
+            }
+            if (w < kTokRowWords) {
+                reinterpret_cast<std::uint32_t*>(xq_dense + g * kXqRow)[w] = word;
+            } else {
+                *reinterpret_cast<std::uint32_t*>(xs_dense + (w - kTokRowWords) * 512 + g * 16) = word;
+            }
+        }
+        // routing lists of this GPU's experts (every block, in shared memory)
         if (warp == 0) {
             int found = 0;
             for (int e0 = 0; e0 < local; e0 += 32) {
@@ -467,9 +501,11 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
         if (block == 0) {
             for (int e = threadIdx.x; e < local; e += kEpThreads) p.counts[p.bank.first_expert + e] = __popc(rt.expert_mask[e]);
         }
-        __syncthreads();
     }
     if (threadIdx.x == 0) stamp(5);
+    // the untagged batch is complete on this GPU once every block has written its share
+    if (!grid_rendezvous(p.sync + 1, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
+    if (threadIdx.x == 0) stamp(6);
 
     // ------------------------------------------------------------ gate/up and down tiles
     const int gu_tiles = inter / kTile;
@@ -526,7 +562,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                     if (++stage == kStages) { stage = 0; phase ^= 1U; }
                 }
             }
-            stamp(6);
+            stamp(7);
         }
     } else if (warp == 1) {
         if (elect_one() && !abort_word) {
@@ -591,7 +627,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                 accum_phase ^= 1U << buffer;
                 buffer = (buffer + 1) % kAccumBuffers;
             }
-            stamp(7);
+            stamp(8);
         }
     } else if (!abort_word) {
         const int quarter = warp & 3;
@@ -671,17 +707,21 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                         // column 16c+n is the (16c+n)-th row of this expert = its (16c+n)-th token
                         const int token = __ffs(remaining) - 1;
                         remaining &= remaining - 1U;
-                        const std::uint16_t value = float_to_bf16_bits(__uint_as_float(d[n]) * alpha);
-                        if (slot == 0) {
-                            p.mixed[static_cast<std::size_t>(pp0 + 16 * c + n) * hidden + row] = value;
-                        } else {
-                            const int home = token / rpg;
-                            const int t_local = token - home * rpg;
-                            int k = 0;
+                        const std::uint32_t value = float_to_bf16_bits(__uint_as_float(d[n]) * alpha);
+                        const std::uint32_t next = __shfl_down_sync(0xffffffffU, value, 1);
+                        const int home = token / rpg;
+                        const int t_local = token - home * rpg;
+                        int k = kTop;                                                 // the shared expert's slot
+                        if (slot != 0) {
+                            k = 0;
 #pragma unroll
                             for (int kk = 1; kk < kTop; ++kk) k = rt.ids[token * kTop + kk] == expert ? kk : k;
-                            std::uint16_t* ret = reinterpret_cast<std::uint16_t*>(p.win[home] + kWinRet + parity * kWinRetParity);
-                            ret[static_cast<std::size_t>(t_local * kTop + k) * hidden + row] = value;
+                        }
+                        // two output features per word: even lanes store {own | next << 16, launch number}
+                        if ((lane & 1) == 0) {
+                            std::uint64_t* ret = reinterpret_cast<std::uint64_t*>(p.win[home] + kWinRet + parity * kWinRetParity) +
+                                                 static_cast<std::size_t>(t_local * kRetSlots + k) * kRetRowWords;
+                            st_tagged(ret + (row >> 1), value | (next << 16), tag);
                         }
                     }
                 }
@@ -691,7 +731,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
             }
             buffer = (buffer + 1) % kAccumBuffers;
         }
-        if (warp == 2 && lane == 0) stamp(8);
+        if (warp == 2 && lane == 0) stamp(9);
     }
     tc_fence_before();
     __syncthreads();
@@ -699,64 +739,43 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
-    if (threadIdx.x == 0) stamp(9);
-
-    // ------------------- all tiles of this GPU done -> the last block to get here tells every home GPU
-    if (threadIdx.x == 0) {
-        __threadfence_system();                               // this block's rows have reached their homes
-        const unsigned before = atomicAdd(p.sync + 1, 1U);
-        if (before + 1U == (p.epoch + 1U) * static_cast<unsigned>(grid)) {
-            __threadfence_system();
-            for (int r = 0; r < world; ++r) {
-                st_release_sys(reinterpret_cast<unsigned*>(p.win[r] + kWinFlagsReturn) + p.rank, flag_target);
-            }
-        }
-    }
     if (threadIdx.x == 0) stamp(10);
-    if (abort_word) return;
-    const int vectors = hidden / 8;
-    if (block * kEpThreads >= rows * vectors) return;          // no share of the combine
-    if (threadIdx.x < world) {
-        if (!wait_flag(reinterpret_cast<const unsigned*>(my_win + kWinFlagsReturn) + threadIdx.x, flag_target)) {
-            give_up(kStatusWaitExpired);
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) stamp(11);
+
     if (abort_word) return;
 
     // ------------------------------------------------------------------ combine (home tokens)
-    const std::uint16_t* ret = reinterpret_cast<const std::uint16_t*>(my_win + kWinRet + parity * kWinRetParity);
-    const int shared_pp0 = slab_of_slot(0, rt.n_active);
-    for (int v = block * kEpThreads + threadIdx.x; v < rows * vectors; v += grid * kEpThreads) {
-        const int row = v / vectors;
-        const int c8 = v - row * vectors;
-        float acc[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.0F;
+    // One thread per four output features: eight routed slots in slot order, then the shared expert;
+    // each operand is polled until its words carry this launch's number.
+    const std::uint64_t* ret = reinterpret_cast<const std::uint64_t*>(my_win + kWinRet + parity * kWinRetParity);
+    const int quads = hidden / 4;
+    for (int v = block * kEpThreads + threadIdx.x; v < rows * quads; v += grid * kEpThreads) {
+        const int row = v / quads;
+        const int q = v - row * quads;
+        float acc[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+        bool ok = true;
 #pragma unroll
         for (int slot = 0; slot < kTop; ++slot) {
             const float w = __ldcg(p.route_weights + row * kTop + slot);
-            const uint4 r = __ldcg(reinterpret_cast<const uint4*>(ret + static_cast<std::size_t>(row * kTop + slot) * hidden + c8 * 8));
-            const std::uint32_t words[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                acc[2 * k] = fmaf(__uint_as_float(words[k] << 16), w, acc[2 * k]);
-                acc[2 * k + 1] = fmaf(__uint_as_float(words[k] & 0xffff0000U), w, acc[2 * k + 1]);
-            }
+            std::uint32_t a0, a1;
+            ok = ok && poll_tagged_pair(ret + static_cast<std::size_t>(row * kRetSlots + slot) * kRetRowWords + 2 * q, tag, &a0, &a1);
+            acc[0] = fmaf(__uint_as_float(a0 << 16), w, acc[0]);
+            acc[1] = fmaf(__uint_as_float(a0 & 0xffff0000U), w, acc[1]);
+            acc[2] = fmaf(__uint_as_float(a1 << 16), w, acc[2]);
+            acc[3] = fmaf(__uint_as_float(a1 & 0xffff0000U), w, acc[3]);
         }
-        const uint4 sh = __ldcg(reinterpret_cast<const uint4*>(p.mixed + static_cast<std::size_t>(shared_pp0 + row) * hidden + c8 * 8));
-        const std::uint32_t sw[4] = {sh.x, sh.y, sh.z, sh.w};
-        std::uint32_t out_words[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float lo = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k])) + __uint_as_float(sw[k] << 16);
-            const float hi = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k + 1])) + __uint_as_float(sw[k] & 0xffff0000U);
-            out_words[k] = static_cast<std::uint32_t>(float_to_bf16_bits(lo)) |
-                           (static_cast<std::uint32_t>(float_to_bf16_bits(hi)) << 16);
+        std::uint32_t s0, s1;
+        ok = ok && poll_tagged_pair(ret + static_cast<std::size_t>(row * kRetSlots + kTop) * kRetRowWords + 2 * q, tag, &s0, &s1);
+        if (!ok) {
+            give_up(kStatusWaitExpired);
+            break;
         }
-        *reinterpret_cast<uint4*>(p.out + static_cast<std::size_t>(row) * hidden + c8 * 8) =
-            make_uint4(out_words[0], out_words[1], out_words[2], out_words[3]);
+        const float o0 = bf16_bits_to_float(float_to_bf16_bits(acc[0])) + __uint_as_float(s0 << 16);
+        const float o1 = bf16_bits_to_float(float_to_bf16_bits(acc[1])) + __uint_as_float(s0 & 0xffff0000U);
+        const float o2 = bf16_bits_to_float(float_to_bf16_bits(acc[2])) + __uint_as_float(s1 << 16);
+        const float o3 = bf16_bits_to_float(float_to_bf16_bits(acc[3])) + __uint_as_float(s1 & 0xffff0000U);
+        *reinterpret_cast<uint2*>(p.out + static_cast<std::size_t>(row) * hidden + q * 4) =
+            make_uint2(static_cast<std::uint32_t>(float_to_bf16_bits(o0)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o1)) << 16),
+                       static_cast<std::uint32_t>(float_to_bf16_bits(o2)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o3)) << 16));
     }
     if (threadIdx.x == 0) stamp(12);
 }
@@ -897,11 +916,8 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
     p.ids = plan->ids;
     p.route_weights = plan->route_weights;
     p.counts = plan->counts;
-    p.xq_tok = plan->xq_tok;
-    p.xs_tok = plan->xs_tok;
     p.hq = plan->hq_pp;
     p.hs = plan->hs_sw;
-    p.mixed = plan->mixed_pp;
     p.sync = plan->mega_sync + 2;
     p.gu_done = plan->gu_done;
     p.status = plan->status;

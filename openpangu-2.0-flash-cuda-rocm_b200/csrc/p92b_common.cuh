@@ -96,7 +96,9 @@ __device__ __forceinline__ void warp_top8(const float* __restrict__ lg, const fl
     unsigned used = 0U;
     float chosen_weight = 0.0F;   // lane k keeps slot k's raw weight
     int chosen_id = 0;
-#pragma unroll
+    // The eight rounds stay a loop: unrolled they are several thousand instructions, and a block that
+    // runs this alone (the routing block of the fused kernels) then waits on instruction fetches.
+#pragma unroll 1
     for (int slot = 0; slot < 8; ++slot) {
         float best = -FLT_MAX;
         int best_id = 256 + lane;
@@ -112,21 +114,17 @@ __device__ __forceinline__ void warp_top8(const float* __restrict__ lg, const fl
                 best_raw = raw[i];
             }
         }
-#pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            const float other = __shfl_xor_sync(0xffffffffU, best, offset);
-            const int other_id = __shfl_xor_sync(0xffffffffU, best_id, offset);
-            const float other_raw = __shfl_xor_sync(0xffffffffU, best_raw, offset);
-            if (other > best || (other == best && other_id < best_id)) {
-                best = other;
-                best_id = other_id;
-                best_raw = other_raw;
-            }
-        }
-        if ((best_id & 31) == lane) used |= 1U << (best_id >> 5);
+        // warp arg-max, lower id on ties: order-preserving integer image of the score (a NaN never wins,
+        // as with the comparisons above), one max over the warp, then the smallest id among the lanes that hold it
+        const std::uint32_t bits = __float_as_uint(best);
+        const std::uint32_t key = best != best ? 0U : (bits & 0x80000000U ? ~bits : bits | 0x80000000U);
+        const std::uint32_t top = __reduce_max_sync(0xffffffffU, key);
+        const int winner = static_cast<int>(__reduce_min_sync(0xffffffffU, key == top ? static_cast<std::uint32_t>(best_id) : 0xffffffffU));
+        const float winner_raw = __shfl_sync(0xffffffffU, best_raw, winner & 31);
+        if ((winner & 31) == lane) used |= 1U << (winner >> 5);
         if (lane == slot) {
-            chosen_weight = best_raw;
-            chosen_id = best_id;
+            chosen_weight = winner_raw;
+            chosen_id = winner;
         }
     }
     float total = 0.0F;
