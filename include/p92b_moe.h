@@ -294,9 +294,11 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* views);
 int p92b_plan_stage_timing(p92b_plan* plan, int enable);
 int p92b_plan_stage_times(const p92b_plan* plan, float* host_ms, int* host_calls);
 
-/* Kernel family for the expert products: 0 automatic, 1 weight-streaming SIMT kernels,
- * 2 tcgen05 block-scaled MMA kernels (TMA + TMEM).  The environment variable P92B_PATH sets the
- * default of new plans.  Both families implement the same arithmetic contract. */
+/* Kernel family for the block: 0 automatic (3 for up to 8 rows, else 2), 1 weight-streaming SIMT
+ * kernels (needs a bank created with P92B_BANK_STREAM_COPY), 2 tcgen05 block-scaled MMA kernels
+ * (TMA + TMEM), one launch per stage, 3 the whole block as one persistent tcgen05 kernel (up to 8
+ * rows).  The environment variable P92B_PATH sets the default of new plans.  All families implement
+ * the same arithmetic contract. */
 int p92b_plan_set_path(p92b_plan* plan, int path);
 
 /* Number of kernels the last p92b_moe_forward on this plan launched. */
