@@ -919,7 +919,7 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
     p.hq = plan->hq_pp;
     p.hs = plan->hs_sw;
     p.sync = plan->mega_sync + 2;
-    p.gu_done = plan->gu_done;
+    p.gu_done = plan->ep_gu_done;
     p.status = plan->status;
     p.trace = plan->trace_on ? plan->mega_trace : nullptr;
     for (int r = 0; r < window->world; ++r) p.win[r] = window->peers[r];

@@ -1,15 +1,17 @@
 // The whole MoE block for up to 8 tokens (decode, MTP verify) as ONE persistent kernel.
 //
-// At these sizes the block is a 140 MB weight stream (≈21 µs at HBM speed) wrapped in a
+// At these sizes the block is a 120 MB weight stream (≈19 µs at HBM speed) wrapped in a
 // few microseconds of routing, so kernel boundaries - five dependent launches - cost
-// as much as the stream itself.  Here one block per SM walks the phases, separated
-// by two device-wide counters instead of launches:
+// as much as the stream itself.  Here one block per SM walks the phases, and what a phase
+// needs from other blocks it gets without a device-wide stop:
 //
 //   P0  every block: its one or two router rows (logits in the reference's exact FP32
 //       order, cuda/nvfp4_ops.cu:161-207) and its slice of the token quantisation
-//       (cuda/nvfp4_ops.cu:818-841, scales written 128x4-tiled);        -> counter 1
-//   P1  every block, redundantly and in shared memory: top-8 of every token
-//       (cuda/nvfp4_ops.cu:357-433), histogram, stable permutation
+//       (cuda/nvfp4_ops.cu:818-841, scales written 128x4-tiled).  Each logit is published
+//       as an 8-byte word {value, launch number}; the quantised rows are covered by an
+//       arrive-only counter that only the TMA producer lanes wait on, later;
+//   P1  every block, redundantly and in shared memory: polls the logit words, top-8 of
+//       every token (cuda/nvfp4_ops.cu:357-433), histogram, stable permutation
 //       (cuda/nvfp4_grouped.cu:117-132), active-expert list; block 0 also writes the
 //       routing products to global memory;
 //   P2  gate/up tiles and P3 down tiles through ONE TMA ring and one tcgen05 pipeline
@@ -17,13 +19,17 @@
 //       tokens in token order (N=16 columns cost nothing at M=128), so it does not depend
 //       on routing; the epilogue keeps the columns routed to the tile's expert.  A down
 //       tile needs the eight gate/up tiles of its expert: per-expert counters, no barrier,
-//       and its weights are already in flight while the producer waits.  Work is dealt
-//       statically and evenly in units of ring stages (a gate/up tile is 10 stages,
-//       a down tile 2);                                                   -> counter 2
-//   P4  weighted combine in slot order + shared expert (cuda/nvfp4_ops.cu:124-142,92-95).
+//       and its weights are already in flight while the producer waits.  Tiles are handed
+//       out dynamically from one device-wide counter, gate/up tiles first, both in expert
+//       order: a block that falls behind simply takes fewer (a gate/up tile is 10 ring
+//       stages, a down tile 2, so the tail is fine-grained);
+//   P4  weighted combine in slot order + shared expert (cuda/nvfp4_ops.cu:124-142,92-95):
+//       the down epilogue publishes its rows as {two BF16, launch number} words and the
+//       combining threads poll the words they need, so the combine of a token starts when
+//       its last row lands, not when the slowest block is done.
 //
-// All blocks are co-resident (one per SM, grid = SM count); every wait on a counter or
-// an mbarrier is bounded by wall time and ends in a status word, never a hang.
+// All blocks are co-resident (one per SM, grid = SM count); every wait on a counter, a
+// word or an mbarrier is bounded by wall time and ends in a status word, never a hang.
 #include "p92b_common.cuh"
 #include "tc_ptx.cuh"
 
@@ -72,8 +78,10 @@ struct MegaParams {
     std::uint8_t* hq;              // [PP][I/2]
     std::uint8_t* hs;              // tiled scales of hq
     std::uint16_t* mixed;          // [PP][H]
-    unsigned* sync;                // [2] monotonic arrival counters
-    std::int32_t* gu_done;         // [257] gate/up tiles finished per active slot
+    unsigned long long* logits_tagged;   // [8][256] {value, launch number}
+    unsigned long long* ret;             // [8][9][1280] {two BF16, launch number}
+    unsigned* sync;                // [0]: blocks that have finished P0 (monotonic across launches)
+    std::int32_t* gu_done;         // [2][264] by launch parity: gate/up tiles finished per active slot, [257] tile counter
     std::int32_t* status;
     unsigned long long* trace;     // optional [grid][64] %globaltimer stamps per block (null: off)
     unsigned epoch;                // launches of this kernel on the plan before this one
@@ -94,6 +102,9 @@ struct Routing {                   // shared-memory copy, identical in every blo
     std::int32_t slot_rows[kMaxActive];              // rows of an active slot
     std::int32_t pp_tok[kMaxActive][kMegaMaxRows];   // padded position of (active slot, token), -1 if not routed
     std::int32_t n_active;
+    std::uint32_t expert_mask[kExperts];             // tokens routed to each expert
+    std::int32_t before[kExperts];                   // assignments with a smaller expert id
+    std::int32_t slot_of[kExperts];                  // active slot an expert has (if any token picked it)
     float logits[kMegaMaxRows * kExperts];
     float bias[kExperts];
 };
@@ -112,6 +123,49 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+// A tagged word: a payload and the launch number it belongs to, stored and loaded as one 8-byte
+// access, so a reader can poll the word itself instead of waiting for a barrier.
+__device__ __forceinline__ void st_tagged(void* p, std::uint32_t payload, std::uint32_t tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged(const void* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_tagged_pair(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ bool poll_tagged(const void* p, std::uint32_t tag, std::uint32_t* payload) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    if (v.y != tag) {
+        const std::uint64_t start = global_timer_ns();
+        do {
+            if (global_timer_ns() - start > 1000000000ULL) return false;
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+        } while (v.y != tag);
+    }
+    *payload = v.x;
+    return true;
+}
+__device__ __forceinline__ bool poll_tagged_pair(const void* p, std::uint32_t tag, std::uint32_t* first, std::uint32_t* second) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    if (v.y != tag || v.w != tag) {
+        const std::uint64_t start = global_timer_ns();
+        do {
+            if (global_timer_ns() - start > 1000000000ULL) return false;
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+        } while (v.y != tag || v.w != tag);
+    }
+    *first = v.x;
+    *second = v.z;
+    return true;
+}
+
 // Bounded wait until *counter has reached `target` (wrap-safe).
 __device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned target) {
     const std::uint64_t start = global_timer_ns();
@@ -121,75 +175,28 @@ __device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned t
     return true;
 }
 
-// Device-wide rendezvous of the co-resident blocks: arrive, then wait for everyone.
-__device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned target) {
-    __shared__ int ok;
+// One arrival per block on a device-wide counter; whoever needs all blocks to have arrived waits for
+// the count itself (wait_counter).
+__device__ __forceinline__ void grid_arrive(unsigned* counter) {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
-        fence_proxy_async_all();
+        fence_proxy_async_all();          // what the block wrote is later read by TMA in other blocks
         atomicAdd(counter, 1U);
-        ok = wait_counter(counter, target) ? 1 : 0;
-        __threadfence();
-        fence_proxy_async_all();
     }
-    __syncthreads();
-    return ok != 0;
 }
 
-// The static deal of tiles to blocks, computed identically by every role of every block.
-struct Deal {
-    int gu_items, dn_items, grid;
-    int n_gu;                      // gate/up tiles of this block: block, block+grid, ...
-    int dn_begin, dn_count;        // contiguous down tiles
-    int total_cap;                 // first left-over down tile
-    int leftovers;
-    __device__ void init(int n_active, int gu_tiles, int dn_tiles, int grid_, int block) {
-        grid = grid_;
-        gu_items = n_active * gu_tiles;
-        dn_items = n_active * dn_tiles;
-        // gate/up tiles go round-robin: the first `r` blocks hold q+1 of them, the rest q.  Down tiles
-        // fill every block up to the common level (in ring stages: 10 per gate/up tile, 2 per down
-        // tile); what is left over goes round-robin again.  Closed forms, no loop over the grid.
-        const int q = gu_items / grid;
-        const int r = gu_items - q * grid;
-        const int stages = gu_items * 10 + dn_items * 2;
-        const int level = stages / grid;                // rounded down: the remainder is dealt round-robin
-        int cap_hi = (level - 10 * (q + 1)) / 2;
-        int cap_lo = (level - 10 * q) / 2;
-        cap_hi = cap_hi < 0 ? 0 : cap_hi;
-        cap_lo = cap_lo < 0 ? 0 : cap_lo;
-        n_gu = q + (block < r ? 1 : 0);
-        const int mine = block < r ? cap_hi : cap_lo;
-        // down tiles are dealt in expert order, lightly loaded blocks first: those are free after one
-        // gate/up tile and take the experts whose gate/up tiles all ran in the first round, while the
-        // blocks with two gate/up tiles become free when the later experts' rows exist
-        const int prefix = block >= r ? (block - r) * cap_lo : (grid - r) * cap_lo + block * cap_hi;
-        total_cap = r * cap_hi + (grid - r) * cap_lo;
-        dn_begin = prefix < dn_items ? prefix : dn_items;
-        dn_count = dn_items - dn_begin < mine ? dn_items - dn_begin : mine;
-        leftovers = dn_items > total_cap ? dn_items - total_cap : 0;
-    }
-    // i-th tile of this block: returns false past the end.  kind 0 gate/up, 1 down.
-    __device__ bool item(int i, int block, int gu_tiles, int dn_tiles, int* kind, int* slot, int* m_tile) const {
-        if (i < n_gu) {
-            const int g = block + i * grid;
-            *kind = 0; *slot = g / gu_tiles; *m_tile = g - *slot * gu_tiles;
-            return true;
-        }
-        i -= n_gu;
-        int d;
-        if (i < dn_count) {
-            d = dn_begin + i;
-        } else {
-            const int j = block + (i - dn_count) * grid;
-            if (j >= leftovers) return false;
-            d = total_cap + j;
-        }
-        *kind = 1; *slot = d / dn_tiles; *m_tile = d - *slot * dn_tiles;
-        return true;
-    }
-};
+// Tiles are handed out through one device-wide counter.  The producer lane takes the numbers (one
+// ahead of the tile it is loading, so the atomic's latency is hidden) and passes each tile to the MMA
+// lane and the epilogue warps through a small queue in shared memory, published by the mbarrier
+// arrivals that already order the three roles.  A negative entry ends the queue.
+constexpr int kTileQueue = 16;       // the producer is never more than 9 tiles ahead of the epilogue
+__device__ __forceinline__ int encode_tile(int kind, int slot, int m_tile) { return (kind << 24) | (slot << 8) | m_tile; }
+__device__ __forceinline__ void decode_tile(int code, int* kind, int* slot, int* m_tile) {
+    *kind = code >> 24;
+    *slot = (code >> 8) & 0xffff;
+    *m_tile = code & 0xff;
+}
 
 __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                       const __grid_constant__ CUtensorMap map_h,
@@ -199,6 +206,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     __shared__ __align__(8) std::uint64_t barrier_words[3 * kStages + 2 * kAccumBuffers];
     __shared__ std::uint32_t tmem_slot_word;
     __shared__ volatile std::uint32_t abort_word;
+    __shared__ volatile int tile_queue[kTileQueue];
+    __shared__ volatile int first_tile_word;
+    __shared__ volatile int rows_ready_word;
 
     const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     const std::uint32_t bars = smem_u32(barrier_words);
@@ -216,6 +226,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     const int assignments = rows * kTop;
     const int grid = gridDim.x;
     const int block = blockIdx.x;
+    const std::uint32_t tag = p.epoch + 1U;                // never 0: fresh scratch reads as "not yet"
+    // this launch's counters were zeroed by the launch before (or at plan creation); it zeroes the next one's
+    std::int32_t* const done = p.gu_done + (p.epoch & 1U) * 264;
+    std::int32_t* const done_next = p.gu_done + ((p.epoch + 1U) & 1U) * 264;
+    unsigned* const tile_counter = reinterpret_cast<unsigned*>(done + kExperts + 1);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -250,6 +265,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     for (int e = threadIdx.x; e < kExperts; e += kMegaThreads) rt.bias[e] = __ldg(p.bias + e);
     pdl_wait();                       // the token rows come from the kernel before this one
     pdl_launch_dependents();
+    // the first tile number is asked for now and used after the routing, the atomic's latency in between
+    if (threadIdx.x == 0) first_tile_word = static_cast<int>(atomicAdd(tile_counter, 1U));
     for (int i = threadIdx.x; i < rows * vec_per_row; i += kMegaThreads) {
         const int r = i / vec_per_row;
         const int c = i - r * vec_per_row;
@@ -290,7 +307,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                 }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
-                if (lane == 0) p.logits[block + q * grid] = value;
+                if (lane == 0) {
+                    p.logits[block + q * grid] = value;
+                    st_tagged(p.logits_tagged + block + q * grid, __float_as_uint(value), tag);
+                }
             }
         } else {
             // T > 1 order: lane l sums columns l, l+32, ...; shuffle-down tree (cuda/nvfp4_ops.cu:178-207)
@@ -306,7 +326,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                 }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
-                if (lane == 0) p.logits[static_cast<std::size_t>(t) * kExperts + block + r * grid] = value;
+                if (lane == 0) {
+                    p.logits[static_cast<std::size_t>(t) * kExperts + block + r * grid] = value;
+                    st_tagged(p.logits_tagged + t * kExperts + block + r * grid, __float_as_uint(value), tag);
+                }
             }
         }
         // token quantisation, one 16-element block per thread across the grid
@@ -331,54 +354,116 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
             p.xs_tok[static_cast<std::size_t>(b >> 2) * 512 + t * 16 + (b & 3)] = scale_bits;
         }
         if (block == 0) {
-            for (int i = threadIdx.x; i <= kExperts; i += kMegaThreads) p.gu_done[i] = 0;
+            for (int i = threadIdx.x; i <= kExperts + 1; i += kMegaThreads) done_next[i] = 0;
         }
     }
     if (threadIdx.x == 0) stamp(1);
-    if (!grid_rendezvous(p.sync + 0, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
-    if (threadIdx.x == 0) stamp(2);
+    grid_arrive(p.sync + 0);          // quantised rows and zeroed counters of this block are out
 
     // ------------------------------------------------------------------ P1
-    if (!abort_word) {
-        // logits were written by other blocks of this launch: read them past L1
-        for (int i = threadIdx.x; i < rows * kExperts; i += kMegaThreads) rt.logits[i] = __ldcg(p.logits + i);
+    {
+        // logits come from all blocks of this launch: each word is polled until it carries this launch's
+        // number.  All of a thread's words are requested before the first is looked at.
+        constexpr int kPerThread = (kMegaMaxRows * kExperts + kMegaThreads - 1) / kMegaThreads;
+        uint2 word[kPerThread];
+        const std::uint64_t poll_start = global_timer_ns();
+        while (true) {
+            // every word still missing is requested again in one batch: one round trip per round, not per word
+            bool missing = false;
+#pragma unroll
+            for (int j = 0; j < kPerThread; ++j) {
+                const int i = threadIdx.x + j * kMegaThreads;
+                if (i < rows * kExperts) word[j] = ld_tagged(p.logits_tagged + i);
+            }
+#pragma unroll
+            for (int j = 0; j < kPerThread; ++j) {
+                const int i = threadIdx.x + j * kMegaThreads;
+                if (i < rows * kExperts) {
+                    if (word[j].y == tag) {
+                        rt.logits[i] = __uint_as_float(word[j].x);
+                    } else {
+                        missing = true;
+                    }
+                }
+            }
+            if (!missing) break;
+            if (global_timer_ns() - poll_start > 1000000000ULL) {
+                give_up(kStatusWaitExpired);
+                break;
+            }
+        }
+        // a thread of the last warp (free unless there are six or more tokens) makes sure every block's share of
+        // the quantised rows is written before the producer lane asks the TMA for them
+        if (threadIdx.x == kMegaThreads - 32) {
+            const bool arrived = wait_counter(p.sync + 0, (p.epoch + 1U) * static_cast<unsigned>(grid));
+            fence_proxy_async_all();      // ordinary stores of other blocks -> this block's TMA loads
+            rows_ready_word = arrived ? 1 : 0;
+        }
         for (int i = threadIdx.x; i < kMaxActive * kMegaMaxRows; i += kMegaThreads) (&rt.pp_tok[0][0])[i] = -1;
+        for (int i = threadIdx.x; i < kExperts; i += kMegaThreads) rt.expert_mask[i] = 0U;
         __syncthreads();
+    }
+    if (threadIdx.x == 0) stamp(2);
+    if (!abort_word) {
         for (int t = warp; t < rows; t += kMegaThreads / 32) {
             warp_top8(rt.logits + t * kExperts, rt.bias, rt.ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
         }
         __syncthreads();
-        // The ranking law of cuda/nvfp4_grouped.cu:117-132 evaluated directly on at most 64 assignments:
-        // position = #(smaller expert id) + #(same id, smaller flat index).
-        int my_rank = 0, my_less = 0, my_same = 0;
-        if (threadIdx.x < assignments) {
-            const int e = rt.ids[threadIdx.x];
-            for (int j = 0; j < assignments; ++j) {
-                const int other = rt.ids[j];
-                my_less += other < e;
-                my_same += other == e;
-                my_rank += other == e && j < static_cast<int>(threadIdx.x);
+        // The ranking law of cuda/nvfp4_grouped.cu:117-132, position = #(smaller expert id) + #(same id,
+        // smaller flat index), through one bit mask of tokens per expert (a token picks an expert at most
+        // once): popcounts give the ranks, a scan over the 256 experts the offsets and the active slots.
+        if (threadIdx.x < assignments) atomicOr(&rt.expert_mask[rt.ids[threadIdx.x]], 1U << (threadIdx.x / kTop));
+        __syncthreads();
+        if (warp == 0) {
+            int count[8], nonempty[8];
+            int count_sum = 0, nonempty_sum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const std::uint32_t m = rt.expert_mask[lane * 8 + i];
+                count[i] = __popc(m);
+                nonempty[i] = m != 0U;
+                count_sum += count[i];
+                nonempty_sum += nonempty[i];
             }
-            rt.rank[threadIdx.x] = my_rank;
-            rt.less[threadIdx.x] = my_less;
+            int count_before = count_sum, nonempty_before = nonempty_sum;       // inclusive scans over lanes
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int c = __shfl_up_sync(0xffffffffU, count_before, off);
+                const int n = __shfl_up_sync(0xffffffffU, nonempty_before, off);
+                if (lane >= off) {
+                    count_before += c;
+                    nonempty_before += n;
+                }
+            }
+            if (lane == 31) rt.n_active = nonempty_before + 1;
+            count_before -= count_sum;
+            nonempty_before -= nonempty_sum;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                rt.before[lane * 8 + i] = count_before;
+                rt.slot_of[lane * 8 + i] = 1 + nonempty_before;
+                count_before += count[i];
+                nonempty_before += nonempty[i];
+            }
         }
         __syncthreads();
         if (threadIdx.x < assignments) {
             const int i = threadIdx.x;
+            const int t = i / kTop;
             const int e = rt.ids[i];
-            int distinct_less = 0;
-            for (int j = 0; j < assignments; ++j) distinct_less += rt.rank[j] == 0 && rt.ids[j] < e;
-            const int slot = 1 + distinct_less;
+            const std::uint32_t m = rt.expert_mask[e];
+            const int my_rank = __popc(m & ((1U << t) - 1U));
+            const int slot = rt.slot_of[e];
+            rt.rank[i] = my_rank;
+            rt.less[i] = rt.before[e];
             rt.slot_a[i] = slot;
-            rt.pp_tok[slot][i / kTop] = (slot - 1) * kTile + my_rank;
+            rt.pp_tok[slot][t] = (slot - 1) * kTile + my_rank;
             if (my_rank == 0) {
                 rt.active[slot] = e;
-                rt.slot_rows[slot] = my_same;
+                rt.slot_rows[slot] = __popc(m);
             }
         } else if (threadIdx.x == assignments) {
-            int distinct = 0;
-            for (int j = 0; j < assignments; ++j) distinct += rt.rank[j] == 0;
-            rt.n_active = distinct + 1;
+            const int distinct = rt.n_active - 1;
             rt.active[0] = kExperts;
             rt.slot_rows[0] = rows;
             for (int t = 0; t < rows; ++t) rt.pp_tok[0][t] = distinct * kTile + t;
@@ -391,40 +476,62 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     const int dn_tiles = hidden / kTile;         // 20
     const int gu_kblocks = (hidden / 2) / kKB;   // 10 stages per gate/up tile
     const int dn_stages = (inter / 2) / kKB / 2; // 2 stages per down tile (two K blocks each)
-    Deal deal;
-    deal.init(rt.n_active, gu_tiles, dn_tiles, grid, block);
+    const int gu_items = abort_word ? 0 : rt.n_active * gu_tiles;
+    const int total_items = abort_word ? 0 : rt.n_active * (gu_tiles + dn_tiles);
 
     if (warp == 0) {
         if (elect_one() && !abort_word) {
             int stage = 0;
             std::uint32_t phase = 0;
-            int kind, slot, m_tile;
-            for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+            int sequence = 0;
+            if (rows_ready_word == 0) give_up(kStatusWaitExpired);
+            const std::uint64_t stream_policy = l2_policy_evict_first();     // weights are read once per launch
+            int current = first_tile_word;
+            while (!abort_word) {
+                if (current >= total_items) {
+                    // end of work: an empty stage carries the closing entry to the MMA lane
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                    tile_queue[sequence % kTileQueue] = -1;
+                    mbar_arrive(weight_bar(stage));
+                    mbar_arrive(token_bar(stage));
+                    break;
+                }
+                const int following = static_cast<int>(atomicAdd(tile_counter, 1U));
+                int kind, slot, m_tile;
+                if (current < gu_items) {
+                    kind = 0; slot = current / gu_tiles; m_tile = current - slot * gu_tiles;
+                } else {
+                    const int d = current - gu_items;
+                    kind = 1; slot = d / dn_tiles; m_tile = d - slot * dn_tiles;
+                }
                 const int expert = rt.active[slot];
                 const int entry = expert == kExperts ? p.bank.local_experts : expert - p.bank.first_expert;
                 const int n_stages = kind == 0 ? gu_kblocks : dn_stages;
                 bool tokens_ready = kind == 0;
+                bool ok = true;
                 for (int s = 0; s < n_stages; ++s) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(kStatusWaitExpired); ok = false; break; }
                     const std::uint32_t st = base + stage * kStage;
-                    if (i == 0 && s < 10) stamp(16 + s);
+                    if (s == 0) tile_queue[sequence % kTileQueue] = encode_tile(kind, slot, m_tile);
+                    if (sequence == 0 && s < 10) stamp(16 + s);
                     mbar_arrive_expect_tx(weight_bar(stage), kWeightTx);
                     if (kind == 0) {
-                        bulk_load(st, p.bank.g13 + ((static_cast<std::size_t>(entry) * gu_tiles + m_tile) * gu_kblocks + s) *
-                                                       kChunkBytes,
-                                  kChunkBytes, weight_bar(stage));
+                        bulk_load_hint(st, p.bank.g13 + ((static_cast<std::size_t>(entry) * gu_tiles + m_tile) * gu_kblocks + s) *
+                                                            kChunkBytes,
+                                       kChunkBytes, weight_bar(stage), stream_policy);
                         mbar_arrive_expect_tx(token_bar(stage), 2 * kSlab);
                         tma_load_2d(st + kOffB0, &map_x, token_bar(stage), s * kKB, 0);
                         bulk_load(st + kOffSfB0, p.xs_tok + static_cast<std::size_t>(s * 4) * 512, kSlab, token_bar(stage));
                     } else {
-                        bulk_load(st, p.bank.g2 + ((static_cast<std::size_t>(entry) * dn_tiles + m_tile) * dn_stages + s) *
-                                                      kChunkBytes,
-                                  kChunkBytes, weight_bar(stage));
+                        bulk_load_hint(st, p.bank.g2 + ((static_cast<std::size_t>(entry) * dn_tiles + m_tile) * dn_stages + s) *
+                                                           kChunkBytes,
+                                       kChunkBytes, weight_bar(stage), stream_policy);
                         if (!tokens_ready) {
                             // the SwiGLU rows of this expert exist once its eight gate/up tiles are done
-                            if (!wait_counter(reinterpret_cast<const unsigned*>(p.gu_done + slot),
+                            if (!wait_counter(reinterpret_cast<const unsigned*>(done + slot),
                                               static_cast<unsigned>(gu_tiles))) {
                                 give_up(kStatusWaitExpired);
+                                ok = false;
                                 break;
                             }
                             fence_proxy_async_all();
@@ -440,7 +547,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1U; }
                 }
-                if (i + 1 == deal.n_gu) stamp(4);           // all gate/up loads issued
+                if (!ok) break;
+                if (current < gu_items && following >= gu_items) stamp(4);   // this block's last gate/up tile issued
+                ++sequence;
+                current = following;
             }
             stamp(5);                                        // all loads issued
         }
@@ -453,21 +563,29 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
             constexpr std::uint32_t idesc = idesc_nvf4(kTile, kN);
             const std::uint32_t sf_tmem = tmem_base + kAccumBuffers * kAccumCols;
             int sf_buffer = 0;
-            int kind, slot, m_tile;
-            for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+            for (int sequence = 0; !abort_word; ++sequence) {
+                // the tile's first stage also publishes its queue entry
+                if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) { give_up(kStatusWaitExpired); break; }
+                const int code = tile_queue[sequence % kTileQueue];
                 if (!mbar_wait(accum_empty(buffer), ((accum_phase >> buffer) & 1U) ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                if (code < 0) {
+                    mbar_arrive(accum_full(buffer));        // pass the closing entry on to the epilogue warps
+                    break;
+                }
+                int kind, slot, m_tile;
+                decode_tile(code, &kind, &slot, &m_tile);
                 tc_fence_after();
                 const std::uint32_t accum = tmem_base + buffer * kAccumCols;
                 const int n_stages = kind == 0 ? gu_kblocks : dn_stages;
                 bool ok = true;
                 for (int s = 0; s < n_stages; ++s) {
-                    if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) {
+                    if (s > 0 && (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase))) {
                         give_up(kStatusWaitExpired);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    if (i == 0 && s < 10) stamp(26 + s);
+                    if (sequence == 0 && s < 10) stamp(26 + s);
                     const std::uint32_t st = base + stage * kStage;
                     const std::uint32_t sfc = sf_tmem + sf_buffer * kSfColsPerBuffer;
                     const int slabs = kind == 0 ? 3 : 4;            // SFA0, SFA1, SFB0 (, SFB1)
@@ -500,7 +618,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                         }
                     }
                     tc_commit(empty_bar(stage));
-                    if (i == 0 && s < 10) stamp(36 + s);
+                    if (sequence == 0 && s < 10) stamp(36 + s);
                     sf_buffer ^= 1;
                     if (++stage == kStages) { stage = 0; phase ^= 1U; }
                 }
@@ -508,8 +626,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                 tc_commit(accum_full(buffer));
                 accum_phase ^= 1U << buffer;
                 buffer = (buffer + 1) % kAccumBuffers;
-                if (i == 0) stamp(6);                        // first tile's MMAs issued
-                if (i + 1 == deal.n_gu) stamp(7);            // gate/up MMAs issued
+                if (sequence == 0) stamp(6);                 // first tile's MMAs issued
             }
             stamp(8);
         }
@@ -528,22 +645,24 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
             }
             if (t < rows) p.pp_of_flat[assignments + t] = rt.pp_tok[0][t];
             for (int e = t; e <= kExperts; e += 128) {
-                int count = 0, before = 0;
-                for (int j = 0; j < assignments; ++j) {
-                    count += rt.ids[j] == e;
-                    before += rt.ids[j] < e;
+                if (e < kExperts) {
+                    p.counts[e] = __popc(rt.expert_mask[e]);
+                    p.offsets[e] = rt.before[e];
+                } else {
+                    p.offsets[e] = assignments;
                 }
-                if (e < kExperts) p.counts[e] = count;
-                p.offsets[e] = before;
             }
         }
         const int quarter = warp & 3;
         int buffer = 0;
         std::uint32_t accum_phase = 0;
-        int kind, slot, m_tile;
-        for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+        for (int sequence = 0; !abort_word; ++sequence) {
             if (!mbar_wait(accum_full(buffer), (accum_phase >> buffer) & 1U)) { give_up(kStatusWaitExpired); break; }
             accum_phase ^= 1U << buffer;
+            const int code = tile_queue[sequence % kTileQueue];
+            if (code < 0) break;
+            int kind, slot, m_tile;
+            decode_tile(code, &kind, &slot, &m_tile);
             tc_fence_after();
             const int expert = rt.active[slot];
             const int entry = expert == kExperts ? p.bank.local_experts : expert - p.bank.first_expert;
@@ -591,21 +710,34 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                     mbar_arrive(accum_empty(buffer));
                     mbar_arrive(accum_empty(buffer));
                     mbar_arrive(accum_empty(buffer));
-                    atomicAdd(p.gu_done + slot, 1);
+                    atomicAdd(done + slot, 1);
                 }
             } else {
                 const float alpha = p.bank.alpha[entry * 3 + 2];
-                const int count = rt.slot_rows[slot];
                 const int pp0 = slab_of_slot(slot, rt.n_active);
                 std::uint32_t d[16];
                 tmem_load16(lane_base, d);
                 tmem_load_wait();
+                // row n of this expert belongs to its n-th routed token; that token's slot says where the
+                // combine expects it (slot 8 = the shared expert)
+                int n = 0;
 #pragma unroll
-                for (int n = 0; n < kMegaMaxRows; ++n) {
-                    if (n < count) {
-                        p.mixed[static_cast<std::size_t>(pp0 + n) * hidden + row] =
-                            float_to_bf16_bits(__uint_as_float(d[n]) * alpha);
+                for (int t = 0; t < kMegaMaxRows; ++t) {
+                    if (t >= rows || rt.pp_tok[slot][t] < 0) continue;             // warp uniform
+                    int k = kTop;
+                    if (slot != 0) {
+                        k = 0;
+#pragma unroll
+                        for (int kk = 1; kk < kTop; ++kk) k = rt.slot_a[t * kTop + kk] == slot ? kk : k;
                     }
+                    std::uint32_t value = 0;
+#pragma unroll
+                    for (int c = 0; c < kMegaMaxRows; ++c) value = c == n ? d[c] : value;   // d[n] without dynamic indexing
+                    value = float_to_bf16_bits(__uint_as_float(value) * alpha);
+                    p.mixed[static_cast<std::size_t>(pp0 + n) * hidden + row] = static_cast<std::uint16_t>(value);
+                    const std::uint32_t next = __shfl_down_sync(0xffffffffU, value, 1);
+                    if ((lane & 1) == 0) st_tagged(p.ret + static_cast<std::size_t>(t * (kTop + 1) + k) * (hidden / 2) + (row >> 1), value | (next << 16), tag);
+                    ++n;
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -624,41 +756,46 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     if (threadIdx.x == 0) stamp(10);
 
     // ------------------------------------------------------------------ P4
-    if (!grid_rendezvous(p.sync + 1, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
-    if (threadIdx.x == 0) stamp(11);
     if (abort_word) return;
-    const int vectors = hidden / 8;
-    for (int v = block * kMegaThreads + threadIdx.x; v < rows * vectors; v += grid * kMegaThreads) {
-        const int row = v / vectors;
-        const int c8 = v - row * vectors;
-        float acc[8];
+    // One thread per four output features: eight routed slots in slot order, then the shared expert;
+    // each operand is polled until its words carry this launch's number.
+    const int quads = hidden / 4;
+    for (int v = block * kMegaThreads + threadIdx.x; v < rows * quads; v += grid * kMegaThreads) {
+        const int row = v / quads;
+        const int q = v - row * quads;
+        float acc[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+        bool ok = true;
+        const unsigned long long* operand = p.ret + static_cast<std::size_t>(row) * (kTop + 1) * (hidden / 2) + 2 * q;
+        uint4 got[kTop + 1];                                  // all nine requested before the first is looked at
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.0F;
+        for (int slot = 0; slot <= kTop; ++slot) got[slot] = ld_tagged_pair(operand + static_cast<std::size_t>(slot) * (hidden / 2));
+#pragma unroll
+        for (int slot = 0; slot <= kTop; ++slot) {
+            if (got[slot].y != tag || got[slot].w != tag) {
+                ok = ok && poll_tagged_pair(operand + static_cast<std::size_t>(slot) * (hidden / 2), tag, &got[slot].x, &got[slot].z);
+            }
+        }
 #pragma unroll
         for (int slot = 0; slot < kTop; ++slot) {
             const float w = rt.weights[row * kTop + slot];
-            const int pp = rt.pp_tok[rt.slot_a[row * kTop + slot]][row];
-            const uint4 r = __ldcg(reinterpret_cast<const uint4*>(p.mixed + static_cast<std::size_t>(pp) * hidden + c8 * 8));
-            const std::uint32_t words[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                acc[2 * k] = fmaf(__uint_as_float(words[k] << 16), w, acc[2 * k]);
-                acc[2 * k + 1] = fmaf(__uint_as_float(words[k] & 0xffff0000U), w, acc[2 * k + 1]);
-            }
+            const std::uint32_t a0 = got[slot].x, a1 = got[slot].z;
+            acc[0] = fmaf(__uint_as_float(a0 << 16), w, acc[0]);
+            acc[1] = fmaf(__uint_as_float(a0 & 0xffff0000U), w, acc[1]);
+            acc[2] = fmaf(__uint_as_float(a1 << 16), w, acc[2]);
+            acc[3] = fmaf(__uint_as_float(a1 & 0xffff0000U), w, acc[3]);
         }
-        const uint4 sh = __ldcg(reinterpret_cast<const uint4*>(
-            p.mixed + static_cast<std::size_t>(rt.pp_tok[0][row]) * hidden + c8 * 8));
-        const std::uint32_t sw[4] = {sh.x, sh.y, sh.z, sh.w};
-        std::uint32_t out_words[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float lo = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k])) + __uint_as_float(sw[k] << 16);
-            const float hi = bf16_bits_to_float(float_to_bf16_bits(acc[2 * k + 1])) + __uint_as_float(sw[k] & 0xffff0000U);
-            out_words[k] = static_cast<std::uint32_t>(float_to_bf16_bits(lo)) |
-                           (static_cast<std::uint32_t>(float_to_bf16_bits(hi)) << 16);
+        const std::uint32_t s0 = got[kTop].x, s1 = got[kTop].z;
+        if (!ok) {
+            give_up(kStatusWaitExpired);
+            break;
         }
-        *reinterpret_cast<uint4*>(p.out + static_cast<std::size_t>(row) * hidden + c8 * 8) =
-            make_uint4(out_words[0], out_words[1], out_words[2], out_words[3]);
+        const float o0 = bf16_bits_to_float(float_to_bf16_bits(acc[0])) + __uint_as_float(s0 << 16);
+        const float o1 = bf16_bits_to_float(float_to_bf16_bits(acc[1])) + __uint_as_float(s0 & 0xffff0000U);
+        const float o2 = bf16_bits_to_float(float_to_bf16_bits(acc[2])) + __uint_as_float(s1 << 16);
+        const float o3 = bf16_bits_to_float(float_to_bf16_bits(acc[3])) + __uint_as_float(s1 & 0xffff0000U);
+        *reinterpret_cast<uint2*>(p.out + static_cast<std::size_t>(row) * hidden + q * 4) =
+            make_uint2(static_cast<std::uint32_t>(float_to_bf16_bits(o0)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o1)) << 16),
+                       static_cast<std::uint32_t>(float_to_bf16_bits(o2)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o3)) << 16));
     }
     if (threadIdx.x == 0) stamp(12);
 }
@@ -701,6 +838,8 @@ cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std
     p.hq = plan->hq_pp;
     p.hs = plan->hs_sw;
     p.mixed = plan->mixed_pp;
+    p.logits_tagged = plan->mega_logits;
+    p.ret = plan->mega_ret;
     p.sync = plan->mega_sync;
     p.gu_done = plan->gu_done;
     p.status = plan->status;

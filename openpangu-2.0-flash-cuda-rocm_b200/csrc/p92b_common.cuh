@@ -87,41 +87,58 @@ __device__ __forceinline__ void warp_top8(const float* __restrict__ lg, const fl
     const int lane = threadIdx.x & 31;
     float raw[8];
     float corrected[8];
+    int id[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int e = lane + 32 * i;
         raw[i] = 1.0F / (1.0F + expf(-lg[e]));
         corrected[i] = raw[i] + bias[e];
+        id[i] = e;
     }
-    unsigned used = 0U;
+    // Each lane first orders its own eight candidates (higher corrected score first, lower id on
+    // ties; a NaN orders last, as a comparison-based scan would never pick it): a 19-comparator
+    // network on registers.  A round of the selection then only looks at the head of each lane's list.
+#define P92B_ORDER(a, b)                                                                              \
+    {                                                                                                 \
+        const bool swap = corrected[b] > corrected[a] || (corrected[b] == corrected[a] && id[b] < id[a]) || \
+                          (corrected[a] != corrected[a] && corrected[b] == corrected[b]);             \
+        const float c0 = swap ? corrected[b] : corrected[a], c1 = swap ? corrected[a] : corrected[b]; \
+        const float r0 = swap ? raw[b] : raw[a], r1 = swap ? raw[a] : raw[b];                         \
+        const int i0 = swap ? id[b] : id[a], i1 = swap ? id[a] : id[b];                               \
+        corrected[a] = c0; corrected[b] = c1; raw[a] = r0; raw[b] = r1; id[a] = i0; id[b] = i1;       \
+    }
+    P92B_ORDER(0, 1) P92B_ORDER(2, 3) P92B_ORDER(4, 5) P92B_ORDER(6, 7)
+    P92B_ORDER(0, 2) P92B_ORDER(1, 3) P92B_ORDER(4, 6) P92B_ORDER(5, 7)
+    P92B_ORDER(1, 2) P92B_ORDER(5, 6)
+    P92B_ORDER(0, 4) P92B_ORDER(1, 5) P92B_ORDER(2, 6) P92B_ORDER(3, 7)
+    P92B_ORDER(2, 4) P92B_ORDER(3, 5)
+    P92B_ORDER(1, 2) P92B_ORDER(3, 4) P92B_ORDER(5, 6)
+#undef P92B_ORDER
     float chosen_weight = 0.0F;   // lane k keeps slot k's raw weight
     int chosen_id = 0;
-    // The eight rounds stay a loop: unrolled they are several thousand instructions, and a block that
+    // The eight rounds stay a loop: unrolled they are a few thousand instructions, and a block that
     // runs this alone (the routing block of the fused kernels) then waits on instruction fetches.
 #pragma unroll 1
     for (int slot = 0; slot < 8; ++slot) {
-        float best = -FLT_MAX;
-        int best_id = 256 + lane;
-        float best_raw = 0.0F;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float c = (used >> i) & 1U ? -FLT_MAX : corrected[i];
-            const int e = lane + 32 * i;
-            // ascending id within the lane, so strict '>' keeps the lower id on ties
-            if (c > best || (c == best && e < best_id)) {
-                best = c;
-                best_id = e;
-                best_raw = raw[i];
-            }
-        }
-        // warp arg-max, lower id on ties: order-preserving integer image of the score (a NaN never wins,
-        // as with the comparisons above), one max over the warp, then the smallest id among the lanes that hold it
+        // warp arg-max over the heads, lower id on ties: order-preserving integer image of the score
+        // (0 for a NaN or an exhausted list), one max over the warp, then the smallest id among the
+        // lanes that hold it
+        const float best = corrected[0];
         const std::uint32_t bits = __float_as_uint(best);
         const std::uint32_t key = best != best ? 0U : (bits & 0x80000000U ? ~bits : bits | 0x80000000U);
         const std::uint32_t top = __reduce_max_sync(0xffffffffU, key);
-        const int winner = static_cast<int>(__reduce_min_sync(0xffffffffU, key == top ? static_cast<std::uint32_t>(best_id) : 0xffffffffU));
-        const float winner_raw = __shfl_sync(0xffffffffU, best_raw, winner & 31);
-        if ((winner & 31) == lane) used |= 1U << (winner >> 5);
+        const int winner = static_cast<int>(__reduce_min_sync(0xffffffffU, key == top ? static_cast<std::uint32_t>(id[0]) : 0xffffffffU));
+        const float winner_raw = __shfl_sync(0xffffffffU, raw[0], winner & 31);
+        if ((winner & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < 7; ++i) {
+                corrected[i] = corrected[i + 1];
+                raw[i] = raw[i + 1];
+                id[i] = id[i + 1];
+            }
+            corrected[7] = __uint_as_float(0x7fc00000U);      // exhausted: key 0
+            id[7] = 0x7fffffff;
+        }
         if (lane == slot) {
             chosen_weight = winner_raw;
             chosen_id = winner;
@@ -238,7 +255,10 @@ struct p92b_plan {
     std::uint8_t* xq_tok = nullptr;       // [16][H/2] token-order NVFP4 rows
     std::uint8_t* xs_tok = nullptr;       // [H/64][512] their scales, one 128-row tile per 4 scale columns
     unsigned* mega_sync = nullptr;        // [2] arrival counters (monotonic across launches)
-    std::int32_t* gu_done = nullptr;      // [257]
+    std::int32_t* gu_done = nullptr;      // [2][264] per launch parity: gate/up tiles finished per active slot, [257] the tile counter
+    std::int32_t* ep_gu_done = nullptr;   // [264] the same for the fused expert-parallel kernel
+    unsigned long long* mega_logits = nullptr;  // [8][256] router logits as {value, launch number} words
+    unsigned long long* mega_ret = nullptr;     // [8][9][1280] down rows as {two BF16, launch number} words
     unsigned mega_epoch = 0;
     unsigned ep_epoch = 0;                // launches of the fused expert-parallel kernel (counters mega_sync[2..3])
     unsigned long long* mega_trace = nullptr;   // [sm_count][64] timer stamps of the last fused launch (P92B_TRACE=1)

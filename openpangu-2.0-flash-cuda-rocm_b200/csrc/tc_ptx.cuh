@@ -104,6 +104,20 @@ __device__ __forceinline__ void bulk_load(std::uint32_t dst, const void* src, st
                  : "memory");
 }
 
+// The same with an L2 policy: weights that are read once per launch are marked "evict first", so a
+// 120 MB stream does not push everything else (code, routing tables, token rows) out of the L2.
+__device__ __forceinline__ std::uint64_t l2_policy_evict_first() {
+    std::uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_load_hint(std::uint32_t dst, const void* src, std::uint32_t bytes, std::uint32_t bar,
+                                               std::uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+                 : "memory");
+}
+
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
