@@ -16,9 +16,11 @@
 //       expert (cuda/nvfp4_ops.cu:124-142,92-95).
 //
 // Inside a GPU the phases are those of the single-GPU decode kernel (decode_mega.cu): router rows
-// and token quantisation spread over the grid, routing lists in shared memory, gate/up and down
-// tiles through one TMA ring and one tcgen05 pipeline, static deal of tiles.  The token side of
-// every MMA is the whole gathered batch (16 or 32 columns).
+// and token quantisation spread over the grid (logits published as tagged words, no device-wide
+// stop), routing lists in shared memory, gate/up and down tiles through one TMA ring and one
+// tcgen05 pipeline, tiles handed out from a device-wide counter.  The token side of every MMA is
+// the whole gathered batch (16 or 32 columns).  The one device-wide rendezvous left is the one
+// behind which the gathered rows are complete in the layout the TMA reads.
 //
 // Nothing that crosses NVLink is ordered by a fence (a system-scope fence costs about 5 µs here, more
 // than the rest of an exchange).  Every word that travels is 8 bytes, {4 bytes of payload, the launch
@@ -89,8 +91,9 @@ struct EpParams {
     std::int32_t* counts;
     std::uint8_t* hq;
     std::uint8_t* hs;
-    unsigned* sync;                // [2] device-wide arrival counters of the plan
-    std::int32_t* gu_done;
+    unsigned long long* logits_tagged;   // [8][256] {value, launch number on this plan}
+    unsigned* sync;                // device-wide arrival counter of the plan (monotonic across launches)
+    std::int32_t* gu_done;         // [2][264] by launch parity: gate/up tiles finished per active slot, [257] tile counter
     std::int32_t* status;
     unsigned long long* trace;
     std::uint8_t* win[kEpMaxWorld];
@@ -190,49 +193,16 @@ __device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned targ
     return ok != 0;
 }
 
-// Static deal of tiles to blocks (same scheme as the single-GPU decode kernel): gate/up tiles
-// round-robin, down tiles fill every block to a common level counted in ring stages.
-struct Deal {
-    int gu_items, dn_items, grid, n_gu, dn_begin, dn_count, total_cap, leftovers;
-    __device__ void init(int n_active, int gu_tiles, int dn_tiles, int grid_, int block) {
-        grid = grid_;
-        gu_items = n_active * gu_tiles;
-        dn_items = n_active * dn_tiles;
-        const int q = gu_items / grid;
-        const int r = gu_items - q * grid;
-        const int stages = gu_items * 10 + dn_items * 2;
-        const int level = stages / grid;
-        int cap_hi = (level - 10 * (q + 1)) / 2;
-        int cap_lo = (level - 10 * q) / 2;
-        cap_hi = cap_hi < 0 ? 0 : cap_hi;
-        cap_lo = cap_lo < 0 ? 0 : cap_lo;
-        n_gu = q + (block < r ? 1 : 0);
-        const int mine = block < r ? cap_hi : cap_lo;
-        const int prefix = block >= r ? (block - r) * cap_lo : (grid - r) * cap_lo + block * cap_hi;
-        total_cap = r * cap_hi + (grid - r) * cap_lo;
-        dn_begin = prefix < dn_items ? prefix : dn_items;
-        dn_count = dn_items - dn_begin < mine ? dn_items - dn_begin : mine;
-        leftovers = dn_items > total_cap ? dn_items - total_cap : 0;
-    }
-    __device__ bool item(int i, int block, int gu_tiles, int dn_tiles, int* kind, int* slot, int* m_tile) const {
-        if (i < n_gu) {
-            const int g = block + i * grid;
-            *kind = 0; *slot = g / gu_tiles; *m_tile = g - *slot * gu_tiles;
-            return true;
-        }
-        i -= n_gu;
-        int d;
-        if (i < dn_count) {
-            d = dn_begin + i;
-        } else {
-            const int j = block + (i - dn_count) * grid;
-            if (j >= leftovers) return false;
-            d = total_cap + j;
-        }
-        *kind = 1; *slot = d / dn_tiles; *m_tile = d - *slot * dn_tiles;
-        return true;
-    }
-};
+// Tiles are handed out through one device-wide counter (same scheme as the single-GPU decode kernel):
+// the producer lane takes the numbers, one ahead, and passes each tile to the MMA lane and the epilogue
+// warps through a small queue in shared memory; a negative entry ends the queue.
+constexpr int kTileQueue = 16;
+__device__ __forceinline__ int encode_tile(int kind, int slot, int m_tile) { return (kind << 24) | (slot << 8) | m_tile; }
+__device__ __forceinline__ void decode_tile(int code, int* kind, int* slot, int* m_tile) {
+    *kind = code >> 24;
+    *slot = (code >> 8) & 0xffff;
+    *m_tile = code & 0xff;
+}
 
 template <int kN>
 struct StageLayout {
@@ -253,6 +223,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     __shared__ __align__(8) std::uint64_t barrier_words[3 * kStages + 2 * kAccumBuffers];
     __shared__ std::uint32_t tmem_slot_word;
     __shared__ volatile std::uint32_t abort_word;
+    __shared__ volatile int tile_queue[kTileQueue];
+    __shared__ volatile int first_tile_word;
 
     const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     const std::uint32_t bars = smem_u32(barrier_words);
@@ -273,6 +245,11 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     const int rpg = p.rows_per_gpu;
     const int parity = static_cast<int>(p.wepoch & 1U);
     const std::uint32_t tag = p.wepoch + 1U;               // never 0: a fresh window reads as "not yet"
+    const std::uint32_t plan_tag = p.epoch + 1U;           // for words that stay on this GPU (the plan's scratch)
+    // this launch's counters were zeroed by the launch before (or at plan creation); it zeroes the next one's
+    std::int32_t* const done = p.gu_done + (p.epoch & 1U) * 264;
+    std::int32_t* const done_next = p.gu_done + ((p.epoch + 1U) & 1U) * 264;
+    unsigned* const tile_counter = reinterpret_cast<unsigned*>(done + kExperts + 1);
     std::uint8_t* const my_win = p.win[p.rank];
 
     if (threadIdx.x == 0) {
@@ -308,6 +285,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     for (int e = threadIdx.x; e < kExperts; e += kEpThreads) rt.bias[e] = __ldg(p.bias + e);
     pdl_wait();
     pdl_launch_dependents();
+    // the first tile number is asked for now and used after the routing, the atomic's latency in between
+    if (threadIdx.x == 0) first_tile_word = static_cast<int>(atomicAdd(tile_counter, 1U));
     for (int i = threadIdx.x; i < rows * vec_per_row; i += kEpThreads) {
         const int r = i / vec_per_row;
         const int c = i - r * vec_per_row;
@@ -349,7 +328,10 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                 }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
-                if (lane == 0) p.logits[block + q * grid] = value;
+                if (lane == 0) {
+                    p.logits[block + q * grid] = value;
+                    st_tagged(p.logits_tagged + block + q * grid, __float_as_uint(value), plan_tag);
+                }
             }
         } else {
             for (int q = warp; q < my_experts * rows; q += kEpThreads / 32) {
@@ -364,7 +346,10 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                 }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
-                if (lane == 0) p.logits[static_cast<std::size_t>(t) * kExperts + block + r * grid] = value;
+                if (lane == 0) {
+                    p.logits[static_cast<std::size_t>(t) * kExperts + block + r * grid] = value;
+                    st_tagged(p.logits_tagged + t * kExperts + block + r * grid, __float_as_uint(value), plan_tag);
+                }
             }
         }
         const int blocks16 = hidden / 16;
@@ -400,18 +385,45 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
             }
         }
         if (block == 0) {
-            for (int i = threadIdx.x; i <= kExperts; i += kEpThreads) p.gu_done[i] = 0;
+            for (int i = threadIdx.x; i <= kExperts + 1; i += kEpThreads) done_next[i] = 0;
         }
     }
     if (threadIdx.x == 0) stamp(1);
-    if (!grid_rendezvous(p.sync + 0, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
-    if (threadIdx.x == 0) stamp(2);
 
     // ------------------------------------------------- routing of the home tokens: block d tells GPU d
     if (!abort_word && block < world) {
         std::uint64_t* dst = reinterpret_cast<std::uint64_t*>(p.win[block] + kWinArrive + parity * kWinArriveParity) +
                              static_cast<std::size_t>(p.rank * rpg) * kTokWords;
-        for (int i = threadIdx.x; i < rows * kExperts; i += kEpThreads) rt.logits[i] = __ldcg(p.logits + i);
+        {
+            // the logits come from all blocks: every word still missing is requested again in one batch
+            constexpr int kPerThread = (kEpMaxLocalRows * kExperts + kEpThreads - 1) / kEpThreads;
+            uint2 word[kPerThread];
+            const std::uint64_t poll_start = global_timer_ns();
+            while (true) {
+                bool missing = false;
+#pragma unroll
+                for (int j = 0; j < kPerThread; ++j) {
+                    const int i = threadIdx.x + j * kEpThreads;
+                    if (i < rows * kExperts) word[j] = ld_tagged(p.logits_tagged + i);
+                }
+#pragma unroll
+                for (int j = 0; j < kPerThread; ++j) {
+                    const int i = threadIdx.x + j * kEpThreads;
+                    if (i < rows * kExperts) {
+                        if (word[j].y == plan_tag) {
+                            rt.logits[i] = __uint_as_float(word[j].x);
+                        } else {
+                            missing = true;
+                        }
+                    }
+                }
+                if (!missing) break;
+                if (global_timer_ns() - poll_start > 1000000000ULL) {
+                    give_up(kStatusWaitExpired);
+                    break;
+                }
+            }
+        }
         __syncthreads();
         if (threadIdx.x == 0) stamp(13);
         for (int t = warp; t < rows; t += kEpThreads / 32) {
@@ -504,7 +516,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     }
     if (threadIdx.x == 0) stamp(5);
     // the untagged batch is complete on this GPU once every block has written its share
-    if (!grid_rendezvous(p.sync + 1, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
+    if (!grid_rendezvous(p.sync, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
     if (threadIdx.x == 0) stamp(6);
 
     // ------------------------------------------------------------ gate/up and down tiles
@@ -512,8 +524,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     const int dn_tiles = hidden / kTile;
     const int gu_kblocks = (hidden / 2) / kKB;
     const int dn_stages = (inter / 2) / kKB / 2;
-    Deal deal;
-    deal.init(abort_word ? 0 : rt.n_active, gu_tiles, dn_tiles, grid, block);
+    const int gu_items = abort_word ? 0 : rt.n_active * gu_tiles;
+    const int total_items = abort_word ? 0 : rt.n_active * (gu_tiles + dn_tiles);
     const int token_row0 = parity * kEpMaxTokens;         // first row of this launch's batch in the token map
     const std::uint8_t* xs_batch = my_win + kWinXs + parity * kWinXsParity;
 
@@ -521,31 +533,51 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
         if (elect_one() && !abort_word) {
             int stage = 0;
             std::uint32_t phase = 0;
-            int kind, slot, m_tile;
-            fence_proxy_async_all();          // the gathered rows were written by ordinary stores (peers', over NVLink)
-            for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+            int sequence = 0;
+            fence_proxy_async_all();          // the gathered rows were written by ordinary stores
+            const std::uint64_t stream_policy = l2_policy_evict_first();     // weights are read once per launch
+            int current = first_tile_word;
+            while (!abort_word) {
+                if (current >= total_items) {
+                    // end of work: an empty stage carries the closing entry to the MMA lane
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                    tile_queue[sequence % kTileQueue] = -1;
+                    mbar_arrive(weight_bar(stage));
+                    mbar_arrive(token_bar(stage));
+                    break;
+                }
+                const int following = static_cast<int>(atomicAdd(tile_counter, 1U));
+                int kind, slot, m_tile;
+                if (current < gu_items) {
+                    kind = 0; slot = current / gu_tiles; m_tile = current - slot * gu_tiles;
+                } else {
+                    const int d = current - gu_items;
+                    kind = 1; slot = d / dn_tiles; m_tile = d - slot * dn_tiles;
+                }
                 const int entry = rt.active[slot];
                 const int n_stages = kind == 0 ? gu_kblocks : dn_stages;
                 bool tokens_ready = kind == 0;
+                bool ok = true;
                 for (int s = 0; s < n_stages; ++s) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(kStatusWaitExpired); ok = false; break; }
                     const std::uint32_t st = base + stage * L::kStage;
+                    if (s == 0) tile_queue[sequence % kTileQueue] = encode_tile(kind, slot, m_tile);
                     mbar_arrive_expect_tx(weight_bar(stage), kChunkBytes);
                     if (kind == 0) {
-                        bulk_load(st, p.bank.g13 + ((static_cast<std::size_t>(entry) * gu_tiles + m_tile) * gu_kblocks + s) *
-                                                       kChunkBytes,
-                                  kChunkBytes, weight_bar(stage));
+                        bulk_load_hint(st, p.bank.g13 + ((static_cast<std::size_t>(entry) * gu_tiles + m_tile) * gu_kblocks + s) *
+                                                            kChunkBytes,
+                                       kChunkBytes, weight_bar(stage), stream_policy);
                         mbar_arrive_expect_tx(token_bar(stage), kN * kKB + kSlab);
                         tma_load_2d(st + kOffB0, &map_tok, token_bar(stage), s * kKB, token_row0);
                         bulk_load(st + L::kOffSfB0, xs_batch + static_cast<std::size_t>(s * 4) * 512, kSlab, token_bar(stage));
                     } else {
-                        bulk_load(st, p.bank.g2 + ((static_cast<std::size_t>(entry) * dn_tiles + m_tile) * dn_stages + s) *
-                                                      kChunkBytes,
-                                  kChunkBytes, weight_bar(stage));
+                        bulk_load_hint(st, p.bank.g2 + ((static_cast<std::size_t>(entry) * dn_tiles + m_tile) * dn_stages + s) *
+                                                           kChunkBytes,
+                                       kChunkBytes, weight_bar(stage), stream_policy);
                         if (!tokens_ready) {
-                            if (!wait_counter(reinterpret_cast<const unsigned*>(p.gu_done + slot),
-                                              static_cast<unsigned>(gu_tiles))) {
+                            if (!wait_counter(reinterpret_cast<const unsigned*>(done + slot), static_cast<unsigned>(gu_tiles))) {
                                 give_up(kStatusWaitExpired);
+                                ok = false;
                                 break;
                             }
                             fence_proxy_async_all();
@@ -561,6 +593,9 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1U; }
                 }
+                if (!ok) break;
+                ++sequence;
+                current = following;
             }
             stamp(7);
         }
@@ -573,15 +608,23 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
             constexpr std::uint32_t idesc = idesc_nvf4(kTile, kN);
             const std::uint32_t sf_tmem = tmem_base + kAccumBuffers * kAccumCols;
             int sf_buffer = 0;
-            int kind, slot, m_tile;
-            for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+            for (int sequence = 0; !abort_word; ++sequence) {
+                // the tile's first stage also publishes its queue entry
+                if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) { give_up(kStatusWaitExpired); break; }
+                const int code = tile_queue[sequence % kTileQueue];
                 if (!mbar_wait(accum_empty(buffer), ((accum_phase >> buffer) & 1U) ^ 1U)) { give_up(kStatusWaitExpired); break; }
+                if (code < 0) {
+                    mbar_arrive(accum_full(buffer));        // pass the closing entry on to the epilogue warps
+                    break;
+                }
+                int kind, slot, m_tile;
+                decode_tile(code, &kind, &slot, &m_tile);
                 tc_fence_after();
                 const std::uint32_t accum = tmem_base + buffer * kAccumCols;
                 const int n_stages = kind == 0 ? gu_kblocks : dn_stages;
                 bool ok = true;
                 for (int s = 0; s < n_stages; ++s) {
-                    if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) {
+                    if (s > 0 && (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase))) {
                         give_up(kStatusWaitExpired);
                         ok = false;
                         break;
@@ -633,10 +676,13 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
         const int quarter = warp & 3;
         int buffer = 0;
         std::uint32_t accum_phase = 0;
-        int kind, slot, m_tile;
-        for (int i = 0; deal.item(i, block, gu_tiles, dn_tiles, &kind, &slot, &m_tile) && !abort_word; ++i) {
+        for (int sequence = 0; !abort_word; ++sequence) {
             if (!mbar_wait(accum_full(buffer), (accum_phase >> buffer) & 1U)) { give_up(kStatusWaitExpired); break; }
             accum_phase ^= 1U << buffer;
+            const int code = tile_queue[sequence % kTileQueue];
+            if (code < 0) break;
+            int kind, slot, m_tile;
+            decode_tile(code, &kind, &slot, &m_tile);
             tc_fence_after();
             const int entry = rt.active[slot];
             const std::uint32_t mask = rt.slot_mask[slot];
@@ -689,7 +735,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                     mbar_arrive(accum_empty(buffer));
                     mbar_arrive(accum_empty(buffer));
                     mbar_arrive(accum_empty(buffer));
-                    atomicAdd(p.gu_done + slot, 1);
+                    atomicAdd(done + slot, 1);
                 }
             } else {
                 const float alpha = p.bank.alpha[entry * 3 + 2];
@@ -918,6 +964,7 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
     p.counts = plan->counts;
     p.hq = plan->hq_pp;
     p.hs = plan->hs_sw;
+    p.logits_tagged = plan->ep_logits;
     p.sync = plan->mega_sync + 2;
     p.gu_done = plan->ep_gu_done;
     p.status = plan->status;

@@ -138,19 +138,6 @@ __device__ __forceinline__ uint4 ld_tagged_pair(const void* p) {
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-__device__ __forceinline__ bool poll_tagged(const void* p, std::uint32_t tag, std::uint32_t* payload) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    if (v.y != tag) {
-        const std::uint64_t start = global_timer_ns();
-        do {
-            if (global_timer_ns() - start > 1000000000ULL) return false;
-            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-        } while (v.y != tag);
-    }
-    *payload = v.x;
-    return true;
-}
 __device__ __forceinline__ bool poll_tagged_pair(const void* p, std::uint32_t tag, std::uint32_t* first, std::uint32_t* second) {
     uint4 v;
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");

@@ -232,7 +232,8 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->xs_tok = c.take<std::uint8_t>(static_cast<std::size_t>(hidden / 64) * 512);
         plan->mega_sync = c.take<unsigned>(4);
         plan->gu_done = c.take<std::int32_t>(2 * 264);
-        plan->ep_gu_done = c.take<std::int32_t>(264);
+        plan->ep_gu_done = c.take<std::int32_t>(2 * 264);
+        plan->ep_logits = c.take<unsigned long long>(static_cast<std::size_t>(8) * kExperts);
         plan->mega_logits = c.take<unsigned long long>(static_cast<std::size_t>(8) * kExperts);
         plan->mega_ret = c.take<unsigned long long>(static_cast<std::size_t>(8) * (kTop + 1) * 1280);
         plan->mega_trace = c.take<unsigned long long>(static_cast<std::size_t>(plan->sm_count) * 64);

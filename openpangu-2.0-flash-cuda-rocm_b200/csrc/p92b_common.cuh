@@ -256,7 +256,8 @@ struct p92b_plan {
     std::uint8_t* xs_tok = nullptr;       // [H/64][512] their scales, one 128-row tile per 4 scale columns
     unsigned* mega_sync = nullptr;        // [2] arrival counters (monotonic across launches)
     std::int32_t* gu_done = nullptr;      // [2][264] per launch parity: gate/up tiles finished per active slot, [257] the tile counter
-    std::int32_t* ep_gu_done = nullptr;   // [264] the same for the fused expert-parallel kernel
+    std::int32_t* ep_gu_done = nullptr;   // [2][264] the same for the fused expert-parallel kernel
+    unsigned long long* ep_logits = nullptr;    // [8][256] its router logits as tagged words
     unsigned long long* mega_logits = nullptr;  // [8][256] router logits as {value, launch number} words
     unsigned long long* mega_ret = nullptr;     // [8][9][1280] down rows as {two BF16, launch number} words
     unsigned mega_epoch = 0;
