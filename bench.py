@@ -182,6 +182,11 @@ def workload_config(name: str, gpus: int) -> dict:
         return {"workload": "decode MTP-verify: T=4 tokens x 44 MoE layers (hidden 2560, 256+1 experts, FFN 1024, top-8)",
                 "tokens_per_step": 4, "layers": LAYERS, "routing": "bias ~N(0,0.01)", "gpus": gpus,
                 "l2": "44 distinct weight sets (55 GB) cycle per step: inputs larger than L2"}
+    if name == "ep_decode512":
+        return {"workload": "batched serving decode: T=512 tokens (128 sequences x 4 MTP positions) x 44 MoE layers, "
+                            "Zipf(1.0) routing", "tokens_per_step": 512, "layers": LAYERS,
+                "routing": "zipf 1.0 (capped at 1/8)", "gpus": gpus,
+                "l2": "44 distinct weight sets cycle per step: inputs larger than L2"}
     if name == "ep_prefill16384":
         return {"workload": "expert-parallel prefill: T=16384 tokens x 1 MoE layer, uniform routing (bias 0)",
                 "tokens_per_step": 16384, "layers": 1, "routing": "uniform", "gpus": gpus,
@@ -209,6 +214,8 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
         rows, n_layers = 4, args.layers or LAYERS
     elif args.workload == "ep_prefill16384":
         rows, n_layers = 16384 // world, args.layers or 1
+    elif args.workload == "ep_decode512":
+        rows, n_layers = 512 // world, args.layers or LAYERS
     else:
         rows, n_layers = 4096 // world, args.layers or 1
     first, local = ep.shard_range(rank, world)
@@ -223,8 +230,12 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
         shard = entries[first * 3:(first + local) * 3] + entries[EXPERTS * 3:]
         banks.append(pkg.ExpertBank(shard, first_expert=first, local_experts=local))
         routers.append(synth.make_router(SEED, l, bias_std=0.0 if args.workload == "ep_prefill16384" else 0.01))
+        if args.workload in ("ep_decode512", "prefill4096"):
+            alpha = 1.0 if args.workload == "ep_decode512" else 1.2
+            routers[-1] = (routers[-1][0], synth.fit_zipf_bias(routers[-1][0], alpha, SEED + l)[0].contiguous())
         if mode != "fused":
-            states.append(ep.EpRank(rank, world, banks[-1], routers[-1][0], routers[-1][1], max_local_rows=rows))
+            states.append(ep.EpRank(rank, world, banks[-1], routers[-1][0], routers[-1][1], max_local_rows=rows,
+                                    share_scratch_with=states[0] if states else None))
         xs.append(synth.make_activations(SEED + 1000 * (rank + 1), l, rows))
         del raw, entries, shard
     outs = [torch.empty_like(x) for x in xs]
@@ -290,7 +301,7 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
 
     step()
     torch.cuda.synchronize()
-    count_plans = [fused_plan] if mode == "fused" else [st.arrivals for st in states]
+    count_plans = [fused_plan] if mode == "fused" else [states[-1].arrivals]
     local_counts = [pl.views(1)["counts"][first:first + local] for pl in count_plans]
     received = [int(c.sum()) for c in local_counts]
     load = torch.tensor([float(np.mean(received))], device="cuda")     # rows arriving per layer
@@ -305,7 +316,7 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak" if decode else "strong", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 -> bf16",
+            "scaling": "weak" if decode else "strong", "exchange": mode, "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 -> bf16",
             "data": "synthetic", "config": dict(workload_config(args.workload, world),
                                                 parallelism=f"ep{world}: {local} experts per GPU, {rows} home tokens per GPU, "
                                                             + {"fused": "one kernel per GPU and layer, dispatch (all-gather) and combine by peer stores "
@@ -334,7 +345,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode4x44", choices=["decode4x44", "prefill4096", "ep_prefill16384"])
+    ap.add_argument("--workload", default="decode4x44", choices=["decode4x44", "prefill4096", "ep_prefill16384", "ep_decode512"])
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -363,9 +374,11 @@ def main() -> None:
         dist.destroy_process_group()
         return
     decode = args.workload == "decode4x44"
-    rows = 4 if decode else 4096
-    n_layers = args.layers or (LAYERS if decode else 1)
-    layers = [synth.make_layer(SEED + rank, l, bias_mode="normal" if decode else "zipf") for l in range(n_layers)]
+    rows = {"decode4x44": 4, "prefill4096": 4096, "ep_prefill16384": 16384, "ep_decode512": 512}[args.workload]
+    n_layers = args.layers or (LAYERS if args.workload in ("decode4x44", "ep_decode512") else 1)
+    bias_mode, alpha = {"decode4x44": ("normal", 0.0), "prefill4096": ("zipf", 1.2), "ep_prefill16384": ("zero", 0.0),
+                        "ep_decode512": ("zipf", 1.0)}[args.workload]
+    layers = [synth.make_layer(SEED + rank, l, bias_mode=bias_mode, zipf_alpha=alpha) for l in range(n_layers)]
     xs = [synth.make_activations(SEED + rank, l, rows) for l in range(n_layers)]
     outs = [torch.empty_like(x) for x in xs]
     plan = pkg.MoePlan(max_rows=rows)

@@ -138,19 +138,33 @@ __global__ void __launch_bounds__(WE* WT * 32) logits_rows_kernel(
 }
 
 // ---- T > 1 order, large batches ----------------------------------------------
-// Same per-lane chains as above, organised for throughput: a block computes 16 experts x 32 tokens,
-// a warp 8 x 8 of them.  K advances in chunks of 256 columns that are stored TRANSPOSED in shared
-// memory - element (row, column l + 32 j) at [row][l][j] - so a lane fetches its eight j-values of
-// a row with one 16-byte read, and the next chunk's global loads are in flight (registers) while the
-// current chunk is multiplied.  The fmaf order of every chain is still j ascending.
-__global__ void __launch_bounds__(256) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
-                                                                const std::uint16_t* __restrict__ w,
-                                                                float* __restrict__ out, int batch_rows, int rows,
-                                                                int columns) {
-    constexpr int TE = 8, TT = 8, WE = 2, WT = 4, KC = 256;
-    constexpr int BE = TE * WE, BT = TT * WT, ROWS = BE + BT;      // 48 staged rows
-    constexpr int PIECES = ROWS * (KC / 8) / 256;                   // 16-byte global pieces per thread per chunk: 6
-    __shared__ __align__(16) std::uint16_t tile[ROWS][32][8];
+// Same per-lane chains as above, organised for throughput: a block computes 16 experts x 8*WT tokens,
+// a warp 8 x 8 of them.  K advances in chunks of 256 columns.  A chunk arrives in shared memory by
+// asynchronous 16-byte copies (no registers, issued a whole chunk ahead), is then TRANSPOSED inside
+// shared memory - element (row, column l + 32 j) to [row][l][j] - so that a lane fetches its eight
+// j-values of a row with one 16-byte read, and is multiplied while the next chunk is on its way.
+// Rows of both images are padded by 16 bytes and the threads of a warp handle eight different rows,
+// so neither the 16-byte reads nor the 2-byte transposing stores meet a bank conflict.  One block
+// synchronisation per chunk.  The fmaf order of every chain is still j ascending.
+__device__ __forceinline__ void async_copy16(std::uint32_t dst_smem, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;          // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(bytes) : "memory");
+}
+
+template <int WT>
+__global__ void __launch_bounds__(64 * WT) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
+                                                                    const std::uint16_t* __restrict__ w,
+                                                                    float* __restrict__ out, int batch_rows, int rows,
+                                                                    int columns) {
+    constexpr int TE = 8, TT = 8, WE = 2, KC = 256;
+    constexpr int THREADS = 32 * WE * WT;
+    constexpr int BE = TE * WE, BT = TT * WT, ROWS = BE + BT;      // staged rows: 16 expert rows + 8 per token warp
+    constexpr int ROW_WORDS = 32 * 4 + 4;                           // 512 bytes + 16 bytes of padding
+    constexpr int PASSES = (ROWS / 8) * 2 * 2 / (WE * WT);          // (row group, j half, lane half) per warp
+    extern __shared__ __align__(16) std::uint8_t large_smem[];
+    std::uint32_t (*raw)[ROWS][ROW_WORDS] = reinterpret_cast<std::uint32_t (*)[ROWS][ROW_WORDS]>(large_smem);
+    std::uint32_t (*tile)[ROWS][ROW_WORDS] =
+        reinterpret_cast<std::uint32_t (*)[ROWS][ROW_WORDS]>(large_smem + 2 * ROWS * ROW_WORDS * 4);
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -163,69 +177,84 @@ __global__ void __launch_bounds__(256) logits_rows_large_kernel(const std::uint1
 #pragma unroll
         for (int j = 0; j < TT; ++j) acc[i][j] = 0.0F;
 
-    uint4 staged[PIECES];
-    auto fetch = [&](int k0) {
+    // global -> raw image: 48 rows x 32 pieces of 16 bytes, six pieces per thread, consecutive threads on
+    // consecutive pieces of a row
+    auto fetch = [&](int k0, int buffer) {
 #pragma unroll
-        for (int q = 0; q < PIECES; ++q) {
-            const int idx = threadIdx.x + q * 256;
-            const int r = idx / (KC / 8);
-            const int c8 = idx - r * (KC / 8);
+        for (int q = 0; q < ROWS * 32 / THREADS; ++q) {
+            const int idx = threadIdx.x + q * THREADS;
+            const int r = idx >> 5, piece = idx & 31;
             const bool is_w = r < BE;
             const int src_row = is_w ? e0 + r : t0 + (r - BE);
             const bool ok = is_w ? src_row < rows : src_row < batch_rows;
-            staged[q] = ok ? __ldg(reinterpret_cast<const uint4*>((is_w ? w : x) + static_cast<std::size_t>(src_row) * columns + k0) + c8)
-                           : make_uint4(0U, 0U, 0U, 0U);
+            const std::uint16_t* src = (is_w ? w : x) + static_cast<std::size_t>(ok ? src_row : 0) * columns + k0 + piece * 8;
+            async_copy16(static_cast<std::uint32_t>(__cvta_generic_to_shared(&raw[buffer][r][piece * 4])), src, ok);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    auto store = [&]() {
+    // raw image -> transposed image.  A lane takes row (group * 8 + lane % 8) and the j value
+    // (half * 4 + lane / 8), and of that j the 16 columns l = 16 * side .. 16 * side + 15.
+    const int r_lo = lane & 7, j_lo = lane >> 3;
+    auto transpose = [&](int buffer) {
 #pragma unroll
-        for (int q = 0; q < PIECES; ++q) {
-            const int idx = threadIdx.x + q * 256;
-            const int r = idx / (KC / 8);
-            const int c8 = idx - r * (KC / 8);
-            // columns 8*c8 .. 8*c8+7 of the chunk: lane (8*c8 + i) & 31, j = (8*c8) >> 5
-            const int j = c8 >> 2;
-            const int l0 = (c8 & 3) * 8;
-            const std::uint32_t words[4] = {staged[q].x, staged[q].y, staged[q].z, staged[q].w};
+        for (int q = 0; q < PASSES; ++q) {
+            const int combo = warp * PASSES + q;                    // 0 .. 23
+            const int group = combo >> 2, half = (combo >> 1) & 1, side = combo & 1;
+            const int r = group * 8 + r_lo;
+            const int j = half * 4 + j_lo;
+            const uint4* src = reinterpret_cast<const uint4*>(&raw[buffer][r][(32 * j + 16 * side) / 2]);
+            std::uint16_t* row = reinterpret_cast<std::uint16_t*>(&tile[buffer][r][0]);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                tile[r][l0 + 2 * i][j] = static_cast<std::uint16_t>(words[i] & 0xffffU);
-                tile[r][l0 + 2 * i + 1][j] = static_cast<std::uint16_t>(words[i] >> 16);
+            for (int h = 0; h < 2; ++h) {
+                const uint4 piece = src[h];
+                const std::uint32_t words[4] = {piece.x, piece.y, piece.z, piece.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int l = 16 * side + 8 * h + 2 * i;
+                    row[l * 8 + j] = static_cast<std::uint16_t>(words[i] & 0xffffU);
+                    row[(l + 1) * 8 + j] = static_cast<std::uint16_t>(words[i] >> 16);
+                }
             }
         }
     };
-    fetch(0);
+    fetch(0, 0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (KC < columns) fetch(KC, 1);
+    transpose(0);
+    int buffer = 0;
     for (int k0 = 0; k0 < columns; k0 += KC) {
-        __syncthreads();                        // everyone is done with the previous chunk
-        store();
+        // chunk k0 is transposed in tile[buffer] (by every thread: not yet visible), chunk k0 + KC is arriving in raw[buffer ^ 1]
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        if (k0 + KC < columns) fetch(k0 + KC);  // in flight during the multiply below
-#pragma unroll
-        for (int hj = 0; hj < 2; ++hj) {        // j = 4*hj .. 4*hj+3
-            uint2 wv[TE], xv[TT];
-#pragma unroll
-            for (int i = 0; i < TE; ++i) wv[i] = *reinterpret_cast<const uint2*>(&tile[we * TE + i][lane][4 * hj]);
-#pragma unroll
-            for (int i = 0; i < TT; ++i) xv[i] = *reinterpret_cast<const uint2*>(&tile[BE + wt * TT + i][lane][4 * hj]);
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                float wf[TE], xf[TT];
-#pragma unroll
-                for (int i = 0; i < TE; ++i) {
-                    const std::uint32_t word = jj < 2 ? wv[i].x : wv[i].y;
-                    wf[i] = __uint_as_float((jj & 1) ? (word & 0xffff0000U) : (word << 16));
-                }
-#pragma unroll
-                for (int i = 0; i < TT; ++i) {
-                    const std::uint32_t word = jj < 2 ? xv[i].x : xv[i].y;
-                    xf[i] = __uint_as_float((jj & 1) ? (word & 0xffff0000U) : (word << 16));
-                }
-#pragma unroll
-                for (int i = 0; i < TE; ++i)
-#pragma unroll
-                    for (int t = 0; t < TT; ++t) acc[i][t] = fmaf(xf[t], wf[i], acc[i][t]);
-            }
+        if (k0 + KC < columns) {
+            if (k0 + 2 * KC < columns) fetch(k0 + 2 * KC, buffer);   // raw[buffer] was transposed before the barrier
+            transpose(buffer ^ 1);                                    // tile[buffer ^ 1] was last read before the barrier
         }
+        uint4 wv[TE], xv[TT];
+#pragma unroll
+        for (int i = 0; i < TE; ++i) wv[i] = *reinterpret_cast<const uint4*>(&tile[buffer][we * TE + i][lane * 4]);
+#pragma unroll
+        for (int i = 0; i < TT; ++i) xv[i] = *reinterpret_cast<const uint4*>(&tile[buffer][BE + wt * TT + i][lane * 4]);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+            float wf[TE], xf[TT];
+#pragma unroll
+            for (int i = 0; i < TE; ++i) {
+                const std::uint32_t word = jj < 2 ? wv[i].x : jj < 4 ? wv[i].y : jj < 6 ? wv[i].z : wv[i].w;
+                wf[i] = __uint_as_float((jj & 1) ? (word & 0xffff0000U) : (word << 16));
+            }
+#pragma unroll
+            for (int i = 0; i < TT; ++i) {
+                const std::uint32_t word = jj < 2 ? xv[i].x : jj < 4 ? xv[i].y : jj < 6 ? xv[i].z : xv[i].w;
+                xf[i] = __uint_as_float((jj & 1) ? (word & 0xffff0000U) : (word << 16));
+            }
+#pragma unroll
+            for (int i = 0; i < TE; ++i)
+#pragma unroll
+                for (int t = 0; t < TT; ++t) acc[i][t] = fmaf(xf[t], wf[i], acc[i][t]);
+        }
+        buffer ^= 1;
     }
 #pragma unroll
     for (int i = 0; i < TE; ++i) {
@@ -289,8 +318,20 @@ cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w,
         return launch_kernel(kernel, grid, dim3(WE * WT * 32), smem, stream, pdl, x, w, out, batch_rows, rows, columns,
                              columns);
     } else if (batch_rows >= 256 && columns % 256 == 0) {
-        dim3 grid((rows + 15) / 16, (batch_rows + 31) / 32);
-        return launch_kernel(logits_rows_large_kernel, grid, dim3(256), 0, stream, pdl, x, w, out, batch_rows, rows, columns);
+        // 16 experts x 16 tokens per block of four warps: small blocks, several per SM, so that one block's
+        // staging and barrier overlap another's multiply
+        constexpr int WT = 2;
+        dim3 grid((rows + 15) / 16, (batch_rows + 8 * WT - 1) / (8 * WT));
+        constexpr std::size_t smem = 4 * (16 + 8 * WT) * (32 * 4 + 4) * 4;     // raw and transposed images, two of each
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t st = cudaFuncSetAttribute(logits_rows_large_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(smem));
+            if (st != cudaSuccess) return st;
+            configured = true;
+        }
+        return launch_kernel(logits_rows_large_kernel<WT>, grid, dim3(64 * WT), smem, stream, pdl, x, w, out, batch_rows, rows,
+                             columns);
     } else {
         constexpr int TE = 8, TT = 8, WE = 2, WT = 4;
         constexpr int KC = 128;

@@ -41,7 +41,8 @@ class EpRank:
     """One GPU's share: its expert shard, two plans (arrivals; home tokens + shared expert)."""
 
     def __init__(self, rank: int, world: int, bank: ExpertBank, router_weight, correction_bias,
-                 max_local_rows: int, max_arrival_rows: Optional[int] = None, routed_scale: float = ROUTED_SCALE):
+                 max_local_rows: int, max_arrival_rows: Optional[int] = None, routed_scale: float = ROUTED_SCALE,
+                 share_scratch_with: Optional["EpRank"] = None):
         self.rank, self.world = rank, world
         self.first, self.local = shard_range(rank, world)
         if bank.first_expert != self.first or bank.local_experts != self.local:
@@ -49,10 +50,18 @@ class EpRank:
         self.bank, self.router_weight, self.bias, self.routed_scale = bank, router_weight, correction_bias, routed_scale
         # worst case every assignment of every GPU lands here
         arrival_rows = max_arrival_rows if max_arrival_rows is not None else max_local_rows * world
+        self.max_local_rows = max_local_rows
+        if share_scratch_with is not None:
+            # layers of one rank run one after the other on one stream: they can use the same plans and buffers
+            other = share_scratch_with
+            if other.max_local_rows < max_local_rows or other.arrivals.max_rows < arrival_rows:
+                raise ValueError("the scratch to share is too small")
+            self.home, self.shared, self.arrivals = other.home, other.shared, other.arrivals
+            self.send, self._fixed = other.send, other._fixed
+            return
         self.home = MoePlan(max_rows=max_local_rows)
         self.shared = MoePlan(max_rows=max_local_rows)
         self.arrivals = MoePlan(max_rows=arrival_rows)
-        self.max_local_rows = max_local_rows
         self.send = torch.empty((max_local_rows * TOP_K, ROW_BYTES), dtype=torch.uint8, device="cuda")
         self._fixed = {}
 
