@@ -179,6 +179,17 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
 int p92b_moe_forward_host(p92b_plan* plan, const p92b_bank* bank, const uint16_t* host_input,
                           const uint16_t* router_weight, const float* correction_bias,
                           uint16_t* host_output, int rows, float routed_scale, void* stream);
+/* The same as a pipeline for a loop over layers: nothing is synchronised, the block is enqueued on
+ * `stream`, and the two copies run on two streams of the plan's own, so that the rows of one call travel
+ * while the blocks of its neighbours compute (two sets of staging rows, used alternately).  The two host
+ * buffers must be page-locked; the input must hold its data when the call is made (it is read by a stream
+ * that is not ordered after `stream`); both must stay valid, and the output may be read, once
+ * p92b_plan_host_flush(plan, stream) has been called and `stream` synchronised: the flush makes `stream`
+ * wait for the copies still going out.  One plan, one thread. */
+int p92b_moe_forward_host_async(p92b_plan* plan, const p92b_bank* bank, const uint16_t* pinned_input,
+                                const uint16_t* router_weight, const float* correction_bias, uint16_t* pinned_output,
+                                int rows, float routed_scale, void* stream);
+int p92b_plan_host_flush(p92b_plan* plan, void* stream);
 
 /* Stage entry points at the reference's split, so each existing call can be replaced alone.
  * ProjectionExecutor::project_expert_gate_up (include/p92/executor.h:31-38; src/executor.cpp:39-71):

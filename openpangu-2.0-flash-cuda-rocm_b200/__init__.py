@@ -100,6 +100,8 @@ SIGNATURES = {
     "p92b_plan_bytes": (c_size_t, [c_void_p]),
     "p92b_moe_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_moe_forward_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "p92b_plan_host_flush": (c_int, [c_void_p, c_void_p]),
+    "p92b_moe_forward_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_project_expert_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_project_expert_down": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_plan_get_views": (c_int, [c_void_p, ctypes.POINTER(PlanViews)]),
@@ -285,6 +287,10 @@ class MoePlan:
     def nbytes(self) -> int:
         return int(load_library().p92b_plan_bytes(self.handle))
 
+    def host_flush(self) -> None:
+        """Make the current stream wait for the copy-outs of run_moe_rows_host_async calls still in flight."""
+        _check(load_library().p92b_plan_host_flush(self.handle, _stream()), "plan_host_flush")
+
     @property
     def last_launches(self) -> int:
         return int(load_library().p92b_plan_last_launches(self.handle))
@@ -401,6 +407,14 @@ class MoeBlock:
                                                     _ptr(self.router_weight), _ptr(self.correction_bias),
                                                     host_out.data_ptr(), rows, self.routed_scale, _stream()),
                "moe_forward_host")
+
+    def run_moe_rows_host_async(self, pinned_in, pinned_out, rows: int) -> None:
+        """The same as a pipeline (copies on the plan's own streams): outputs are valid after
+        ``plan.host_flush()`` and a synchronisation of the current stream."""
+        _check(load_library().p92b_moe_forward_host_async(self.plan.handle, self.bank.handle, pinned_in.data_ptr(),
+                                                          _ptr(self.router_weight), _ptr(self.correction_bias),
+                                                          pinned_out.data_ptr(), rows, self.routed_scale, _stream()),
+               "moe_forward_host_async")
 
     def project_expert_gate_up(self, expert_ids, input, gate_output, up_output, batch_rows: int = 1) -> None:
         """ProjectionExecutor::project_expert_gate_up (src/executor.cpp:39-71)."""

@@ -243,6 +243,8 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->ep_zero_counts = c.take<std::int32_t>(kExperts + 1);
         plan->stage_in = c.take<std::uint16_t>(rows * hidden);
         plan->stage_out = c.take<std::uint16_t>(rows * hidden);
+        plan->stage_in_b = c.take<std::uint16_t>(rows * hidden);
+        plan->stage_out_b = c.take<std::uint16_t>(rows * hidden);
         plan->status = c.take<std::int32_t>(1);
         if (pass == 0) {
             plan->bytes = c.used;
@@ -286,6 +288,13 @@ void p92b_plan_destroy(p92b_plan* plan) {
     for (cudaEvent_t& ev : plan->stage_events) {
         if (ev != nullptr) cudaEventDestroy(ev);
     }
+    for (int i = 0; i < 2; ++i) {
+        if (plan->in_ready[i] != nullptr) cudaEventDestroy(plan->in_ready[i]);
+        if (plan->block_done[i] != nullptr) cudaEventDestroy(plan->block_done[i]);
+        if (plan->out_done[i] != nullptr) cudaEventDestroy(plan->out_done[i]);
+    }
+    if (plan->copy_in_stream != nullptr) cudaStreamDestroy(plan->copy_in_stream);
+    if (plan->copy_out_stream != nullptr) cudaStreamDestroy(plan->copy_out_stream);
     if (plan->storage != nullptr) cudaFree(plan->storage);
     delete plan;
 }
@@ -503,6 +512,62 @@ int p92b_moe_forward_host(p92b_plan* plan, const p92b_bank* bank, const uint16_t
     st = cudaMemcpyAsync(host_output, plan->stage_out, bytes, cudaMemcpyDeviceToHost, stream);
     if (st != cudaSuccess) return st;
     return cudaStreamSynchronize(stream);
+}
+
+// Pipelined host calls.  Three streams: the caller's (the block), one for rows coming in, one for rows
+// going out; two sets of staging rows used alternately.  Call n (set b = n & 1):
+//   in stream    waits until block n-2 has read set b, copies the rows in, records in_ready[b]
+//   caller's     waits for in_ready[b] and for the copy-out of call n-2 (it read set b), runs the block,
+//                records block_done[b]
+//   out stream   waits for block_done[b], copies the rows out, records out_done[b]
+// so the copies of a call overlap the blocks of its neighbours, and the caller's stream never carries a copy.
+static cudaError_t host_pipeline_setup(p92b_plan* plan) {
+    if (plan->copy_in_stream != nullptr) return cudaSuccess;
+    cudaError_t st = cudaStreamCreateWithFlags(&plan->copy_in_stream, cudaStreamNonBlocking);
+    if (st == cudaSuccess) st = cudaStreamCreateWithFlags(&plan->copy_out_stream, cudaStreamNonBlocking);
+    for (int i = 0; i < 2 && st == cudaSuccess; ++i) {
+        st = cudaEventCreateWithFlags(&plan->in_ready[i], cudaEventDisableTiming);
+        if (st == cudaSuccess) st = cudaEventCreateWithFlags(&plan->block_done[i], cudaEventDisableTiming);
+        if (st == cudaSuccess) st = cudaEventCreateWithFlags(&plan->out_done[i], cudaEventDisableTiming);
+    }
+    return st;
+}
+
+int p92b_moe_forward_host_async(p92b_plan* plan, const p92b_bank* bank, const uint16_t* pinned_input,
+                                const uint16_t* router_weight, const float* correction_bias, uint16_t* pinned_output,
+                                int rows, float routed_scale, void* stream_) {
+    if (plan == nullptr || pinned_input == nullptr || pinned_output == nullptr || rows <= 0 || rows > plan->max_rows) {
+        return cudaErrorInvalidValue;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    cudaError_t st = host_pipeline_setup(plan);
+    if (st != cudaSuccess) return st;
+    const std::size_t bytes = static_cast<std::size_t>(rows) * plan->hidden * sizeof(std::uint16_t);
+    const unsigned n = plan->host_calls++;
+    const int b = static_cast<int>(n & 1U);
+    std::uint16_t* rows_in = b == 0 ? plan->stage_in : plan->stage_in_b;
+    std::uint16_t* rows_out = b == 0 ? plan->stage_out : plan->stage_out_b;
+    if (n >= 2 && (st = cudaStreamWaitEvent(plan->copy_in_stream, plan->block_done[b], 0)) != cudaSuccess) return st;
+    if ((st = cudaMemcpyAsync(rows_in, pinned_input, bytes, cudaMemcpyHostToDevice, plan->copy_in_stream)) != cudaSuccess) return st;
+    if ((st = cudaEventRecord(plan->in_ready[b], plan->copy_in_stream)) != cudaSuccess) return st;
+    if ((st = cudaStreamWaitEvent(stream, plan->in_ready[b], 0)) != cudaSuccess) return st;
+    if (n >= 2 && (st = cudaStreamWaitEvent(stream, plan->out_done[b], 0)) != cudaSuccess) return st;
+    st = static_cast<cudaError_t>(p92b_moe_forward(plan, bank, rows_in, router_weight, correction_bias, rows_out, rows,
+                                                   routed_scale, stream_));
+    if (st != cudaSuccess) return st;
+    if ((st = cudaEventRecord(plan->block_done[b], stream)) != cudaSuccess) return st;
+    if ((st = cudaStreamWaitEvent(plan->copy_out_stream, plan->block_done[b], 0)) != cudaSuccess) return st;
+    if ((st = cudaMemcpyAsync(pinned_output, rows_out, bytes, cudaMemcpyDeviceToHost, plan->copy_out_stream)) != cudaSuccess) return st;
+    return cudaEventRecord(plan->out_done[b], plan->copy_out_stream);
+}
+
+int p92b_plan_host_flush(p92b_plan* plan, void* stream_) {
+    if (plan == nullptr) return cudaErrorInvalidValue;
+    if (plan->copy_out_stream == nullptr || plan->host_calls == 0) return cudaSuccess;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    cudaError_t st = cudaStreamWaitEvent(stream, plan->out_done[0], 0);
+    if (st == cudaSuccess && plan->host_calls >= 2) st = cudaStreamWaitEvent(stream, plan->out_done[1], 0);
+    return st;
 }
 
 int p92b_project_expert_gate_up(p92b_plan* plan, const p92b_bank* bank, const int32_t* expert_ids,

@@ -237,6 +237,15 @@ struct p92b_plan {
     std::uint16_t* mixed = nullptr;       // [9*max_rows][H]     position space
     std::uint16_t* stage_in = nullptr;    // [max_rows][H]  host-call staging
     std::uint16_t* stage_out = nullptr;   // [max_rows][H]
+    // pipelined host calls: second pair of staging rows, copy streams and the events between the three streams
+    std::uint16_t* stage_in_b = nullptr;
+    std::uint16_t* stage_out_b = nullptr;
+    cudaStream_t copy_in_stream = nullptr;
+    cudaStream_t copy_out_stream = nullptr;
+    cudaEvent_t in_ready[2] = {};
+    cudaEvent_t block_done[2] = {};
+    cudaEvent_t out_done[2] = {};
+    unsigned host_calls = 0;
     std::int32_t* status = nullptr;       // [1]
     // tensor-core path: operands in the padded position space (every expert's rows start on a
     // multiple of 32 or 128), scales in the 128x4-tiled layout

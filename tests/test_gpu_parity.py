@@ -423,6 +423,17 @@ def test_host_buffer_entry_point(cuda, pkg, layer0):
     host_out = torch.empty_like(host_in).pin_memory()
     block.run_moe_rows_host(host_in, host_out, rows)
     assert torch.equal(host_out.view(torch.int16), dev_out.cpu().view(torch.int16))
+    # the pipelined form: five calls in a row on one plan, one flush and one synchronisation at the end
+    inputs = [synth.make_activations(47 + i, 0, rows) for i in range(5)]
+    pinned_in = [t.cpu().pin_memory() for t in inputs]
+    pinned_out = [torch.zeros_like(t).pin_memory() for t in pinned_in]
+    for a, b in zip(pinned_in, pinned_out):
+        block.run_moe_rows_host_async(a, b, rows)
+    plan.host_flush()
+    torch.cuda.current_stream().synchronize()
+    for t, got in zip(inputs, pinned_out):
+        block.run_moe_rows(t, dev_out, rows)
+        assert torch.equal(got.view(torch.int16), dev_out.cpu().view(torch.int16))
     plan.close()
 
 
