@@ -372,6 +372,7 @@ int p92b_ep_experts(p92b_plan* plan, const p92b_bank* bank, const uint8_t* recv_
                                                                   sources, local, total_rows, plan->xq_pp, plan->xs_sw,
                                                                   plan->pp_of_flat, plan->hidden / 2, plan->hidden / 16);
     if ((st = cudaGetLastError()) != cudaSuccess) return st;
+    plan->wide_rows = 0;          // the lists above carry one tile prefix only
     if ((st = launch_experts_tc(plan, bank, 1 << 20, false, stream)) != cudaSuccess) return st;
     if ((st = launch_experts_tc(plan, bank, 1 << 20, true, stream)) != cudaSuccess) return st;
     ep_gather_rows_kernel<<<warps_grid(total_rows), 256, 0, stream>>>(plan->mixed_pp, plan->pp_of_flat, out_rows,
@@ -401,6 +402,7 @@ static int ep_combine_impl(p92b_plan* home_plan, p92b_plan* shared_plan, const p
     ep_shared_rows_kernel<<<warps_grid(rows), 256, 0, stream>>>(home_plan->xq, home_plan->xs, rows, sp->xq_pp, sp->xs_sw,
                                                                 sp->hidden / 2, sp->hidden / 16);
     if ((st = cudaGetLastError()) != cudaSuccess) return st;
+    sp->wide_rows = 0;
     if ((st = launch_experts_tc(sp, bank, rows, false, stream)) != cudaSuccess) return st;
     if ((st = launch_experts_tc(sp, bank, rows, true, stream)) != cudaSuccess) return st;
     dim3 grid((home_plan->hidden / 8 + 255) / 256, rows);
@@ -472,6 +474,7 @@ int p92b_ep_experts_fixed(p92b_plan* plan, const p92b_bank* bank, const uint8_t*
                                                                    sources, local, cap_rows, plan->xq_pp, plan->xs_sw,
                                                                    plan->pp_of_flat, plan->hidden / 2, plan->hidden / 16);
     if ((st = cudaGetLastError()) != cudaSuccess) return st;
+    plan->wide_rows = 0;
     if ((st = launch_experts_tc(plan, bank, expert_rows_bound, false, stream)) != cudaSuccess) return st;
     if ((st = launch_experts_tc(plan, bank, expert_rows_bound, true, stream)) != cudaSuccess) return st;
     ep_gather_fixed_kernel<<<warps_grid(slots), 256, 0, stream>>>(plan->mixed_pp, plan->pp_of_flat, out_slots, slots,

@@ -541,7 +541,13 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
     switch (which) {
         case 0: return launch_tc<1, 16>(plan, plan->map_h[0], p, stream, pdl);
         case 1: return launch_tc<1, 32>(plan, plan->map_h[1], p, stream, pdl);
-        default: return launch_tc<1, 64>(plan, plan->map_h[2], p, stream, pdl);
+        default:
+            if (plan->wide_rows == 128) {
+                // every expert segment starts on a multiple of 128 padded rows, so 128-row tiles stay inside it
+                p.tile_prefix = plan->tile_prefix_wide;
+                return launch_tc<1, 128>(plan, plan->map_h[3], p, stream, pdl);
+            }
+            return launch_tc<1, 64>(plan, plan->map_h[2], p, stream, pdl);
     }
 }
 

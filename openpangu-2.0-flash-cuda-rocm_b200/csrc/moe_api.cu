@@ -216,6 +216,7 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->active_count = c.take<std::int32_t>(1);
         plan->pp_off = c.take<std::int32_t>(kExperts + 2);
         plan->tile_prefix = c.take<std::int32_t>(kExperts + 2);
+        plan->tile_prefix_wide = c.take<std::int32_t>(kExperts + 2);
         plan->pp_of_flat = c.take<std::int32_t>(rows * (kTop + 1));
         plan->chunk_hist = c.take<std::int32_t>(static_cast<std::size_t>(plan->chunks) * kExperts);
         plan->xq = c.take<std::uint8_t>(rows * (hidden / 2));

@@ -227,6 +227,8 @@ struct p92b_plan {
     std::int32_t* active_count = nullptr; // [1]
     std::int32_t* pp_off = nullptr;       // [258] padded offsets (tensor-core path)
     std::int32_t* tile_prefix = nullptr;  // [258]
+    std::int32_t* tile_prefix_wide = nullptr;   // [258] the same prefix for token tiles twice as wide (down product)
+    int wide_rows = 0;                    // token tile tile_prefix_wide was last built for (0: not built)
     std::int32_t* pp_of_flat = nullptr;   // [9*max_rows] padded position of (row, slot), shared rows last
     std::int32_t* chunk_hist = nullptr;   // [chunks][256]
     int chunks = 0;

@@ -109,8 +109,10 @@ struct RouteLists {
     std::int32_t* active_count;  // [1]
     std::int32_t* pp_off;        // [258] padded offsets (null: not wanted)
     std::int32_t* tile_prefix;   // [258] exclusive prefix of token tiles over the active list, total last
+    std::int32_t* tile_prefix_wide;   // the same for tiles of tile_rows_wide rows (null: not wanted)
     int pad_align;
     int tile_rows;
+    int tile_rows_wide;
     bool enabled;
 };
 
@@ -142,6 +144,16 @@ __device__ __forceinline__ void write_route_lists(int e, int count, int offset, 
         lists.pp_off[kExperts + 1] = pp + padded + (rows + align - 1) / align * align;
         lists.tile_prefix[0] = 0;
         lists.tile_prefix[1 + slot + (count > 0 ? 1 : 0)] = shared_tiles + before + tiles;   // total, after the last active
+    }
+    if (lists.tile_prefix_wide == nullptr) return;
+    const int wide = lists.tile_rows_wide;
+    const int tiles_w = (count + wide - 1) / wide;
+    const int shared_w = (rows + wide - 1) / wide;
+    const int before_w = block_exclusive_scan_256(tiles_w, scan_scratch);
+    if (count > 0) lists.tile_prefix_wide[1 + slot] = shared_w + before_w;
+    if (e == kExperts - 1) {
+        lists.tile_prefix_wide[0] = 0;
+        lists.tile_prefix_wide[1 + slot + (count > 0 ? 1 : 0)] = shared_w + before_w + tiles_w;
     }
 }
 
@@ -350,6 +362,9 @@ cudaError_t launch_route_fused(p92b_plan* plan, const float* bias, float routed_
     lists.tile_rows = tile_rows;
     lists.pp_off = plan->pp_off;
     lists.tile_prefix = plan->tile_prefix;
+    lists.tile_rows_wide = tile_rows;
+    lists.tile_prefix_wide = nullptr;
+    plan->wide_rows = 0;
     plan->last_launches += 1;
     return launch_kernel(route_fused_kernel, dim3(1), dim3(256), 0, stream, pdl, plan->logits, bias, plan->ids,
                          plan->route_weights, routed_scale, rows, plan->order, plan->position, lists, plan->row_token,
@@ -375,6 +390,12 @@ cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignm
     const bool padded = route_lists && pad_align > 0;
     lists.pp_off = padded ? plan->pp_off : nullptr;
     lists.tile_prefix = padded ? plan->tile_prefix : nullptr;
+    // large batches: the down product takes token tiles twice as wide as the gate/up product (one
+    // accumulator per tile instead of two, so 128 columns still leave room for two buffers)
+    const bool wide = padded && tile_rows == 64;
+    lists.tile_rows_wide = wide ? 128 : lists.tile_rows;
+    lists.tile_prefix_wide = wide ? plan->tile_prefix_wide : nullptr;
+    plan->wide_rows = wide ? 128 : 0;
     std::int32_t* row_token = route_lists ? plan->row_token : nullptr;
     std::int32_t* pp_of_flat = padded ? plan->pp_of_flat : nullptr;
     if (assignments <= kWarps * 1024) {
@@ -475,6 +496,8 @@ extern "C" int p92b_moe_permute_static(const int32_t* expert_ids, int assignment
     lists.enabled = false;
     lists.pad_align = 1;
     lists.tile_rows = 1;
+    lists.tile_rows_wide = 1;
+    lists.tile_prefix_wide = nullptr;
     if (assignments <= kWarps * 1024) {
         permute_small_kernel<<<1, 256, 0, stream>>>(expert_ids, assignments, order, position, lists, nullptr, nullptr,
                                                     status);
