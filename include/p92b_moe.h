@@ -251,7 +251,8 @@ int p92b_ep_combine_fixed(p92b_plan* home_plan, p92b_plan* shared_plan, const p9
  * single-device ones (cuda/nvfp4_grouped.cu:117-132, cuda/nvfp4_ops.cu:124-142).
  *
  * A window is this GPU's exchange memory (p92b_ep_window_bytes, allocated with cudaMalloc) plus the
- * mapped windows of its peers.  Set-up, once: every process creates its window, publishes the 64-byte
+ * mapped windows of its peers; it serves this call (world * rows_per_gpu <= 32, rows_per_gpu <= 8) and
+ * p92b_ep_forward_gathered below (rows_per_gpu <= 128, world * rows_per_gpu <= 1024).  Set-up, once: every process creates its window, publishes the 64-byte
  * inter-process handle (p92b_ep_window_handle) to all others by any means, and connects with the
  * handles of all ranks in rank order (its own entry is ignored).  world * rows_per_gpu <= 32,
  * rows_per_gpu <= 8.  All GPUs must call p92b_ep_forward_fused the same number of times on a window,
@@ -264,7 +265,7 @@ int p92b_ep_combine_fixed(p92b_plan* home_plan, p92b_plan* shared_plan, const p9
 typedef struct p92b_ep_window p92b_ep_window;
 int p92b_ep_window_create(p92b_ep_window** out, int rank, int world, int rows_per_gpu);
 void p92b_ep_window_destroy(p92b_ep_window* window);
-size_t p92b_ep_window_bytes(void);
+size_t p92b_ep_window_bytes(const p92b_ep_window* window);
 int p92b_ep_window_handle(const p92b_ep_window* window, uint8_t* handle64);
 int p92b_ep_window_connect(p92b_ep_window* window, const uint8_t* handles /* [world][64] */);
 /* The same for windows that live in THIS process (one process driving several GPUs with peer access
@@ -273,6 +274,19 @@ int p92b_ep_window_connect_local(p92b_ep_window* window, p92b_ep_window* const* 
 int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window, const uint16_t* input,
                           const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
                           float routed_scale, void* stream);
+
+/* Medium batches (tens of tokens per GPU, up to 1024 in flight), same idea, several launches: every GPU
+ * stores its quantised rows and top-8 ids into every peer's window (all-gather), runs the reference's
+ * permutation law over the whole batch and keeps its own experts' segments, computes them with the grouped
+ * tcgen05 kernels, stores each result row into its home GPU's window, and the home GPU combines in slot
+ * order and adds its shared expert.  No NCCL call, no host synchronisation, nothing but bounded polls of
+ * {payload, call number} words between GPUs.  Same window and calling rules as p92b_ep_forward_fused
+ * (both kinds of call may be mixed on one window as long as all GPUs mix them identically); the plan
+ * must have been created for at least world * rows_per_gpu rows.  After the call the plan's ids view
+ * holds the ids of ALL tokens of the batch in (home GPU, token) order. */
+int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window, const uint16_t* input,
+                             const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
+                             float routed_scale, void* stream);
 
 /* Device views of the last p92b_moe_forward's intermediates, for tests and
  * tracing (the reference keeps the same buffers as Model::Impl members,

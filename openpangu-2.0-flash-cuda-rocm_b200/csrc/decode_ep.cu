@@ -831,15 +831,9 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
 }  // namespace p92b
 
 // ---- the window object ---------------------------------------------------------------------------
-struct p92b_ep_window {
-    int rank = 0, world = 1, rows_per_gpu = 0;
-    std::uint8_t* local = nullptr;
-    std::uint8_t* peers[p92b::kEpMaxWorld] = {};
-    bool opened[p92b::kEpMaxWorld] = {};
-    bool connected = false;
-    unsigned epoch = 0;
-    CUtensorMap map_tok[2] = {};
-};
+namespace p92b {
+std::size_t ep_gathered_bytes(int world, int rows_per_gpu);      // ep_gathered.cu
+}
 
 extern "C" {
 
@@ -848,7 +842,7 @@ int p92b_ep_window_create(p92b_ep_window** out, int rank, int world, int rows_pe
     if (out == nullptr) return cudaErrorInvalidValue;
     *out = nullptr;
     if (world <= 0 || world > kEpMaxWorld || rank < 0 || rank >= world || kExperts % world != 0 || rows_per_gpu <= 0 ||
-        rows_per_gpu > kEpMaxLocalRows || world * rows_per_gpu > kEpMaxTokens) {
+        rows_per_gpu > 128 || world * rows_per_gpu > 1024) {
         return cudaErrorInvalidValue;
     }
     p92b_ep_window* w = new (std::nothrow) p92b_ep_window();
@@ -856,8 +850,11 @@ int p92b_ep_window_create(p92b_ep_window** out, int rank, int world, int rows_pe
     w->rank = rank;
     w->world = world;
     w->rows_per_gpu = rows_per_gpu;
-    cudaError_t st = cudaMalloc(reinterpret_cast<void**>(&w->local), kWinBytes);
-    if (st == cudaSuccess) st = cudaMemset(w->local, 0, kWinBytes);
+    w->fused_ok = rows_per_gpu <= kEpMaxLocalRows && world * rows_per_gpu <= kEpMaxTokens;
+    w->gathered_base = (kWinBytes + 255) / 256 * 256;
+    w->bytes = w->gathered_base + ep_gathered_bytes(world, rows_per_gpu);
+    cudaError_t st = cudaMalloc(reinterpret_cast<void**>(&w->local), w->bytes);
+    if (st == cudaSuccess) st = cudaMemset(w->local, 0, w->bytes);
     if (st == cudaSuccess) st = cudaDeviceSynchronize();
     bool ok = st == cudaSuccess;
     ok = ok && make_operand_map(&w->map_tok[0], w->local + kWinXq, 2 * kEpMaxTokens, kXqRow, 16) == cudaSuccess;
@@ -873,7 +870,7 @@ int p92b_ep_window_create(p92b_ep_window** out, int rank, int world, int rows_pe
     return cudaSuccess;
 }
 
-size_t p92b_ep_window_bytes(void) { return p92b::kWinBytes; }
+size_t p92b_ep_window_bytes(const p92b_ep_window* window) { return window == nullptr ? 0 : window->bytes; }
 
 int p92b_ep_window_handle(const p92b_ep_window* window, uint8_t* handle64) {
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "inter-process handle size");
@@ -932,7 +929,7 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
         correction_bias == nullptr || output == nullptr || rows <= 0 || rows > window->rows_per_gpu) {
         return cudaErrorInvalidValue;
     }
-    if (!window->connected || !plan->tc_ready || !bank->tc_ready || plan->hidden != 2560 || plan->intermediate != 1024 ||
+    if (!window->connected || !window->fused_ok || !plan->tc_ready || !bank->tc_ready || plan->hidden != 2560 || plan->intermediate != 1024 ||
         bank->view.hidden != 2560 || bank->view.intermediate != 1024 || bank->view.local_experts != kExperts / window->world ||
         bank->view.first_expert != window->rank * (kExperts / window->world) ||
         plan->pp_rows < static_cast<std::size_t>(std::min(bank->view.local_experts,

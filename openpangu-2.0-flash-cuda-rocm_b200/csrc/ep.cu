@@ -314,6 +314,20 @@ __global__ void __launch_bounds__(256) ep_gather_fixed_kernel(const std::uint16_
     for (int k = lane; k < hidden / 8; k += 32) dst[k] = src[k];
 }
 
+}  // namespace
+
+// Lists of a GPU's experts from per-source histograms, for callers in other files.
+cudaError_t launch_ep_lists(const std::int32_t* recv_counts, int count_stride, int sources, int first_expert, int local,
+                            int shared_rows, int tile_rows, p92b_plan* plan, cudaStream_t stream) {
+    if (static_cast<std::size_t>(sources) * (local + 1) > static_cast<std::size_t>(plan->ep_words)) return cudaErrorInvalidValue;
+    ep_lists_kernel<<<1, 256, 0, stream>>>(recv_counts, count_stride, sources, first_expert, local, shared_rows, tile_rows,
+                                           plan->counts, plan->pp_off, plan->active, plan->active_count, plan->tile_prefix,
+                                           plan->ep_src_base, plan->ep_src_start);
+    return cudaGetLastError();
+}
+
+namespace {
+
 inline unsigned warps_grid(int rows) { return static_cast<unsigned>((rows + 7) / 8); }
 
 }  // namespace

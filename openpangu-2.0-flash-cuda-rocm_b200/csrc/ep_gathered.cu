@@ -1,0 +1,371 @@
+// Expert-parallel MoE block for medium batches (tens of tokens per GPU, up to 1024 in flight): the
+// exchanges are done by the library's own kernels with stores into the peers' windows over NVLink,
+// like the single-kernel decode path (decode_ep.cu), but the block is a short sequence of launches
+// and the expert products are the grouped tcgen05 kernels, so an expert may have any number of rows.
+//
+//   dispatch = all-gather.  Every GPU quantises its tokens and stores rows, scales and top-8 ids
+//       into every peer's window (1.5 KB per token and peer: 0.75 MB per GPU for 512 tokens, a
+//       microsecond of NVLink).  Every GPU then has the whole batch, runs the reference's
+//       permutation law on ALL assignments (cuda/nvfp4_grouped.cu:117-132) and keeps the segments of
+//       its own experts: per expert the rows are ordered by (home GPU, token, slot), exactly as one
+//       GPU would order them.
+//   combine = direct placement.  After the down product each result row is stored into its home
+//       GPU's window at [token][slot]; the home GPU sums in slot order and adds its shared expert
+//       (cuda/nvfp4_ops.cu:124-142,92-95), which it computed in the same grouped launches.
+//
+// As in decode_ep.cu every word that crosses NVLink is 8 bytes {payload, call number} and is polled
+// by its reader: no fence, no flag, no collective library, no host synchronisation; windows are
+// double-buffered by call parity.  All polls are bounded by wall time and end in the plan's status word.
+#include "p92b_common.cuh"
+#include "tc_ptx.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+
+namespace p92b {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kTokIdWords = kTop, kTokRowWords = 320, kTokScaleWords = 40;
+constexpr int kTokWords = kTokIdWords + kTokRowWords + kTokScaleWords;     // 368 tagged words per token
+constexpr int kRetRowWords = 1280;                                         // two BF16 per tagged word
+
+struct Regions {
+    std::size_t arrive_parity, ret_parity, ret_base;
+    __host__ __device__ Regions(int world, int rows_per_gpu) {
+        arrive_parity = static_cast<std::size_t>(world) * rows_per_gpu * kTokWords * 8;
+        ret_base = 2 * arrive_parity;
+        ret_parity = static_cast<std::size_t>(rows_per_gpu) * kTop * kRetRowWords * 8;
+    }
+};
+
+__device__ __forceinline__ void st_tagged(void* p, std::uint32_t payload, std::uint32_t tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged(const void* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_tagged_pair(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ bool expired(std::uint64_t start) { return global_timer_ns() - start > 1000000000ULL; }
+
+struct Peers {
+    std::uint8_t* base[16];        // every GPU's gathered regions
+};
+
+// ---- 1. quantise the home tokens and store them, with their ids, into every window -----------------
+// One thread per 16-element block (cuda/nvfp4_ops.cu:818-841); 160 blocks per row, so whole warps.
+__global__ void __launch_bounds__(256) epg_push_kernel(const std::uint16_t* __restrict__ x,
+                                                       const std::int32_t* __restrict__ my_ids, Peers peers,
+                                                       std::size_t arrive_offset, int rank, int world, int rows,
+                                                       int rows_per_gpu, int hidden, float quant_scale, std::uint32_t tag) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int blocks16 = hidden / 16;
+    const int g = blockIdx.x * blockDim.x + threadIdx.x;
+    const std::size_t first_word = static_cast<std::size_t>(rank) * rows_per_gpu * kTokWords;
+    if (g < rows * blocks16) {
+        const int t = g / blocks16;
+        const int b = g - t * blocks16;
+        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(t) * hidden + b * 16);
+        const uint4 lo = __ldg(src);
+        const uint4 hi = __ldg(src + 1);
+        const std::uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = __uint_as_float(words[i] << 16);
+            v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+        }
+        std::uint8_t scale_bits;
+        const uint2 packed = quantize_block16(v, quant_scale, &scale_bits);
+        std::uint32_t scales4 = scale_bits;
+        scales4 |= __shfl_down_sync(0xffffffffU, static_cast<std::uint32_t>(scale_bits), 1) << 8;
+        scales4 |= __shfl_down_sync(0xffffffffU, static_cast<std::uint32_t>(scale_bits), 2) << 16;
+        scales4 |= __shfl_down_sync(0xffffffffU, static_cast<std::uint32_t>(scale_bits), 3) << 24;
+        for (int d = 0; d < world; ++d) {
+            std::uint64_t* dst = reinterpret_cast<std::uint64_t*>(peers.base[d] + arrive_offset) + first_word +
+                                 static_cast<std::size_t>(t) * kTokWords + kTokIdWords;
+            st_tagged(dst + 2 * b, packed.x, tag);
+            st_tagged(dst + 2 * b + 1, packed.y, tag);
+            if ((b & 3) == 0) st_tagged(dst + kTokRowWords + (b >> 2), scales4, tag);
+        }
+    }
+    // ids of all token slots of this GPU (-1: slot not filled this time), by the first threads of the grid
+    if (g < rows_per_gpu * kTop) {
+        const int t = g / kTop;
+        const std::uint32_t id = static_cast<std::uint32_t>(t < rows ? my_ids[g] : -1);
+        for (int d = 0; d < world; ++d) {
+            std::uint64_t* dst = reinterpret_cast<std::uint64_t*>(peers.base[d] + arrive_offset) + first_word +
+                                 static_cast<std::size_t>(t) * kTokWords;
+            st_tagged(dst + (g - t * kTop), id, tag);
+        }
+    }
+}
+
+// ---- 2. the ids of the whole batch ---------------------------------------------------------------
+// Empty token slots are given an expert that is not this GPU's, so they never become rows here.
+__global__ void __launch_bounds__(256) epg_collect_ids_kernel(const std::uint64_t* __restrict__ arrive, int assignments,
+                                                              int dump_expert, std::uint32_t tag,
+                                                              std::int32_t* __restrict__ ids_all, std::int32_t* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int a = blockIdx.x * blockDim.x + threadIdx.x;
+    if (a >= assignments) return;
+    const int g = a / kTop;
+    const void* word = arrive + static_cast<std::size_t>(g) * kTokWords + (a - g * kTop);
+    uint2 v = ld_tagged(word);
+    if (v.y != tag) {
+        const std::uint64_t start = global_timer_ns();
+        do {
+            if (expired(start)) {
+                atomicCAS(status, kStatusOk, kStatusWaitExpired);
+                ids_all[a] = dump_expert;
+                return;
+            }
+            v = ld_tagged(word);
+        } while (v.y != tag);
+    }
+    const std::int32_t e = static_cast<std::int32_t>(v.x);
+    ids_all[a] = e >= 0 && e < kExperts ? e : dump_expert;
+}
+
+// ---- 3. rows of this GPU's experts into the padded position space ---------------------------------
+// One warp per assignment of the batch, then one per home token (the shared expert's rows).
+__global__ void __launch_bounds__(256) epg_scatter_kernel(const std::uint64_t* __restrict__ arrive,
+                                                          const std::int32_t* __restrict__ ids_all,
+                                                          const std::int32_t* __restrict__ position,
+                                                          const std::int32_t* __restrict__ offsets_all,
+                                                          const std::int32_t* __restrict__ pp_off, int first_expert,
+                                                          int local, int assignments, int rank, int rows, int rows_per_gpu,
+                                                          std::uint8_t* __restrict__ xq_pp, std::uint8_t* __restrict__ xs_sw,
+                                                          std::int32_t* __restrict__ pp_of_assignment, std::uint32_t tag,
+                                                          std::int32_t* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= assignments + rows) return;
+    int token, pp;
+    if (unit < assignments) {
+        const int e = ids_all[unit];
+        const int le = e - first_expert;
+        if (le < 0 || le >= local) {
+            if (lane == 0) pp_of_assignment[unit] = -1;
+            return;
+        }
+        token = unit / kTop;
+        pp = pp_off[e] + position[unit] - offsets_all[e];
+        if (lane == 0) pp_of_assignment[unit] = pp;
+    } else {
+        const int t = unit - assignments;
+        token = rank * rows_per_gpu + t;
+        pp = pp_off[kExperts] + t;
+    }
+    const std::uint64_t* src = arrive + static_cast<std::size_t>(token) * kTokWords + kTokIdWords;
+    constexpr int kPerLane = (kTokRowWords + kTokScaleWords + 31) / 32;       // 12
+    uint2 word[kPerLane];
+    const std::uint64_t start = global_timer_ns();
+    while (true) {
+        bool missing = false;
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+            const int w = lane + 32 * j;
+            word[j] = w < kTokRowWords + kTokScaleWords ? ld_tagged(src + w) : make_uint2(0U, tag);
+        }
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) missing = missing || word[j].y != tag;
+        if (!__any_sync(0xffffffffU, missing)) break;
+        if (__any_sync(0xffffffffU, expired(start))) {          // one decision for the whole warp
+            if (lane == 0) atomicCAS(status, kStatusOk, kStatusWaitExpired);
+            return;
+        }
+    }
+    std::uint32_t* row_out = reinterpret_cast<std::uint32_t*>(xq_pp + static_cast<std::size_t>(pp) * (kTokRowWords * 4));
+    const std::size_t upp = static_cast<std::size_t>(pp);
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+        const int w = lane + 32 * j;
+        if (w < kTokRowWords) {
+            row_out[w] = word[j].x;
+        } else if (w < kTokRowWords + kTokScaleWords) {
+            const int c = w - kTokRowWords;                                   // four scale columns 4c .. 4c+3
+            *reinterpret_cast<std::uint32_t*>(xs_sw + ((upp >> 7) * kTokScaleWords + c) * 512 + (upp & 31) * 16 +
+                                              ((upp >> 5) & 3) * 4) = word[j].x;
+        }
+    }
+}
+
+// ---- 4. result rows to their home GPUs ----------------------------------------------------------------
+__global__ void __launch_bounds__(256) epg_return_kernel(const std::uint16_t* __restrict__ mixed_pp,
+                                                         const std::int32_t* __restrict__ pp_of_assignment, Peers peers,
+                                                         std::size_t ret_offset, int assignments, int rows_per_gpu,
+                                                         int hidden, std::uint32_t tag) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int a = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (a >= assignments) return;
+    const int pp = pp_of_assignment[a];
+    if (pp < 0) return;
+    const int token = a / kTop;
+    const int home = token / rows_per_gpu;
+    const int slot_row = (token - home * rows_per_gpu) * kTop + (a - token * kTop);
+    const std::uint32_t* src = reinterpret_cast<const std::uint32_t*>(mixed_pp + static_cast<std::size_t>(pp) * hidden);
+    std::uint64_t* dst = reinterpret_cast<std::uint64_t*>(peers.base[home] + ret_offset) +
+                         static_cast<std::size_t>(slot_row) * kRetRowWords;
+    for (int w = lane; w < hidden / 2; w += 32) st_tagged(dst + w, __ldcg(src + w), tag);
+}
+
+// ---- 5. combine on the home GPU ----------------------------------------------------------------------
+// One thread per four output features: eight routed slots in slot order (polled), then the shared expert.
+__global__ void __launch_bounds__(256) epg_combine_kernel(const std::uint64_t* __restrict__ ret,
+                                                          const float* __restrict__ route_weights,
+                                                          const std::uint16_t* __restrict__ mixed_pp,
+                                                          const std::int32_t* __restrict__ pp_off,
+                                                          std::uint16_t* __restrict__ out, int rows, int hidden,
+                                                          std::uint32_t tag, std::int32_t* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int quads = hidden / 4;
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= rows * quads) return;
+    const int row = v / quads;
+    const int q = v - row * quads;
+    const std::uint64_t* operand = ret + static_cast<std::size_t>(row) * kTop * kRetRowWords + 2 * q;
+    uint4 got[kTop];
+    const std::uint64_t start = global_timer_ns();
+    while (true) {
+        bool missing = false;
+#pragma unroll
+        for (int slot = 0; slot < kTop; ++slot) got[slot] = ld_tagged_pair(operand + static_cast<std::size_t>(slot) * kRetRowWords);
+#pragma unroll
+        for (int slot = 0; slot < kTop; ++slot) missing = missing || got[slot].y != tag || got[slot].w != tag;
+        if (!missing) break;
+        if (expired(start)) {
+            atomicCAS(status, kStatusOk, kStatusWaitExpired);
+            return;
+        }
+    }
+    float acc[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+    for (int slot = 0; slot < kTop; ++slot) {
+        const float w = route_weights[row * kTop + slot];
+        acc[0] = fmaf(__uint_as_float(got[slot].x << 16), w, acc[0]);
+        acc[1] = fmaf(__uint_as_float(got[slot].x & 0xffff0000U), w, acc[1]);
+        acc[2] = fmaf(__uint_as_float(got[slot].z << 16), w, acc[2]);
+        acc[3] = fmaf(__uint_as_float(got[slot].z & 0xffff0000U), w, acc[3]);
+    }
+    const uint2 sh = *reinterpret_cast<const uint2*>(mixed_pp + static_cast<std::size_t>(pp_off[kExperts] + row) * hidden + 4 * q);
+    const float o0 = bf16_bits_to_float(float_to_bf16_bits(acc[0])) + __uint_as_float(sh.x << 16);
+    const float o1 = bf16_bits_to_float(float_to_bf16_bits(acc[1])) + __uint_as_float(sh.x & 0xffff0000U);
+    const float o2 = bf16_bits_to_float(float_to_bf16_bits(acc[2])) + __uint_as_float(sh.y << 16);
+    const float o3 = bf16_bits_to_float(float_to_bf16_bits(acc[3])) + __uint_as_float(sh.y & 0xffff0000U);
+    *reinterpret_cast<uint2*>(out + static_cast<std::size_t>(row) * hidden + 4 * q) =
+        make_uint2(static_cast<std::uint32_t>(float_to_bf16_bits(o0)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o1)) << 16),
+                   static_cast<std::uint32_t>(float_to_bf16_bits(o2)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o3)) << 16));
+}
+
+}  // namespace
+
+std::size_t ep_gathered_bytes(int world, int rows_per_gpu) {
+    const Regions r(world, rows_per_gpu);
+    return r.ret_base + 2 * r.ret_parity;
+}
+
+cudaError_t launch_ep_lists(const std::int32_t* recv_counts, int count_stride, int sources, int first_expert, int local,
+                            int shared_rows, int tile_rows, p92b_plan* plan, cudaStream_t stream);   // ep.cu
+
+}  // namespace p92b
+
+extern "C" {
+
+int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window, const uint16_t* input,
+                             const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
+                             float routed_scale, void* stream_) {
+    using namespace p92b;
+    if (plan == nullptr || bank == nullptr || window == nullptr || input == nullptr || router_weight == nullptr ||
+        correction_bias == nullptr || output == nullptr || rows <= 0 || rows > window->rows_per_gpu) {
+        return cudaErrorInvalidValue;
+    }
+    const int world = window->world;
+    const int rpg = window->rows_per_gpu;
+    const int local = kExperts / world;
+    // one source: its token count is the batch; several: every slot of every GPU, empty ones marked by their owner
+    const int tokens = world == 1 ? rows : world * rpg;
+    if (!window->connected || !plan->tc_ready || !bank->tc_ready || plan->hidden != 2560 || plan->intermediate != 1024 ||
+        bank->view.hidden != 2560 || bank->view.intermediate != 1024 || bank->view.local_experts != local ||
+        bank->view.first_expert != window->rank * local || plan->max_rows < tokens) {
+        return cudaErrorNotSupported;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
+    const int hidden = plan->hidden;
+    const int assignments = tokens * kTop;
+    const Regions regions(world, rpg);
+    const unsigned call = window->epoch++;
+    const std::uint32_t tag = call + 1U;
+    const int parity = static_cast<int>(call & 1U);
+    const std::size_t arrive_offset = window->gathered_base + parity * regions.arrive_parity;
+    const std::size_t ret_offset = window->gathered_base + regions.ret_base + parity * regions.ret_parity;
+    Peers peers {};
+    for (int r = 0; r < world; ++r) peers.base[r] = window->peers[r];
+    const std::uint64_t* my_arrive = reinterpret_cast<const std::uint64_t*>(window->local + arrive_offset);
+    const std::uint64_t* my_ret = reinterpret_cast<const std::uint64_t*>(window->local + ret_offset);
+    plan->last_launches = 0;
+
+    // router of the home tokens (ids into plan->ids, weights stay in plan->route_weights for the combine)
+    cudaError_t st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, world == 1 && rows == 1,
+                                          stream, pdl);
+    if (st != cudaSuccess) return st;
+    st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream, pdl);
+    if (st != cudaSuccess) return st;
+    const int push_threads = std::max(rows * (hidden / 16), rpg * kTop);
+    st = launch_kernel(epg_push_kernel, dim3((push_threads + 255) / 256), dim3(256), 0, stream, pdl, input,
+                       static_cast<const std::int32_t*>(plan->ids), peers, arrive_offset, window->rank, world, rows, rpg,
+                       hidden, 1.0F, tag);
+    if (st != cudaSuccess) return st;
+    // the batch: ids of every token (plan->ids is reused: the home ids have been sent), the reference's
+    // permutation law over all of them, then the lists of this GPU's experts + its shared-expert rows
+    const int dump_expert = world == 1 ? 0 : (bank->view.first_expert + local) % kExperts;
+    st = launch_kernel(epg_collect_ids_kernel, dim3((assignments + 255) / 256), dim3(256), 0, stream, pdl, my_arrive,
+                       assignments, dump_expert, tag, plan->ids, plan->status);
+    if (st != cudaSuccess) return st;
+    st = launch_permute(plan, plan->ids, assignments, plan->order, plan->position, plan->epg_counts, plan->epg_offsets,
+                        false, 0, 1, stream, pdl);
+    if (st != cudaSuccess) return st;
+    // a token picks an expert at most once: no expert has more rows than there are tokens
+    const int tile_rows = tc_tile_rows(tokens);
+    st = launch_ep_lists(plan->epg_counts + bank->view.first_expert, local, 1, bank->view.first_expert, local, rows,
+                         tile_rows, plan, stream);
+    if (st != cudaSuccess) return st;
+    plan->wide_rows = 0;
+    const int units = assignments + rows;
+    st = launch_kernel(epg_scatter_kernel, dim3((units + 7) / 8), dim3(256), 0, stream, false, my_arrive,
+                       static_cast<const std::int32_t*>(plan->ids), static_cast<const std::int32_t*>(plan->position),
+                       static_cast<const std::int32_t*>(plan->epg_offsets), static_cast<const std::int32_t*>(plan->pp_off),
+                       bank->view.first_expert, local, assignments, window->rank, rows, rpg, plan->xq_pp, plan->xs_sw,
+                       plan->pp_of_flat, tag, plan->status);
+    if (st != cudaSuccess) return st;
+    if ((st = launch_experts_tc(plan, bank, tokens, false, stream, false)) != cudaSuccess) return st;
+    if ((st = launch_experts_tc(plan, bank, tokens, true, stream, false)) != cudaSuccess) return st;
+    st = launch_kernel(epg_return_kernel, dim3((assignments + 7) / 8), dim3(256), 0, stream, false,
+                       static_cast<const std::uint16_t*>(plan->mixed_pp), static_cast<const std::int32_t*>(plan->pp_of_flat),
+                       peers, ret_offset, assignments, rpg, hidden, tag);
+    if (st != cudaSuccess) return st;
+    st = launch_kernel(epg_combine_kernel, dim3((rows * (hidden / 4) + 255) / 256), dim3(256), 0, stream, pdl, my_ret,
+                       static_cast<const float*>(plan->route_weights), static_cast<const std::uint16_t*>(plan->mixed_pp),
+                       static_cast<const std::int32_t*>(plan->pp_off), output, rows, hidden, tag, plan->status);
+    plan->last_launches += 7;
+    plan->last_path = 2;
+    return st;
+}
+
+}  // extern "C"

@@ -242,6 +242,8 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->ep_src_base = c.take<std::int32_t>(plan->ep_words);
         plan->ep_src_start = c.take<std::int32_t>(plan->ep_words);
         plan->ep_zero_counts = c.take<std::int32_t>(kExperts + 1);
+        plan->epg_counts = c.take<std::int32_t>(kExperts + 1);
+        plan->epg_offsets = c.take<std::int32_t>(kExperts + 2);
         plan->stage_in = c.take<std::uint16_t>(rows * hidden);
         plan->stage_out = c.take<std::uint16_t>(rows * hidden);
         plan->stage_in_b = c.take<std::uint16_t>(rows * hidden);

@@ -280,12 +280,29 @@ struct p92b_plan {
     std::int32_t* ep_src_base = nullptr;
     std::int32_t* ep_src_start = nullptr;
     std::int32_t* ep_zero_counts = nullptr;
+    std::int32_t* epg_counts = nullptr;   // [257] histogram and [258] offsets of the whole gathered batch
+    std::int32_t* epg_offsets = nullptr;
     int ep_words = 0;
     // optional stage timing (host side)
     bool timing = false;
     cudaEvent_t stage_events[P92B_STAGES + 1] = {};
     float stage_ms[P92B_STAGES] = {};
     int timed_calls = 0;
+};
+
+// Exchange memory of one GPU for the kernels that do their own expert-parallel exchanges
+// (decode_ep.cu, ep_gathered.cu): this GPU's window plus the mapped windows of its peers.
+struct p92b_ep_window {
+    int rank = 0, world = 1, rows_per_gpu = 0;
+    std::uint8_t* local = nullptr;
+    std::uint8_t* peers[16] = {};
+    bool opened[16] = {};
+    bool connected = false;
+    bool fused_ok = false;                // small enough for the single-kernel path
+    unsigned epoch = 0;                   // calls so far (the same number on every GPU)
+    std::size_t bytes = 0;
+    std::size_t gathered_base = 0;        // offset of the regions of the multi-kernel gathered path
+    CUtensorMap map_tok[2] = {};
 };
 
 namespace p92b {

@@ -203,6 +203,19 @@ def forward_fused(window: EpWindow, plan: MoePlan, bank: ExpertBank, router_weig
            "ep_forward_fused")
 
 
+GATHERED_MAX_ROWS = 128      # home tokens per GPU the gathered multi-kernel path takes ...
+GATHERED_MAX_TOKENS = 1024   # ... and tokens in flight over all GPUs
+
+
+def forward_gathered(window: EpWindow, plan: MoePlan, bank: ExpertBank, router_weight, correction_bias, x, out, rows: int,
+                     routed_scale: float = ROUTED_SCALE) -> None:
+    """The block on this GPU's `rows` home tokens, exchanges by the library's own kernels (peer stores and
+    polled words, no NCCL, no host synchronisation).  `plan` needs max_rows >= world * rows_per_gpu."""
+    _check(load_library().p92b_ep_forward_gathered(plan.handle, bank.handle, window.handle, _ptr(x), _ptr(router_weight),
+                                                   _ptr(correction_bias), _ptr(out), rows, routed_scale, _stream()),
+           "ep_forward_gathered")
+
+
 FIXED_MAX_ROWS = 64      # per-GPU batch up to which forward_auto takes the fixed-capacity exchange
 
 

@@ -190,3 +190,32 @@ def test_fused_kernel_gives_up_when_a_peer_never_arrives(cuda, pkg, layer0):
     finally:
         for w in windows:
             w.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [1, 4, 33, 100])
+def test_gathered_path_world_one_matches_block(cuda, pkg, layer0, rows):
+    """One GPU owning all experts: push into its own window, permutation law over the batch, grouped
+    tcgen05 products, result rows placed through the window, combine; both window parities."""
+    torch = cuda
+    from p92moe_b200 import ep, synth
+
+    window = ep.EpWindow(0, 1, 128)
+    plan = pkg.MoePlan(max_rows=128)
+    try:
+        for call in range(3):
+            x = synth.make_activations(740 + call, 0, rows)
+            out = torch.full_like(x, float("nan"))
+            ep.forward_gathered(window, plan, layer0.bank, layer0.router_weight, layer0.bias, x, out, rows)
+            torch.cuda.synchronize()
+            v = plan.views(rows)
+            assert int(v["status"][0]) == 0
+            want, ref = _single_gpu_reference(pkg, layer0, x, rows)
+            assert torch.equal(v["expert_ids"], ref["expert_ids"])
+            assert torch.equal(v["expert_weights"], ref["expert_weights"])
+            got, exp = out.float().cpu().numpy(), want.float().cpu().numpy()
+            assert np.isfinite(got).all()
+            rel = np.linalg.norm(got - exp) / np.linalg.norm(exp)
+            assert rel <= 1e-2 and np.abs(got - exp).max() <= 2e-2, (call, rel)
+    finally:
+        window.close()

@@ -42,6 +42,9 @@ def _worker(rank: int, world: int, port: int, schedule, result) -> None:
                           local_experts=local)
     rows_per_gpu = max(max(rows) for rows in schedule)
     window = ep.EpWindow(rank, world, rows_per_gpu)
+    wide_rows = 24                                                    # a second window for the gathered path at a larger batch
+    wide_window = ep.EpWindow(rank, world, wide_rows)
+    wide_plan = pkg.MoePlan(max_rows=world * wide_rows)
     fused_plan = pkg.MoePlan(max_rows=world * rows_per_gpu)
     state = ep.EpRank(rank, world, bank, layer.router_weight, layer.bias, max_local_rows=rows_per_gpu)
     ok, worst = True, 0.0
@@ -58,13 +61,17 @@ def _worker(rank: int, world: int, port: int, schedule, result) -> None:
         mine, n = xs[rank], rows[rank]
         ref = want[at:at + n].float().cpu().numpy()
         ref_ids = plan.views(total)["expert_ids"][at:at + n]
-        for kind in ("fused", "fixed", "exact"):
+        for kind in ("fused", "gathered", "fixed", "exact"):
             out = torch.full_like(mine, float("nan"))
             if kind == "fused":
                 ep.forward_fused(window, fused_plan, bank, layer.router_weight, layer.bias, mine, out, n)
                 torch.cuda.synchronize()
                 ok &= int(fused_plan.views(n)["status"][0]) == 0
                 ok &= bool(torch.equal(fused_plan.views(n)["expert_ids"], ref_ids))
+            elif kind == "gathered":
+                ep.forward_gathered(window, fused_plan, bank, layer.router_weight, layer.bias, mine, out, n)
+                torch.cuda.synchronize()
+                ok &= int(fused_plan.views(n)["status"][0]) == 0
             elif kind == "fixed":
                 ep.forward_nccl_fixed(state, mine, out, n, 8 * rows_per_gpu)
             else:
@@ -74,9 +81,29 @@ def _worker(rank: int, world: int, port: int, schedule, result) -> None:
             rel = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
             worst = max(worst, rel)
             ok &= bool(np.isfinite(got).all()) and rel <= 1e-2 and float(np.abs(got - ref).max()) <= 2e-2
+    # the gathered path at 24 tokens per GPU, ragged: rank r brings 24 - r tokens
+    for call in range(2):
+        rows = [wide_rows - r for r in range(world)]
+        xs = [synth.make_activations(1300 + 16 * call + r, 0, n) for r, n in enumerate(rows)]
+        x_all = torch.cat(xs).contiguous()
+        total = x_all.shape[0]
+        plan = pkg.MoePlan(max_rows=total)
+        plan.set_path(2)
+        want = torch.empty_like(x_all)
+        pkg.MoeBlock(layer.bank, layer.router_weight, layer.bias, plan).run_moe_rows(x_all, want, total)
+        at, n = sum(rows[:rank]), rows[rank]
+        out = torch.full_like(xs[rank], float("nan"))
+        ep.forward_gathered(wide_window, wide_plan, bank, layer.router_weight, layer.bias, xs[rank], out, n)
+        torch.cuda.synchronize()
+        ok &= int(wide_plan.views(1)["status"][0]) == 0
+        got, ref = out.float().cpu().numpy(), want[at:at + n].float().cpu().numpy()
+        rel = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+        worst = max(worst, rel)
+        ok &= bool(np.isfinite(got).all()) and rel <= 1e-2 and float(np.abs(got - ref).max()) <= 2e-2
     dist.barrier()
     torch.cuda.synchronize()
     window.close()
+    wide_window.close()
     result[rank] = (bool(ok), worst)
     dist.destroy_process_group()
 
