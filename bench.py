@@ -222,7 +222,7 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     mode = os.environ.get("P92B_EP_EXCHANGE", "")
     if not mode:
         mode = "fused" if rows <= ep.FUSED_MAX_ROWS and world * rows <= ep.FUSED_MAX_TOKENS else \
-            "fixed" if rows <= ep.FIXED_MAX_ROWS else "exact"
+            "gathered" if rows <= ep.GATHERED_MAX_ROWS and world * rows <= ep.GATHERED_MAX_TOKENS else "exact"
     banks, routers, states, xs = [], [], [], []
     for l in range(n_layers):
         raw = synth.make_raw_layer(SEED, l)                     # same weights on every rank; keep the shard
@@ -233,14 +233,14 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
         if args.workload in ("ep_decode512", "prefill4096"):
             alpha = 1.0 if args.workload == "ep_decode512" else 1.2
             routers[-1] = (routers[-1][0], synth.fit_zipf_bias(routers[-1][0], alpha, SEED + l)[0].contiguous())
-        if mode != "fused":
+        if mode in ("fixed", "exact"):
             states.append(ep.EpRank(rank, world, banks[-1], routers[-1][0], routers[-1][1], max_local_rows=rows,
                                     share_scratch_with=states[0] if states else None))
         xs.append(synth.make_activations(SEED + 1000 * (rank + 1), l, rows))
         del raw, entries, shard
     outs = [torch.empty_like(x) for x in xs]
     window = fused_plan = None
-    if mode == "fused":
+    if mode in ("fused", "gathered"):
         window = ep.EpWindow(rank, world, rows)                 # one window and one plan serve all layers
         fused_plan = pkg.MoePlan(max_rows=world * rows)
     torch.cuda.synchronize()
@@ -248,6 +248,8 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     def forward(l, x, o):
         if mode == "fused":
             ep.forward_fused(window, fused_plan, banks[l], routers[l][0], routers[l][1], x, o, rows)
+        elif mode == "gathered":
+            ep.forward_gathered(window, fused_plan, banks[l], routers[l][0], routers[l][1], x, o, rows)
         elif mode == "fixed":
             ep.forward_nccl_fixed(states[l], x, o, rows, 8 * rows)
         else:
@@ -301,7 +303,7 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
 
     step()
     torch.cuda.synchronize()
-    count_plans = [fused_plan] if mode == "fused" else [states[-1].arrivals]
+    count_plans = [fused_plan] if mode in ("fused", "gathered") else [states[-1].arrivals]
     local_counts = [pl.views(1)["counts"][first:first + local] for pl in count_plans]
     received = [int(c.sum()) for c in local_counts]
     load = torch.tensor([float(np.mean(received))], device="cuda")     # rows arriving per layer
@@ -321,13 +323,16 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
                                                 parallelism=f"ep{world}: {local} experts per GPU, {rows} home tokens per GPU, "
                                                             + {"fused": "one kernel per GPU and layer, dispatch (all-gather) and combine by peer stores "
                                                                         "over NVLink inside the kernel",
+                                                               "gathered": "all-gather dispatch and direct placement of result rows by the "
+                                                                           "library's own kernels (peer stores over NVLink, polled words), "
+                                                                           "grouped tcgen05 products in between; no NCCL, no host sync",
                                                                "fixed": "NCCL all-to-all dispatch and combine, fixed-capacity blocks, "
                                                                         "no host sync",
                                                                "exact": "NCCL all-to-all dispatch and combine, exact-size splits"}[mode]),
             "clocks": sampler.stop(),
             "e2e": {"value": world * rows / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": bytes_io,
                     "d2h_bytes_per_step": bytes_io, "ms_per_step": e2e_s * 1e3},
-            "gpu_launches": steps * n_layers * {"fused": 1, "fixed": 16, "exact": 16}[mode],
+            "gpu_launches": steps * n_layers * {"fused": 1, "gathered": 11, "fixed": 16, "exact": 16}[mode],
             "roofline": {"bound": "hbm", "kernel": "moe_decode_ep_kernel (per-GPU shard)" if mode == "fused"
                          else "expert_tc_kernel (per-GPU shard)", "achieved": gbs,
                          "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,

@@ -252,7 +252,7 @@ int p92b_ep_combine_fixed(p92b_plan* home_plan, p92b_plan* shared_plan, const p9
  *
  * A window is this GPU's exchange memory (p92b_ep_window_bytes, allocated with cudaMalloc) plus the
  * mapped windows of its peers; it serves this call (world * rows_per_gpu <= 32, rows_per_gpu <= 8) and
- * p92b_ep_forward_gathered below (rows_per_gpu <= 128, world * rows_per_gpu <= 1024).  Set-up, once: every process creates its window, publishes the 64-byte
+ * p92b_ep_forward_gathered below (rows_per_gpu <= 512, world * rows_per_gpu <= 1024).  Set-up, once: every process creates its window, publishes the 64-byte
  * inter-process handle (p92b_ep_window_handle) to all others by any means, and connects with the
  * handles of all ranks in rank order (its own entry is ignored).  world * rows_per_gpu <= 32,
  * rows_per_gpu <= 8.  All GPUs must call p92b_ep_forward_fused the same number of times on a window,

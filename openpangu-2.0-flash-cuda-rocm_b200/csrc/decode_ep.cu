@@ -842,7 +842,7 @@ int p92b_ep_window_create(p92b_ep_window** out, int rank, int world, int rows_pe
     if (out == nullptr) return cudaErrorInvalidValue;
     *out = nullptr;
     if (world <= 0 || world > kEpMaxWorld || rank < 0 || rank >= world || kExperts % world != 0 || rows_per_gpu <= 0 ||
-        rows_per_gpu > 128 || world * rows_per_gpu > 1024) {
+        rows_per_gpu > 512 || world * rows_per_gpu > 1024) {
         return cudaErrorInvalidValue;
     }
     p92b_ep_window* w = new (std::nothrow) p92b_ep_window();

@@ -348,15 +348,17 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
     if (st != cudaSuccess) return st;
     plan->wide_rows = 0;
     const int units = assignments + rows;
-    st = launch_kernel(epg_scatter_kernel, dim3((units + 7) / 8), dim3(256), 0, stream, false, my_arrive,
+    st = launch_kernel(epg_scatter_kernel, dim3((units + 7) / 8), dim3(256), 0, stream, pdl, my_arrive,
                        static_cast<const std::int32_t*>(plan->ids), static_cast<const std::int32_t*>(plan->position),
                        static_cast<const std::int32_t*>(plan->epg_offsets), static_cast<const std::int32_t*>(plan->pp_off),
                        bank->view.first_expert, local, assignments, window->rank, rows, rpg, plan->xq_pp, plan->xs_sw,
                        plan->pp_of_flat, tag, plan->status);
     if (st != cudaSuccess) return st;
-    if ((st = launch_experts_tc(plan, bank, tokens, false, stream, false)) != cudaSuccess) return st;
-    if ((st = launch_experts_tc(plan, bank, tokens, true, stream, false)) != cudaSuccess) return st;
-    st = launch_kernel(epg_return_kernel, dim3((assignments + 7) / 8), dim3(256), 0, stream, false,
+    // every kernel of the chain waits for its predecessor before it finishes, so the lists two launches up are
+    // complete when the down product looks at them
+    if ((st = launch_experts_tc(plan, bank, tokens, false, stream, pdl)) != cudaSuccess) return st;
+    if ((st = launch_experts_tc(plan, bank, tokens, true, stream, pdl)) != cudaSuccess) return st;
+    st = launch_kernel(epg_return_kernel, dim3((assignments + 7) / 8), dim3(256), 0, stream, pdl,
                        static_cast<const std::uint16_t*>(plan->mixed_pp), static_cast<const std::int32_t*>(plan->pp_of_flat),
                        peers, ret_offset, assignments, rpg, hidden, tag);
     if (st != cudaSuccess) return st;

@@ -203,7 +203,7 @@ def forward_fused(window: EpWindow, plan: MoePlan, bank: ExpertBank, router_weig
            "ep_forward_fused")
 
 
-GATHERED_MAX_ROWS = 128      # home tokens per GPU the gathered multi-kernel path takes ...
+GATHERED_MAX_ROWS = 512      # home tokens per GPU the gathered multi-kernel path takes ...
 GATHERED_MAX_TOKENS = 1024   # ... and tokens in flight over all GPUs
 
 
