@@ -334,26 +334,42 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                 }
             }
         } else {
-            for (int q = warp; q < my_experts * rows; q += kEpThreads / 32) {
-                const int r = q / rows;
-                const int t = q - r * rows;
+            // a warp runs the chains of two tokens against one router row side by side (same order within
+            // each chain)
+            const int token_pairs = (rows + 1) / 2;
+            for (int q = warp; q < my_experts * token_pairs; q += kEpThreads / 32) {
+                const int r = q / token_pairs;
+                const int t0 = 2 * (q - r * token_pairs);
+                const bool second = t0 + 1 < rows;
                 const std::uint16_t* wr = w_rows + r * hidden;
-                const std::uint16_t* xr = x_rows + t * hidden;
-                float value = 0.0F;
+                const std::uint16_t* xa = x_rows + t0 * hidden;
+                const std::uint16_t* xb = x_rows + (second ? t0 + 1 : t0) * hidden;
+                float va = 0.0F, vb = 0.0F;
 #pragma unroll 8
                 for (int c = lane; c < hidden; c += 32) {
-                    value = fmaf(bf16_bits_to_float(xr[c]), bf16_bits_to_float(wr[c]), value);
+                    const float wv = bf16_bits_to_float(wr[c]);
+                    va = fmaf(bf16_bits_to_float(xa[c]), wv, va);
+                    vb = fmaf(bf16_bits_to_float(xb[c]), wv, vb);
                 }
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
+                for (int off = 16; off > 0; off >>= 1) {
+                    va += __shfl_down_sync(0xffffffffU, va, off);
+                    vb += __shfl_down_sync(0xffffffffU, vb, off);
+                }
                 if (lane == 0) {
-                    p.logits[static_cast<std::size_t>(t) * kExperts + block + r * grid] = value;
-                    st_tagged(p.logits_tagged + t * kExperts + block + r * grid, __float_as_uint(value), plan_tag);
+                    const int e = block + r * grid;
+                    p.logits[static_cast<std::size_t>(t0) * kExperts + e] = va;
+                    st_tagged(p.logits_tagged + t0 * kExperts + e, __float_as_uint(va), plan_tag);
+                    if (second) {
+                        p.logits[static_cast<std::size_t>(t0 + 1) * kExperts + e] = vb;
+                        st_tagged(p.logits_tagged + (t0 + 1) * kExperts + e, __float_as_uint(vb), plan_tag);
+                    }
                 }
             }
         }
+        // (the blocks at the END of the grid quantise: those have one router row, the others two)
         const int blocks16 = hidden / 16;
-        const int g = block * kEpThreads + threadIdx.x;
+        const int g = (grid - 1 - block) * kEpThreads + threadIdx.x;
         if (g < rows * blocks16) {
             const int t = g / blocks16;
             const int b = g - t * blocks16;

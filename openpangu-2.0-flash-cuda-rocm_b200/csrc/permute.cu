@@ -26,15 +26,17 @@ constexpr int kChunk = 256;          // flat indices per warp in the multi-block
 constexpr int kWarps = 8;
 
 // Counts the experts of one chunk into hist[256] (owned by the calling warp).
+// `cached` (optional): the chunk's ids already in shared memory, cached[i - begin].
 __device__ __forceinline__ void warp_histogram(const std::int32_t* __restrict__ ids, int begin, int end,
-                                               std::int32_t* hist, std::int32_t* status) {
+                                               std::int32_t* hist, std::int32_t* status,
+                                               const std::int16_t* cached = nullptr) {
     const int lane = threadIdx.x & 31;
     for (int e = lane; e < kExperts; e += 32) hist[e] = 0;
     __syncwarp();
     for (int base = begin; base < end; base += 32) {
         const int i = base + lane;
         const bool valid = i < end;
-        int e = valid ? ids[i] : -1;
+        int e = valid ? (cached != nullptr ? static_cast<int>(cached[i - begin]) : ids[i]) : -1;
         if (valid && (e < 0 || e >= kExperts)) {
             atomicCAS(status, kStatusOk, kStatusBadExpertId);
             e = e < 0 ? 0 : kExperts - 1;
@@ -53,14 +55,15 @@ __device__ __forceinline__ void warp_scatter(const std::int32_t* __restrict__ id
                                              std::int32_t* __restrict__ position,
                                              std::int32_t* __restrict__ row_token,
                                              const std::int32_t* offsets, const std::int32_t* pp_off,
-                                             std::int32_t* __restrict__ pp_of_flat) {
+                                             std::int32_t* __restrict__ pp_of_flat,
+                                             const std::int16_t* cached = nullptr) {
     const int lane = threadIdx.x & 31;
     for (int e = lane; e < kExperts; e += 32) running[e] = base[e];
     __syncwarp();
     for (int step = begin; step < end; step += 32) {
         const int i = step + lane;
         const bool valid = i < end;
-        int e = valid ? ids[i] : -1;
+        int e = valid ? (cached != nullptr ? static_cast<int>(cached[i - begin]) : ids[i]) : -1;
         if (valid) e = e < 0 ? 0 : (e >= kExperts ? kExperts - 1 : e);
         const unsigned peers = __match_any_sync(0xffffffffU, e);
         const int rank = __popc(peers & ((1U << lane) - 1U));
@@ -171,7 +174,15 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
     const int per_warp = ((assignments + kWarps - 1) / kWarps + 31) / 32 * 32;
     const int begin = min(assignments, warp * per_warp);
     const int end = min(assignments, begin + per_warp);
-    warp_histogram(ids, begin, end, hist[warp], status);
+    // the warp's ids once into shared memory, all loads in flight together: the two passes below are chains of
+    // dependent 32-wide steps and would otherwise pay a global-memory round trip per step
+    __shared__ std::int16_t cached_ids[kWarps][1024];
+    for (int i = begin + (threadIdx.x & 31); i < end; i += 32) {
+        const int e = ids[i];
+        cached_ids[warp][i - begin] = static_cast<std::int16_t>(e < -1 ? -1 : (e > kExperts ? kExperts : e));   // out-of-range stays out of range
+    }
+    __syncwarp();
+    warp_histogram(ids, begin, end, hist[warp], status, cached_ids[warp]);
     __syncthreads();
     const int e = threadIdx.x;
     int total = 0;
@@ -188,7 +199,7 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
     write_route_lists(e, total, offset, assignments, rows, lists, scan_scratch);
     __syncthreads();
     warp_scatter(ids, begin, end, hist[warp], running[warp], order, position, row_token, lists.offsets, lists.pp_off,
-                 pp_of_flat);
+                 pp_of_flat, cached_ids[warp]);
     if (row_token != nullptr) {
         for (int t = threadIdx.x; t < rows; t += blockDim.x) {
             row_token[assignments + t] = t;
