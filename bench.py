@@ -304,7 +304,7 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     step()
     torch.cuda.synchronize()
     count_plans = [fused_plan] if mode in ("fused", "gathered") else [states[-1].arrivals]
-    local_counts = [pl.views(1)["counts"][first:first + local] for pl in count_plans]
+    local_counts = [pl.device_counts()[first:first + local].clone() for pl in count_plans]
     received = [int(c.sum()) for c in local_counts]
     load = torch.tensor([float(np.mean(received))], device="cuda")     # rows arriving per layer
     loads = [torch.zeros_like(load) for _ in range(world)]

@@ -318,9 +318,11 @@ class MoePlan:
 
         a = rows * TOP_K
         mixed_index = grab(v.mixed_index, (a + rows,), torch.int32)
-        span = int(mixed_index.max()) + 1
-        typestr_rows = torch.as_tensor(_DeviceSpan(v.mixed, (span, self.hidden), "<i2"), device="cuda")
-        mixed = typestr_rows[mixed_index.long()].contiguous().view(torch.bfloat16)
+        mixed = None
+        if int(mixed_index.min()) >= 0:            # (the expert-parallel paths keep other things in this index)
+            span = int(mixed_index.max()) + 1
+            typestr_rows = torch.as_tensor(_DeviceSpan(v.mixed, (span, self.hidden), "<i2"), device="cuda")
+            mixed = typestr_rows[mixed_index.long()].contiguous().view(torch.bfloat16)
         return {
             "mixed": mixed,            # [rows*8 + rows, hidden] in (row, slot) order, shared rows last
             "logits": grab(v.logits, (rows, EXPERTS), torch.float32),
@@ -334,6 +336,14 @@ class MoePlan:
             "status": grab(v.status, (1,), torch.int32),
             "trace": torch.as_tensor(_DeviceSpan(v.trace, (v.trace_blocks, 64), "<i8"), device="cuda").clone(),
         }
+
+    def status(self) -> int:
+        """The plan's status word: 0, or the first error a kernel recorded (synchronises the device)."""
+        import torch
+
+        v = PlanViews()
+        _check(load_library().p92b_plan_get_views(self.handle, ctypes.byref(v)), "plan_get_views")
+        return int(_device_copy(v.status, (1,), torch.int32)[0])
 
     def device_counts(self):
         """Zero-copy int32 [256] view of the last call's per-expert row counts (valid until the next call)."""

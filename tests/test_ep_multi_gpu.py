@@ -71,7 +71,7 @@ def _worker(rank: int, world: int, port: int, schedule, result) -> None:
             elif kind == "gathered":
                 ep.forward_gathered(window, fused_plan, bank, layer.router_weight, layer.bias, mine, out, n)
                 torch.cuda.synchronize()
-                ok &= int(fused_plan.views(n)["status"][0]) == 0
+                ok &= fused_plan.status() == 0
             elif kind == "fixed":
                 ep.forward_nccl_fixed(state, mine, out, n, 8 * rows_per_gpu)
             else:
@@ -95,7 +95,7 @@ def _worker(rank: int, world: int, port: int, schedule, result) -> None:
         out = torch.full_like(xs[rank], float("nan"))
         ep.forward_gathered(wide_window, wide_plan, bank, layer.router_weight, layer.bias, xs[rank], out, n)
         torch.cuda.synchronize()
-        ok &= int(wide_plan.views(1)["status"][0]) == 0
+        ok &= wide_plan.status() == 0
         got, ref = out.float().cpu().numpy(), want[at:at + n].float().cpu().numpy()
         rel = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
         worst = max(worst, rel)
