@@ -168,7 +168,13 @@ size_t p92b_plan_bytes(const p92b_plan* plan);
  * (src/model.cpp:1486-1573): router logits -> top-8 -> permutation -> NVFP4
  * gate/up + SwiGLU -> NVFP4 down -> weighted combine (device law,
  * cuda/nvfp4_ops.cu:124-142) -> + shared expert.  input/output: BF16 [rows][hidden].
- * rows == 1 uses the T=1 logits order, rows > 1 the T>1 order, as the reference does. */
+ * rows == 1 uses the T=1 logits order, rows > 1 the T>1 order, as the reference does.
+ *
+ * For up to 8 rows the block is ONE persistent kernel with one thread block per SM whose blocks hand
+ * data to one another (p92b_plan_set_path).  They must all be resident at once: do not run it while
+ * kernels on other streams keep SMs occupied for long.  Every wait inside is bounded: if the blocks cannot
+ * make progress within about a second the call ends with 2 in the plan's status word (p92b_plan_get_views)
+ * instead of hanging.  The same holds for p92b_ep_forward_fused. */
 int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input,
                      const uint16_t* router_weight, const float* correction_bias, uint16_t* output,
                      int rows, float routed_scale, void* stream);
