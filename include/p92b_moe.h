@@ -282,14 +282,13 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
                           float routed_scale, void* stream);
 
 /* Medium batches (tens of tokens per GPU, up to 1024 in flight), same idea, several launches: every GPU
- * stores its quantised rows and top-8 ids into every peer's window (all-gather), runs the reference's
- * permutation law over the whole batch and keeps its own experts' segments, computes them with the grouped
+ * stores its quantised rows and top-8 ids into every peer's window (all-gather), ranks the rows of its own
+ * experts over the whole batch by the reference's permutation law, computes them with the grouped
  * tcgen05 kernels, stores each result row into its home GPU's window, and the home GPU combines in slot
  * order and adds its shared expert.  No NCCL call, no host synchronisation, nothing but bounded polls of
  * {payload, call number} words between GPUs.  Same window and calling rules as p92b_ep_forward_fused
  * (both kinds of call may be mixed on one window as long as all GPUs mix them identically); the plan
- * must have been created for at least world * rows_per_gpu rows.  After the call the plan's ids view
- * holds the ids of ALL tokens of the batch in (home GPU, token) order. */
+ * must have been created for at least world * rows_per_gpu rows. */
 int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window, const uint16_t* input,
                              const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
                              float routed_scale, void* stream);

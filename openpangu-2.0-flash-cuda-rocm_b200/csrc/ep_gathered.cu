@@ -5,10 +5,9 @@
 //
 //   dispatch = all-gather.  Every GPU quantises its tokens and stores rows, scales and top-8 ids
 //       into every peer's window (1.5 KB per token and peer: 0.75 MB per GPU for 512 tokens, a
-//       microsecond of NVLink).  Every GPU then has the whole batch, runs the reference's
-//       permutation law on ALL assignments (cuda/nvfp4_grouped.cu:117-132) and keeps the segments of
-//       its own experts: per expert the rows are ordered by (home GPU, token, slot), exactly as one
-//       GPU would order them.
+//       microsecond of NVLink).  Every GPU then has the whole batch and ranks the rows of its own
+//       experts by the reference's law (cuda/nvfp4_grouped.cu:117-132): per expert the rows are
+//       ordered by (home GPU, token, slot), exactly as one GPU would order them.
 //   combine = direct placement.  After the down product each result row is stored into its home
 //       GPU's window at [token][slot]; the home GPU sums in slot order and adds its shared expert
 //       (cuda/nvfp4_ops.cu:124-142,92-95), which it computed in the same grouped launches.
@@ -110,44 +109,145 @@ __global__ void __launch_bounds__(256) epg_push_kernel(const std::uint16_t* __re
     }
 }
 
-// ---- 2. the ids of the whole batch ---------------------------------------------------------------
-// Empty token slots are given an expert that is not this GPU's, so they never become rows here.
-__global__ void __launch_bounds__(256) epg_collect_ids_kernel(const std::uint64_t* __restrict__ arrive, int assignments,
-                                                              int dump_expert, std::uint32_t tag,
-                                                              std::int32_t* __restrict__ ids_all, std::int32_t* status) {
+// ---- 2. routing lists of this GPU's experts from the ids of the whole batch -------------------------
+// One block.  A token picks an expert at most once, so per local expert a bit mask of tokens says
+// everything: its popcount is the expert's row count, the popcount below a token's bit is that row's
+// rank - the order of cuda/nvfp4_grouped.cu:117-132 (same expert: by flat index = by token), without
+// sorting the assignments of other GPUs' experts.  Writes what the grouped expert kernels read
+// (counts, 128-aligned padded offsets, active list with the shared expert first, token-tile prefix)
+// and the padded position of every assignment (-1: not this GPU's expert, or an empty token slot).
+constexpr int kRouteThreads = 1024;
+constexpr int kMaskWords = 32;                       // up to 1024 tokens
+constexpr int kRoutePerThread = 8;                   // up to 8192 assignments
+
+__global__ void __launch_bounds__(kRouteThreads) epg_route_kernel(const std::uint64_t* __restrict__ arrive, int tokens,
+                                                                  int first_expert, int local, int shared_rows,
+                                                                  int tile_rows, std::uint32_t tag,
+                                                                  std::int32_t* __restrict__ counts,
+                                                                  std::int32_t* __restrict__ pp_off,
+                                                                  std::int32_t* __restrict__ active,
+                                                                  std::int32_t* __restrict__ active_count,
+                                                                  std::int32_t* __restrict__ tile_prefix,
+                                                                  std::int32_t* __restrict__ pp_of_assignment,
+                                                                  std::int32_t* status) {
+    extern __shared__ std::uint32_t route_smem[];
+    std::uint32_t* mask = route_smem;                                   // [local][kMaskWords]
+    std::int32_t* expert_pp = reinterpret_cast<std::int32_t*>(route_smem + local * kMaskWords);   // [local]
     pdl_wait();
     pdl_launch_dependents();
-    const int a = blockIdx.x * blockDim.x + threadIdx.x;
-    if (a >= assignments) return;
-    const int g = a / kTop;
-    const void* word = arrive + static_cast<std::size_t>(g) * kTokWords + (a - g * kTop);
-    uint2 v = ld_tagged(word);
-    if (v.y != tag) {
+    const int assignments = tokens * kTop;
+    for (int i = threadIdx.x; i < local * kMaskWords; i += kRouteThreads) mask[i] = 0U;
+    __syncthreads();
+    std::int32_t mine[kRoutePerThread];
+    {
+        uint2 word[kRoutePerThread];
         const std::uint64_t start = global_timer_ns();
-        do {
+        while (true) {
+            bool missing = false;
+#pragma unroll
+            for (int j = 0; j < kRoutePerThread; ++j) {
+                const int a = threadIdx.x + j * kRouteThreads;
+                if (a < assignments) {
+                    const int g = a / kTop;
+                    word[j] = ld_tagged(arrive + static_cast<std::size_t>(g) * kTokWords + (a - g * kTop));
+                } else {
+                    word[j] = make_uint2(0xffffffffU, tag);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kRoutePerThread; ++j) {
+                const int a = threadIdx.x + j * kRouteThreads;
+                if (a < assignments && word[j].y != tag) missing = true;
+            }
+            if (!missing) break;
             if (expired(start)) {
                 atomicCAS(status, kStatusOk, kStatusWaitExpired);
-                ids_all[a] = dump_expert;
-                return;
+#pragma unroll
+                for (int j = 0; j < kRoutePerThread; ++j) {
+                    if (word[j].y != tag) word[j].x = 0xffffffffU;         // treated as an empty slot
+                }
+                break;
             }
-            v = ld_tagged(word);
-        } while (v.y != tag);
+        }
+#pragma unroll
+        for (int j = 0; j < kRoutePerThread; ++j) {
+            const int a = threadIdx.x + j * kRouteThreads;
+            mine[j] = -1;
+            if (a < assignments) {
+                const int le = static_cast<std::int32_t>(word[j].x) - first_expert;
+                if (static_cast<std::int32_t>(word[j].x) >= 0 && le >= 0 && le < local) {
+                    mine[j] = le;
+                    const int g = a / kTop;
+                    atomicOr(&mask[le * kMaskWords + (g >> 5)], 1U << (g & 31));
+                }
+            }
+        }
     }
-    const std::int32_t e = static_cast<std::int32_t>(v.x);
-    ids_all[a] = e >= 0 && e < kExperts ? e : dump_expert;
+    __syncthreads();
+    for (int e = threadIdx.x; e < kExperts; e += kRouteThreads) {
+        const int le = e - first_expert;
+        int count = 0;
+        if (le >= 0 && le < local) {
+#pragma unroll 8
+            for (int w = 0; w < kMaskWords; ++w) count += __popc(mask[le * kMaskWords + w]);
+        }
+        counts[e] = count;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // 256 entries: a serial pass keeps the three prefixes in one place
+        int pp = 0, slot = 0, tiles = 0;
+        if (shared_rows > 0) {
+            active[slot++] = kExperts;
+            tile_prefix[0] = 0;
+            tiles = (shared_rows + tile_rows - 1) / tile_rows;
+        }
+        for (int e = 0; e < kExperts; ++e) {
+            pp_off[e] = pp;
+            const int le = e - first_expert;
+            if (le < 0 || le >= local) continue;
+            expert_pp[le] = pp;
+            int c = 0;
+            for (int w = 0; w < kMaskWords; ++w) c += __popc(mask[le * kMaskWords + w]);
+            if (c > 0) {
+                active[slot] = e;
+                tile_prefix[slot] = tiles;
+                ++slot;
+                tiles += (c + tile_rows - 1) / tile_rows;
+                pp += (c + 127) / 128 * 128;
+            }
+        }
+        pp_off[kExperts] = pp;
+        pp_off[kExperts + 1] = pp + (shared_rows + 127) / 128 * 128;
+        counts[kExperts] = shared_rows;
+        tile_prefix[slot] = tiles;
+        *active_count = slot;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kRoutePerThread; ++j) {
+        const int a = threadIdx.x + j * kRouteThreads;
+        if (a >= assignments) continue;
+        int pp = -1;
+        if (mine[j] >= 0) {
+            const int g = a / kTop;
+            const std::uint32_t* m = mask + mine[j] * kMaskWords;
+            int rank = __popc(m[g >> 5] & ((1U << (g & 31)) - 1U));
+            for (int w = 0; w < (g >> 5); ++w) rank += __popc(m[w]);
+            pp = expert_pp[mine[j]] + rank;
+        }
+        pp_of_assignment[a] = pp;
+    }
 }
 
 // ---- 3. rows of this GPU's experts into the padded position space ---------------------------------
 // One warp per assignment of the batch, then one per home token (the shared expert's rows).
 __global__ void __launch_bounds__(256) epg_scatter_kernel(const std::uint64_t* __restrict__ arrive,
-                                                          const std::int32_t* __restrict__ ids_all,
-                                                          const std::int32_t* __restrict__ position,
-                                                          const std::int32_t* __restrict__ offsets_all,
-                                                          const std::int32_t* __restrict__ pp_off, int first_expert,
-                                                          int local, int assignments, int rank, int rows, int rows_per_gpu,
+                                                          const std::int32_t* __restrict__ pp_of_assignment,
+                                                          const std::int32_t* __restrict__ pp_off, int assignments,
+                                                          int rank, int rows, int rows_per_gpu,
                                                           std::uint8_t* __restrict__ xq_pp, std::uint8_t* __restrict__ xs_sw,
-                                                          std::int32_t* __restrict__ pp_of_assignment, std::uint32_t tag,
-                                                          std::int32_t* status) {
+                                                          std::uint32_t tag, std::int32_t* status) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -155,15 +255,9 @@ __global__ void __launch_bounds__(256) epg_scatter_kernel(const std::uint64_t* _
     if (unit >= assignments + rows) return;
     int token, pp;
     if (unit < assignments) {
-        const int e = ids_all[unit];
-        const int le = e - first_expert;
-        if (le < 0 || le >= local) {
-            if (lane == 0) pp_of_assignment[unit] = -1;
-            return;
-        }
+        pp = pp_of_assignment[unit];
+        if (pp < 0) return;
         token = unit / kTop;
-        pp = pp_off[e] + position[unit] - offsets_all[e];
-        if (lane == 0) pp_of_assignment[unit] = pp;
     } else {
         const int t = unit - assignments;
         token = rank * rows_per_gpu + t;
@@ -332,27 +426,26 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
                        static_cast<const std::int32_t*>(plan->ids), peers, arrive_offset, window->rank, world, rows, rpg,
                        hidden, 1.0F, tag);
     if (st != cudaSuccess) return st;
-    // the batch: ids of every token (plan->ids is reused: the home ids have been sent), the reference's
-    // permutation law over all of them, then the lists of this GPU's experts + its shared-expert rows
-    const int dump_expert = world == 1 ? 0 : (bank->view.first_expert + local) % kExperts;
-    st = launch_kernel(epg_collect_ids_kernel, dim3((assignments + 255) / 256), dim3(256), 0, stream, pdl, my_arrive,
-                       assignments, dump_expert, tag, plan->ids, plan->status);
-    if (st != cudaSuccess) return st;
-    st = launch_permute(plan, plan->ids, assignments, plan->order, plan->position, plan->epg_counts, plan->epg_offsets,
-                        false, 0, 1, stream, pdl);
-    if (st != cudaSuccess) return st;
-    // a token picks an expert at most once: no expert has more rows than there are tokens
+    // routing lists of this GPU's experts (+ its shared-expert rows) from the ids of the whole batch; a token picks
+    // an expert at most once, so no expert has more rows than there are tokens
     const int tile_rows = tc_tile_rows(tokens);
-    st = launch_ep_lists(plan->epg_counts + bank->view.first_expert, local, 1, bank->view.first_expert, local, rows,
-                         tile_rows, plan, stream);
+    const std::size_t route_smem = static_cast<std::size_t>(local) * (kMaskWords + 1) * 4;
+    static bool configured = false;
+    if (!configured) {
+        st = cudaFuncSetAttribute(epg_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(kExperts * (kMaskWords + 1) * 4));
+        if (st != cudaSuccess) return st;
+        configured = true;
+    }
+    st = launch_kernel(epg_route_kernel, dim3(1), dim3(kRouteThreads), route_smem, stream, pdl, my_arrive, tokens,
+                       bank->view.first_expert, local, rows, tile_rows, tag, plan->counts, plan->pp_off, plan->active,
+                       plan->active_count, plan->tile_prefix, plan->pp_of_flat, plan->status);
     if (st != cudaSuccess) return st;
     plan->wide_rows = 0;
     const int units = assignments + rows;
     st = launch_kernel(epg_scatter_kernel, dim3((units + 7) / 8), dim3(256), 0, stream, pdl, my_arrive,
-                       static_cast<const std::int32_t*>(plan->ids), static_cast<const std::int32_t*>(plan->position),
-                       static_cast<const std::int32_t*>(plan->epg_offsets), static_cast<const std::int32_t*>(plan->pp_off),
-                       bank->view.first_expert, local, assignments, window->rank, rows, rpg, plan->xq_pp, plan->xs_sw,
-                       plan->pp_of_flat, tag, plan->status);
+                       static_cast<const std::int32_t*>(plan->pp_of_flat), static_cast<const std::int32_t*>(plan->pp_off),
+                       assignments, window->rank, rows, rpg, plan->xq_pp, plan->xs_sw, tag, plan->status);
     if (st != cudaSuccess) return st;
     // every kernel of the chain waits for its predecessor before it finishes, so the lists two launches up are
     // complete when the down product looks at them
@@ -365,7 +458,7 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
     st = launch_kernel(epg_combine_kernel, dim3((rows * (hidden / 4) + 255) / 256), dim3(256), 0, stream, pdl, my_ret,
                        static_cast<const float*>(plan->route_weights), static_cast<const std::uint16_t*>(plan->mixed_pp),
                        static_cast<const std::int32_t*>(plan->pp_off), output, rows, hidden, tag, plan->status);
-    plan->last_launches += 7;
+    plan->last_launches = 9;
     plan->last_path = 2;
     return st;
 }

@@ -193,15 +193,15 @@ def test_fused_kernel_gives_up_when_a_peer_never_arrives(cuda, pkg, layer0):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("rows", [1, 4, 33, 100])
+@pytest.mark.parametrize("rows", [1, 4, 33, 100, 300])
 def test_gathered_path_world_one_matches_block(cuda, pkg, layer0, rows):
     """One GPU owning all experts: push into its own window, permutation law over the batch, grouped
     tcgen05 products, result rows placed through the window, combine; both window parities."""
     torch = cuda
     from p92moe_b200 import ep, synth
 
-    window = ep.EpWindow(0, 1, 128)
-    plan = pkg.MoePlan(max_rows=128)
+    window = ep.EpWindow(0, 1, 512)
+    plan = pkg.MoePlan(max_rows=512)
     try:
         for call in range(3):
             x = synth.make_activations(740 + call, 0, rows)
