@@ -133,6 +133,7 @@ __global__ void __launch_bounds__(kRouteThreads) epg_route_kernel(const std::uin
     extern __shared__ std::uint32_t route_smem[];
     std::uint32_t* mask = route_smem;                                   // [local][kMaskWords]
     std::int32_t* expert_pp = reinterpret_cast<std::int32_t*>(route_smem + local * kMaskWords);   // [local]
+    std::int32_t* expert_rows = expert_pp + local;                                                  // [local]
     pdl_wait();
     pdl_launch_dependents();
     const int assignments = tokens * kTop;
@@ -192,6 +193,7 @@ __global__ void __launch_bounds__(kRouteThreads) epg_route_kernel(const std::uin
             for (int w = 0; w < kMaskWords; ++w) count += __popc(mask[le * kMaskWords + w]);
         }
         counts[e] = count;
+        if (le >= 0 && le < local) expert_rows[le] = count;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -207,8 +209,7 @@ __global__ void __launch_bounds__(kRouteThreads) epg_route_kernel(const std::uin
             const int le = e - first_expert;
             if (le < 0 || le >= local) continue;
             expert_pp[le] = pp;
-            int c = 0;
-            for (int w = 0; w < kMaskWords; ++w) c += __popc(mask[le * kMaskWords + w]);
+            const int c = expert_rows[le];
             if (c > 0) {
                 active[slot] = e;
                 tile_prefix[slot] = tiles;
@@ -429,11 +430,11 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
     // routing lists of this GPU's experts (+ its shared-expert rows) from the ids of the whole batch; a token picks
     // an expert at most once, so no expert has more rows than there are tokens
     const int tile_rows = tc_tile_rows(tokens);
-    const std::size_t route_smem = static_cast<std::size_t>(local) * (kMaskWords + 1) * 4;
+    const std::size_t route_smem = static_cast<std::size_t>(local) * (kMaskWords + 2) * 4;
     static bool configured = false;
     if (!configured) {
         st = cudaFuncSetAttribute(epg_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(kExperts * (kMaskWords + 1) * 4));
+                                  static_cast<int>(kExperts * (kMaskWords + 2) * 4));
         if (st != cudaSuccess) return st;
         configured = true;
     }
