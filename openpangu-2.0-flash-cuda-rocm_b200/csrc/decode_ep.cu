@@ -127,46 +127,6 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// A tagged word: the payload and the launch number it belongs to, stored and loaded as one 8-byte access.
-__device__ __forceinline__ void st_tagged(void* p, std::uint32_t payload, std::uint32_t tag) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
-}
-__device__ __forceinline__ uint2 ld_tagged(const void* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint4 ld_tagged_pair(const void* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
-// Bounded polls: false after about a second.
-__device__ __forceinline__ bool poll_tagged(const void* p, std::uint32_t tag, std::uint32_t* payload) {
-    uint2 v = ld_tagged(p);
-    if (v.y != tag) {
-        const std::uint64_t start = global_timer_ns();
-        do {
-            if (global_timer_ns() - start > 1000000000ULL) return false;
-            v = ld_tagged(p);
-        } while (v.y != tag);
-    }
-    *payload = v.x;
-    return true;
-}
-__device__ __forceinline__ bool poll_tagged_pair(const void* p, std::uint32_t tag, std::uint32_t* first, std::uint32_t* second) {
-    uint4 v = ld_tagged_pair(p);
-    if (v.y != tag || v.w != tag) {
-        const std::uint64_t start = global_timer_ns();
-        do {
-            if (global_timer_ns() - start > 1000000000ULL) return false;
-            v = ld_tagged_pair(p);
-        } while (v.y != tag || v.w != tag);
-    }
-    *first = v.x;
-    *second = v.z;
-    return true;
-}
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 __device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned target) {

@@ -40,20 +40,7 @@ struct Regions {
     }
 };
 
-__device__ __forceinline__ void st_tagged(void* p, std::uint32_t payload, std::uint32_t tag) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
-}
-__device__ __forceinline__ uint2 ld_tagged(const void* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint4 ld_tagged_pair(const void* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ bool expired(std::uint64_t start) { return global_timer_ns() - start > 1000000000ULL; }
+__device__ __forceinline__ bool expired(std::uint64_t start) { return poll_expired(start); }
 
 struct Peers {
     std::uint8_t* base[16];        // every GPU's gathered regions

@@ -530,6 +530,8 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
         switch (which) {
             case 0: return launch_tc<0, 16>(plan, plan->map_x[0], p, stream, pdl);
             case 1: return launch_tc<0, 32>(plan, plan->map_x[1], p, stream, pdl);
+            // (128-column tiles were tried here too: one accumulator buffer and three stages then, 377 µs against
+            // 283 µs at T=4096)
             default: return launch_tc<0, 64>(plan, plan->map_x[2], p, stream, pdl);
         }
     }

@@ -86,6 +86,53 @@ __device__ __forceinline__ bool mbar_wait(std::uint32_t bar, std::uint32_t parit
     }
 }
 
+// ---- tagged words ----------------------------------------------------------------
+// Data handed from one block (or one GPU) to another without a barrier or a fence: every word is
+// 8 bytes, {4 bytes of payload, the number of the launch it belongs to}, stored and loaded as ONE
+// access, and the reader polls the word itself until the number is the one it waits for.  The loads
+// carry no memory clobber so that a caller can request many words before looking at the first.
+__device__ __forceinline__ void st_tagged(void* p, std::uint32_t payload, std::uint32_t tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged(const void* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+// Two neighbouring words: (payload, tag, payload, tag).
+__device__ __forceinline__ uint4 ld_tagged_pair(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+// Bounded polls: false after about a second of wall time.
+__device__ __forceinline__ bool poll_expired(std::uint64_t start) { return global_timer_ns() - start > 1000000000ULL; }
+__device__ __forceinline__ bool poll_tagged(const void* p, std::uint32_t tag, std::uint32_t* payload) {
+    uint2 v = ld_tagged(p);
+    if (v.y != tag) {
+        const std::uint64_t start = global_timer_ns();
+        do {
+            if (poll_expired(start)) return false;
+            v = ld_tagged(p);
+        } while (v.y != tag);
+    }
+    *payload = v.x;
+    return true;
+}
+__device__ __forceinline__ bool poll_tagged_pair(const void* p, std::uint32_t tag, std::uint32_t* first, std::uint32_t* second) {
+    uint4 v = ld_tagged_pair(p);
+    if (v.y != tag || v.w != tag) {
+        const std::uint64_t start = global_timer_ns();
+        do {
+            if (poll_expired(start)) return false;
+            v = ld_tagged_pair(p);
+        } while (v.y != tag || v.w != tag);
+    }
+    *first = v.x;
+    *second = v.z;
+    return true;
+}
+
 // ---- TMA ----------------------------------------------------------------------
 // The innermost coordinate x must be a multiple of 16 bytes' worth of elements;
 // every call site passes multiples of 128 bytes.
