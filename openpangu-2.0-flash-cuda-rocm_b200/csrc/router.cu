@@ -152,7 +152,7 @@ __device__ __forceinline__ void async_copy16(std::uint32_t dst_smem, const void*
 }
 
 template <int WT>
-__global__ void __launch_bounds__(64 * WT) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
+__global__ void __launch_bounds__(64 * WT, 3) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
                                                                     const std::uint16_t* __restrict__ w,
                                                                     float* __restrict__ out, int batch_rows, int rows,
                                                                     int columns) {
@@ -171,11 +171,13 @@ __global__ void __launch_bounds__(64 * WT) logits_rows_large_kernel(const std::u
     const int warp = threadIdx.x >> 5;
     const int we = warp % WE, wt = warp / WE;
     const int e0 = blockIdx.x * BE, t0 = blockIdx.y * BT;
-    float acc[TE][TT];
+    // accumulators in pairs of tokens: sm_100 has a two-wide FP32 fused multiply-add (each half an ordinary
+    // round-to-nearest fmaf, so the chains are unchanged), which halves the instructions of the inner product
+    float2 acc[TE][TT / 2];
 #pragma unroll
     for (int i = 0; i < TE; ++i)
 #pragma unroll
-        for (int j = 0; j < TT; ++j) acc[i][j] = 0.0F;
+        for (int j = 0; j < TT / 2; ++j) acc[i][j] = make_float2(0.0F, 0.0F);
 
     // global -> raw image: 48 rows x 32 pieces of 16 bytes, six pieces per thread, consecutive threads on
     // consecutive pieces of a row
@@ -250,9 +252,11 @@ __global__ void __launch_bounds__(64 * WT) logits_rows_large_kernel(const std::u
                 xf[i] = __uint_as_float((jj & 1) ? (word & 0xffff0000U) : (word << 16));
             }
 #pragma unroll
-            for (int i = 0; i < TE; ++i)
+            for (int i = 0; i < TE; ++i) {
+                const float2 w2 = make_float2(wf[i], wf[i]);
 #pragma unroll
-                for (int t = 0; t < TT; ++t) acc[i][t] = fmaf(xf[t], wf[i], acc[i][t]);
+                for (int t = 0; t < TT / 2; ++t) acc[i][t] = __ffma2_rn(make_float2(xf[2 * t], xf[2 * t + 1]), w2, acc[i][t]);
+            }
         }
         buffer ^= 1;
     }
@@ -260,7 +264,7 @@ __global__ void __launch_bounds__(64 * WT) logits_rows_large_kernel(const std::u
     for (int i = 0; i < TE; ++i) {
 #pragma unroll
         for (int t = 0; t < TT; ++t) {
-            float value = acc[i][t];
+            float value = (t & 1) ? acc[i][t / 2].y : acc[i][t / 2].x;
 #pragma unroll
             for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_down_sync(0xffffffffU, value, offset);
             const int e = e0 + we * TE + i;
