@@ -378,7 +378,7 @@ def main() -> None:
         run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps)
         dist.destroy_process_group()
         return
-    decode = args.workload == "decode4x44"
+    decode = args.workload == "decode4x44"       # the fused kernel: any workload of up to 8 rows
     rows = {"decode4x44": 4, "prefill4096": 4096, "ep_prefill16384": 16384, "ep_decode512": 512}[args.workload]
     n_layers = args.layers or (LAYERS if args.workload in ("decode4x44", "ep_decode512") else 1)
     bias_mode, alpha = {"decode4x44": ("normal", 0.0), "prefill4096": ("zipf", 1.2), "ep_prefill16384": ("zero", 0.0),
@@ -473,10 +473,10 @@ def main() -> None:
     pk = peaks()
     if decode:
         # the whole block is one kernel (moe_decode_kernel): its algorithmic bytes are the layer's
-        # (D+1 experts x 3 matrices packed + scales, the router weight, the token rows in and out);
-        # its device time is the event pair recorded around it on the launch stream (stage 0)
-        # duration: the timed region launches exactly one kernel per layer back to back, so the
-        # average launch duration is the CUDA-event step time over the layer count
+        # (D+1 experts x 3 matrices packed + scales, the router weight, the token rows in and out).
+        # The timed region launches exactly one kernel per layer back to back on one stream, so the
+        # average launch duration is the CUDA-event step time over the layer count (an event pair
+        # around every single launch would break the overlap of consecutive launches)
         kernel, k_bytes, k_us = "moe_decode_kernel", layer_bytes, ms_per_step * 1e3 / n_layers
     else:
         # dominant kernel of the multi-kernel path: gate/up + SwiGLU + re-quantise
