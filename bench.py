@@ -486,9 +486,9 @@ def main() -> None:
         k_us = stage_us["gate_up_swiglu"]
     k_gbs = k_bytes / (k_us * 1e-6) / 1e9
     # DRAM traffic per launch: one ncu capture of this kernel (profiles/) measured read + write bytes at
-    # 1.02 x the algorithmic bytes of its launches (decode) / 1.19 x (prefill gate/up); traffic grows with
+    # 1.02 x the algorithmic bytes of its launches (decode) / 1.09 x (prefill gate/up); traffic grows with
     # the experts hit exactly as the algorithmic bytes do, so the ratio is applied to this run's bytes
-    traffic = k_bytes * (1.02 if decode else 1.19)
+    traffic = k_bytes * (1.02 if decode else 1.09)
     roofline = {"bound": "hbm", "kernel": kernel, "achieved": k_gbs, "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": k_gbs / pk["hbm_gbs"], "traffic": traffic,
                 "traffic_source": "ncu capture of a 3-layer case, scaled by algorithmic bytes", "peak_source": pk["source"],
