@@ -42,7 +42,7 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kBlockKBytes = 128;                 // one swizzle row: 256 E2M1 values
 constexpr int kSfSlab = 2048;                     // 128 rows x 16 scales of one K block
-constexpr int kEpilogueWarps = 8;                 // two per TMEM quarter: they split the column chunks
+constexpr int kEpilogueWarps = 16;                // four per TMEM quarter: they split the 16-column chunks
 constexpr int kThreadsTc = 64 + 32 * kEpilogueWarps;
 
 template <int MODE, int N>
@@ -289,8 +289,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        // Eight warps: warp w reads TMEM lanes 32*(w & 3) .. +31 (one output row per lane) and the two
-        // warps of a quarter take alternate 16-column chunks.  A chunk is processed without any
+        // Sixteen warps: warp w reads TMEM lanes 32*(w & 3) .. +31 (one output row per lane) and the four
+        // warps of a quarter take every fourth 16-column chunk.  A chunk is processed without any
         // data-dependent branch so the sixteen per-column dependency chains interleave; only the
         // stores are predicated on the column being a real token.
         const int quarter = warp & 3;
@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                 std::uint8_t* hq_base = p.hq + static_cast<std::size_t>(it.pp0) * (inter / 2) + (row >> 1);
                 const int n_base = it.pp0 & 127;
 #pragma unroll 1
-                for (int c0 = half * 16; c0 < N; c0 += 32) {
+                for (int c0 = half * 16; c0 < N; c0 += 16 * (kEpilogueWarps / 4)) {
                     if (c0 >= it.valid) break;                                    // warp uniform
                     std::uint32_t g[16], u[16];
                     tmem_load16(lane_base + c0, g);
@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                 const int hidden = p.m_total;
                 std::uint16_t* out_base = p.out + static_cast<std::size_t>(it.pp0) * hidden + row;
 #pragma unroll 1
-                for (int c0 = half * 16; c0 < N; c0 += 32) {
+                for (int c0 = half * 16; c0 < N; c0 += 16 * (kEpilogueWarps / 4)) {
                     if (c0 >= it.valid) break;
                     std::uint32_t d[16];
                     tmem_load16(lane_base + c0, d);
@@ -392,6 +392,267 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(accum_empty(buffer));
             if (C::kAccumBuffers == 2) buffer ^= 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// ---- gate/up for large batches: two 64-row token tiles per weight stage ---------------------------
+// At thousands of tokens the gate/up product is bound by L2-to-SM traffic: every 64-row token tile of an
+// expert pulls the expert's 128-row weight tile (36 KB per K block) across again.  Here an item is a PAIR
+// of neighbouring token tiles (one 128-row slab of the padded position space): a weight stage is loaded
+// once and multiplied with both, which halves the weight traffic of experts with more than 64 rows.
+// Each half keeps its own accumulator pair (gate | up, 64 columns each); three such buffers rotate, so
+// the epilogue of one item still overlaps the loads and MMAs of the next.
+struct GuPair {
+    static constexpr int kN = 64;
+    static constexpr int kChunk = 2 * (kTileM * kBlockKBytes + kSfSlab);            // 36,864: one chunk of the bank's stream
+    static constexpr int kOffSfA = 2 * kTileM * kBlockKBytes;
+    static constexpr int kOffB0 = kChunk;
+    static constexpr int kOffB1 = kOffB0 + kN * kBlockKBytes;
+    static constexpr int kOffSfB = kOffB1 + kN * kBlockKBytes;
+    static constexpr int kStageBytes = kOffSfB + kSfSlab;                           // 55,296
+    static constexpr int kStages = 4;
+    static constexpr int kAccumCols = 2 * kN;                                       // gate at +0, up at +64
+    static constexpr int kAccumBuffers = 3;
+    static constexpr int kSfCols = 3 * 16;                                          // SFA gate, SFA up, SFB
+    static constexpr int kTmemCols = 512;                                           // 3 * 128 + 2 * 48 = 480
+    static constexpr int kBarriers = 3 * kStages + 2 * kAccumBuffers;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + 16 + 1024;
+    // the epilogue (SwiGLU + re-quantisation, about 40 instructions per element) is what the issue slots are spent
+    // on: four warps per TMEM quarter, each taking one 16-column chunk of a half
+    static constexpr int kEpilogueWarps = 16;
+    static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+};
+
+__global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(const __grid_constant__ CUtensorMap map_b,
+                                                                        const TcParams p) {
+    using C = GuPair;
+    extern __shared__ std::uint8_t smem_raw[];
+    const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    const std::uint32_t bars = base + C::kStages * C::kStageBytes;
+    auto weight_bar = [&](int s) { return bars + 8U * s; };
+    auto token_bar = [&](int s) { return bars + 8U * (C::kStages + s); };
+    auto empty_bar = [&](int s) { return bars + 8U * (2 * C::kStages + s); };
+    auto accum_full = [&](int b) { return bars + 8U * (3 * C::kStages + b); };
+    auto accum_empty = [&](int b) { return bars + 8U * (3 * C::kStages + C::kAccumBuffers + b); };
+    const std::uint32_t tmem_slot = bars + 8U * C::kBarriers;
+    volatile std::uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile std::uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+    volatile std::uint32_t* abort_ptr = tmem_slot_ptr + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int k_blocks = p.k_bytes / kBlockKBytes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(weight_bar(s), 1);
+            mbar_init(token_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < C::kAccumBuffers; ++b) {
+            mbar_init(accum_full(b), 1);
+            mbar_init(accum_empty(b), C::kEpilogueWarps);
+        }
+        *abort_ptr = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    pdl_wait();                       // routing lists and token rows come from the kernels upstream
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    pdl_launch_dependents();
+    const std::uint32_t tmem_base = *tmem_slot_ptr;
+    const int total_items = p.tile_prefix[*p.route.active_count] * p.m_tiles;       // tile_prefix counts 128-row slabs here
+    auto give_up = [&]() {
+        *abort_ptr = 1;
+        atomicCAS(p.status, kStatusOk, kStatusWaitExpired);
+    };
+
+    if (warp == 0) {
+        if (elect_one()) {
+            int stage = 0;
+            std::uint32_t phase = 0;
+            for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
+                Item it;
+                if (!decode_item<2 * C::kN>(p, item, &it)) continue;
+                const bool two = it.valid > C::kN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(); break; }
+                    const std::uint32_t st = base + stage * C::kStageBytes;
+                    mbar_arrive_expect_tx(weight_bar(stage), C::kChunk);
+                    bulk_load(st, p.bank.g13 + ((static_cast<std::size_t>(it.entry) * p.m_tiles + it.m_tile) * k_blocks + kb) *
+                                                   kChunkBytes,
+                              kChunkBytes, weight_bar(stage));
+                    mbar_arrive_expect_tx(token_bar(stage), (two ? 2 : 1) * C::kN * kBlockKBytes + kSfSlab);
+                    tma_load_2d(st + C::kOffB0, &map_b, token_bar(stage), kb * kBlockKBytes, it.pp0);
+                    if (two) tma_load_2d(st + C::kOffB1, &map_b, token_bar(stage), kb * kBlockKBytes, it.pp0 + C::kN);
+                    bulk_load(st + C::kOffSfB,
+                              p.b_sf + (static_cast<std::size_t>(it.pp0 >> 7) * (p.k_bytes / 32) + kb * 4) * 512, kSfSlab,
+                              token_bar(stage));
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            int stage = 0;
+            std::uint32_t phase = 0;
+            int next_buffer = 0;
+            std::uint32_t accum_phase = 0;                      // bit b = phase of buffer b
+            constexpr std::uint32_t idesc = idesc_nvf4(kTileM, C::kN);
+            const std::uint32_t sf_tmem = tmem_base + C::kAccumBuffers * C::kAccumCols;
+            int sf_buffer = 0;
+            for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
+                Item it;
+                if (!decode_item<2 * C::kN>(p, item, &it)) continue;
+                const int halves = it.valid > C::kN ? 2 : 1;
+                int buffer[2];
+                bool ok = true;
+                for (int h = 0; h < halves && ok; ++h) {
+                    buffer[h] = next_buffer;
+                    next_buffer = (next_buffer + 1) % C::kAccumBuffers;
+                    if (!mbar_wait(accum_empty(buffer[h]), ((accum_phase >> buffer[h]) & 1U) ^ 1U)) { give_up(); ok = false; }
+                }
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(weight_bar(stage), phase) || !mbar_wait(token_bar(stage), phase)) {
+                        give_up();
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const std::uint32_t st = base + stage * C::kStageBytes;
+                    const std::uint32_t sfc = sf_tmem + sf_buffer * C::kSfCols;
+#pragma unroll
+                    for (int o = 0; o < 3; ++o) {
+                        const std::uint32_t slab = o < 2 ? st + C::kOffSfA + o * kSfSlab : st + C::kOffSfB;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) tc_copy_sf(sfc + o * 16 + k * 4, desc_scale_atom(slab + k * 512));
+                    }
+                    for (int h = 0; h < halves; ++h) {
+                        const std::uint32_t accum = tmem_base + buffer[h] * C::kAccumCols;
+                        const std::uint64_t b_desc = desc_k_major_sw128(st + (h == 0 ? C::kOffB0 : C::kOffB1));
+                        // rows 64..127 of the slab are quarters 2 and 3 of its 128-row scale tile: two TMEM columns further
+                        const std::uint32_t b_quarter = h == 0 ? 0U : 2U;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                            for (int a = 0; a < 2; ++a) {
+                                const std::uint64_t a_desc = desc_k_major_sw128(st + a * kTileM * kBlockKBytes);
+                                mma_nvf4(accum + a * C::kN, a_desc + 2 * k, b_desc + 2 * k, idesc, sfc + a * 16 + k * 4,
+                                         sfc + 32 + k * 4 + b_quarter, kb > 0 || k > 0);
+                            }
+                        }
+                    }
+                    tc_commit(empty_bar(stage));
+                    sf_buffer ^= 1;
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
+                }
+                if (!ok) break;
+                for (int h = 0; h < halves; ++h) {
+                    tc_commit(accum_full(buffer[h]));
+                    accum_phase ^= 1U << buffer[h];
+                }
+            }
+        }
+    } else {
+        // epilogue: the code of expert_tc_kernel<0, 64>, once per half of the item
+        const int quarter = warp & 3;
+        const int sub = (warp - 2) >> 2;                  // 0..3: which 16-column chunk of every 64
+        int next_buffer = 0;
+        std::uint32_t accum_phase = 0;
+        for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
+            Item it;
+            if (!decode_item<2 * C::kN>(p, item, &it)) continue;
+            const int halves = it.valid > C::kN ? 2 : 1;
+            const float alpha_g = p.bank.alpha[it.entry * 3 + 0];
+            const float alpha_u = p.bank.alpha[it.entry * 3 + 1];
+            const int inter = p.m_total;
+            const int row = it.m_tile * kTileM + quarter * 32 + lane;
+            const int sf_col = row >> 4;
+            bool ok = true;
+            for (int hh = 0; hh < halves; ++hh) {
+                const int buffer = next_buffer;
+                next_buffer = (next_buffer + 1) % C::kAccumBuffers;
+                if (!mbar_wait(accum_full(buffer), (accum_phase >> buffer) & 1U)) { give_up(); ok = false; break; }
+                accum_phase ^= 1U << buffer;
+                tc_fence_after();
+                const int pp0 = it.pp0 + hh * C::kN;
+                const int valid = hh == 0 ? min(C::kN, it.valid) : it.valid - C::kN;
+                const std::uint32_t lane_base =
+                    tmem_base + buffer * C::kAccumCols + (static_cast<std::uint32_t>(quarter * 32) << 16);
+                std::uint8_t* hs_base = p.hs + (static_cast<std::size_t>(pp0 >> 7) * (inter / 64) + (sf_col >> 2)) * 512 + (sf_col & 3);
+                std::uint8_t* hq_base = p.hq + static_cast<std::size_t>(pp0) * (inter / 2) + (row >> 1);
+                const int n_base = pp0 & 127;
+#pragma unroll 1
+                for (int c0 = sub * 16; c0 < C::kN; c0 += 16 * (C::kEpilogueWarps / 4)) {
+                    if (c0 >= valid) break;                                       // warp uniform
+                    std::uint32_t g[16], u[16];
+                    tmem_load16(lane_base + c0, g);
+                    tmem_load16(lane_base + C::kN + c0, u);
+                    tmem_load_wait();
+                    float h[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[j]) * alpha_g));
+                        const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[j]) * alpha_u));
+                        h[j] = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
+                    }
+                    std::uint32_t packed[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        packed[k] = (__float_as_uint(fabsf(h[2 * k])) >> 16) | (__float_as_uint(fabsf(h[2 * k + 1])) & 0xffff0000U);
+                    }
+#pragma unroll
+                    for (int off = 8; off > 0; off >>= 1) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            const std::uint32_t other = __shfl_xor_sync(0xffffffffU, packed[k], off);
+                            __nv_bfloat162 a2 = *reinterpret_cast<__nv_bfloat162*>(&packed[k]);
+                            const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&other);
+                            a2 = __hmax2(a2, b2);
+                            packed[k] = *reinterpret_cast<std::uint32_t*>(&a2);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float amax = __uint_as_float((j & 1) ? (packed[j >> 1] & 0xffff0000U) : (packed[j >> 1] << 16));
+                        const __nv_fp8_e4m3 scale(amax * (p.quant_scale / 6.0F));
+                        const float decoded = static_cast<float>(scale);
+                        const float multiplier = decoded == 0.0F ? 0.0F : p.quant_scale / decoded;
+                        const float q = h[j] * multiplier;
+                        const float q_next = __shfl_xor_sync(0xffffffffU, q, 1);
+                        const int n = c0 + j;
+                        if (n < valid) {
+                            if ((lane & 1) == 0) {
+                                hq_base[static_cast<std::size_t>(n) * (inter / 2)] =
+                                    static_cast<std::uint8_t>(__nv_fp4x2_e2m1(make_float2(q, q_next)).__x);
+                            }
+                            if ((lane & 15) == 0) {
+                                const int tn = n_base + n;
+                                hs_base[(tn & 31) * 16 + (tn >> 5) * 4] = scale.__x;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accum_empty(buffer));
+            }
+            if (!ok) break;
         }
     }
     tc_fence_before();
@@ -530,9 +791,22 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
         switch (which) {
             case 0: return launch_tc<0, 16>(plan, plan->map_x[0], p, stream, pdl);
             case 1: return launch_tc<0, 32>(plan, plan->map_x[1], p, stream, pdl);
-            // (128-column tiles were tried here too: one accumulator buffer and three stages then, 377 µs against
-            // 283 µs at T=4096)
-            default: return launch_tc<0, 64>(plan, plan->map_x[2], p, stream, pdl);
+            default:
+                if (plan->wide_rows == 128 && std::getenv("P92B_NO_GU_PAIR") == nullptr) {
+                    // large batches: pairs of 64-row token tiles share one weight stage (one 128-column tile was
+                    // tried too: a single accumulator buffer and three stages then, 377 µs against 283 µs at T=4096)
+                    p.tile_prefix = plan->tile_prefix_wide;
+                    static bool configured = false;
+                    if (!configured) {
+                        cudaError_t st = cudaFuncSetAttribute(expert_gu_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                              GuPair::kSmemBytes);
+                        if (st != cudaSuccess) return st;
+                        configured = true;
+                    }
+                    return launch_kernel(expert_gu_pair_kernel, dim3(plan->sm_count), dim3(GuPair::kThreads), GuPair::kSmemBytes,
+                                         stream, pdl, plan->map_x[2], p);
+                }
+                return launch_tc<0, 64>(plan, plan->map_x[2], p, stream, pdl);
         }
     }
     p.b_sf = plan->hs_sw;
