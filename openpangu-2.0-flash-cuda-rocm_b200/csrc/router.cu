@@ -13,6 +13,8 @@
 // Selection is pure comparison with ties to the lower id, which is order
 // independent, so the top-8 itself is free to use a warp-per-token layout.
 #include "p92b_common.cuh"
+
+#include <cstdlib>
 #include "tc_ptx.cuh"
 
 #include <cfloat>
@@ -151,12 +153,12 @@ __device__ __forceinline__ void async_copy16(std::uint32_t dst_smem, const void*
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(bytes) : "memory");
 }
 
-template <int WT>
-__global__ void __launch_bounds__(64 * WT, 3) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
+template <int WT, int TT, int MIN_BLOCKS>
+__global__ void __launch_bounds__(64 * WT, MIN_BLOCKS) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
                                                                     const std::uint16_t* __restrict__ w,
                                                                     float* __restrict__ out, int batch_rows, int rows,
                                                                     int columns) {
-    constexpr int TE = 8, TT = 8, WE = 2, KC = 256;
+    constexpr int TE = 8, WE = 2, KC = 256;
     constexpr int THREADS = 32 * WE * WT;
     constexpr int BE = TE * WE, BT = TT * WT, ROWS = BE + BT;      // staged rows: 16 expert rows + 8 per token warp
     constexpr int ROW_WORDS = 32 * 4 + 4;                           // 512 bytes + 16 bytes of padding
@@ -324,18 +326,16 @@ cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w,
     } else if (batch_rows >= 256 && columns % 256 == 0) {
         // 16 experts x 16 tokens per block of four warps: small blocks, several per SM, so that one block's
         // staging and barrier overlap another's multiply
-        constexpr int WT = 2;
-        dim3 grid((rows + 15) / 16, (batch_rows + 8 * WT - 1) / (8 * WT));
-        constexpr std::size_t smem = 4 * (16 + 8 * WT) * (32 * 4 + 4) * 4;     // raw and transposed images, two of each
-        static bool configured = false;
-        if (!configured) {
-            cudaError_t st = cudaFuncSetAttribute(logits_rows_large_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  static_cast<int>(smem));
+        auto launch_large = [&](auto kernel, int wt, int tt) -> cudaError_t {
+            dim3 grid((rows + 15) / 16, (batch_rows + tt * wt - 1) / (tt * wt));
+            const std::size_t smem = static_cast<std::size_t>(4) * (16 + tt * wt) * (32 * 4 + 4) * 4;   // raw and transposed images, two of each
+            cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
             if (st != cudaSuccess) return st;
-            configured = true;
-        }
-        return launch_kernel(logits_rows_large_kernel<WT>, grid, dim3(64 * WT), smem, stream, pdl, x, w, out, batch_rows, rows,
-                             columns);
+            return launch_kernel(kernel, grid, dim3(64 * wt), smem, stream, pdl, x, w, out, batch_rows, rows, columns);
+        };
+        // (measured at T=4096: this shape 230 µs; eight warps of 8 x 4 outputs, two blocks per SM: 237 µs; four
+        // warps of 8 x 4, four blocks per SM: 291 µs; eight warps of 8 x 8, one block per SM: 296 µs)
+        return launch_large(logits_rows_large_kernel<2, 8, 3>, 2, 8);
     } else {
         constexpr int TE = 8, TT = 8, WE = 2, WT = 4;
         constexpr int KC = 128;
