@@ -140,29 +140,30 @@ __global__ void __launch_bounds__(WE* WT * 32) logits_rows_kernel(
 }
 
 // ---- T > 1 order, large batches ----------------------------------------------
-// Same per-lane chains as above, organised for throughput: a block computes 16 experts x 8*WT tokens,
-// a warp 8 x 8 of them.  K advances in chunks of 256 columns.  A chunk arrives in shared memory by
-// asynchronous 16-byte copies (no registers, issued a whole chunk ahead), is then TRANSPOSED inside
-// shared memory - element (row, column l + 32 j) to [row][l][j] - so that a lane fetches its eight
-// j-values of a row with one 16-byte read, and is multiplied while the next chunk is on its way.
-// Rows of both images are padded by 16 bytes and the threads of a warp handle eight different rows,
-// so neither the 16-byte reads nor the 2-byte transposing stores meet a bank conflict.  One block
-// synchronisation per chunk.  The fmaf order of every chain is still j ascending.
+// Same per-lane chains as above, organised for throughput: a block of four warps computes 16 experts x
+// 16 tokens, a warp 8 x 8 of them.  K advances in chunks of 256 columns that sit TRANSPOSED in shared
+// memory - element (row, column l + 32 j) at [row][l][j] - so that a lane fetches its eight j-values of
+// a row with one 16-byte read.  A chunk arrives by asynchronous 16-byte copies issued a whole chunk ahead
+// (no registers; loading into registers instead left the global latency exposed: 274 µs against 230 µs
+// at T=4096), and is transposed inside shared memory with 16-byte reads, byte permutes and 8-byte
+// stores laid out so that every bank is hit exactly twice per instruction, the minimum for 256 bytes.
+// Two buffers of each image, one block synchronisation per chunk.  The fmaf order of every
+// chain is still j ascending; the multiply uses the two-wide FP32 fused multiply-add of sm_100, each half
+// of which is an ordinary round-to-nearest fmaf.
 __device__ __forceinline__ void async_copy16(std::uint32_t dst_smem, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;          // 0: the 16 bytes are zero-filled
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(bytes) : "memory");
 }
 
-template <int WT, int TT, int MIN_BLOCKS>
-__global__ void __launch_bounds__(64 * WT, MIN_BLOCKS) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
-                                                                    const std::uint16_t* __restrict__ w,
-                                                                    float* __restrict__ out, int batch_rows, int rows,
-                                                                    int columns) {
-    constexpr int TE = 8, WE = 2, KC = 256;
-    constexpr int THREADS = 32 * WE * WT;
-    constexpr int BE = TE * WE, BT = TT * WT, ROWS = BE + BT;      // staged rows: 16 expert rows + 8 per token warp
+template <int MIN_BLOCKS>
+__global__ void __launch_bounds__(128, MIN_BLOCKS) logits_rows_large_kernel(const std::uint16_t* __restrict__ x,
+                                                                           const std::uint16_t* __restrict__ w,
+                                                                           float* __restrict__ out, int batch_rows, int rows,
+                                                                           int columns) {
+    constexpr int TE = 8, TT = 8, WE = 2, WT = 2, KC = 256;
+    constexpr int BE = TE * WE, BT = TT * WT, ROWS = BE + BT;      // 16 expert rows + 16 token rows
     constexpr int ROW_WORDS = 32 * 4 + 4;                           // 512 bytes + 16 bytes of padding
-    constexpr int PASSES = (ROWS / 8) * 2 * 2 / (WE * WT);          // (row group, j half, lane half) per warp
+    static_assert(ROWS == 32, "one transposition unit per thread: 32 rows x 2 j-quads x 2 lane halves = 128 threads");
     extern __shared__ __align__(16) std::uint8_t large_smem[];
     std::uint32_t (*raw)[ROWS][ROW_WORDS] = reinterpret_cast<std::uint32_t (*)[ROWS][ROW_WORDS]>(large_smem);
     std::uint32_t (*tile)[ROWS][ROW_WORDS] =
@@ -173,20 +174,18 @@ __global__ void __launch_bounds__(64 * WT, MIN_BLOCKS) logits_rows_large_kernel(
     const int warp = threadIdx.x >> 5;
     const int we = warp % WE, wt = warp / WE;
     const int e0 = blockIdx.x * BE, t0 = blockIdx.y * BT;
-    // accumulators in pairs of tokens: sm_100 has a two-wide FP32 fused multiply-add (each half an ordinary
-    // round-to-nearest fmaf, so the chains are unchanged), which halves the instructions of the inner product
     float2 acc[TE][TT / 2];
 #pragma unroll
     for (int i = 0; i < TE; ++i)
 #pragma unroll
         for (int j = 0; j < TT / 2; ++j) acc[i][j] = make_float2(0.0F, 0.0F);
 
-    // global -> raw image: 48 rows x 32 pieces of 16 bytes, six pieces per thread, consecutive threads on
-    // consecutive pieces of a row
+    // global -> raw image, asynchronously: 32 rows x 32 pieces of 16 bytes, eight per thread, consecutive
+    // threads on consecutive pieces of a row
     auto fetch = [&](int k0, int buffer) {
 #pragma unroll
-        for (int q = 0; q < ROWS * 32 / THREADS; ++q) {
-            const int idx = threadIdx.x + q * THREADS;
+        for (int q = 0; q < ROWS * 32 / 128; ++q) {
+            const int idx = threadIdx.x + q * 128;
             const int r = idx >> 5, piece = idx & 31;
             const bool is_w = r < BE;
             const int src_row = is_w ? e0 + r : t0 + (r - BE);
@@ -196,28 +195,28 @@ __global__ void __launch_bounds__(64 * WT, MIN_BLOCKS) logits_rows_large_kernel(
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    // raw image -> transposed image.  A lane takes row (group * 8 + lane % 8) and the j value
-    // (half * 4 + lane / 8), and of that j the 16 columns l = 16 * side .. 16 * side + 15.
-    const int r_lo = lane & 7, j_lo = lane >> 3;
+    // raw image -> transposed image.  A thread takes, for one row, four j-values (j = 4q .. 4q+3) of sixteen
+    // neighbouring lanes: eight 16-byte reads, byte permutes, sixteen 8-byte stores whose lanes are spread
+    // over sixteen rows and both j-quads, so every bank is hit exactly twice per instruction.
+    const int s_row = (warp >> 1) * 16 + (lane >> 4) * 8 + (lane & 7);
+    const int s_q = (lane >> 3) & 1;
+    const int s_side = warp & 1;
     auto transpose = [&](int buffer) {
+        const uint4* src = reinterpret_cast<const uint4*>(&raw[buffer][s_row][(128 * s_q + 16 * s_side) / 2]);
+        std::uint32_t* row = &tile[buffer][s_row][0];
 #pragma unroll
-        for (int q = 0; q < PASSES; ++q) {
-            const int combo = warp * PASSES + q;                    // 0 .. 23
-            const int group = combo >> 2, half = (combo >> 1) & 1, side = combo & 1;
-            const int r = group * 8 + r_lo;
-            const int j = half * 4 + j_lo;
-            const uint4* src = reinterpret_cast<const uint4*>(&raw[buffer][r][(32 * j + 16 * side) / 2]);
-            std::uint16_t* row = reinterpret_cast<std::uint16_t*>(&tile[buffer][r][0]);
+        for (int h = 0; h < 2; ++h) {
+            const uint4 p0 = src[h], p1 = src[4 + h], p2 = src[8 + h], p3 = src[12 + h];     // j = 4q .. 4q+3: 64 bytes apart
+            const std::uint32_t words[4][4] = {{p0.x, p0.y, p0.z, p0.w}, {p1.x, p1.y, p1.z, p1.w},
+                                               {p2.x, p2.y, p2.z, p2.w}, {p3.x, p3.y, p3.z, p3.w}};
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint4 piece = src[h];
-                const std::uint32_t words[4] = {piece.x, piece.y, piece.z, piece.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int l = 16 * side + 8 * h + 2 * i;
-                    row[l * 8 + j] = static_cast<std::uint16_t>(words[i] & 0xffffU);
-                    row[(l + 1) * 8 + j] = static_cast<std::uint16_t>(words[i] >> 16);
-                }
+            for (int i = 0; i < 8; ++i) {
+                const unsigned select = (i & 1) ? 0x7632U : 0x5410U;       // the high or the low BF16 of both words
+                const int l = 16 * s_side + 8 * h + i;
+                uint2 v;
+                v.x = __byte_perm(words[0][i >> 1], words[1][i >> 1], select);     // j = 4q, 4q+1
+                v.y = __byte_perm(words[2][i >> 1], words[3][i >> 1], select);     // j = 4q+2, 4q+3
+                *reinterpret_cast<uint2*>(row + l * 4 + 2 * s_q) = v;
             }
         }
     };
@@ -324,18 +323,19 @@ cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w,
         return launch_kernel(kernel, grid, dim3(WE * WT * 32), smem, stream, pdl, x, w, out, batch_rows, rows, columns,
                              columns);
     } else if (batch_rows >= 256 && columns % 256 == 0) {
-        // 16 experts x 16 tokens per block of four warps: small blocks, several per SM, so that one block's
-        // staging and barrier overlap another's multiply
-        auto launch_large = [&](auto kernel, int wt, int tt) -> cudaError_t {
-            dim3 grid((rows + 15) / 16, (batch_rows + tt * wt - 1) / (tt * wt));
-            const std::size_t smem = static_cast<std::size_t>(4) * (16 + tt * wt) * (32 * 4 + 4) * 4;   // raw and transposed images, two of each
-            cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        // 16 experts x 16 tokens per block of four warps.  (Measured at T=4096 with the chunk copied asynchronously
+        // into shared memory and transposed there: 230 µs with this block shape, 237 - 296 µs with three others.)
+        dim3 grid((rows + 15) / 16, (batch_rows + 15) / 16);
+        constexpr std::size_t smem = 4 * 32 * (32 * 4 + 4) * 4;     // raw and transposed images of 32 padded rows, two of each
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t st = cudaFuncSetAttribute(logits_rows_large_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(smem));
             if (st != cudaSuccess) return st;
-            return launch_kernel(kernel, grid, dim3(64 * wt), smem, stream, pdl, x, w, out, batch_rows, rows, columns);
-        };
-        // (measured at T=4096: this shape 230 µs; eight warps of 8 x 4 outputs, two blocks per SM: 237 µs; four
-        // warps of 8 x 4, four blocks per SM: 291 µs; eight warps of 8 x 8, one block per SM: 296 µs)
-        return launch_large(logits_rows_large_kernel<2, 8, 3>, 2, 8);
+            configured = true;
+        }
+        return launch_kernel(logits_rows_large_kernel<3>, grid, dim3(128), smem, stream, pdl, x, w, out, batch_rows, rows,
+                             columns);
     } else {
         constexpr int TE = 8, TT = 8, WE = 2, WT = 4;
         constexpr int KC = 128;
