@@ -145,7 +145,8 @@ __global__ void __launch_bounds__(WE* WT * 32) logits_rows_kernel(
 // memory - element (row, column l + 32 j) at [row][l][j] - so that a lane fetches its eight j-values of
 // a row with one 16-byte read.  A chunk arrives by asynchronous 16-byte copies issued a whole chunk ahead
 // (no registers; loading into registers instead left the global latency exposed: 274 µs against 230 µs
-// at T=4096), and is transposed inside shared memory with 16-byte reads, byte permutes and 8-byte
+// at T=4096; one 512-byte bulk copy of the TMA unit per row was slower too: 242 µs against 199 µs), and is
+// transposed inside shared memory with 16-byte reads, byte permutes and 8-byte
 // stores laid out so that every bank is hit exactly twice per instruction, the minimum for 256 bytes.
 // Two buffers of each image, one block synchronisation per chunk.  The fmaf order of every
 // chain is still j ascending; the multiply uses the two-wide FP32 fused multiply-add of sm_100, each half
