@@ -666,7 +666,8 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
 // Quantises the token rows into the padded position space of the tensor-core
 // kernels: row pp gets the NVFP4 bytes of its token, and the scales go straight
 // into the 128x4-tiled layout (cuda/nvfp4_ops.cu:818-841 and :869-890 in one pass).
-// One warp per (row, slot) assignment or shared row; lane l owns 16-element blocks l, l+32, ...
+// One warp per TOKEN: the row is read and quantised once (lane l owns 16-element blocks l, l+32, ...)
+// and written to the nine places it is needed, its eight routed slots and its shared-expert row.
 __global__ void __launch_bounds__(256) quantize_padded_kernel(const std::uint16_t* __restrict__ x,
                                                               const std::int32_t* __restrict__ pp_of_flat,
                                                               std::uint8_t* __restrict__ xq,
@@ -675,13 +676,17 @@ __global__ void __launch_bounds__(256) quantize_padded_kernel(const std::uint16_
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
-    const int index = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // 0 .. 9*rows
-    if (index >= rows * (kTop + 1)) return;
-    const int token = index < rows * kTop ? index / kTop : index - rows * kTop;
-    const std::size_t pp = static_cast<std::size_t>(pp_of_flat[index]);
+    const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (token >= rows) return;
     const int blocks = hidden / 16;
     const int col_blocks = (blocks + 3) / 4;
-    for (int b = lane; b < blocks; b += 32) {
+    constexpr int kMaxPerLane = 8;                   // hidden <= 4096
+    uint2 packed[kMaxPerLane];
+    std::uint8_t scale_bits[kMaxPerLane];
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+        const int b = lane + 32 * j;
+        if (b >= blocks) break;
         const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(token) * hidden + b * 16);
         const uint4 lo = __ldg(src);
         const uint4 hi = __ldg(src + 1);
@@ -692,11 +697,20 @@ __global__ void __launch_bounds__(256) quantize_padded_kernel(const std::uint16_
             v[2 * i] = __uint_as_float(words[i] << 16);
             v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
         }
-        std::uint8_t scale_bits;
-        const uint2 packed = quantize_block16(v, global_scale, &scale_bits);
-        *reinterpret_cast<uint2*>(xq + pp * (hidden / 2) + b * 8) = packed;
-        const std::size_t at = ((pp >> 7) * col_blocks + (b >> 2)) * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4 + (b & 3);
-        xs[at] = scale_bits;
+        packed[j] = quantize_block16(v, global_scale, &scale_bits[j]);
+    }
+    for (int place = 0; place <= kTop; ++place) {
+        const int index = place < kTop ? token * kTop + place : rows * kTop + token;
+        const std::size_t pp = static_cast<std::size_t>(pp_of_flat[index]);
+        std::uint8_t* row_q = xq + pp * (hidden / 2);
+        std::uint8_t* row_s = xs + (pp >> 7) * col_blocks * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4;
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j) {
+            const int b = lane + 32 * j;
+            if (b >= blocks) break;
+            *reinterpret_cast<uint2*>(row_q + b * 8) = packed[j];
+            row_s[(b >> 2) * 512 + (b & 3)] = scale_bits[j];
+        }
     }
 }
 
@@ -758,7 +772,8 @@ int tc_pad_align(int rows) { (void)rows; return 128; }
 
 cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x, int rows, cudaStream_t stream,
                                    bool pdl) {
-    const int warps = rows * (kTop + 1);
+    if (plan->hidden > 4096) return cudaErrorNotSupported;
+    const int warps = rows;                        // one per token
     return launch_kernel(quantize_padded_kernel, dim3((warps + 7) / 8), dim3(256), 0, stream, pdl, x,
                          static_cast<const std::int32_t*>(plan->pp_of_flat), plan->xq_pp, plan->xs_sw, rows,
                          plan->hidden, 1.0F);
