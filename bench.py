@@ -223,6 +223,23 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
     if not mode:
         mode = "fused" if rows <= ep.FUSED_MAX_ROWS and world * rows <= ep.FUSED_MAX_TOKENS else \
             "gathered" if rows <= ep.GATHERED_MAX_ROWS and world * rows <= ep.GATHERED_MAX_TOKENS else "exact"
+    window = fused_plan = None
+    if mode in ("fused", "gathered"):
+        # one window and one plan serve all layers.  If the windows cannot be mapped into one another (no
+        # inter-process memory handles in this environment), every rank falls back to the NCCL orchestration.
+        ok = 1
+        try:
+            window = ep.EpWindow(rank, world, rows)
+            fused_plan = pkg.MoePlan(max_rows=world * rows)
+        except Exception as exc:                                 # noqa: BLE001 - any failure means "no peer windows"
+            ok = 0
+            if rank == 0:
+                print(f"peer windows unavailable ({exc}); using the NCCL exchange", file=sys.stderr)
+        agreed = torch.tensor([ok], device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed[0]) == 0:
+            window = fused_plan = None
+            mode = "fixed" if rows <= ep.FIXED_MAX_ROWS else "exact"
     banks, routers, states, xs = [], [], [], []
     for l in range(n_layers):
         raw = synth.make_raw_layer(SEED, l)                     # same weights on every rank; keep the shard
@@ -239,10 +256,6 @@ def run_expert_parallel(args, pkg, synth, world, rank, local_rank, warmup, steps
         xs.append(synth.make_activations(SEED + 1000 * (rank + 1), l, rows))
         del raw, entries, shard
     outs = [torch.empty_like(x) for x in xs]
-    window = fused_plan = None
-    if mode in ("fused", "gathered"):
-        window = ep.EpWindow(rank, world, rows)                 # one window and one plan serve all layers
-        fused_plan = pkg.MoePlan(max_rows=world * rows)
     torch.cuda.synchronize()
 
     def forward(l, x, o):
