@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the tensor-core expert
-// kernels use: mbarrier, TMA (tiled and untiled bulk copies, no multicast),
+// kernels use: mbarrier, TMA (tiled and untiled bulk copies, each to one thread block only),
 // tcgen05 (TMEM allocation, block-scaled MMA, SMEM->TMEM scale copies, TMEM
 // loads, commit) and the two shared-memory descriptor forms they need.
 #pragma once
