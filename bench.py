@@ -493,15 +493,15 @@ def main() -> None:
         kernel, k_bytes, k_us = "moe_decode_kernel", layer_bytes, ms_per_step * 1e3 / n_layers
     else:
         # dominant kernel of the multi-kernel path: gate/up + SwiGLU + re-quantise
-        kernel = "expert_tc_kernel<0,64>"
+        kernel = "expert_gu_pair_kernel" if rows > 32 else "expert_tc_kernel<0,N>"
         k_bytes = (d_mean + 1) * 2 * (EXPERT_BYTES // 3) + rows * (HIDDEN // 2 + HIDDEN // 16) + \
             9 * rows * (INTER // 2 + INTER // 16)
         k_us = stage_us["gate_up_swiglu"]
     k_gbs = k_bytes / (k_us * 1e-6) / 1e9
     # DRAM traffic per launch: one ncu capture of this kernel (profiles/) measured read + write bytes at
-    # 1.02 x the algorithmic bytes of its launches (decode) / 1.09 x (prefill gate/up); traffic grows with
+    # 1.02 x the algorithmic bytes of its launches (decode) / 1.12 x (prefill gate/up); traffic grows with
     # the experts hit exactly as the algorithmic bytes do, so the ratio is applied to this run's bytes
-    traffic = k_bytes * (1.02 if decode else 1.09)
+    traffic = k_bytes * (1.02 if decode else 1.12)
     roofline = {"bound": "hbm", "kernel": kernel, "achieved": k_gbs, "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": k_gbs / pk["hbm_gbs"], "traffic": traffic,
                 "traffic_source": "ncu capture of a 3-layer case, scaled by algorithmic bytes", "peak_source": pk["source"],
