@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """MoE-layer throughput benchmark (tokens/s) with roofline and CPU baseline.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode4x44|prefill4096]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode4x44|prefill4096|ep_prefill16384|ep_decode512]
     python bench.py --impl reference ...     # the CPU restatement of the reference's path
 
 One "step" is one pass of the MoE block over one batch of synthetic tokens:
@@ -9,6 +9,12 @@ One "step" is one pass of the MoE block over one batch of synthetic tokens:
                (layers 2..45), an independent weight set per layer (55 GB resident), so
                nothing a step touches is L2-resident when it is touched again.
   prefill4096: T=4096 tokens through one MoE layer, Zipf(1.2)-skewed routing.
+  ep_prefill16384, ep_decode512: the expert-parallel configurations (T=16384 x 1 layer, uniform routing;
+               T=512 x 44 layers, Zipf(1.0)); on one GPU they run the single-GPU block at that size.
+Under torchrun (N > 1, one rank per GPU) the step is expert-parallel: 256/N experts per GPU, every GPU home to
+its own tokens (decode: 4 per GPU, weak scaling; the others split their T over the GPUs).  Small batches take
+the kernels that do their own exchanges over NVLink, large ones NCCL all-to-alls; P92B_EP_EXCHANGE=
+fused|gathered|fixed|exact overrides the choice.
 Rank 0 prints ONE JSON line.  `value` is device-timed with inputs resident in HBM; `e2e` is
 the same metric through the host-buffer C-ABI call, host<->device copies inside the timed region.
 """
