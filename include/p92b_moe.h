@@ -83,6 +83,12 @@ int p92b_nvfp4_swizzle_scales(const uint8_t* linear, uint8_t* swizzled, int rows
 int p92b_nvfp4_pack_weight(const uint16_t* input, uint8_t* packed, uint8_t* scales, size_t elements,
                            float* weight_scale_2, void* stream);
 
+/* The same for `matrices` equally sized tensors stored back to back (what a loader that quantises a
+ * whole layer does, the per-tensor loop of cuda/nvfp4_pack.cu:235-262): per-tensor amax and scale, three launches
+ * for the batch.  weight_scale_2[matrices]. */
+int p92b_nvfp4_pack_weight_batch(const uint16_t* input, uint8_t* packed, uint8_t* scales, size_t elements_per_matrix,
+                                 int matrices, float* weight_scale_2, void* stream);
+
 /* p92::cuda::swiglu (include/p92/kernels.h:100-104; cuda/nvfp4_ops.cu:97-105,948-956). */
 int p92b_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* output, int elements, void* stream);
 
@@ -134,6 +140,17 @@ int p92b_moe_permute(p92b_plan* plan, const int32_t* expert_ids, int assignments
 #define P92B_STATIC_PERMUTE_SCRATCH_BYTES (P92B_STATIC_PERMUTE_MAX_ASSIGNMENTS / 256 * 256 * 4 + 256)
 int p92b_moe_permute_static(const int32_t* expert_ids, int assignments, int32_t* order, int32_t* position,
                             int32_t* counts, int32_t* offsets, void* stream);
+/* Status of the p92b_moe_permute_static calls made so far on `stream` of the current device (no
+ * counterpart in the reference).  An expert id outside 0..255 does not fault: it is counted as
+ * expert 0 or 255 and the call records 1 in a status word that sits in the same built-in array,
+ * out of the caller's reach; a caller without a plan has no p92b_plan_get_views to read it through.
+ * This copies the word of the most recent call into *host_status (0 = every id was in range) and
+ * synchronises `stream`; it allocates nothing either.  Each permutation call clears the word when it
+ * starts, so ask before issuing the next one.
+ * Host threads: the first call on a device by either entry point looks the array up; two threads
+ * doing that at once is harmless, but their kernels would share the array, so they must be
+ * serialised all the same. */
+int p92b_moe_permute_static_status(int32_t* host_status, void* stream);
 
 /* ---- expert bank --------------------------------------------------------- */
 

@@ -71,12 +71,14 @@ SIGNATURES = {
     "p92b_nvfp4_swizzled_scale_bytes": (c_size_t, [c_int, c_int]),
     "p92b_nvfp4_swizzle_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "p92b_nvfp4_pack_weight": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "p92b_nvfp4_pack_weight_batch": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p, c_void_p]),
     "p92b_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "p92b_expert_combine_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "p92b_add_inplace": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_moe_permute": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "p92b_moe_permute_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "p92b_moe_permute_static_status": (c_int, [ctypes.POINTER(c_int), c_void_p]),
     "p92b_ep_row_bytes": (c_size_t, [c_int]),
     "p92b_ep_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p]),
     "p92b_ep_experts": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
@@ -208,6 +210,14 @@ def nvfp4_pack_weight(input, packed, scales, weight_scale_2) -> None:
                                                  _ptr(weight_scale_2), _stream()), "nvfp4_pack_weight")
 
 
+def nvfp4_pack_weight_batch(input, packed, scales, weight_scale_2) -> None:
+    """input BF16 [matrices, elements]: every matrix quantised with its own per-tensor scale."""
+    matrices = input.shape[0]
+    _check(load_library().p92b_nvfp4_pack_weight_batch(_ptr(input), _ptr(packed), _ptr(scales),
+                                                       input.numel() // matrices, matrices, _ptr(weight_scale_2),
+                                                       _stream()), "nvfp4_pack_weight_batch")
+
+
 def swiglu(gate, up, output, elements: int) -> None:
     _check(load_library().p92b_swiglu(_ptr(gate), _ptr(up), _ptr(output), elements, _stream()), "swiglu")
 
@@ -233,6 +243,14 @@ def moe_permute_static(expert_ids, order, position, counts, offsets) -> None:
     capture."""
     _check(load_library().p92b_moe_permute_static(_ptr(expert_ids), expert_ids.numel(), _ptr(order), _ptr(position),
                                                   _ptr(counts), _ptr(offsets), _stream()), "moe_permute_static")
+
+
+def moe_permute_static_status() -> int:
+    """Status word of the last moe_permute_static call on the current stream: 0, or 1 if an expert id
+    outside 0..255 was met (and counted as expert 0 or 255).  Synchronises the stream; allocates nothing."""
+    word = c_int(-1)
+    _check(load_library().p92b_moe_permute_static_status(ctypes.byref(word), _stream()), "moe_permute_static_status")
+    return int(word.value)
 
 
 class ExpertBank:

@@ -914,17 +914,8 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const bool wide = window->world * window->rows_per_gpu > 16 || std::getenv("P92B_EP_WIDE") != nullptr;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t st = cudaFuncSetAttribute(moe_decode_ep_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              StageLayout<16>::kSmem);
-        if (st == cudaSuccess) {
-            st = cudaFuncSetAttribute(moe_decode_ep_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      StageLayout<32>::kSmem);
-        }
-        if (st != cudaSuccess) return st;
-        configured = true;
-    }
+    if (cudaError_t st = ensure_dynamic_smem<moe_decode_ep_kernel<16>>(StageLayout<16>::kSmem); st != cudaSuccess) return st;
+    if (cudaError_t st = ensure_dynamic_smem<moe_decode_ep_kernel<32>>(StageLayout<32>::kSmem); st != cudaSuccess) return st;
     EpParams p {};
     p.bank = bank->view;
     p.x = input;

@@ -786,12 +786,7 @@ cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std
         plan->intermediate != 1024) {
         return cudaErrorNotSupported;
     }
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t st = cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMegaSmem);
-        if (st != cudaSuccess) return st;
-        configured = true;
-    }
+    if (cudaError_t st = ensure_dynamic_smem<moe_decode_kernel>(kMegaSmem); st != cudaSuccess) return st;
     MegaParams p {};
     p.bank = bank->view;
     p.x = x;

@@ -60,8 +60,54 @@ __global__ void __launch_bounds__(256) amax_kernel(const std::uint16_t* __restri
 }
 
 // cuda/nvfp4_pack.cu:255: weight_scale_2 = amax / (6 * 448).
-__global__ void weight_scale_kernel(const unsigned* maximum, float* weight_scale_2) {
-    *weight_scale_2 = __fdiv_rn(__uint_as_float(*maximum), 6.0F * 448.0F);
+__global__ void weight_scale_kernel(const unsigned* maximum, float* weight_scale_2, int matrices) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m < matrices) weight_scale_2[m] = __fdiv_rn(__uint_as_float(maximum[m]), 6.0F * 448.0F);
+}
+
+// The two kernels above for a batch of equally sized matrices stored back to back: blockIdx.y = matrix.
+__global__ void __launch_bounds__(256) amax_batch_kernel(const std::uint16_t* __restrict__ input, std::size_t elements,
+                                                         unsigned* maximum) {
+    unsigned local = 0;
+    const std::size_t vectors = elements / 8;
+    const uint4* src = reinterpret_cast<const uint4*>(input + static_cast<std::size_t>(blockIdx.y) * elements);
+    for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vectors;
+         i += static_cast<std::size_t>(gridDim.x) * blockDim.x) {
+        const uint4 v = src[i];
+        const std::uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            local = max(local, (words[k] << 16) & 0x7fffffffU);
+            local = max(local, words[k] & 0x7fff0000U);
+        }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) local = max(local, __shfl_xor_sync(0xffffffffU, local, offset));
+    if ((threadIdx.x & 31) == 0 && local != 0) atomicMax(maximum + blockIdx.y, local);
+}
+
+__global__ void __launch_bounds__(256) quantize_batch_kernel(const std::uint16_t* __restrict__ input,
+                                                             std::uint8_t* __restrict__ output,
+                                                             std::uint8_t* __restrict__ scales, long groups_per_matrix,
+                                                             const float* __restrict__ weight_scale_2) {
+    const long local_group = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (local_group >= groups_per_matrix) return;
+    const long group = static_cast<long>(blockIdx.y) * groups_per_matrix + local_group;
+    const float global_scale = __fdiv_rn(1.0F, weight_scale_2[blockIdx.y]);
+    const uint4* src = reinterpret_cast<const uint4*>(input + group * 16);
+    const uint4 a = src[0];
+    const uint4 b = src[1];
+    const std::uint32_t words[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __uint_as_float(words[i] << 16);
+        v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+    }
+    std::uint8_t scale_bits;
+    const uint2 packed = quantize_block16(v, global_scale, &scale_bits);
+    *reinterpret_cast<uint2*>(output + group * 8) = packed;
+    scales[group] = scale_bits;
 }
 
 // cuda/nvfp4_ops.cu:869-890: linear [row][K/16] -> 128-row x 4-column tiles.
@@ -183,11 +229,10 @@ __global__ void __launch_bounds__(256) combine_shared_kernel(const std::uint16_t
 
 // Row-major packed weights + tiled scales of one matrix -> the chunk stream (see BankView).
 // One thread per 16 bytes: first the weight pieces, then the scale bytes.
-__global__ void __launch_bounds__(256) retile_kernel(const std::uint8_t* __restrict__ weight,
-                                                     const std::uint8_t* __restrict__ scales,
-                                                     std::uint8_t* __restrict__ chunks, int rows, int k_bytes,
-                                                     int blocks_per_chunk, int slot) {
-    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+__device__ __forceinline__ void retile_piece(const std::uint8_t* __restrict__ weight,
+                                             const std::uint8_t* __restrict__ scales,
+                                             std::uint8_t* __restrict__ chunks, long index, int rows, int k_bytes,
+                                             int blocks_per_chunk, int slot) {
     const int pieces_per_row = k_bytes / 16;
     const int k_blocks = k_bytes / 128;
     const int chunks_per_tile = k_blocks / blocks_per_chunk;
@@ -219,6 +264,20 @@ __global__ void __launch_bounds__(256) retile_kernel(const std::uint8_t* __restr
     *reinterpret_cast<uint4*>(chunks + chunk * kChunkBytes + kChunkScaleOffset + which * kChunkScaleBytes + within * 16) = v;
 }
 
+// All entries of one kind in one launch: blockIdx.y = entry, the matrix pointers come from the
+// caller's table of reference-format projections (entry * 3 + kind), uploaded once.
+__global__ void __launch_bounds__(256) retile_table_kernel(const p92b_expert_projection* __restrict__ table, int kind,
+                                                           std::uint8_t* __restrict__ chunks, std::size_t entry_bytes,
+                                                           int rows, int k_bytes, int blocks_per_chunk, int slot,
+                                                           float* __restrict__ alpha) {
+    const int entry = blockIdx.y;
+    const p92b_expert_projection src = table[entry * 3 + kind];
+    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index == 0) alpha[entry * 3 + kind] = *src.alpha;
+    retile_piece(src.weight, src.scales_swizzled, chunks + static_cast<std::size_t>(entry) * entry_bytes, index, rows,
+                 k_bytes, blocks_per_chunk, slot);
+}
+
 inline unsigned blocks_for(long n, int per_block) { return static_cast<unsigned>((n + per_block - 1) / per_block); }
 
 }  // namespace
@@ -238,12 +297,14 @@ cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t
                          output, rows, hidden);
 }
 
-cudaError_t launch_retile(const std::uint8_t* weight, const std::uint8_t* scales_swizzled, std::uint8_t* chunks,
-                          int rows, int k_bytes, int blocks_per_chunk, int slot, cudaStream_t stream) {
+cudaError_t launch_retile_table(const p92b_expert_projection* device_table, int entries, int kind, std::uint8_t* chunks,
+                                std::size_t entry_bytes, int rows, int k_bytes, int blocks_per_chunk, int slot,
+                                float* alpha, cudaStream_t stream) {
     const long threads = static_cast<long>(rows) * (k_bytes / 16) +
                          static_cast<long>(rows / 128) * (k_bytes / 128) * (kChunkScaleBytes / 16);
-    retile_kernel<<<blocks_for(threads, 256), 256, 0, stream>>>(weight, scales_swizzled, chunks, rows, k_bytes,
-                                                               blocks_per_chunk, slot);
+    retile_table_kernel<<<dim3(blocks_for(threads, 256), entries), 256, 0, stream>>>(device_table, kind, chunks, entry_bytes,
+                                                                                      rows, k_bytes, blocks_per_chunk, slot,
+                                                                                      alpha);
     return cudaGetLastError();
 }
 
@@ -297,9 +358,29 @@ int p92b_nvfp4_pack_weight(const uint16_t* input, uint8_t* packed, uint8_t* scal
     if (st != cudaSuccess) return st;
     const unsigned blocks = static_cast<unsigned>(std::min<size_t>((elements / 8 + 255) / 256, 148 * 16));
     amax_kernel<<<blocks, 256, 0, s>>>(input, elements, reinterpret_cast<unsigned*>(weight_scale_2));
-    weight_scale_kernel<<<1, 1, 0, s>>>(reinterpret_cast<const unsigned*>(weight_scale_2), weight_scale_2);
+    weight_scale_kernel<<<1, 32, 0, s>>>(reinterpret_cast<const unsigned*>(weight_scale_2), weight_scale_2, 1);
     const long groups = static_cast<long>(elements / 16);
     quantize_kernel<<<blocks_for(groups, 256), 256, 0, s>>>(input, packed, scales, groups, 0.0F, weight_scale_2);
+    return cudaGetLastError();
+}
+
+int p92b_nvfp4_pack_weight_batch(const uint16_t* input, uint8_t* packed, uint8_t* scales, size_t elements_per_matrix,
+                                 int matrices, float* weight_scale_2, void* stream) {
+    if (input == nullptr || packed == nullptr || scales == nullptr || weight_scale_2 == nullptr || matrices <= 0 ||
+        matrices > 65535 || elements_per_matrix == 0 || elements_per_matrix % 16 != 0) {
+        return cudaErrorInvalidValue;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t st = cudaMemsetAsync(weight_scale_2, 0, sizeof(float) * matrices, s);
+    if (st != cudaSuccess) return st;
+    const unsigned blocks = static_cast<unsigned>(std::min<size_t>((elements_per_matrix / 8 + 255) / 256, 64));
+    amax_batch_kernel<<<dim3(blocks, matrices), 256, 0, s>>>(input, elements_per_matrix,
+                                                              reinterpret_cast<unsigned*>(weight_scale_2));
+    weight_scale_kernel<<<(matrices + 255) / 256, 256, 0, s>>>(reinterpret_cast<const unsigned*>(weight_scale_2),
+                                                                weight_scale_2, matrices);
+    const long groups = static_cast<long>(elements_per_matrix / 16);
+    quantize_batch_kernel<<<dim3(blocks_for(groups, 256), matrices), 256, 0, s>>>(input, packed, scales, groups,
+                                                                                   weight_scale_2);
     return cudaGetLastError();
 }
 

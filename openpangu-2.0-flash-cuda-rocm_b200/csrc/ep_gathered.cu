@@ -418,13 +418,8 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
     // an expert at most once, so no expert has more rows than there are tokens
     const int tile_rows = tc_tile_rows(tokens);
     const std::size_t route_smem = static_cast<std::size_t>(local) * (kMaskWords + 2) * 4;
-    static bool configured = false;
-    if (!configured) {
-        st = cudaFuncSetAttribute(epg_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(kExperts * (kMaskWords + 2) * 4));
-        if (st != cudaSuccess) return st;
-        configured = true;
-    }
+    st = ensure_dynamic_smem<epg_route_kernel>(static_cast<int>(kExperts * (kMaskWords + 2) * 4));
+    if (st != cudaSuccess) return st;
     st = launch_kernel(epg_route_kernel, dim3(1), dim3(kRouteThreads), route_smem, stream, pdl, my_arrive, tokens,
                        bank->view.first_expert, local, rows, tile_rows, tag, plan->counts, plan->pp_off, plan->active,
                        plan->active_count, plan->tile_prefix, plan->pp_of_flat, plan->status);

@@ -736,12 +736,7 @@ cudaError_t launch_tc(const p92b_plan* plan, const CUtensorMap& map_b, const TcP
                       bool pdl) {
     using C = Tc<MODE, N>;
     auto kernel = expert_tc_kernel<MODE, N>;
-    static bool configured = false;          // once per process: not a stream operation
-    if (!configured) {
-        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        if (st != cudaSuccess) return st;
-        configured = true;
-    }
+    if (cudaError_t st = ensure_dynamic_smem<expert_tc_kernel<MODE, N>>(C::kSmemBytes); st != cudaSuccess) return st;
     return launch_kernel(kernel, dim3(plan->sm_count), dim3(kThreadsTc), C::kSmemBytes, stream, pdl, map_b, p);
 }
 
@@ -811,13 +806,7 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
                     // large batches: pairs of 64-row token tiles share one weight stage (one 128-column tile was
                     // tried too: a single accumulator buffer and three stages then, 377 µs against 283 µs at T=4096)
                     p.tile_prefix = plan->tile_prefix_wide;
-                    static bool configured = false;
-                    if (!configured) {
-                        cudaError_t st = cudaFuncSetAttribute(expert_gu_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                              GuPair::kSmemBytes);
-                        if (st != cudaSuccess) return st;
-                        configured = true;
-                    }
+                    if (cudaError_t st = ensure_dynamic_smem<expert_gu_pair_kernel>(GuPair::kSmemBytes); st != cudaSuccess) return st;
                     return launch_kernel(expert_gu_pair_kernel, dim3(plan->sm_count), dim3(GuPair::kThreads), GuPair::kSmemBytes,
                                          stream, pdl, plan->map_x[2], p);
                 }

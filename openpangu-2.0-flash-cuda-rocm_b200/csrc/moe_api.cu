@@ -111,43 +111,47 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
     const std::size_t dn_sf = static_cast<std::size_t>(hidden) * (intermediate / 16);
     const std::size_t g13_entry = static_cast<std::size_t>(intermediate / 128) * (hidden / 256) * kChunkBytes;
     const std::size_t g2_entry = static_cast<std::size_t>(hidden / 128) * (intermediate / 512) * kChunkBytes;
+    p92b_expert_projection* device_table = nullptr;
 #define BANK_TRY(call)            \
     do {                          \
         st = (call);              \
         if (st != cudaSuccess) {  \
+            cudaFree(device_table); \
             cudaFree(bank->storage); \
             delete bank;          \
             return st;            \
         }                         \
     } while (0)
-    for (int e = 0; e < entries; ++e) {
-        for (int kind = 0; kind < 3; ++kind) {
-            const p92b_expert_projection& src = host_entries[e * 3 + kind];
-            if (kind < 2) {
-                BANK_TRY(launch_retile(src.weight, src.scales_swizzled, g13 + static_cast<std::size_t>(e) * g13_entry,
-                                       intermediate, hidden / 2, 1, kind, stream));
-                if (stream_copy) {
+    // the caller's table goes to the device once; three launches (one per matrix kind) then retile every
+    // entry and pick up its alpha, instead of a launch and a copy per matrix
+    const std::size_t table_bytes = static_cast<std::size_t>(entries) * 3 * sizeof(p92b_expert_projection);
+    BANK_TRY(cudaMalloc(&device_table, table_bytes));
+    BANK_TRY(cudaMemcpyAsync(device_table, host_entries, table_bytes, cudaMemcpyHostToDevice, stream));
+    BANK_TRY(launch_retile_table(device_table, entries, 0, g13, g13_entry, intermediate, hidden / 2, 1, 0, alpha, stream));
+    BANK_TRY(launch_retile_table(device_table, entries, 1, g13, g13_entry, intermediate, hidden / 2, 1, 1, alpha, stream));
+    BANK_TRY(launch_retile_table(device_table, entries, 2, g2, g2_entry, hidden, intermediate / 2, 2, 0, alpha, stream));
+    if (stream_copy) {
+        for (int e = 0; e < entries; ++e) {
+            for (int kind = 0; kind < 3; ++kind) {
+                const p92b_expert_projection& src = host_entries[e * 3 + kind];
+                if (kind < 2) {
                     BANK_TRY(cudaMemcpyAsync(w13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_bytes, src.weight,
                                              gu_bytes, cudaMemcpyDeviceToDevice, stream));
                     BANK_TRY(launch_unswizzle(src.scales_swizzled,
                                               sf13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_sf, intermediate,
                                               hidden / 16, stream));
-                }
-            } else {
-                BANK_TRY(launch_retile(src.weight, src.scales_swizzled, g2 + static_cast<std::size_t>(e) * g2_entry,
-                                       hidden, intermediate / 2, 2, 0, stream));
-                if (stream_copy) {
+                } else {
                     BANK_TRY(cudaMemcpyAsync(w2 + static_cast<std::size_t>(e) * dn_bytes, src.weight, dn_bytes,
                                              cudaMemcpyDeviceToDevice, stream));
                     BANK_TRY(launch_unswizzle(src.scales_swizzled, sf2 + static_cast<std::size_t>(e) * dn_sf, hidden,
                                               intermediate / 16, stream));
                 }
             }
-            BANK_TRY(cudaMemcpyAsync(alpha + e * 3 + kind, src.alpha, sizeof(float), cudaMemcpyDeviceToDevice, stream));
         }
     }
     BANK_TRY(cudaStreamSynchronize(stream));
 #undef BANK_TRY
+    cudaFree(device_table);
     bank->view.g13 = g13;
     bank->view.g2 = g2;
     bank->view.w13 = w13;

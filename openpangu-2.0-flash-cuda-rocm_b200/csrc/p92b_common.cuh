@@ -326,6 +326,24 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, std::
     return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 
+// Opt-in to more than 48 KB of dynamic shared memory.  The attribute belongs to the (kernel, device)
+// pair, not to the process: a host that drives several GPUs from one process has to set it once on
+// each of them, so the "already done" flag is kept per device (one table per kernel through the
+// non-type template parameter).
+constexpr int kMaxDevices = 64;
+template <auto Kernel>
+cudaError_t ensure_dynamic_smem(int bytes) {
+    static bool configured[kMaxDevices] = {};
+    int device = 0;
+    cudaError_t st = cudaGetDevice(&device);
+    if (st != cudaSuccess) return st;
+    const bool tracked = device >= 0 && device < kMaxDevices;
+    if (tracked && configured[device]) return cudaSuccess;
+    st = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (st == cudaSuccess && tracked) configured[device] = true;
+    return st;
+}
+
 // kernel launchers (defined across the .cu files)
 cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w, float* out,
                                  int batch_rows, int rows, int columns, bool gemv_order,
@@ -352,10 +370,12 @@ cudaError_t launch_down(const p92b_plan* plan, const BankView& bank, const Route
                         cudaStream_t stream);
 cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,
                              cudaStream_t stream);
-// Writes one matrix (row-major packed weights + 128x4-tiled scales) into the chunk stream.
+// Writes the matrices of one kind (0/1/2 = gate/up/down) of all `entries` of a table of reference-format
+// projections (device copy, entry * 3 + kind) into the chunk stream, and their alpha values.
 // blocks_per_chunk 1: gate (slot 0) or up (slot 1) of a K block; 2: K blocks 2s, 2s+1 of a down matrix.
-cudaError_t launch_retile(const std::uint8_t* weight, const std::uint8_t* scales_swizzled, std::uint8_t* chunks,
-                          int rows, int k_bytes, int blocks_per_chunk, int slot, cudaStream_t stream);
+cudaError_t launch_retile_table(const p92b_expert_projection* device_table, int entries, int kind, std::uint8_t* chunks,
+                                std::size_t entry_bytes, int rows, int k_bytes, int blocks_per_chunk, int slot,
+                                float* alpha, cudaStream_t stream);
 cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* mixed_index,
                                   const float* route_weights, std::uint16_t* output, int rows,
                                   int hidden, cudaStream_t stream, bool pdl = false);

@@ -447,6 +447,11 @@ cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignm
 // address, so the address is fetched once per device with cudaGetSymbolAddress
 // (that device current) and handed to the kernels as an ordinary pointer.
 // Layout: [chunks][256] int32 chunk histograms, then the status word.
+//
+// The address cache below is filled on first use per device.  Two host threads that make their
+// first call on the same device at the same time both look the address up and both store the
+// same value: harmless, but the kernels of their calls would still share the one array, so such
+// calls have to be serialised by the caller for that reason anyway.
 // ---------------------------------------------------------------------------
 namespace {
 
@@ -523,3 +528,18 @@ extern "C" int p92b_moe_permute_static(const int32_t* expert_ids, int assignment
     return cudaGetLastError();
 }
 
+// The status word of the calls above lives in the same built-in array, where a caller cannot
+// reach it; this copies it out.  Like the permutation itself it allocates nothing: one
+// cudaMemcpyAsync into the caller's host word, then a synchronisation of `stream`.
+extern "C" int p92b_moe_permute_static_status(int32_t* host_status, void* stream_) {
+    using namespace p92b;
+    if (host_status == nullptr) return cudaErrorInvalidValue;
+    std::int32_t* scratch = nullptr;
+    cudaError_t st = static_scratch(&scratch);
+    if (st != cudaSuccess) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    st = cudaMemcpyAsync(host_status, scratch + kStaticChunks * kExperts, sizeof(std::int32_t), cudaMemcpyDeviceToHost,
+                         stream);
+    if (st != cudaSuccess) return st;
+    return cudaStreamSynchronize(stream);
+}

@@ -314,12 +314,7 @@ cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w,
         const std::size_t smem = static_cast<std::size_t>(TE * WE + TT * WT) * columns * 2;
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
         auto kernel = logits_rows_kernel<TE, TT, WE, WT>;
-        static bool configured = false;
-        if (!configured) {
-            cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            if (st != cudaSuccess) return st;
-            configured = true;
-        }
+        if (cudaError_t st = ensure_dynamic_smem<logits_rows_kernel<TE, TT, WE, WT>>(200 * 1024); st != cudaSuccess) return st;
         dim3 grid((rows + TE * WE - 1) / (TE * WE), 1);
         return launch_kernel(kernel, grid, dim3(WE * WT * 32), smem, stream, pdl, x, w, out, batch_rows, rows, columns,
                              columns);
@@ -328,13 +323,7 @@ cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w,
         // into shared memory and transposed there: 230 µs with this block shape, 237 - 296 µs with three others.)
         dim3 grid((rows + 15) / 16, (batch_rows + 15) / 16);
         constexpr std::size_t smem = 4 * 32 * (32 * 4 + 4) * 4;     // raw and transposed images of 32 padded rows, two of each
-        static bool configured = false;
-        if (!configured) {
-            cudaError_t st = cudaFuncSetAttribute(logits_rows_large_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  static_cast<int>(smem));
-            if (st != cudaSuccess) return st;
-            configured = true;
-        }
+        if (cudaError_t st = ensure_dynamic_smem<logits_rows_large_kernel<3>>(static_cast<int>(smem)); st != cudaSuccess) return st;
         return launch_kernel(logits_rows_large_kernel<3>, grid, dim3(128), smem, stream, pdl, x, w, out, batch_rows, rows,
                              columns);
     } else {

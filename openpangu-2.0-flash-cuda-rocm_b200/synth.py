@@ -17,7 +17,7 @@ from typing import Optional
 
 import torch
 
-from . import (EXPERTS, HIDDEN, INTERMEDIATE, TOP_K, ExpertBank, nvfp4_pack_weight,
+from . import (EXPERTS, HIDDEN, INTERMEDIATE, TOP_K, ExpertBank, nvfp4_pack_weight, nvfp4_pack_weight_batch,
                nvfp4_swizzle_scales, nvfp4_swizzled_scale_bytes)
 
 MATRIX_BYTES = INTERMEDIATE * HIDDEN // 2      # gate, up and down all pack to 1,310,720 bytes
@@ -64,6 +64,33 @@ def make_raw_layer(seed: int, layer: int, experts: int = EXPERTS, hidden: int = 
         assert nvfp4_swizzled_scale_bytes(rows, cols // 16) == sbytes
         nvfp4_swizzle_scales(linear[i], swizzled[i], rows, cols // 16)
     return RawLayer(packed, linear, swizzled, alpha)
+
+
+def make_raw_layer_batched(seed: int, layer: int, experts: int = EXPERTS, hidden: int = HIDDEN,
+                           intermediate: int = INTERMEDIATE, std: float = 0.02) -> RawLayer:
+    """The same distributions as make_raw_layer in a dozen launches instead of several thousand: all
+    matrices of the layer are drawn by one call of the generator (so the bytes differ from
+    make_raw_layer's for the same seed), quantised by the batched weight quantiser, and their scales
+    tiled per matrix shape (equally shaped matrices stored back to back tile like one tall matrix,
+    because every matrix has a multiple of 128 rows).  Used where set-up time matters: the smoke test
+    and the benchmark's 44 layers."""
+    n = experts + 1
+    elements = intermediate * hidden
+    g = _generator(seed, layer, 4)
+    w = torch.empty((3 * n, elements), dtype=torch.bfloat16, device="cuda").normal_(0.0, std, generator=g)   # [kind][entry]
+    packed = torch.empty((3 * n, elements // 2), dtype=torch.uint8, device="cuda")
+    linear = torch.empty((3 * n, elements // 16), dtype=torch.uint8, device="cuda")
+    swizzled = torch.empty_like(linear)
+    alpha = torch.empty(3 * n, dtype=torch.float32, device="cuda")
+    nvfp4_pack_weight_batch(w, packed, linear, alpha)
+    del w
+    nvfp4_swizzle_scales(linear[:2 * n], swizzled[:2 * n], 2 * n * intermediate, hidden // 16)
+    nvfp4_swizzle_scales(linear[2 * n:], swizzled[2 * n:], n * hidden, intermediate // 16)
+
+    def by_entry(t):            # [kind][entry] -> [entry][kind], the reference's bank order
+        return t.view(3, n, -1).transpose(0, 1).contiguous().view(3 * n, -1)
+
+    return RawLayer(by_entry(packed), by_entry(linear), by_entry(swizzled), by_entry(alpha).view(-1))
 
 
 @dataclass
@@ -130,14 +157,15 @@ def fit_zipf_bias(router_weight: torch.Tensor, alpha: float, seed: int, sample_r
 
 
 def make_layer(seed: int, layer: int, bias_mode: str = "normal", zipf_alpha: float = 1.2,
-               keep_raw: bool = False, stream_copy: bool = False) -> Layer:
-    """bias_mode: 'normal' (~N(0,0.01)), 'zero', or 'zipf' (fitted, see fit_zipf_bias)."""
+               keep_raw: bool = False, stream_copy: bool = False, batched: bool = False) -> Layer:
+    """bias_mode: 'normal' (~N(0,0.01)), 'zero', or 'zipf' (fitted, see fit_zipf_bias).
+    batched: draw and quantise the layer with make_raw_layer_batched (other bytes, same distributions)."""
     router_weight, bias = make_router(seed, layer, bias_std=0.0 if bias_mode == "zero" else 0.01)
     info = {}
     if bias_mode == "zipf":
         bias, achieved = fit_zipf_bias(router_weight, zipf_alpha, seed + layer)
         info["zipf_share_max"] = float(achieved.max())
-    raw = make_raw_layer(seed, layer)
+    raw = make_raw_layer_batched(seed, layer) if batched else make_raw_layer(seed, layer)
     bank = ExpertBank(raw.entries(), stream_copy=stream_copy)
     torch.cuda.synchronize()
     return Layer(router_weight, bias.contiguous(), bank, raw if keep_raw else None, info)

@@ -25,7 +25,7 @@ def _make_ids(rows, seed, hot=None):
     return ids
 
 
-def _run_both(torch, pkg, lib, ids):
+def _run_both(torch, pkg, lib, ids, orc=None):
     n = ids.size
     d_ids = torch.from_numpy(ids).cuda()
     stream = torch.cuda.current_stream().cuda_stream
@@ -47,20 +47,48 @@ def _run_both(torch, pkg, lib, ids):
     for g, w in zip(got, want):
         assert torch.equal(g, w)
     plan.close()
+    if orc is not None:
+        # and against the CPU restatement of the reference's ranking law directly
+        for g, w in zip(got, orc.permute(ids)):
+            assert np.array_equal(g.cpu().numpy(), w)
+    assert pkg.moe_permute_static_status() == 0
     return got
 
 
-def test_static_permutation_matches_plan_based_entry_point_twice_in_a_row(cuda, pkg):
+def test_static_permutation_matches_plan_based_entry_point_twice_in_a_row(cuda, pkg, orc):
     torch = cuda
     lib = pkg.load_library()
     # multi-block path (uses the built-in histogram scratch), then a different, smaller multi-block
     # case whose chunks are a subset of the first call's: stale histograms must not leak
-    first = _run_both(torch, pkg, lib, _make_ids(4096, seed=1))
-    second = _run_both(torch, pkg, lib, _make_ids(1500, seed=2, hot=200))
+    first = _run_both(torch, pkg, lib, _make_ids(4096, seed=1), orc)
+    second = _run_both(torch, pkg, lib, _make_ids(1500, seed=2, hot=200), orc)
     assert first[0].numel() == 4096 * 8 and second[0].numel() == 1500 * 8
     # single-block path and the largest size the array serves
-    _run_both(torch, pkg, lib, _make_ids(5, seed=3))
-    _run_both(torch, pkg, lib, _make_ids(8192, seed=4))
+    _run_both(torch, pkg, lib, _make_ids(5, seed=3), orc)
+    _run_both(torch, pkg, lib, _make_ids(8192, seed=4), orc)
+
+
+@pytest.mark.parametrize("rows", [6, 2000])
+def test_static_permutation_reports_an_out_of_range_id_and_accepts_null_outputs(cuda, pkg, orc, rows):
+    """An id outside 0..255 is counted as expert 0 / 255 (no fault) and leaves 1 in the status word,
+    which the accessor copies out; the next clean call reads 0 again.  order and position are optional."""
+    torch = cuda
+    lib = pkg.load_library()
+    ids = _make_ids(rows, seed=10 + rows)
+    bad = ids.copy()
+    bad[rows // 2, 3] = 256
+    stream = torch.cuda.current_stream().cuda_stream
+    for case, expect in ((bad, 1), (ids, 0)):
+        d_ids = torch.from_numpy(case).cuda()
+        counts = torch.full((256,), -1, dtype=torch.int32, device="cuda")
+        offsets = torch.full((257,), -1, dtype=torch.int32, device="cuda")
+        assert lib.p92b_moe_permute_static(d_ids.data_ptr(), case.size, None, None, counts.data_ptr(), offsets.data_ptr(),
+                                           stream) == 0
+        assert pkg.moe_permute_static_status() == expect
+        clamped = np.minimum(case, 255)
+        _, _, o_counts, o_offsets = orc.permute(clamped)
+        assert np.array_equal(counts.cpu().numpy(), o_counts)
+        assert np.array_equal(offsets.cpu().numpy(), o_offsets)
 
 
 def test_static_permutation_rejects_sizes_beyond_the_built_in_scratch(cuda, pkg):
