@@ -298,6 +298,14 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
                           const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
                           float routed_scale, void* stream);
 
+/* The same with page-locked HOST rows in and out, pipelined like p92b_moe_forward_host_async (copies on the
+ * plan's own two streams, two sets of staging rows; p92b_plan_host_flush + a synchronisation of `stream`
+ * before the outputs are read). */
+int p92b_ep_forward_fused_host_async(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window,
+                                     const uint16_t* pinned_input, const uint16_t* router_weight,
+                                     const float* correction_bias, uint16_t* pinned_output, int rows, float routed_scale,
+                                     void* stream);
+
 /* Medium batches (tens of tokens per GPU, up to 1024 in flight), same idea, several launches: every GPU
  * stores its quantised rows and top-8 ids into every peer's window (all-gather), ranks the rows of its own
  * experts over the whole batch by the reference's permutation law, computes them with the grouped

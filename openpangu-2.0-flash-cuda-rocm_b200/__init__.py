@@ -95,6 +95,7 @@ SIGNATURES = {
     "p92b_ep_window_connect_local": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
     "p92b_ep_forward_gathered": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_ep_forward_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "p92b_ep_forward_fused_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_bank_create": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(ExpertProjection), c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "p92b_bank_destroy": (None, [c_void_p]),
     "p92b_bank_bytes": (c_size_t, [c_void_p]),

@@ -955,4 +955,23 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
                          pdl, window->map_tok[0], plan->map_h[0], p);
 }
 
+int p92b_ep_forward_fused_host_async(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window,
+                                     const uint16_t* pinned_input, const uint16_t* router_weight,
+                                     const float* correction_bias, uint16_t* pinned_output, int rows, float routed_scale,
+                                     void* stream_) {
+    using namespace p92b;
+    if (plan == nullptr || pinned_input == nullptr || pinned_output == nullptr || rows <= 0 || rows > plan->max_rows) {
+        return cudaErrorInvalidValue;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    std::uint16_t *rows_in = nullptr, *rows_out = nullptr;
+    int set = 0;
+    cudaError_t st = host_pipeline_begin(plan, pinned_input, rows, stream, &rows_in, &rows_out, &set);
+    if (st != cudaSuccess) return st;
+    st = static_cast<cudaError_t>(p92b_ep_forward_fused(plan, bank, window, rows_in, router_weight, correction_bias,
+                                                        rows_out, rows, routed_scale, stream_));
+    if (st != cudaSuccess) return st;
+    return host_pipeline_end(plan, pinned_output, rows, stream, set);
+}
+
 }  // extern "C"

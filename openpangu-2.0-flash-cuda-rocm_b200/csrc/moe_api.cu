@@ -540,6 +540,42 @@ static cudaError_t host_pipeline_setup(p92b_plan* plan) {
     return st;
 }
 
+}  // extern "C"
+
+namespace p92b {
+
+cudaError_t host_pipeline_begin(p92b_plan* plan, const std::uint16_t* pinned_input, int rows, cudaStream_t stream,
+                                std::uint16_t** rows_in, std::uint16_t** rows_out, int* set) {
+    cudaError_t st = host_pipeline_setup(plan);
+    if (st != cudaSuccess) return st;
+    const std::size_t bytes = static_cast<std::size_t>(rows) * plan->hidden * sizeof(std::uint16_t);
+    const unsigned n = plan->host_calls++;
+    const int b = static_cast<int>(n & 1U);
+    *set = b;
+    *rows_in = b == 0 ? plan->stage_in : plan->stage_in_b;
+    *rows_out = b == 0 ? plan->stage_out : plan->stage_out_b;
+    if (n >= 2 && (st = cudaStreamWaitEvent(plan->copy_in_stream, plan->block_done[b], 0)) != cudaSuccess) return st;
+    if ((st = cudaMemcpyAsync(*rows_in, pinned_input, bytes, cudaMemcpyHostToDevice, plan->copy_in_stream)) != cudaSuccess) return st;
+    if ((st = cudaEventRecord(plan->in_ready[b], plan->copy_in_stream)) != cudaSuccess) return st;
+    if ((st = cudaStreamWaitEvent(stream, plan->in_ready[b], 0)) != cudaSuccess) return st;
+    if (n >= 2 && (st = cudaStreamWaitEvent(stream, plan->out_done[b], 0)) != cudaSuccess) return st;
+    return cudaSuccess;
+}
+
+cudaError_t host_pipeline_end(p92b_plan* plan, std::uint16_t* pinned_output, int rows, cudaStream_t stream, int set) {
+    const std::size_t bytes = static_cast<std::size_t>(rows) * plan->hidden * sizeof(std::uint16_t);
+    const std::uint16_t* rows_out = set == 0 ? plan->stage_out : plan->stage_out_b;
+    cudaError_t st = cudaEventRecord(plan->block_done[set], stream);
+    if (st != cudaSuccess) return st;
+    if ((st = cudaStreamWaitEvent(plan->copy_out_stream, plan->block_done[set], 0)) != cudaSuccess) return st;
+    if ((st = cudaMemcpyAsync(pinned_output, rows_out, bytes, cudaMemcpyDeviceToHost, plan->copy_out_stream)) != cudaSuccess) return st;
+    return cudaEventRecord(plan->out_done[set], plan->copy_out_stream);
+}
+
+}  // namespace p92b
+
+extern "C" {
+
 int p92b_moe_forward_host_async(p92b_plan* plan, const p92b_bank* bank, const uint16_t* pinned_input,
                                 const uint16_t* router_weight, const float* correction_bias, uint16_t* pinned_output,
                                 int rows, float routed_scale, void* stream_) {
@@ -547,25 +583,14 @@ int p92b_moe_forward_host_async(p92b_plan* plan, const p92b_bank* bank, const ui
         return cudaErrorInvalidValue;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    cudaError_t st = host_pipeline_setup(plan);
+    std::uint16_t *rows_in = nullptr, *rows_out = nullptr;
+    int set = 0;
+    cudaError_t st = host_pipeline_begin(plan, pinned_input, rows, stream, &rows_in, &rows_out, &set);
     if (st != cudaSuccess) return st;
-    const std::size_t bytes = static_cast<std::size_t>(rows) * plan->hidden * sizeof(std::uint16_t);
-    const unsigned n = plan->host_calls++;
-    const int b = static_cast<int>(n & 1U);
-    std::uint16_t* rows_in = b == 0 ? plan->stage_in : plan->stage_in_b;
-    std::uint16_t* rows_out = b == 0 ? plan->stage_out : plan->stage_out_b;
-    if (n >= 2 && (st = cudaStreamWaitEvent(plan->copy_in_stream, plan->block_done[b], 0)) != cudaSuccess) return st;
-    if ((st = cudaMemcpyAsync(rows_in, pinned_input, bytes, cudaMemcpyHostToDevice, plan->copy_in_stream)) != cudaSuccess) return st;
-    if ((st = cudaEventRecord(plan->in_ready[b], plan->copy_in_stream)) != cudaSuccess) return st;
-    if ((st = cudaStreamWaitEvent(stream, plan->in_ready[b], 0)) != cudaSuccess) return st;
-    if (n >= 2 && (st = cudaStreamWaitEvent(stream, plan->out_done[b], 0)) != cudaSuccess) return st;
     st = static_cast<cudaError_t>(p92b_moe_forward(plan, bank, rows_in, router_weight, correction_bias, rows_out, rows,
                                                    routed_scale, stream_));
     if (st != cudaSuccess) return st;
-    if ((st = cudaEventRecord(plan->block_done[b], stream)) != cudaSuccess) return st;
-    if ((st = cudaStreamWaitEvent(plan->copy_out_stream, plan->block_done[b], 0)) != cudaSuccess) return st;
-    if ((st = cudaMemcpyAsync(pinned_output, rows_out, bytes, cudaMemcpyDeviceToHost, plan->copy_out_stream)) != cudaSuccess) return st;
-    return cudaEventRecord(plan->out_done[b], plan->copy_out_stream);
+    return host_pipeline_end(plan, pinned_output, rows, stream, set);
 }
 
 int p92b_plan_host_flush(p92b_plan* plan, void* stream_) {

@@ -388,6 +388,14 @@ cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x
                                    bool pdl = false);
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
                               cudaStream_t stream, bool pdl = false);
+// Pipelined host-buffer calls (moe_api.cu).  Three streams: the caller's (the block), one for rows coming in, one
+// for rows going out; two sets of staging rows used alternately.  begin: the copy-in of this call is enqueued on
+// the plan's in-stream (after the block of call n-2 has read the set) and `stream` is made to wait for it and for
+// the copy-out of call n-2; the caller then enqueues its block from *rows_in to *rows_out on `stream`; end: the
+// copy-out is enqueued on the plan's out-stream behind the block.
+cudaError_t host_pipeline_begin(p92b_plan* plan, const std::uint16_t* pinned_input, int rows, cudaStream_t stream,
+                                std::uint16_t** rows_in, std::uint16_t** rows_out, int* set);
+cudaError_t host_pipeline_end(p92b_plan* plan, std::uint16_t* pinned_output, int rows, cudaStream_t stream, int set);
 // fused decode kernel (decode_mega.cu)
 int decode_mega_max_rows();
 cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std::uint16_t* x,

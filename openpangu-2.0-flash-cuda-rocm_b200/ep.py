@@ -203,6 +203,16 @@ def forward_fused(window: EpWindow, plan: MoePlan, bank: ExpertBank, router_weig
            "ep_forward_fused")
 
 
+def forward_fused_host_async(window: EpWindow, plan: MoePlan, bank: ExpertBank, router_weight, correction_bias,
+                             pinned_in, pinned_out, rows: int, routed_scale: float = ROUTED_SCALE) -> None:
+    """forward_fused with page-locked host tensors, copies pipelined on the plan's own streams; outputs are valid
+    after ``plan.host_flush()`` and a synchronisation of the current stream."""
+    _check(load_library().p92b_ep_forward_fused_host_async(plan.handle, bank.handle, window.handle, pinned_in.data_ptr(),
+                                                           _ptr(router_weight), _ptr(correction_bias),
+                                                           pinned_out.data_ptr(), rows, routed_scale, _stream()),
+           "ep_forward_fused_host_async")
+
+
 GATHERED_MAX_ROWS = 512      # home tokens per GPU the gathered multi-kernel path takes ...
 GATHERED_MAX_TOKENS = 1024   # ... and tokens in flight over all GPUs
 

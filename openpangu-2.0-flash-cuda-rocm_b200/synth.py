@@ -117,6 +117,21 @@ def make_activations(seed: int, layer: int, rows: int, hidden: int = HIDDEN) -> 
         torch.bfloat16)
 
 
+def host_router_inputs(seed: int, layer: int, rows: int, bias_std: float = 0.01, hidden: int = HIDDEN, stream: int = 0):
+    """Router weight, correction bias and token rows of one layer drawn on the HOST (numpy), as BF16 / FP32
+    torch CPU tensors: the one generator a GPU run and a CPU run of the same workload both take their routing
+    inputs from, so that both route the same tokens to the same experts.  `stream` separates the token rows of
+    different ranks; router weight and bias depend on (seed, layer) only."""
+    import numpy as np
+
+    rng = np.random.default_rng([seed, layer])
+    router = torch.from_numpy((rng.standard_normal((EXPERTS, hidden), dtype=np.float32) * np.float32(0.02))).to(torch.bfloat16)
+    bias = torch.from_numpy((rng.standard_normal(EXPERTS, dtype=np.float32) * np.float32(bias_std)))
+    rng_x = np.random.default_rng([seed, layer, 7, stream])
+    x = torch.from_numpy(rng_x.standard_normal((rows, hidden), dtype=np.float32)).to(torch.bfloat16)
+    return router, bias, x
+
+
 def zipf_target(alpha: float, seed: int, experts: int = EXPERTS, top_k: int = TOP_K) -> torch.Tensor:
     """Share of assignments per expert: min(1/top_k, c * rank^-alpha), c solved so shares sum to 1,
     ranks assigned by a seeded permutation of the expert ids.  (An expert is chosen at most once per
