@@ -98,6 +98,12 @@ int p92b_expert_combine(const uint16_t* expert_rows, const float* route_weights,
 int p92b_expert_combine_rows(const uint16_t* expert_rows, const float* route_weights, uint16_t* output,
                              int batch_rows, int experts, int elements, void* stream);
 
+/* p92::cuda::rmsnorm (include/p92/kernels.h:77-83; cuda/nvfp4_ops.cu:67-90,907-918): the operator the engine runs
+ * before (pre_mlp_norm) and after (post_mlp_norm) the MoE block, src/model.cpp:211-218,1210-1217.  Bit-exact with
+ * the reference's kernel (same summation order, same fast-math rsqrtf and division).  elements <= 24576. */
+int p92b_rmsnorm(const uint16_t* input, const uint16_t* weight, uint16_t* output, int rows, int elements, float epsilon,
+                 void* stream);
+
 /* p92::cuda::add_inplace (include/p92/kernels.h:95-98; cuda/nvfp4_ops.cu:92-95). */
 int p92b_add_inplace(uint16_t* destination, const uint16_t* source, int elements, void* stream);
 
@@ -165,7 +171,7 @@ int p92b_moe_permute_static_status(int32_t* host_status, void* stream);
  * memory), which the SIMT kernel family (p92b_plan_set_path 1) and the two un-fused stage
  * entry points need; without it those return cudaErrorNotSupported.
  * first_expert / local_experts select the expert-parallel shard this bank holds
- * (0 / 256 on one GPU). */
+ * (0 / 256 on one GPU); local_experts = 0 makes a bank of one entry for p92b_dense_forward. */
 #define P92B_BANK_STREAM_COPY 1
 int p92b_bank_create(p92b_bank** bank, const p92b_expert_projection* host_entries, int first_expert,
                      int local_experts, int hidden, int intermediate, int flags, void* stream);
@@ -195,6 +201,25 @@ size_t p92b_plan_bytes(const p92b_plan* plan);
 int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input,
                      const uint16_t* router_weight, const float* correction_bias, uint16_t* output,
                      int rows, float routed_scale, void* stream);
+
+/* The block with the two RMSNorms the engine runs either side of it (src/model.cpp:211-218 decode, :1210-1217
+ * prefill rows): output = rmsnorm(block(rmsnorm(input, pre_norm_weight)), post_norm_weight), each norm the reference's
+ * operator bit for bit (p92b_rmsnorm), so the routing equals the reference's on the same `mixed_` rows.  Either weight
+ * may be NULL (that norm is skipped); norm_epsilon is the engine's kNormEpsilon (src/model.cpp:57).  For up to 8 rows
+ * both norms run inside the one persistent kernel - the pre-norm where it stages the token rows, the post-norm behind
+ * its combine - so the engine saves two launches per layer; larger batches run p92b_rmsnorm around the pipeline. */
+int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input, const uint16_t* pre_norm_weight,
+                            const uint16_t* post_norm_weight, float norm_epsilon, const uint16_t* router_weight,
+                            const float* correction_bias, uint16_t* output, int rows, float routed_scale, void* stream);
+
+/* Replaces Model::Impl::run_dense / run_dense_rows (src/model.cpp:1476-1484,1668-1675), the dense SwiGLU MLP of
+ * layers 0-1 (intermediate 9216): output = down(bf16 swiglu(gate(x), up(x))), each projection the quantise + NVFP4
+ * product of ProjectionExecutor::project_rows (src/executor.cpp:148-179).  It runs on the grouped tcgen05 kernels as
+ * a bank with no routed experts: create the bank with local_experts = 0 and the MLP's gate/up/down as its only
+ * three entries (p92b_bank_create), the plan with the MLP's intermediate size.  Same rounding chain as an expert:
+ * x -> FP4; gate, up -> BF16; SwiGLU -> BF16 -> FP4; down -> BF16. */
+int p92b_dense_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input, uint16_t* output, int rows,
+                       void* stream);
 
 /* Same block, HOST input and output buffers (pinned or pageable): copies the
  * rows in, runs p92b_moe_forward, copies the result out and synchronises the

@@ -75,6 +75,7 @@ SIGNATURES = {
     "p92b_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "p92b_expert_combine_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "p92b_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
     "p92b_add_inplace": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_moe_permute": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "p92b_moe_permute_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -103,6 +104,8 @@ SIGNATURES = {
     "p92b_plan_destroy": (None, [c_void_p]),
     "p92b_plan_bytes": (c_size_t, [c_void_p]),
     "p92b_moe_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "p92b_moe_forward_normed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "p92b_dense_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_moe_forward_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_plan_host_flush": (c_int, [c_void_p, c_void_p]),
     "p92b_moe_forward_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
@@ -226,6 +229,11 @@ def swiglu(gate, up, output, elements: int) -> None:
 def expert_combine_rows(expert_rows, route_weights, output, batch_rows: int, experts: int, elements: int) -> None:
     _check(load_library().p92b_expert_combine_rows(_ptr(expert_rows), _ptr(route_weights), _ptr(output), batch_rows,
                                                    experts, elements, _stream()), "expert_combine_rows")
+
+
+def rmsnorm(input, weight, output, rows: int, elements: int, epsilon: float = 1.0e-5) -> None:
+    _check(load_library().p92b_rmsnorm(_ptr(input), _ptr(weight), _ptr(output), rows, elements, epsilon, _stream()),
+           "rmsnorm")
 
 
 def add_inplace(destination, source, elements: int) -> None:
@@ -411,6 +419,13 @@ def _device_copy(ptr: int, shape: tuple, dtype):
     return out.view(torch.bfloat16) if dtype == torch.bfloat16 else out
 
 
+def run_dense_rows(plan: "MoePlan", bank: "ExpertBank", normalized, hidden_out, rows: int) -> None:
+    """Model::Impl::run_dense_rows (src/model.cpp:1476-1484): the dense SwiGLU MLP; `bank` was created with
+    local_experts=0 from the MLP's (gate, up, down) entries, `plan` with its intermediate size."""
+    _check(load_library().p92b_dense_forward(plan.handle, bank.handle, _ptr(normalized), _ptr(hidden_out), rows, _stream()),
+           "dense_forward")
+
+
 class MoeBlock:
     """The MoE block of one layer: mirrors Model::Impl::run_moe / run_moe_rows."""
 
@@ -426,6 +441,16 @@ class MoeBlock:
                                                _ptr(self.router_weight), _ptr(self.correction_bias),
                                                _ptr(hidden_out), rows, self.routed_scale, _stream()),
                "moe_forward")
+
+    def run_moe_rows_normed(self, mixed, pre_norm_weight, post_norm_weight, normalized_out, rows: int,
+                            epsilon: float = 1.0e-5) -> None:
+        """rmsnorm(pre_mlp_norm) -> run_moe_rows -> rmsnorm(post_mlp_norm) as one call (src/model.cpp:211-218,
+        1210-1217); either weight may be None."""
+        _check(load_library().p92b_moe_forward_normed(self.plan.handle, self.bank.handle, _ptr(mixed),
+                                                      _ptr(pre_norm_weight), _ptr(post_norm_weight), epsilon,
+                                                      _ptr(self.router_weight), _ptr(self.correction_bias),
+                                                      _ptr(normalized_out), rows, self.routed_scale, _stream()),
+               "moe_forward_normed")
 
     def run_moe(self, normalized, hidden_out) -> None:
         """Single-token form (src/model.cpp:1677-1729)."""

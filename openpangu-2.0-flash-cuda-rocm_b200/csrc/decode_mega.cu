@@ -33,6 +33,8 @@
 #include "p92b_common.cuh"
 #include "tc_ptx.cuh"
 
+#include <cstdlib>
+
 namespace p92b {
 
 using namespace ptx;
@@ -83,6 +85,10 @@ struct MegaParams {
     unsigned* sync;                // [0]: blocks that have finished P0 (monotonic across launches)
     std::int32_t* gu_done;         // [2][264] by launch parity: gate/up tiles finished per active slot, [257] tile counter
     std::int32_t* status;
+    const std::uint16_t* pre_norm_w;     // optional: RMSNorm weight applied to the token rows before anything else
+    const std::uint16_t* post_norm_w;    // optional: RMSNorm weight applied to the block's output rows
+    unsigned long long* hidden_tagged;   // [8][H/2] {two BF16 of the un-normalised output, launch number} (post-norm only)
+    float norm_eps;
     unsigned long long* trace;     // optional [grid][64] %globaltimer stamps per block (null: off)
     unsigned epoch;                // launches of this kernel on the plan before this one
     float routed_scale;
@@ -166,6 +172,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     __shared__ volatile int tile_queue[kTileQueue];
     __shared__ volatile int first_tile_word;
     __shared__ volatile int rows_ready_word;
+    __shared__ float norm_partial[kMegaMaxRows][8];
+    __shared__ float norm_inverse[kMegaMaxRows];
 
     const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     const std::uint32_t bars = smem_u32(barrier_words);
@@ -233,6 +241,43 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // RMSNorm, the reference operator's arithmetic (cuda/nvfp4_ops.cu:67-90): 256 chains per row (chain t: elements
+    // t, t+256, ... with fmaf), a shuffle-down tree per 32 chains, a second tree over the eight results, then
+    // rsqrtf(sum / H + eps).  Eight "virtual warps" of 32 chains per row are dealt to the block's six warps.
+    auto row_sum_of_squares = [&](const std::uint16_t* rows_bf16, int n_rows) {
+        for (int vw = warp; vw < n_rows * 8; vw += kMegaThreads / 32) {
+            const int r = vw >> 3, w8 = vw & 7;
+            const std::uint16_t* xr = rows_bf16 + r * hidden;
+            float square_sum = 0.0F;
+            for (int i = w8 * 32 + lane; i < hidden; i += 256) {
+                const float value = bf16_bits_to_float(xr[i]);
+                square_sum = fmaf(value, value, square_sum);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) square_sum += __shfl_down_sync(0xffffffffU, square_sum, off);
+            if (lane == 0) norm_partial[r][w8] = square_sum;
+        }
+        __syncthreads();
+        for (int r = warp; r < n_rows; r += kMegaThreads / 32) {
+            float total = lane < 8 ? norm_partial[r][lane] : 0.0F;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) total += __shfl_down_sync(0xffffffffU, total, off);
+            if (lane == 0) norm_inverse[r] = rsqrtf(total / static_cast<float>(hidden) + p.norm_eps);
+        }
+        __syncthreads();
+    };
+    if (p.pre_norm_w != nullptr) {
+        // every block normalises all token rows for itself, in place in shared memory: from here on the kernel sees
+        // the rows the reference's rmsnorm(pre_mlp_norm) would have written (src/model.cpp:211-212,1210-1211)
+        row_sum_of_squares(x_rows, rows);
+        for (int i = threadIdx.x; i < rows * hidden; i += kMegaThreads) {
+            const int r = i / hidden;
+            const int c = i - r * hidden;
+            x_rows[i] = float_to_bf16_bits(bf16_bits_to_float(x_rows[i]) * norm_inverse[r] *
+                                           bf16_bits_to_float(__ldg(p.pre_norm_w + c)));
+        }
+        __syncthreads();
+    }
     const std::uint32_t tmem_base = tmem_slot_word;
     auto stamp = [&](int slot) {
         if (p.trace != nullptr) p.trace[static_cast<std::size_t>(block) * 64 + slot] = global_timer_ns();
@@ -265,8 +310,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
                 if (lane == 0) {
-                    p.logits[block + q * grid] = value;
-                    st_tagged(p.logits_tagged + block + q * grid, __float_as_uint(value), tag);
+                    const int e = block + q * grid;
+                    p.logits[e] = value;
+                    st_tagged(p.logits_tagged + e, __float_as_uint(value), tag);
                 }
             }
         } else {
@@ -766,9 +812,34 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
         const float o1 = bf16_bits_to_float(float_to_bf16_bits(acc[1])) + __uint_as_float(s0 & 0xffff0000U);
         const float o2 = bf16_bits_to_float(float_to_bf16_bits(acc[2])) + __uint_as_float(s1 << 16);
         const float o3 = bf16_bits_to_float(float_to_bf16_bits(acc[3])) + __uint_as_float(s1 & 0xffff0000U);
-        *reinterpret_cast<uint2*>(p.out + static_cast<std::size_t>(row) * hidden + q * 4) =
-            make_uint2(static_cast<std::uint32_t>(float_to_bf16_bits(o0)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o1)) << 16),
-                       static_cast<std::uint32_t>(float_to_bf16_bits(o2)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o3)) << 16));
+        const std::uint32_t w0 = static_cast<std::uint32_t>(float_to_bf16_bits(o0)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o1)) << 16);
+        const std::uint32_t w1 = static_cast<std::uint32_t>(float_to_bf16_bits(o2)) | (static_cast<std::uint32_t>(float_to_bf16_bits(o3)) << 16);
+        if (p.post_norm_w == nullptr) {
+            *reinterpret_cast<uint2*>(p.out + static_cast<std::size_t>(row) * hidden + q * 4) = make_uint2(w0, w1);
+        } else {
+            unsigned long long* words = p.hidden_tagged + static_cast<std::size_t>(row) * (hidden / 2) + 2 * q;
+            st_tagged(words, w0, tag);
+            st_tagged(words + 1, w1, tag);
+        }
+    }
+    if (p.post_norm_w != nullptr && block < rows) {
+        // rmsnorm(post_mlp_norm) of output row `block` (src/model.cpp:216-217,1215-1216): its values were computed all
+        // over the grid; this block collects the row, sums the squares in the operator's order and writes the row out
+        std::uint16_t* h_row = reinterpret_cast<std::uint16_t*>(smem_raw + (base - smem_u32(smem_raw)));
+        bool ok = true;
+        for (int i = threadIdx.x; i < hidden / 2; i += kMegaThreads) {
+            std::uint32_t pair = 0;
+            ok = poll_tagged(p.hidden_tagged + static_cast<std::size_t>(block) * (hidden / 2) + i, tag, &pair) && ok;
+            reinterpret_cast<std::uint32_t*>(h_row)[i] = pair;
+        }
+        if (!ok) give_up(kStatusWaitExpired);
+        __syncthreads();
+        row_sum_of_squares(h_row, 1);
+        const float inverse = norm_inverse[0];
+        for (int i = threadIdx.x; i < hidden; i += kMegaThreads) {
+            p.out[static_cast<std::size_t>(block) * hidden + i] =
+                float_to_bf16_bits(bf16_bits_to_float(h_row[i]) * inverse * bf16_bits_to_float(__ldg(p.post_norm_w + i)));
+        }
     }
     if (threadIdx.x == 0) stamp(12);
 }
@@ -781,7 +852,8 @@ int decode_mega_max_rows() { return kMegaMaxRows; }
 
 cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std::uint16_t* x,
                                const std::uint16_t* router_w, const float* bias, std::uint16_t* out, int rows,
-                               float routed_scale, cudaStream_t stream, bool pdl) {
+                               float routed_scale, cudaStream_t stream, bool pdl, const std::uint16_t* pre_norm_w,
+                               const std::uint16_t* post_norm_w, float norm_eps) {
     if (!plan->tc_ready || !bank->tc_ready || rows <= 0 || rows > kMegaMaxRows || plan->hidden != 2560 ||
         plan->intermediate != 1024) {
         return cudaErrorNotSupported;
@@ -811,6 +883,10 @@ cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std
     p.sync = plan->mega_sync;
     p.gu_done = plan->gu_done;
     p.status = plan->status;
+    p.pre_norm_w = pre_norm_w;
+    p.post_norm_w = post_norm_w;
+    p.hidden_tagged = plan->mega_hidden;
+    p.norm_eps = norm_eps;
     p.trace = plan->trace_on ? plan->mega_trace : nullptr;
     p.epoch = plan->mega_epoch++;
     p.routed_scale = routed_scale;

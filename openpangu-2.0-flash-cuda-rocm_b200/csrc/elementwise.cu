@@ -178,6 +178,56 @@ __global__ void __launch_bounds__(256) add_kernel(std::uint16_t* __restrict__ de
     }
 }
 
+// RMSNorm of BF16 rows, bit-exact with the reference operator (cuda/nvfp4_ops.cu:67-90, called either side of
+// the block, src/model.cpp:211-218,1210-1217): the sum of squares is the reference's 256 chains per row - chain t
+// takes elements t, t+256, ... with fmaf - reduced by a shuffle-down tree per 32 chains and a second tree over the
+// eight results (block_sum, :38-51); inverse = rsqrtf(sum / elements + eps) and out = bf16(x * inverse * w), all in
+// a file compiled with --use_fast_math like the reference, with `elements` a run-time value as there.  The row is
+// staged in shared memory with 16-byte loads; the chains then read it conflict-free.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const std::uint16_t* __restrict__ input,
+                                                           const std::uint16_t* __restrict__ weight,
+                                                           std::uint16_t* __restrict__ output, int elements,
+                                                           int input_stride, int output_stride, float epsilon) {
+    extern __shared__ __align__(16) std::uint16_t norm_row[];
+    __shared__ float warp_sums[8];
+    __shared__ float inverse_shared;
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+    const std::uint16_t* in = input + static_cast<std::size_t>(blockIdx.x) * input_stride;
+    std::uint16_t* out = output + static_cast<std::size_t>(blockIdx.x) * output_stride;
+    const bool vector_ok = (elements & 7) == 0 && (input_stride & 7) == 0 && (reinterpret_cast<std::uintptr_t>(input) & 15) == 0;
+    if (vector_ok) {
+        for (int i = threadIdx.x; i < elements / 8; i += 256) {
+            reinterpret_cast<uint4*>(norm_row)[i] = __ldg(reinterpret_cast<const uint4*>(in) + i);
+        }
+    } else {
+        for (int i = threadIdx.x; i < elements; i += 256) norm_row[i] = in[i];
+    }
+    __syncthreads();
+    float square_sum = 0.0F;
+    for (int i = threadIdx.x; i < elements; i += 256) {
+        const float value = bf16_bits_to_float(norm_row[i]);
+        square_sum = fmaf(value, value, square_sum);
+    }
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) square_sum += __shfl_down_sync(0xffffffffU, square_sum, offset);
+    if (lane == 0) warp_sums[warp] = square_sum;
+    __syncthreads();
+    if (warp == 0) {
+        float total = lane < 8 ? warp_sums[lane] : 0.0F;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_down_sync(0xffffffffU, total, offset);
+        if (lane == 0) inverse_shared = rsqrtf(total / static_cast<float>(elements) + epsilon);
+    }
+    __syncthreads();
+    const float inverse = inverse_shared;
+    for (int i = threadIdx.x; i < elements; i += 256) {
+        out[i] = float_to_bf16_bits(bf16_bits_to_float(norm_row[i]) * inverse * bf16_bits_to_float(__ldg(weight + i)));
+    }
+}
+
 // Fused tail of the block: the weighted combine above (gathering each slot's
 // down row from position space), rounded to BF16 exactly where the reference
 // stores `hidden_`, then the shared expert's BF16 down row added and rounded
@@ -297,6 +347,16 @@ cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t
                          output, rows, hidden);
 }
 
+cudaError_t launch_rmsnorm(const std::uint16_t* input, const std::uint16_t* weight, std::uint16_t* output, int rows,
+                           int elements, int input_stride, int output_stride, float epsilon, cudaStream_t stream, bool pdl) {
+    if (input == nullptr || weight == nullptr || output == nullptr || rows <= 0 || elements <= 0 || elements > 24576 ||
+        input_stride < elements || output_stride < elements || !(epsilon > 0.0F)) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_kernel(rmsnorm_rows_kernel, dim3(rows), dim3(256), static_cast<std::size_t>(elements) * 2, stream, pdl,
+                         input, weight, output, elements, input_stride, output_stride, epsilon);
+}
+
 cudaError_t launch_retile_table(const p92b_expert_projection* device_table, int entries, int kind, std::uint8_t* chunks,
                                 std::size_t entry_bytes, int rows, int k_bytes, int blocks_per_chunk, int slot,
                                 float* alpha, cudaStream_t stream) {
@@ -405,6 +465,12 @@ int p92b_expert_combine_rows(const uint16_t* expert_rows, const float* route_wei
 int p92b_expert_combine(const uint16_t* expert_rows, const float* route_weights, uint16_t* output,
                         int experts, int elements, void* stream) {
     return p92b_expert_combine_rows(expert_rows, route_weights, output, 1, experts, elements, stream);
+}
+
+int p92b_rmsnorm(const uint16_t* input, const uint16_t* weight, uint16_t* output, int rows, int elements, float epsilon,
+                 void* stream) {
+    return launch_rmsnorm(input, weight, output, rows, elements, elements, elements, epsilon,
+                          static_cast<cudaStream_t>(stream), false);
 }
 
 int p92b_add_inplace(uint16_t* destination, const uint16_t* source, int elements, void* stream) {

@@ -714,6 +714,41 @@ __global__ void __launch_bounds__(256) quantize_padded_kernel(const std::uint16_
     }
 }
 
+// The same for rows that each have ONE destination (the dense MLP's token rows, the (row, slot) intermediate rows
+// of the down stage entry point): row i of `x` [n][width] goes to padded position index[i] (i itself if index is null).
+__global__ void __launch_bounds__(256) quantize_rows_to_pp_kernel(const std::uint16_t* __restrict__ x,
+                                                                  const std::int32_t* __restrict__ index,
+                                                                  std::uint8_t* __restrict__ xq,
+                                                                  std::uint8_t* __restrict__ xs, int n, int width,
+                                                                  float global_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const int blocks = width / 16;
+    const int col_blocks = (blocks + 3) / 4;
+    const std::size_t pp = static_cast<std::size_t>(index != nullptr ? index[row] : row);
+    std::uint8_t* row_q = xq + pp * (width / 2);
+    std::uint8_t* row_s = xs + (pp >> 7) * col_blocks * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4;
+    for (int b = lane; b < blocks; b += 32) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(row) * width + b * 16);
+        const uint4 lo = __ldg(src);
+        const uint4 hi = __ldg(src + 1);
+        const std::uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = __uint_as_float(words[i] << 16);
+            v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+        }
+        std::uint8_t scale_bits;
+        const uint2 packed = quantize_block16(v, global_scale, &scale_bits);
+        *reinterpret_cast<uint2*>(row_q + b * 8) = packed;
+        row_s[(b >> 2) * 512 + (b & 3)] = scale_bits;
+    }
+}
+
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -774,8 +809,15 @@ cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x
                          plan->hidden, 1.0F);
 }
 
+cudaError_t launch_quantize_rows_to_pp(const std::uint16_t* x, const std::int32_t* index, std::uint8_t* xq,
+                                       std::uint8_t* xs, int n, int width, cudaStream_t stream, bool pdl) {
+    if (x == nullptr || xq == nullptr || xs == nullptr || n <= 0 || width <= 0 || width % 64 != 0) return cudaErrorInvalidValue;
+    return launch_kernel(quantize_rows_to_pp_kernel, dim3((n + 7) / 8), dim3(256), 0, stream, pdl, x, index, xq, xs, n, width,
+                         1.0F);
+}
+
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
-                              cudaStream_t stream, bool pdl) {
+                              cudaStream_t stream, bool pdl, const TcIo* io) {
     if (!bank->tc_ready || !plan->tc_ready) return cudaErrorNotSupported;
     TcParams p {};
     p.bank = bank->view;
@@ -814,7 +856,7 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
         }
     }
     p.b_sf = plan->hs_sw;
-    p.out = plan->mixed_pp;
+    p.out = io != nullptr && io->down_out != nullptr ? io->down_out : plan->mixed_pp;
     p.k_bytes = plan->intermediate / 2;
     p.m_total = plan->hidden;
     p.m_tiles = plan->hidden / kTileM;

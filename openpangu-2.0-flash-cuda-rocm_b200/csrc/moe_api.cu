@@ -73,7 +73,7 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
                      int local_experts, int hidden, int intermediate, int flags, void* stream_) {
     if (out == nullptr) return cudaErrorInvalidValue;
     *out = nullptr;
-    if (host_entries == nullptr || first_expert < 0 || local_experts <= 0 ||
+    if (host_entries == nullptr || first_expert < 0 || local_experts < 0 ||
         first_expert + local_experts > kExperts || hidden <= 0 || intermediate <= 0 || hidden % 256 != 0 ||
         intermediate % 512 != 0 || (flags & ~P92B_BANK_STREAM_COPY) != 0) {
         return cudaErrorInvalidValue;
@@ -242,6 +242,8 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->mega_logits = c.take<unsigned long long>(static_cast<std::size_t>(8) * kExperts);
         plan->mega_ret = c.take<unsigned long long>(static_cast<std::size_t>(8) * (kTop + 1) * 1280);
         plan->mega_trace = c.take<unsigned long long>(static_cast<std::size_t>(plan->sm_count) * 64);
+        plan->mega_hidden = c.take<unsigned long long>(static_cast<std::size_t>(8) * (hidden / 2));
+        plan->normed = c.take<std::uint16_t>(rows * hidden);
         plan->ep_words = 16 * (kExperts + 1);
         plan->ep_src_base = c.take<std::int32_t>(plan->ep_words);
         plan->ep_src_start = c.take<std::int32_t>(plan->ep_words);
@@ -382,6 +384,14 @@ int p92b_moe_permute(p92b_plan* plan, const int32_t* expert_ids, int assignments
 int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input,
                      const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
                      float routed_scale, void* stream_) {
+    return p92b_moe_forward_normed(plan, bank, input, nullptr, nullptr, 0.0F, router_weight, correction_bias, output, rows,
+                                   routed_scale, stream_);
+}
+
+int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input, const uint16_t* pre_norm_weight,
+                            const uint16_t* post_norm_weight, float norm_epsilon, const uint16_t* router_weight,
+                            const float* correction_bias, uint16_t* output, int rows, float routed_scale, void* stream_) {
+    if ((pre_norm_weight != nullptr || post_norm_weight != nullptr) && !(norm_epsilon > 0.0F)) return cudaErrorInvalidValue;
     if (plan == nullptr || bank == nullptr || input == nullptr || router_weight == nullptr ||
         correction_bias == nullptr || output == nullptr || rows <= 0 || rows > plan->max_rows ||
         !shapes_match(plan, bank) || bank->view.first_expert != 0 || bank->view.local_experts != kExperts) {
@@ -417,7 +427,7 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
         cudaError_t st = mark();
         if (st != cudaSuccess) return st;
         st = launch_decode_mega(plan, bank, input, router_weight, correction_bias, output, rows, routed_scale, stream,
-                                pdl);
+                                pdl, pre_norm_weight, post_norm_weight, norm_epsilon);
         if (st != cudaSuccess) return st;
         for (int i = 0; i < P92B_STAGES; ++i) {
             if ((st = mark()) != cudaSuccess) return st;
@@ -435,8 +445,15 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
     }
     const int pad_align = tc ? tc_pad_align(rows) : 1;
     const int tile_rows = tc ? tc_tile_rows(rows) : (1 << 30);
-    cudaError_t st = mark();
-    if (st != cudaSuccess) return st;
+    cudaError_t st = cudaSuccess;
+    if (pre_norm_weight != nullptr) {
+        // the multi-kernel pipeline reads the token rows in three kernels: normalise them once into the plan's scratch
+        st = launch_rmsnorm(input, pre_norm_weight, plan->normed, rows, hidden, hidden, hidden, norm_epsilon, stream, pdl);
+        if (st != cudaSuccess) return st;
+        input = plan->normed;
+        plan->last_launches += 1;
+    }
+    if ((st = mark()) != cudaSuccess) return st;
     st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream, pdl);
     if (st != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
@@ -489,6 +506,12 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
     }
     plan->last_launches += 3;
     if (st != cudaSuccess) return st;
+    if (post_norm_weight != nullptr) {
+        // in place: a block holds its whole row in shared memory before it writes
+        st = launch_rmsnorm(output, post_norm_weight, output, rows, hidden, hidden, hidden, norm_epsilon, stream, pdl);
+        if (st != cudaSuccess) return st;
+        plan->last_launches += 1;
+    }
     if (debug_sync && !plan->timing && (st = mark()) != cudaSuccess) return st;
     if (plan->timing) {
         if ((st = mark()) != cudaSuccess) return st;
@@ -501,6 +524,32 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
         plan->timed_calls += 1;
     }
     return cudaSuccess;
+}
+
+int p92b_dense_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input, uint16_t* output, int rows,
+                       void* stream_) {
+    if (plan == nullptr || bank == nullptr || input == nullptr || output == nullptr || rows <= 0 || rows > plan->max_rows ||
+        !shapes_match(plan, bank)) {
+        return cudaErrorInvalidValue;
+    }
+    if (!plan->tc_ready || !bank->tc_ready) return cudaErrorNotSupported;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    static const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
+    plan->last_launches = 0;
+    plan->last_path = 2;
+    // the MLP is the bank's last entry; every row is "routed" to it and to nothing else, so its rows sit at padded
+    // positions 0 .. rows-1 in token order and the down product can write the caller's rows directly
+    cudaError_t st = launch_dense_lists(plan, rows, tc_tile_rows(rows), stream, pdl);
+    if (st != cudaSuccess) return st;
+    st = launch_quantize_rows_to_pp(input, nullptr, plan->xq_pp, plan->xs_sw, rows, plan->hidden, stream, pdl);
+    if (st != cudaSuccess) return st;
+    st = launch_experts_tc(plan, bank, rows, false, stream, pdl);
+    if (st != cudaSuccess) return st;
+    TcIo io {};
+    io.down_out = output;
+    st = launch_experts_tc(plan, bank, rows, true, stream, pdl, &io);
+    plan->last_launches += 3;
+    return st;
 }
 
 int p92b_moe_forward_host(p92b_plan* plan, const p92b_bank* bank, const uint16_t* host_input,

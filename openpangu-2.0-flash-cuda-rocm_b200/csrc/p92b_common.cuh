@@ -271,6 +271,8 @@ struct p92b_plan {
     unsigned long long* ep_logits = nullptr;    // [8][256] its router logits as tagged words
     unsigned long long* mega_logits = nullptr;  // [8][256] router logits as {value, launch number} words
     unsigned long long* mega_ret = nullptr;     // [8][9][1280] down rows as {two BF16, launch number} words
+    unsigned long long* mega_hidden = nullptr;  // [8][H/2] un-normalised output rows as tagged words (fused post-norm)
+    std::uint16_t* normed = nullptr;            // [max_rows][H] pre-normalised rows of the multi-kernel path
     unsigned mega_epoch = 0;
     unsigned ep_epoch = 0;                // launches of the fused expert-parallel kernel (counters mega_sync[2..3])
     unsigned long long* mega_trace = nullptr;   // [sm_count][64] timer stamps of the last fused launch (P92B_TRACE=1)
@@ -379,6 +381,9 @@ cudaError_t launch_retile_table(const p92b_expert_projection* device_table, int 
 cudaError_t launch_combine_shared(const std::uint16_t* mixed, const std::int32_t* mixed_index,
                                   const float* route_weights, std::uint16_t* output, int rows,
                                   int hidden, cudaStream_t stream, bool pdl = false);
+cudaError_t launch_rmsnorm(const std::uint16_t* input, const std::uint16_t* weight, std::uint16_t* output, int rows,
+                           int elements, int input_stride, int output_stride, float epsilon, cudaStream_t stream,
+                           bool pdl = false);
 // tensor-core path (expert_tc.cu)
 cudaError_t make_operand_map(CUtensorMap* map, const void* base, std::size_t rows, std::size_t row_bytes,
                              int box_rows);
@@ -386,8 +391,16 @@ int tc_tile_rows(int rows);
 int tc_pad_align(int rows);
 cudaError_t launch_quantize_padded(const p92b_plan* plan, const std::uint16_t* x, int rows, cudaStream_t stream,
                                    bool pdl = false);
+cudaError_t launch_quantize_rows_to_pp(const std::uint16_t* x, const std::int32_t* index, std::uint8_t* xq,
+                                       std::uint8_t* xs, int n, int width, cudaStream_t stream, bool pdl = false);
+// Optional redirections of the grouped kernels' outputs (null members: the plan's own buffers).
+struct TcIo {
+    std::uint16_t* down_out = nullptr;      // down product: BF16 rows [padded position][H] written here instead of mixed_pp
+};
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
-                              cudaStream_t stream, bool pdl = false);
+                              cudaStream_t stream, bool pdl = false, const TcIo* io = nullptr);
+// Routing lists of a call in which every row goes to the bank's last entry only (the dense MLP).
+cudaError_t launch_dense_lists(p92b_plan* plan, int rows, int tile_rows, cudaStream_t stream, bool pdl = false);
 // Pipelined host-buffer calls (moe_api.cu).  Three streams: the caller's (the block), one for rows coming in, one
 // for rows going out; two sets of staging rows used alternately.  begin: the copy-in of this call is enqueued on
 // the plan's in-stream (after the block of call n-2 has read the set) and `stream` is made to wait for it and for
@@ -400,6 +413,7 @@ cudaError_t host_pipeline_end(p92b_plan* plan, std::uint16_t* pinned_output, int
 int decode_mega_max_rows();
 cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std::uint16_t* x,
                                const std::uint16_t* router_w, const float* bias, std::uint16_t* out, int rows,
-                               float routed_scale, cudaStream_t stream, bool pdl);
+                               float routed_scale, cudaStream_t stream, bool pdl, const std::uint16_t* pre_norm_w = nullptr,
+                               const std::uint16_t* post_norm_w = nullptr, float norm_eps = 0.0F);
 
 }  // namespace p92b

@@ -356,9 +356,54 @@ __global__ void __launch_bounds__(256) route_fused_kernel(
     }
 }
 
+// Lists for a call without routing: all `rows` rows belong to entry 256 (the bank's last entry), which starts at
+// padded position 0; no routed expert has rows.
+__global__ void __launch_bounds__(256) dense_lists_kernel(RouteLists lists, int rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = threadIdx.x;
+    lists.counts[e] = 0;
+    lists.offsets[e] = 0;
+    lists.pp_off[e] = 0;
+    if (e == 0) {
+        lists.counts[kExperts] = rows;
+        lists.offsets[kExperts] = 0;
+        lists.offsets[kExperts + 1] = rows;
+        lists.active[0] = kExperts;
+        *lists.active_count = 1;
+        lists.pp_off[kExperts] = 0;
+        lists.pp_off[kExperts + 1] = (rows + lists.pad_align - 1) / lists.pad_align * lists.pad_align;
+        lists.tile_prefix[0] = 0;
+        lists.tile_prefix[1] = (rows + lists.tile_rows - 1) / lists.tile_rows;
+        if (lists.tile_prefix_wide != nullptr) {
+            lists.tile_prefix_wide[0] = 0;
+            lists.tile_prefix_wide[1] = (rows + lists.tile_rows_wide - 1) / lists.tile_rows_wide;
+        }
+    }
+}
+
 }  // namespace
 
 int route_fused_max_rows() { return kFusedMaxRows; }
+
+cudaError_t launch_dense_lists(p92b_plan* plan, int rows, int tile_rows, cudaStream_t stream, bool pdl) {
+    RouteLists lists {};
+    lists.counts = plan->counts;
+    lists.offsets = plan->offsets;
+    lists.active = plan->active;
+    lists.active_count = plan->active_count;
+    lists.enabled = true;
+    lists.pad_align = 128;
+    lists.tile_rows = tile_rows;
+    lists.pp_off = plan->pp_off;
+    lists.tile_prefix = plan->tile_prefix;
+    const bool wide = tile_rows == 64;
+    lists.tile_rows_wide = wide ? 128 : tile_rows;
+    lists.tile_prefix_wide = wide ? plan->tile_prefix_wide : nullptr;
+    plan->wide_rows = wide ? 128 : 0;
+    plan->last_launches += 1;
+    return launch_kernel(dense_lists_kernel, dim3(1), dim3(256), 0, stream, pdl, lists, rows);
+}
 
 cudaError_t launch_route_fused(p92b_plan* plan, const float* bias, float routed_scale, const std::uint16_t* x,
                                int rows, int pad_align, int tile_rows, cudaStream_t stream, bool pdl) {

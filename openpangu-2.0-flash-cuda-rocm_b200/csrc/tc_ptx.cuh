@@ -165,6 +165,7 @@ __device__ __forceinline__ void bulk_load_hint(std::uint32_t dst, const void* sr
                  : "memory");
 }
 
+
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

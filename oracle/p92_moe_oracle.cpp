@@ -440,6 +440,44 @@ void orc_scatter_add_scaled_rows(std::uint16_t* destination, const std::uint16_t
     }
 }
 
+// cuda/nvfp4_ops.cu:67-90 rmsnorm_kernel with 256 threads (:14, :907-918): thread t sums the squares of elements
+// t, t+256, ... with fmaf; block_sum (:38-51) is a shuffle-down tree over each 32 threads, then the same tree over
+// the eight warp results (lanes 8..31 contribute zeros); inverse = rsqrtf(sum / elements + epsilon); out =
+// bf16(x * inverse * w).  The CUDA build's rsqrtf and fast-math division are hardware approximations, so this
+// restatement (1 / sqrtf, IEEE division) agrees with the kernel to a BF16 last place, not bit for bit.
+void orc_rmsnorm(const std::uint16_t* input, const std::uint16_t* weight, std::uint16_t* output, int rows, int elements,
+                 float epsilon) {
+    for (int row = 0; row < rows; ++row) {
+        const std::uint16_t* in = input + static_cast<std::size_t>(row) * elements;
+        float chain[256];
+        for (int t = 0; t < 256; ++t) {
+            float s = 0.0F;
+            for (int i = t; i < elements; i += 256) {
+                const float v = bf16_to_float(in[i]);
+                s = std::fmaf(v, v, s);
+            }
+            chain[t] = s;
+        }
+        float warp_sum[32] = {};
+        for (int w = 0; w < 8; ++w) {
+            float lane[32];
+            for (int l = 0; l < 32; ++l) lane[l] = chain[w * 32 + l];
+            for (int offset = 16; offset > 0; offset >>= 1) {
+                for (int l = 0; l < 32; ++l) lane[l] = lane[l] + (l + offset < 32 ? lane[l + offset] : lane[l]);
+            }
+            warp_sum[w] = lane[0];
+        }
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            for (int l = 0; l < 32; ++l) warp_sum[l] = warp_sum[l] + (l + offset < 32 ? warp_sum[l + offset] : warp_sum[l]);
+        }
+        const float inverse = 1.0F / std::sqrt(warp_sum[0] / static_cast<float>(elements) + epsilon);
+        for (int i = 0; i < elements; ++i) {
+            output[static_cast<std::size_t>(row) * elements + i] =
+                float_to_bf16(bf16_to_float(in[i]) * inverse * bf16_to_float(weight[i]));
+        }
+    }
+}
+
 // cuda/nvfp4_ops.cu:92-95 add_kernel.
 void orc_add_inplace(std::uint16_t* destination, const std::uint16_t* source, long n) {
     for (long i = 0; i < n; ++i) {

@@ -69,6 +69,7 @@ def cpu() -> ctypes.CDLL:
         lib.orc_expert_combine_rows.argtypes = [u16p, f32p, u16p, c_int, c_int, c_int]
         lib.orc_scatter_add_scaled_rows.argtypes = [u16p, u16p, i32p, f32p, c_int, c_int]
         lib.orc_add_inplace.argtypes = [u16p, u16p, c_long]
+        lib.orc_rmsnorm.argtypes = [u16p, u16p, u16p, c_int, c_int, c_float]
         lib.orc_moe_forward.argtypes = [u16p, u16p, f32p, u8p, u8p, f32p, c_long, c_long, u16p, c_int, c_int, c_int,
                                         c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         lib.orc_fnv1a_bf16.argtypes = [u16p, c_long]
@@ -115,6 +116,8 @@ def ref() -> ctypes.CDLL:
         lib.ref_swiglu.argtypes = [P, P, P, c_int, P]
         lib.ref_expert_combine_rows.argtypes = [P, P, P, c_int, c_int, c_int, P]
         lib.ref_add_inplace.argtypes = [P, P, c_int, P]
+        if hasattr(lib, "ref_rmsnorm"):
+            lib.ref_rmsnorm.argtypes = [P, P, P, c_int, c_int, c_float, P]
         lib.ref_moe_forward_rows.argtypes = [P, P, P, P, P, f32p, c_long, c_long, P, c_int, c_int, c_int, c_int,
                                              c_float, P, P, P, P, P]
         _ref = lib
@@ -190,6 +193,14 @@ def swizzle_scales(linear: np.ndarray) -> np.ndarray:
     rows, cols = linear.shape
     out = np.empty(cpu().orc_swizzled_scale_bytes(rows, cols), dtype=np.uint8)
     cpu().orc_swizzle_scales(np.ascontiguousarray(linear), out, rows, cols)
+    return out
+
+
+def rmsnorm(x: np.ndarray, weight: np.ndarray, epsilon: float = 1.0e-5) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty_like(x)
+    cpu().orc_rmsnorm(x.reshape(-1), np.ascontiguousarray(weight, dtype=np.uint16), out.reshape(-1), x.shape[0], x.shape[1],
+                      epsilon)
     return out
 
 

@@ -77,6 +77,11 @@ int ref_expert_combine_rows(const std::uint16_t* expert_rows, const float* route
     return ref::expert_combine_rows(expert_rows, route_weights, output, batch_rows, experts, elements, s);
 }
 
+int ref_rmsnorm(const std::uint16_t* input, const std::uint16_t* weight, std::uint16_t* output, int rows,
+                int elements, float epsilon, cudaStream_t s) {
+    return ref::rmsnorm(input, weight, output, rows, elements, epsilon, s);
+}
+
 int ref_add_inplace(std::uint16_t* destination, const std::uint16_t* source, int elements,
                     cudaStream_t s) {
     return ref::add_inplace(destination, source, elements, s);
