@@ -178,6 +178,46 @@ int p92b_bank_create(p92b_bank** bank, const p92b_expert_projection* host_entrie
 void p92b_bank_destroy(p92b_bank* bank);
 size_t p92b_bank_bytes(const p92b_bank* bank);
 
+/* ---- weight container ("P92FP41") and resident loading ----------------------------------------------- */
+
+/* Replaces p92::Nvfp4Artifact (include/p92/nvfp4_artifact.h:36-71; src/nvfp4_artifact.cpp:65-146): read-only maps
+ * of manifest.bin (48-byte header + 128-byte records sorted by name), weights.nvfp4, scales.e4m3 and, if present,
+ * scales.swizzled.e4m3, with the reference reader's checks (magic, version, record size, file sizes, name order,
+ * rows % 128, columns % 16, weight_scale_2 > 0, extents inside the files).  Where the reference throws, these
+ * return cudaErrorInvalidValue (cudaErrorFileNotFound for a missing file) and keep the reference's message text for
+ * p92b_artifact_last_error (per thread).  Host side only: no GPU is needed to open and query a container. */
+typedef struct p92b_artifact p92b_artifact;
+typedef struct p92b_artifact_record {      /* binary layout of p92::Nvfp4Record (include/p92/nvfp4_artifact.h:24-32) */
+    char name[96];
+    uint32_t rows;
+    uint32_t columns;
+    uint64_t weight_offset;
+    uint64_t scale_offset;
+    float weight_scale_2;
+    uint32_t reserved;
+} p92b_artifact_record;
+int p92b_artifact_open(p92b_artifact** artifact, const char* directory);
+void p92b_artifact_close(p92b_artifact* artifact);
+int p92b_artifact_tensor_count(const p92b_artifact* artifact);
+int p92b_artifact_has_swizzled_scales(const p92b_artifact* artifact);
+int p92b_artifact_at(const p92b_artifact* artifact, int index, p92b_artifact_record* record);
+int p92b_artifact_find(const p92b_artifact* artifact, const char* name, p92b_artifact_record* record);
+const uint8_t* p92b_artifact_weight(const p92b_artifact* artifact, const p92b_artifact_record* record);   /* host pointers */
+const uint8_t* p92b_artifact_scales(const p92b_artifact* artifact, const p92b_artifact_record* record);
+const char* p92b_artifact_last_error(void);
+
+/* Replaces ResidentWeights::open + find (src/resident.cpp:75-162) and the table build of Model::Impl::bind_weights
+ * (src/model.cpp:667-681,724,772-805) for ONE layer: uploads the layer's routed experts first_expert ..
+ * first_expert + local_experts - 1 ("model.layers.<l>.mlp.experts.<e>.{gate,up,down}_proj.weight") and its shared
+ * expert ("...mlp.shared_experts...") and retiles them straight into a bank.  Scales are taken from
+ * scales.swizzled.e4m3 when the container has it, else tiled on the device, as the reference does.  The staging
+ * copies are freed before the call returns; the bank holds the only resident copy. */
+int p92b_bank_create_from_artifact(p92b_bank** bank, const p92b_artifact* artifact, int layer_index, int first_expert,
+                                   int local_experts, void* stream);
+/* The same for the dense MLP of layers 0-1 ("model.layers.<l>.mlp.{gate,up,down}_proj.weight", src/model.cpp:720):
+ * a bank of one entry for p92b_dense_forward. */
+int p92b_dense_bank_create_from_artifact(p92b_bank** bank, const p92b_artifact* artifact, int layer_index, void* stream);
+
 /* ---- plan + whole block -------------------------------------------------- */
 
 /* Replaces nvfp4_grouped_plan_create/_destroy (include/p92/kernels.h:25-30) and

@@ -44,6 +44,15 @@ class ExpertProjection(ctypes.Structure):
     _fields_ = [("weight", c_void_p), ("scales_swizzled", c_void_p), ("alpha", c_void_p)]
 
 
+class ArtifactRecord(ctypes.Structure):
+    """Binary layout of p92::Nvfp4Record (include/p92/nvfp4_artifact.h:24-32)."""
+
+    _pack_ = 1
+    _fields_ = [("name", ctypes.c_char * 96), ("rows", ctypes.c_uint32), ("columns", ctypes.c_uint32),
+                ("weight_offset", ctypes.c_uint64), ("scale_offset", ctypes.c_uint64), ("weight_scale_2", c_float),
+                ("reserved", ctypes.c_uint32)]
+
+
 class PlanViews(ctypes.Structure):
     _fields_ = [
         ("logits", c_void_p),
@@ -100,6 +109,17 @@ SIGNATURES = {
     "p92b_bank_create": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(ExpertProjection), c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "p92b_bank_destroy": (None, [c_void_p]),
     "p92b_bank_bytes": (c_size_t, [c_void_p]),
+    "p92b_artifact_open": (c_int, [ctypes.POINTER(c_void_p), ctypes.c_char_p]),
+    "p92b_artifact_close": (None, [c_void_p]),
+    "p92b_artifact_tensor_count": (c_int, [c_void_p]),
+    "p92b_artifact_has_swizzled_scales": (c_int, [c_void_p]),
+    "p92b_artifact_at": (c_int, [c_void_p, c_int, ctypes.POINTER(ArtifactRecord)]),
+    "p92b_artifact_find": (c_int, [c_void_p, ctypes.c_char_p, ctypes.POINTER(ArtifactRecord)]),
+    "p92b_artifact_weight": (c_void_p, [c_void_p, ctypes.POINTER(ArtifactRecord)]),
+    "p92b_artifact_scales": (c_void_p, [c_void_p, ctypes.POINTER(ArtifactRecord)]),
+    "p92b_artifact_last_error": (ctypes.c_char_p, []),
+    "p92b_bank_create_from_artifact": (c_int, [ctypes.POINTER(c_void_p), c_void_p, c_int, c_int, c_int, c_void_p]),
+    "p92b_dense_bank_create_from_artifact": (c_int, [ctypes.POINTER(c_void_p), c_void_p, c_int, c_void_p]),
     "p92b_plan_create": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_int]),
     "p92b_plan_destroy": (None, [c_void_p]),
     "p92b_plan_bytes": (c_size_t, [c_void_p]),
@@ -119,7 +139,8 @@ SIGNATURES = {
     "p92b_version": (ctypes.c_char_p, []),
 }
 
-_CUDA_ERROR_NAMES = {1: "cudaErrorInvalidValue", 2: "cudaErrorMemoryAllocation", 801: "cudaErrorNotSupported"}
+_CUDA_ERROR_NAMES = {1: "cudaErrorInvalidValue", 2: "cudaErrorMemoryAllocation", 301: "cudaErrorFileNotFound",
+                     801: "cudaErrorNotSupported"}
 
 
 class P92Error(RuntimeError):
@@ -286,6 +307,14 @@ class ExpertBank:
         self.first_expert, self.local_experts = first_expert, local_experts
         self.hidden, self.intermediate = hidden, intermediate
 
+    @classmethod
+    def _adopt(cls, handle, first_expert: int, local_experts: int) -> "ExpertBank":
+        bank = cls.__new__(cls)
+        bank.handle = handle
+        bank.first_expert, bank.local_experts = first_expert, local_experts
+        bank.hidden = bank.intermediate = None          # the library knows; a plan of the wrong shape is rejected by it
+        return bank
+
     @property
     def nbytes(self) -> int:
         return int(load_library().p92b_bank_bytes(self.handle))
@@ -293,6 +322,75 @@ class ExpertBank:
     def close(self) -> None:
         if getattr(self, "handle", None):
             load_library().p92b_bank_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Nvfp4Artifact:
+    """The engine's NVFP4 weight container, opened read-only (mirrors p92::Nvfp4Artifact,
+    include/p92/nvfp4_artifact.h:36-71).  Needs no GPU."""
+
+    def __init__(self, directory: str):
+        handle = c_void_p()
+        code = load_library().p92b_artifact_open(ctypes.byref(handle), os.fsencode(directory))
+        if code != 0:
+            raise P92Error("artifact_open: " + load_library().p92b_artifact_last_error().decode(), code)
+        self.handle = handle
+
+    @property
+    def tensor_count(self) -> int:
+        return int(load_library().p92b_artifact_tensor_count(self.handle))
+
+    @property
+    def has_swizzled_scales(self) -> bool:
+        return bool(load_library().p92b_artifact_has_swizzled_scales(self.handle))
+
+    def at(self, index: int) -> ArtifactRecord:
+        record = ArtifactRecord()
+        code = load_library().p92b_artifact_at(self.handle, index, ctypes.byref(record))
+        if code != 0:
+            raise P92Error("artifact_at: " + load_library().p92b_artifact_last_error().decode(), code)
+        return record
+
+    def find(self, name: str) -> ArtifactRecord:
+        record = ArtifactRecord()
+        code = load_library().p92b_artifact_find(self.handle, name.encode(), ctypes.byref(record))
+        if code != 0:
+            raise P92Error("artifact_find: " + load_library().p92b_artifact_last_error().decode(), code)
+        return record
+
+    def weight_bytes(self, record: ArtifactRecord) -> bytes:
+        ptr = load_library().p92b_artifact_weight(self.handle, ctypes.byref(record))
+        return ctypes.string_at(ptr, record.rows * record.columns // 2)
+
+    def scale_bytes(self, record: ArtifactRecord) -> bytes:
+        ptr = load_library().p92b_artifact_scales(self.handle, ctypes.byref(record))
+        return ctypes.string_at(ptr, record.rows * record.columns // 16)
+
+    def load_bank(self, layer_index: int, first_expert: int = 0, local_experts: int = EXPERTS) -> "ExpertBank":
+        """One layer's experts + shared expert uploaded into a bank (ResidentWeights::open + the table build)."""
+        handle = c_void_p()
+        code = load_library().p92b_bank_create_from_artifact(ctypes.byref(handle), self.handle, layer_index, first_expert,
+                                                             local_experts, _stream())
+        if code != 0:
+            raise P92Error("bank_create_from_artifact: " + load_library().p92b_artifact_last_error().decode(), code)
+        return ExpertBank._adopt(handle, first_expert, local_experts)
+
+    def load_dense_bank(self, layer_index: int) -> "ExpertBank":
+        handle = c_void_p()
+        code = load_library().p92b_dense_bank_create_from_artifact(ctypes.byref(handle), self.handle, layer_index, _stream())
+        if code != 0:
+            raise P92Error("dense_bank_create_from_artifact: " + load_library().p92b_artifact_last_error().decode(), code)
+        return ExpertBank._adopt(handle, 0, 0)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            load_library().p92b_artifact_close(self.handle)
             self.handle = None
 
     def __del__(self):

@@ -420,9 +420,11 @@ int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16
     static const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
     const bool tc = plan->path >= 2 || (plan->path == 0 && plan->tc_ready && bank->tc_ready);
     if (tc && (!plan->tc_ready || !bank->tc_ready)) return cudaErrorNotSupported;
-    if (plan->path == 3 && rows > decode_mega_max_rows()) return cudaErrorInvalidValue;
+    // the single-kernel form is written for the model's expert shape; other shapes take the multi-kernel pipeline
+    const bool mega_shape = plan->hidden == 2560 && plan->intermediate == 1024;
+    if (plan->path == 3 && (rows > decode_mega_max_rows() || !mega_shape)) return cudaErrorInvalidValue;
     plan->last_path = tc ? 2 : 1;
-    if (tc && plan->path != 2 && rows <= decode_mega_max_rows()) {
+    if (tc && plan->path != 2 && rows <= decode_mega_max_rows() && mega_shape) {
         // the whole block as one persistent kernel; in timing mode its time is reported as stage 0
         cudaError_t st = mark();
         if (st != cudaSuccess) return st;

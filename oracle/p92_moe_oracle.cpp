@@ -588,6 +588,19 @@ void orc_moe_forward(const std::uint16_t* x, const std::uint16_t* router_w, cons
     }
 }
 
+// Model::Impl::run_dense_rows (src/model.cpp:1476-1484): gate and up projections of the token rows, SwiGLU in
+// BF16, down projection; each projection is project_rows above.  weights/scales: the three matrices (gate, up,
+// down) back to back at `weight_stride` / `scale_stride`, linear scales.
+void orc_dense_forward(const std::uint16_t* x, const std::uint8_t* weights, const std::uint8_t* scales,
+                       const float* alphas, long weight_stride, long scale_stride, std::uint16_t* out, int rows,
+                       int hidden, int intermediate) {
+    std::vector<std::uint16_t> gate(static_cast<std::size_t>(rows) * intermediate), up(gate.size());
+    project_rows(x, rows, weights, scales, alphas[0], intermediate, hidden, gate.data());
+    project_rows(x, rows, weights + weight_stride, scales + scale_stride, alphas[1], intermediate, hidden, up.data());
+    orc_swiglu(gate.data(), up.data(), gate.data(), static_cast<long>(rows) * intermediate);
+    project_rows(gate.data(), rows, weights + 2 * weight_stride, scales + 2 * scale_stride, alphas[2], hidden, intermediate, out);
+}
+
 // FNV-1a over BF16 bytes, low byte first: the determinism hash of
 // tests/moe_forward_test.cpp:61-70.
 std::uint64_t orc_fnv1a_bf16(const std::uint16_t* values, long n) {

@@ -69,6 +69,7 @@ def cpu() -> ctypes.CDLL:
         lib.orc_expert_combine_rows.argtypes = [u16p, f32p, u16p, c_int, c_int, c_int]
         lib.orc_scatter_add_scaled_rows.argtypes = [u16p, u16p, i32p, f32p, c_int, c_int]
         lib.orc_add_inplace.argtypes = [u16p, u16p, c_long]
+        lib.orc_dense_forward.argtypes = [u16p, u8p, u8p, f32p, c_long, c_long, u16p, c_int, c_int, c_int]
         lib.orc_rmsnorm.argtypes = [u16p, u16p, u16p, c_int, c_int, c_float]
         lib.orc_moe_forward.argtypes = [u16p, u16p, f32p, u8p, u8p, f32p, c_long, c_long, u16p, c_int, c_int, c_int,
                                         c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
@@ -201,6 +202,16 @@ def rmsnorm(x: np.ndarray, weight: np.ndarray, epsilon: float = 1.0e-5) -> np.nd
     out = np.empty_like(x)
     cpu().orc_rmsnorm(x.reshape(-1), np.ascontiguousarray(weight, dtype=np.uint16), out.reshape(-1), x.shape[0], x.shape[1],
                       epsilon)
+    return out
+
+
+def dense_forward(x, weights, scales, alphas, hidden, intermediate):
+    """weights [3, stride] packed (gate, up, down), scales [3, stride] linear, alphas [3]."""
+    rows = x.shape[0]
+    out = np.empty((rows, hidden), dtype=np.uint16)
+    cpu().orc_dense_forward(np.ascontiguousarray(x), weights.reshape(-1), scales.reshape(-1),
+                            np.ascontiguousarray(alphas, dtype=np.float32), weights.shape[1], scales.shape[1], out, rows,
+                            hidden, intermediate)
     return out
 
 
