@@ -167,12 +167,9 @@ int p92b_moe_permute_static_status(int32_t* host_status, void* stream);
  * the last three entries are the shared expert.  The weights are copied into
  * the library's own layout - a tile stream in which the bytes of every pipeline stage of the
  * tensor-core kernels are contiguous ("retiled for TMA") - and the caller may free its copies
- * afterwards.  flags: P92B_BANK_STREAM_COPY additionally keeps a row-major copy (twice the
- * memory), which the SIMT kernel family (p92b_plan_set_path 1) and the two un-fused stage
- * entry points need; without it those return cudaErrorNotSupported.
+ * afterwards.  flags: reserved, pass 0.
  * first_expert / local_experts select the expert-parallel shard this bank holds
  * (0 / 256 on one GPU); local_experts = 0 makes a bank of one entry for p92b_dense_forward. */
-#define P92B_BANK_STREAM_COPY 1
 int p92b_bank_create(p92b_bank** bank, const p92b_expert_projection* host_entries, int first_expert,
                      int local_experts, int hidden, int intermediate, int flags, void* stream);
 void p92b_bank_destroy(p92b_bank* bank);
@@ -279,7 +276,9 @@ int p92b_moe_forward_host_async(p92b_plan* plan, const p92b_bank* bank, const ui
                                 int rows, float routed_scale, void* stream);
 int p92b_plan_host_flush(p92b_plan* plan, void* stream);
 
-/* Stage entry points at the reference's split, so each existing call can be replaced alone.
+/* Stage entry points at the reference's split, so each existing call can be replaced alone.  Both run on the
+ * grouped tcgen05 kernels from the same bank as the whole-block call (an epilogue that stores BF16 gate and up
+ * un-fused; the down product writing the caller's (row, slot) rows), at any row count the plan holds.
  * ProjectionExecutor::project_expert_gate_up (include/p92/executor.h:31-38; src/executor.cpp:39-71):
  * gate_output / up_output BF16 [rows][8][intermediate] in (row, slot) order. */
 int p92b_project_expert_gate_up(p92b_plan* plan, const p92b_bank* bank, const int32_t* expert_ids,
@@ -289,6 +288,34 @@ int p92b_project_expert_gate_up(p92b_plan* plan, const p92b_bank* bank, const in
  * input_rows BF16 [rows*8][intermediate], output_rows BF16 [rows*8][hidden], (row, slot) order. */
 int p92b_project_expert_down(p92b_plan* plan, const p92b_bank* bank, const int32_t* expert_ids,
                              const uint16_t* input_rows, uint16_t* output_rows, int rows, void* stream);
+
+/* Stand-ins for the reference's grouped-projection plan and call, argument for argument
+ * (nvfp4_grouped_plan_create / _destroy, include/p92/kernels.h:25-30; nvfp4_grouped_m1 / nvfp4_grouped_rows,
+ * :32-53; cuda/nvfp4_grouped.cu:223-374), for callers that hold rows they quantised themselves and a device table of
+ * Nvfp4ExpertProjection entries (tests/moe_forward_test.cpp:209-221,258-272; src/executor.cpp:60-70,96-106):
+ *   - the plan is created for `groups` problems of a [rows x columns] matrix: groups = batch_rows * 16 for the gate
+ *     and up pair (first_output, second_output, projection_kind 0), batch_rows * 8 for one matrix (second_output
+ *     NULL; projection_kind 0, 1 or 2 = gate, up, down);
+ *   - packed_input / input_scales_swizzled: the caller's NVFP4 rows and their 128x4-tiled scales, one row per token
+ *     (expert_distinct_input_rows 0: the 8 slots of a token share it) or one per (token, slot) (1);
+ *   - expert_bank: DEVICE array, entry expert * 3 + kind, read IN PLACE (matrices row-major, 16-byte aligned, scales
+ *     128x4-tiled): no bank has to be built, no copy of the weights is made;
+ *   - outputs BF16 [batch_rows * 8][rows] in (token, slot) order, bf16(alpha * product) like the reference's epilogue.
+ * Rows that share an expert share its weight stream (the reference runs one N=1 problem per (token, slot)); the
+ * results are the same numbers.  The reference caps batch_rows at 4 (include/p92/executor.h:61-62); here any
+ * groups / 8 rows.  rows % 128 == 0, columns % 256 == 0.  Errors as cuda/nvfp4_grouped.cu:227-233,354-359; a matrix
+ * pointer that is not 16-byte aligned ends the kernel with 3 in the status word (p92b_nvfp4_grouped_plan_status). */
+typedef struct p92b_grouped_plan p92b_grouped_plan;
+int p92b_nvfp4_grouped_plan_create(p92b_grouped_plan** plan, int groups, int rows, int columns);
+void p92b_nvfp4_grouped_plan_destroy(p92b_grouped_plan* plan);
+int p92b_nvfp4_grouped_m1(p92b_grouped_plan* plan, const uint8_t* packed_input, const uint8_t* input_scales_swizzled,
+                          const p92b_expert_projection* expert_bank, const int32_t* expert_ids, uint16_t* first_output,
+                          uint16_t* second_output, int projection_kind, int distinct_input_rows, void* stream);
+int p92b_nvfp4_grouped_rows(p92b_grouped_plan* plan, const uint8_t* packed_input, const uint8_t* input_scales_swizzled,
+                            const p92b_expert_projection* expert_bank, const int32_t* expert_ids, uint16_t* first_output,
+                            uint16_t* second_output, int projection_kind, int batch_rows, int expert_distinct_input_rows,
+                            void* stream);
+int p92b_nvfp4_grouped_plan_status(const p92b_grouped_plan* plan, const int32_t** device_status);
 
 /* ---- expert parallelism -------------------------------------------------- */
 /* No counterpart in the reference (its CUDA backend is single-device, src/executor.cpp:20-23);
@@ -396,7 +423,8 @@ typedef struct p92b_plan_views {
     const int32_t* offsets;       /* [257] */
     const uint16_t* mixed;        /* BF16 down outputs [mixed rows][hidden] */
     const int32_t* mixed_index;   /* [rows*8 + rows]: row of `mixed` holding assignment (row, slot), then the shared rows */
-    const int32_t* status;        /* device int: 0 ok, else the first error a kernel recorded: 1 expert id out of range (clamped), 2 a bounded wait gave up */
+    const int32_t* status;        /* device int: 0 ok, else the first error a kernel recorded: 1 expert id out of range (clamped), 2 a bounded wait gave up,
+                                     3 a matrix of a caller's projection table is not 16-byte aligned */
     const unsigned long long* trace; /* [trace_blocks][64] %globaltimer stamps of the last fused decode launch
                                         (written only when P92B_TRACE is set in the environment) */
     int trace_blocks;
@@ -414,11 +442,10 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* views);
 int p92b_plan_stage_timing(p92b_plan* plan, int enable);
 int p92b_plan_stage_times(const p92b_plan* plan, float* host_ms, int* host_calls);
 
-/* Kernel family for the block: 0 automatic (3 for up to 8 rows, else 2), 1 weight-streaming SIMT
- * kernels (needs a bank created with P92B_BANK_STREAM_COPY), 2 tcgen05 block-scaled MMA kernels
- * (TMA + TMEM), one launch per stage, 3 the whole block as one persistent tcgen05 kernel (up to 8
- * rows).  The environment variable P92B_PATH sets the default of new plans.  All families implement
- * the same arithmetic contract. */
+/* Kernel family for the block: 0 automatic (3 for up to 8 rows, else 2), 2 tcgen05 block-scaled MMA kernels
+ * (TMA + TMEM), one launch per stage, at any size, 3 the whole block as one persistent tcgen05 kernel (up to 8
+ * rows).  The environment variable P92B_PATH sets the default of new plans.  Both implement the same
+ * arithmetic contract. */
 int p92b_plan_set_path(p92b_plan* plan, int path);
 
 /* Number of kernels the last p92b_moe_forward on this plan launched. */

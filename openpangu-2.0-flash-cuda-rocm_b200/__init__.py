@@ -131,6 +131,11 @@ SIGNATURES = {
     "p92b_moe_forward_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_project_expert_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_project_expert_down": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "p92b_nvfp4_grouped_plan_create": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_int]),
+    "p92b_nvfp4_grouped_plan_destroy": (None, [c_void_p]),
+    "p92b_nvfp4_grouped_plan_status": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "p92b_nvfp4_grouped_m1": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "p92b_nvfp4_grouped_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "p92b_plan_get_views": (c_int, [c_void_p, ctypes.POINTER(PlanViews)]),
     "p92b_plan_set_path": (c_int, [c_void_p, c_int]),
     "p92b_plan_last_launches": (c_int, [c_void_p]),
@@ -289,12 +294,10 @@ class ExpertBank:
     ``entries``: sequence of (weight, scales_swizzled, alpha) CUDA tensors in the
     reference's bank order ``expert * 3 + kind`` (kind 0/1/2 = gate/up/down), the
     shared expert's three entries last.  The tensors may be freed afterwards.
-    ``stream_copy`` also keeps the row-major copy the SIMT kernel family and the un-fused stage
-    entry points read (twice the memory).
     """
 
     def __init__(self, entries: Sequence[tuple], first_expert: int = 0, local_experts: int = EXPERTS,
-                 hidden: int = HIDDEN, intermediate: int = INTERMEDIATE, stream_copy: bool = False):
+                 hidden: int = HIDDEN, intermediate: int = INTERMEDIATE):
         if len(entries) != (local_experts + 1) * 3:
             raise ValueError("invalid expert bank: need (local_experts + 1) * 3 entries")
         array = (ExpertProjection * len(entries))()
@@ -302,7 +305,7 @@ class ExpertBank:
             array[i].weight, array[i].scales_swizzled, array[i].alpha = w.data_ptr(), s.data_ptr(), a.data_ptr()
         handle = c_void_p()
         _check(load_library().p92b_bank_create(ctypes.byref(handle), array, first_expert, local_experts, hidden,
-                                               intermediate, 1 if stream_copy else 0, _stream()), "bank_create")
+                                               intermediate, 0, _stream()), "bank_create")
         self.handle = handle
         self.first_expert, self.local_experts = first_expert, local_experts
         self.hidden, self.intermediate = hidden, intermediate
@@ -478,7 +481,7 @@ class MoePlan:
         _check(load_library().p92b_plan_get_views(self.handle, ctypes.byref(v)), "plan_get_views")
         return torch.as_tensor(_DeviceSpan(v.counts, (EXPERTS,), "<i4"), device="cuda")
 
-    PATH_AUTO, PATH_STREAM, PATH_TENSOR_CORE, PATH_FUSED_DECODE = 0, 1, 2, 3
+    PATH_AUTO, PATH_TENSOR_CORE, PATH_FUSED_DECODE = 0, 2, 3
 
     def set_path(self, path: int) -> None:
         _check(load_library().p92b_plan_set_path(self.handle, path), "plan_set_path")
@@ -491,6 +494,42 @@ class MoePlan:
     def close(self) -> None:
         if getattr(self, "handle", None):
             load_library().p92b_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class GroupedPlan:
+    """Stand-in for p92::cuda::Nvfp4GroupedPlan (include/p92/kernels.h:25-53): `groups` problems of a
+    [rows x columns] matrix; grouped_rows reads the caller's device table of Nvfp4ExpertProjection in place."""
+
+    def __init__(self, groups: int, rows: int, columns: int):
+        handle = c_void_p()
+        _check(load_library().p92b_nvfp4_grouped_plan_create(ctypes.byref(handle), groups, rows, columns),
+               "nvfp4_grouped_plan_create")
+        self.handle, self.groups, self.rows, self.columns = handle, groups, rows, columns
+
+    def grouped_rows(self, packed_input, input_scales_swizzled, expert_bank, expert_ids, first_output, second_output,
+                     projection_kind: int, batch_rows: int, expert_distinct_input_rows: bool) -> None:
+        _check(load_library().p92b_nvfp4_grouped_rows(self.handle, _ptr(packed_input), _ptr(input_scales_swizzled),
+                                                      _ptr(expert_bank), _ptr(expert_ids), _ptr(first_output),
+                                                      _ptr(second_output), projection_kind, batch_rows,
+                                                      int(expert_distinct_input_rows), _stream()), "nvfp4_grouped_rows")
+
+    def status(self) -> int:
+        import torch
+
+        word = c_void_p()
+        _check(load_library().p92b_nvfp4_grouped_plan_status(self.handle, ctypes.byref(word)), "nvfp4_grouped_plan_status")
+        return int(_device_copy(word.value, (1,), torch.int32)[0])
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            load_library().p92b_nvfp4_grouped_plan_destroy(self.handle)
             self.handle = None
 
     def __del__(self):

@@ -126,22 +126,6 @@ __global__ void __launch_bounds__(256) swizzle_kernel(const std::uint8_t* __rest
     swizzled[destination] = linear[index];
 }
 
-// Inverse of the above, used when a bank is built from reference-format entries.
-__global__ void __launch_bounds__(256) unswizzle_kernel(const std::uint8_t* __restrict__ swizzled,
-                                                        std::uint8_t* __restrict__ linear, int rows,
-                                                        int scale_columns, int column_blocks) {
-    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (index >= static_cast<long>(rows) * scale_columns) return;
-    const int row = static_cast<int>(index / scale_columns);
-    const int column = static_cast<int>(index - static_cast<long>(row) * scale_columns);
-    const int row_block = row >> 7;
-    const int row_in_block = row & 127;
-    const std::size_t source =
-        (static_cast<std::size_t>(row_block) * column_blocks + (column >> 2)) * 512 + (row_in_block & 31) * 16 +
-        (row_in_block >> 5) * 4 + (column & 3);
-    linear[index] = swizzled[source];
-}
-
 // cuda/nvfp4_ops.cu:97-105: bf16( g / (1 + expf(-g)) * u ), fast-math like the reference.
 __global__ void __launch_bounds__(256) swiglu_kernel(const std::uint16_t* __restrict__ gate,
                                                      const std::uint16_t* __restrict__ up,
@@ -365,14 +349,6 @@ cudaError_t launch_retile_table(const p92b_expert_projection* device_table, int 
     retile_table_kernel<<<dim3(blocks_for(threads, 256), entries), 256, 0, stream>>>(device_table, kind, chunks, entry_bytes,
                                                                                       rows, k_bytes, blocks_per_chunk, slot,
                                                                                       alpha);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,
-                             cudaStream_t stream) {
-    const long n = static_cast<long>(rows) * scale_columns;
-    unswizzle_kernel<<<blocks_for(n, 256), 256, 0, stream>>>(swizzled, linear, rows, scale_columns,
-                                                            (scale_columns + 3) / 4);
     return cudaGetLastError();
 }
 

@@ -8,20 +8,20 @@
 // shared-memory ring and the tensor core consumes them at a small N - and with
 // hundreds of tokens per expert (prefill) the same code is a grouped GEMM.
 //
-// One block = 6 warps, persistent over work items (expert, token tile, 128-row tile):
-//   warp 0  producer: one elected lane issues the TMA copies of a K block
-//           (256 elements = 128 bytes per row): the weight side is one untiled bulk copy of
-//           a contiguous chunk of the bank's tile stream (boxes already in the swizzled
-//           shared-memory image, scale slabs behind them), the token side a tiled box
-//           load plus its 2 KB scale slab; weights and tokens complete on separate mbarriers;
-//   warp 1  MMA issuer: owns TMEM; per K block copies the scale slabs SMEM->TMEM
-//           (tcgen05.cp) and issues 4 MMAs of K=64 per weight operand; commits the
-//           stage back to the producer and, after the last K block, the
+// One block = 18 warps, persistent over work items (expert, token tile, 128-row tile):
+//   warp 0  producer: one elected lane issues the copies of a K block (256 elements = 128 bytes per row): the
+//           weight side is one untiled bulk copy of a contiguous chunk of the bank's tile stream (boxes already in
+//           the swizzled shared-memory image, scale slabs behind them), the token side a tiled box load plus its
+//           2 KB scale slab; weights and tokens complete on separate mbarriers.  When the weights are read in place
+//           from a caller's table of reference-format matrices (SRC 1) the whole warp gathers the box with 16-byte
+//           asynchronous copies, writing the same swizzled image;
+//   warp 1  MMA issuer: owns TMEM; per K block copies the scale slabs SMEM->TMEM (tcgen05.cp) and issues 4 MMAs of
+//           K=64 per weight operand; commits the stage back to the producer and, after the last K block, the
 //           accumulator to the epilogue;
-//   warps 2-5  epilogue: each reads its 32-lane quarter of the accumulator
-//           (tcgen05.ld), applies the per-tensor scale, rounds to BF16 where the
-//           reference does, and either fuses SwiGLU + re-quantisation to NVFP4
-//           (gate/up) or stores the BF16 down rows.
+//   warps 2-17  epilogue, four per TMEM quarter: each reads 16-column chunks of its 32 lanes of the accumulator
+//           (tcgen05.ld), applies the per-tensor scale, rounds to BF16 where the reference does, and either fuses
+//           SwiGLU + re-quantisation to NVFP4 (MODE 0), stores the BF16 down rows (MODE 1) or stores BF16 gate and
+//           up rows un-fused (MODE 2, the reference's project_expert_gate_up result).
 // Scale factors stay in the 128x4-tiled layout the reference keeps them in
 // (cuda/nvfp4_ops.cu:869-890): one 512-byte tile is exactly one tcgen05.cp atom.
 //
@@ -47,7 +47,7 @@ constexpr int kThreadsTc = 64 + 32 * kEpilogueWarps;
 
 template <int MODE, int N>
 struct Tc {
-    static constexpr int kA = MODE == 0 ? 2 : 1;
+    static constexpr int kA = MODE == 1 ? 1 : 2;          // gate and up share a token tile (MODE 0 fused, MODE 2 un-fused)
     static constexpr int kABytes = kTileM * kBlockKBytes;
     static constexpr int kBBytes = N * kBlockKBytes;
     static constexpr int kWeightBytes = kA * (kABytes + kSfSlab);          // per stage, independent of the tokens
@@ -88,6 +88,13 @@ struct TcParams {
     int m_total;                       // output rows per expert matrix
     int m_tiles;
     int routing_is_upstream;           // 1: the routing lists are written by the kernel just before this one in the stream
+    // optional redirections (stage entry points, p92b_nvfp4_grouped_rows)
+    const std::int32_t* out_row;       // null: output rows sit at their padded position; else [dense position] -> output row
+    std::uint16_t* gate_out;           // MODE 2: BF16 [output row][m_total]
+    std::uint16_t* up_out;
+    const p92b_expert_projection* table;   // SRC 1: device table of reference-format matrices, entry expert * 3 + kind
+    int table_kind;                    // SRC 1, MODE 1: which of an expert's three matrices
+    int skip_shared;                   // 1: the shared expert's items are not computed (the caller has none)
 };
 
 struct Item {
@@ -97,6 +104,7 @@ struct Item {
     int m_tile;
     int pp0;
     int valid;     // tokens of this tile that exist
+    int dense0;    // dense (unpadded) position of the tile's first row
 };
 
 template <int N>
@@ -115,10 +123,21 @@ __device__ __forceinline__ bool decode_item(const TcParams& p, int item, Item* i
     it->count = p.route.counts[it->expert];
     it->pp0 = p.pp_off[it->expert] + n_tile * N;
     it->valid = min(N, it->count - n_tile * N);
+    it->dense0 = p.route.offsets[it->expert] + n_tile * N;
+    if (p.skip_shared && it->expert == kExperts) return false;
+    if (p.table != nullptr) {          // weights in place: the table is indexed by the global expert id
+        it->entry = it->expert;
+        return it->expert >= 0 && it->expert < kExperts;
+    }
     return it->entry >= 0 && it->entry <= p.bank.local_experts;
 }
 
-template <int MODE, int N>
+// 16-byte asynchronous copy global -> shared (through the load/store unit, not the bulk-copy engine).
+__device__ __forceinline__ void async_copy16_tc(std::uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+
+template <int MODE, int N, int SRC>
 __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_constant__ CUtensorMap map_b,
                                                                    const TcParams p) {
     using C = Tc<MODE, N>;
@@ -142,7 +161,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
-            mbar_init(weight_bar(s), 1);
+            // in-place weights: the scale slabs arrive by bulk copy (one arrival with the byte count), the boxes by
+            // the 32 producer lanes' own copies (one arrival each, after their copies have landed)
+            mbar_init(weight_bar(s), SRC == 1 ? 33 : 1);
             mbar_init(token_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
@@ -160,7 +181,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
     }
     // the routing lists come from the kernel just upstream (gate/up) or from one further up (down):
     // only the former has to wait for its predecessor before it can look at its work list
-    if (p.routing_is_upstream) pdl_wait();
+    if (p.routing_is_upstream || SRC == 1) pdl_wait();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -172,7 +193,76 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         atomicCAS(p.status, kStatusOk, kStatusWaitExpired);
     };
 
-    if (warp == 0) {
+    if (warp == 0 && SRC == 1) {
+        // ------------------------------------------------ producer, weights read in place
+        // The matrices are row-major [rows][K/2] wherever the caller keeps them, so a stage's box is gathered: 128
+        // rows x eight 16-byte pieces per box, piece j of row r to r * 128 + ((j ^ (r & 7)) * 16) - the image a
+        // 128-byte-swizzle tile load would have written.  A lane's copies of a stage form one group; a stage is
+        // handed to the MMA lane (fence to the asynchronous proxy, arrival) when its group has landed, kLag stages
+        // behind the one being issued, so kLag stages of copies are always in flight.
+        constexpr int kLag = C::kStages - 1;
+        int stage = 0, oldest = 0, in_flight = 0;
+        std::uint32_t phase = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < total_items && !*abort_ptr && ok; item += gridDim.x) {
+            Item it;
+            if (!decode_item<N>(p, item, &it)) continue;
+            const p92b_expert_projection first = p.table[it.entry * 3 + (MODE == 1 ? p.table_kind : 0)];
+            const p92b_expert_projection second = MODE == 1 ? first : p.table[it.entry * 3 + 1];
+            if (((reinterpret_cast<std::uintptr_t>(first.weight) | reinterpret_cast<std::uintptr_t>(second.weight) |
+                  reinterpret_cast<std::uintptr_t>(first.scales_swizzled) | reinterpret_cast<std::uintptr_t>(second.scales_swizzled)) & 15U) != 0U) {
+                *abort_ptr = 1;                                       // the copies need 16-byte aligned matrices
+                atomicCAS(p.status, kStatusOk, kStatusBadPointer);
+                break;
+            }
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(); ok = false; break; }
+                const std::uint32_t st = base + stage * C::kStageBytes;
+#pragma unroll
+                for (int a = 0; a < C::kA; ++a) {
+                    const std::uint8_t* src = (a == 0 ? first.weight : second.weight) +
+                                              static_cast<std::size_t>(it.m_tile) * kTileM * p.k_bytes + kb * kBlockKBytes;
+#pragma unroll 8
+                    for (int q = 0; q < kTileM * 8 / 32; ++q) {
+                        const int piece = lane + 32 * q;
+                        const int r = piece >> 3, j = piece & 7;
+                        async_copy16_tc(st + a * C::kABytes + r * 128 + ((j ^ (r & 7)) * 16),
+                                        src + static_cast<std::size_t>(r) * p.k_bytes + j * 16);
+                    }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                if (lane == 0) {
+                    // scale slabs: row block m_tile, scale column blocks 4 kb .. 4 kb + 3 of the 128x4 tiling: 2 KB contiguous
+                    mbar_arrive_expect_tx(weight_bar(stage), C::kA * kSfSlab);
+#pragma unroll
+                    for (int a = 0; a < C::kA; ++a) {
+                        const std::uint8_t* sf = (a == 0 ? first.scales_swizzled : second.scales_swizzled) +
+                                                 (static_cast<std::size_t>(it.m_tile) * (k_blocks * 4) + kb * 4) * 512;
+                        bulk_load(st + C::kOffSfA + a * kSfSlab, sf, kSfSlab, weight_bar(stage));
+                    }
+                    mbar_arrive_expect_tx(token_bar(stage), C::kTokenBytes);
+                    tma_load_2d(st + C::kOffB, &map_b, token_bar(stage), kb * kBlockKBytes, it.pp0);
+                    const std::uint8_t* bsf = p.b_sf + (static_cast<std::size_t>(it.pp0 >> 7) * (p.k_bytes / 32) + kb * 4) * 512;
+                    bulk_load(st + C::kOffSfB, bsf, kSfSlab, token_bar(stage));
+                }
+                if (++in_flight > kLag) {
+                    asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
+                    fence_proxy_async();
+                    mbar_arrive(weight_bar(oldest));
+                    if (++oldest == C::kStages) oldest = 0;
+                    --in_flight;
+                }
+                if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        fence_proxy_async();
+        while (in_flight > 0) {
+            mbar_arrive(weight_bar(oldest));
+            if (++oldest == C::kStages) oldest = 0;
+            --in_flight;
+        }
+    } else if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (elect_one()) {
             int stage = 0;
@@ -186,7 +276,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                     const std::uint32_t st = base + stage * C::kStageBytes;
                     // weights never depend on the upstream kernel: they start streaming at once
                     mbar_arrive_expect_tx(weight_bar(stage), C::kWeightBytes);
-                    if constexpr (MODE == 0) {
+                    if constexpr (MODE != 1) {
                         // one chunk = gate box, up box and both scale slabs of this (row tile, K block)
                         const std::uint8_t* chunk = p.bank.g13 +
                             ((static_cast<std::size_t>(it.entry) * p.m_tiles + it.m_tile) * k_blocks + kb) * kChunkBytes;
@@ -369,10 +459,32 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                         }
                     }
                 }
+            } else if constexpr (MODE == 2) {
+                // gate and up rows as the reference's project_expert_gate_up returns them: bf16(alpha * product),
+                // row (token, slot) of the caller's [rows * 8][intermediate] buffers
+                const float alpha_g = SRC == 1 ? *p.table[it.entry * 3 + 0].alpha : p.bank.alpha[it.entry * 3 + 0];
+                const float alpha_u = SRC == 1 ? *p.table[it.entry * 3 + 1].alpha : p.bank.alpha[it.entry * 3 + 1];
+                const int inter = p.m_total;
+#pragma unroll 1
+                for (int c0 = half * 16; c0 < N; c0 += 16 * (kEpilogueWarps / 4)) {
+                    if (c0 >= it.valid) break;
+                    std::uint32_t g[16], u[16];
+                    tmem_load16(lane_base + c0, g);
+                    tmem_load16(lane_base + C::kAccumStride + c0, u);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int n = c0 + j;
+                        if (n < it.valid) {
+                            const std::size_t r = static_cast<std::size_t>(p.out_row != nullptr ? p.out_row[it.dense0 + n] : it.pp0 + n);
+                            p.gate_out[r * inter + row] = float_to_bf16_bits(__uint_as_float(g[j]) * alpha_g);
+                            p.up_out[r * inter + row] = float_to_bf16_bits(__uint_as_float(u[j]) * alpha_u);
+                        }
+                    }
+                }
             } else {
-                const float alpha = p.bank.alpha[it.entry * 3 + 2];
+                const float alpha = SRC == 1 ? *p.table[it.entry * 3 + p.table_kind].alpha : p.bank.alpha[it.entry * 3 + 2];
                 const int hidden = p.m_total;
-                std::uint16_t* out_base = p.out + static_cast<std::size_t>(it.pp0) * hidden + row;
 #pragma unroll 1
                 for (int c0 = half * 16; c0 < N; c0 += 16 * (kEpilogueWarps / 4)) {
                     if (c0 >= it.valid) break;
@@ -383,7 +495,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                     for (int j = 0; j < 16; ++j) {
                         const int n = c0 + j;
                         if (n < it.valid) {
-                            out_base[static_cast<std::size_t>(n) * hidden] = float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
+                            const std::size_t r = static_cast<std::size_t>(p.out_row != nullptr ? p.out_row[it.dense0 + n] : it.pp0 + n);
+                            p.out[r * hidden + row] = float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
                         }
                     }
                 }
@@ -766,12 +879,12 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-template <int MODE, int N>
+template <int MODE, int N, int SRC = 0>
 cudaError_t launch_tc(const p92b_plan* plan, const CUtensorMap& map_b, const TcParams& p, cudaStream_t stream,
                       bool pdl) {
     using C = Tc<MODE, N>;
-    auto kernel = expert_tc_kernel<MODE, N>;
-    if (cudaError_t st = ensure_dynamic_smem<expert_tc_kernel<MODE, N>>(C::kSmemBytes); st != cudaSuccess) return st;
+    auto kernel = expert_tc_kernel<MODE, N, SRC>;
+    if (cudaError_t st = ensure_dynamic_smem<expert_tc_kernel<MODE, N, SRC>>(C::kSmemBytes); st != cudaSuccess) return st;
     return launch_kernel(kernel, dim3(plan->sm_count), dim3(kThreadsTc), C::kSmemBytes, stream, pdl, map_b, p);
 }
 
@@ -818,9 +931,10 @@ cudaError_t launch_quantize_rows_to_pp(const std::uint16_t* x, const std::int32_
 
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
                               cudaStream_t stream, bool pdl, const TcIo* io) {
-    if (!bank->tc_ready || !plan->tc_ready) return cudaErrorNotSupported;
+    const bool in_place = io != nullptr && io->table != nullptr;
+    if (!plan->tc_ready || (!in_place && (bank == nullptr || !bank->tc_ready))) return cudaErrorNotSupported;
     TcParams p {};
-    p.bank = bank->view;
+    if (bank != nullptr) p.bank = bank->view;
     p.route.counts = plan->counts;
     p.route.offsets = plan->offsets;
     p.route.row_token = plan->row_token;
@@ -830,9 +944,19 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
     p.tile_prefix = plan->tile_prefix;
     p.status = plan->status;
     p.quant_scale = 1.0F;
+    if (io != nullptr) {
+        p.out_row = io->out_row;
+        p.gate_out = io->gate_out;
+        p.up_out = io->up_out;
+        p.table = io->table;
+        p.table_kind = io->table_kind;
+        p.skip_shared = io->skip_shared ? 1 : 0;
+    }
+    const bool unfused = io != nullptr && io->gate_out != nullptr;
+    const bool single = io != nullptr && io->single_matrix;      // one matrix of the token-row side (gate or up alone)
     const int n = tc_tile_rows(rows);
     const int which = n == 16 ? 0 : n == 32 ? 1 : 2;
-    p.routing_is_upstream = down ? 0 : 1;
+    p.routing_is_upstream = down && !(io != nullptr && io->wait_upstream) ? 0 : 1;
     if (!down) {
         p.b_sf = plan->xs_sw;
         p.hq = plan->hq_pp;
@@ -840,6 +964,27 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
         p.k_bytes = plan->hidden / 2;
         p.m_total = plan->intermediate;
         p.m_tiles = plan->intermediate / kTileM;
+        if (single) {
+            if (!in_place || io->down_out == nullptr) return cudaErrorInvalidValue;
+            p.out = io->down_out;
+            switch (which) {
+                case 0: return launch_tc<1, 16, 1>(plan, plan->map_x[0], p, stream, pdl);
+                case 1: return launch_tc<1, 32, 1>(plan, plan->map_x[1], p, stream, pdl);
+                default: return launch_tc<1, 64, 1>(plan, plan->map_x[2], p, stream, pdl);
+            }
+        }
+        if (unfused) {
+            if (io->up_out == nullptr) return cudaErrorInvalidValue;
+            switch (which) {
+                case 0: return in_place ? launch_tc<2, 16, 1>(plan, plan->map_x[0], p, stream, pdl)
+                                        : launch_tc<2, 16, 0>(plan, plan->map_x[0], p, stream, pdl);
+                case 1: return in_place ? launch_tc<2, 32, 1>(plan, plan->map_x[1], p, stream, pdl)
+                                        : launch_tc<2, 32, 0>(plan, plan->map_x[1], p, stream, pdl);
+                default: return in_place ? launch_tc<2, 64, 1>(plan, plan->map_x[2], p, stream, pdl)
+                                         : launch_tc<2, 64, 0>(plan, plan->map_x[2], p, stream, pdl);
+            }
+        }
+        if (in_place) return cudaErrorNotSupported;              // the fused gate/up epilogue reads the bank's stream
         switch (which) {
             case 0: return launch_tc<0, 16>(plan, plan->map_x[0], p, stream, pdl);
             case 1: return launch_tc<0, 32>(plan, plan->map_x[1], p, stream, pdl);
@@ -860,6 +1005,13 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
     p.k_bytes = plan->intermediate / 2;
     p.m_total = plan->hidden;
     p.m_tiles = plan->hidden / kTileM;
+    if (in_place) {
+        switch (which) {
+            case 0: return launch_tc<1, 16, 1>(plan, plan->map_h[0], p, stream, pdl);
+            case 1: return launch_tc<1, 32, 1>(plan, plan->map_h[1], p, stream, pdl);
+            default: return launch_tc<1, 64, 1>(plan, plan->map_h[2], p, stream, pdl);
+        }
+    }
     switch (which) {
         case 0: return launch_tc<1, 16>(plan, plan->map_h[0], p, stream, pdl);
         case 1: return launch_tc<1, 32>(plan, plan->map_h[1], p, stream, pdl);
@@ -871,6 +1023,44 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
             }
             return launch_tc<1, 64>(plan, plan->map_h[2], p, stream, pdl);
     }
+}
+
+// Rows that the caller has already quantised in the reference's layout (packed [R][K/2], scales 128x4-tiled over
+// the R rows): assignment i takes source row src_row (i itself, or its token i / 8 when the eight slots of a token
+// share one row) and is copied to padded position pp_of_flat[i], its scale bytes to the tiled position of that row.
+namespace {
+__global__ void __launch_bounds__(256) gather_quantized_rows_kernel(const std::uint8_t* __restrict__ packed,
+                                                                    const std::uint8_t* __restrict__ scales_swizzled,
+                                                                    const std::int32_t* __restrict__ pp_of_flat,
+                                                                    std::uint8_t* __restrict__ xq, std::uint8_t* __restrict__ xs,
+                                                                    int assignments, int k_bytes, int distinct_rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= assignments) return;
+    const std::size_t src = static_cast<std::size_t>(distinct_rows ? i : i / kTop);
+    const std::size_t pp = static_cast<std::size_t>(pp_of_flat[i]);
+    const uint4* from = reinterpret_cast<const uint4*>(packed + src * k_bytes);
+    uint4* to = reinterpret_cast<uint4*>(xq + pp * k_bytes);
+    for (int v = lane; v < k_bytes / 16; v += 32) to[v] = __ldg(from + v);
+    const int scale_columns = k_bytes / 8;                       // K / 16
+    const int col_blocks = (scale_columns + 3) / 4;
+    const std::uint8_t* sf_from = scales_swizzled + (src >> 7) * col_blocks * 512 + (src & 31) * 16 + ((src >> 5) & 3) * 4;
+    std::uint8_t* sf_to = xs + (pp >> 7) * col_blocks * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4;
+    for (int c = lane; c < scale_columns; c += 32) sf_to[(c >> 2) * 512 + (c & 3)] = sf_from[(c >> 2) * 512 + (c & 3)];
+}
+}  // namespace
+
+cudaError_t launch_gather_quantized_rows(const std::uint8_t* packed, const std::uint8_t* scales_swizzled,
+                                         const std::int32_t* pp_of_flat, std::uint8_t* xq, std::uint8_t* xs, int assignments,
+                                         int k_bytes, bool distinct_rows, cudaStream_t stream, bool pdl) {
+    if (packed == nullptr || scales_swizzled == nullptr || assignments <= 0 || k_bytes % 16 != 0 ||
+        (reinterpret_cast<std::uintptr_t>(packed) & 15U) != 0U) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_kernel(gather_quantized_rows_kernel, dim3((assignments + 7) / 8), dim3(256), 0, stream, pdl, packed,
+                         scales_swizzled, pp_of_flat, xq, xs, assignments, k_bytes, distinct_rows ? 1 : 0);
 }
 
 }  // namespace p92b

@@ -29,34 +29,18 @@ struct Carver {
 };
 
 struct BankLayout {
-    std::size_t g13, g2, w13, w2, sf13, sf2, alpha, total;
+    std::size_t g13, g2, alpha, total;
 };
 
-BankLayout bank_layout(int entries, int hidden, int inter, bool stream_copy) {
+BankLayout bank_layout(int entries, int hidden, int inter) {
     BankLayout l {};
     Carver c;
     const std::size_t e = static_cast<std::size_t>(entries);
     l.g13 = c.used; c.take<std::uint8_t>(e * (inter / 128) * (hidden / 256) * kChunkBytes);
     l.g2 = c.used; c.take<std::uint8_t>(e * (hidden / 128) * (inter / 512) * kChunkBytes);
-    if (stream_copy) {
-        l.w13 = c.used; c.take<std::uint8_t>(e * 2 * inter * (hidden / 2));
-        l.w2 = c.used; c.take<std::uint8_t>(e * hidden * (inter / 2));
-        l.sf13 = c.used; c.take<std::uint8_t>(e * 2 * inter * (hidden / 16));
-        l.sf2 = c.used; c.take<std::uint8_t>(e * hidden * (inter / 16));
-    }
     l.alpha = c.used; c.take<float>(e * 3);
     l.total = c.used;
     return l;
-}
-
-RouteView route_view(const p92b_plan* plan) {
-    RouteView r {};
-    r.counts = plan->counts;
-    r.offsets = plan->offsets;
-    r.row_token = plan->row_token;
-    r.active = plan->active;
-    r.active_count = plan->active_count;
-    return r;
 }
 
 bool shapes_match(const p92b_plan* plan, const p92b_bank* bank) {
@@ -75,7 +59,7 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
     *out = nullptr;
     if (host_entries == nullptr || first_expert < 0 || local_experts < 0 ||
         first_expert + local_experts > kExperts || hidden <= 0 || intermediate <= 0 || hidden % 256 != 0 ||
-        intermediate % 512 != 0 || (flags & ~P92B_BANK_STREAM_COPY) != 0) {
+        intermediate % 512 != 0 || flags != 0) {
         return cudaErrorInvalidValue;
     }
     const int entries = local_experts + 1;
@@ -85,11 +69,10 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
             return cudaErrorInvalidValue;
         }
     }
-    const bool stream_copy = (flags & P92B_BANK_STREAM_COPY) != 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     p92b_bank* bank = new (std::nothrow) p92b_bank();
     if (bank == nullptr) return cudaErrorMemoryAllocation;
-    const BankLayout l = bank_layout(entries, hidden, intermediate, stream_copy);
+    const BankLayout l = bank_layout(entries, hidden, intermediate);
     cudaError_t st = cudaMalloc(&bank->storage, l.total);
     if (st != cudaSuccess) {
         delete bank;
@@ -99,16 +82,8 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
     std::uint8_t* base = static_cast<std::uint8_t*>(bank->storage);
     std::uint8_t* g13 = base + l.g13;
     std::uint8_t* g2 = base + l.g2;
-    std::uint8_t* w13 = stream_copy ? base + l.w13 : nullptr;
-    std::uint8_t* w2 = stream_copy ? base + l.w2 : nullptr;
-    std::uint8_t* sf13 = stream_copy ? base + l.sf13 : nullptr;
-    std::uint8_t* sf2 = stream_copy ? base + l.sf2 : nullptr;
     float* alpha = reinterpret_cast<float*>(base + l.alpha);
 
-    const std::size_t gu_bytes = static_cast<std::size_t>(intermediate) * (hidden / 2);
-    const std::size_t dn_bytes = static_cast<std::size_t>(hidden) * (intermediate / 2);
-    const std::size_t gu_sf = static_cast<std::size_t>(intermediate) * (hidden / 16);
-    const std::size_t dn_sf = static_cast<std::size_t>(hidden) * (intermediate / 16);
     const std::size_t g13_entry = static_cast<std::size_t>(intermediate / 128) * (hidden / 256) * kChunkBytes;
     const std::size_t g2_entry = static_cast<std::size_t>(hidden / 128) * (intermediate / 512) * kChunkBytes;
     p92b_expert_projection* device_table = nullptr;
@@ -130,34 +105,11 @@ int p92b_bank_create(p92b_bank** out, const p92b_expert_projection* host_entries
     BANK_TRY(launch_retile_table(device_table, entries, 0, g13, g13_entry, intermediate, hidden / 2, 1, 0, alpha, stream));
     BANK_TRY(launch_retile_table(device_table, entries, 1, g13, g13_entry, intermediate, hidden / 2, 1, 1, alpha, stream));
     BANK_TRY(launch_retile_table(device_table, entries, 2, g2, g2_entry, hidden, intermediate / 2, 2, 0, alpha, stream));
-    if (stream_copy) {
-        for (int e = 0; e < entries; ++e) {
-            for (int kind = 0; kind < 3; ++kind) {
-                const p92b_expert_projection& src = host_entries[e * 3 + kind];
-                if (kind < 2) {
-                    BANK_TRY(cudaMemcpyAsync(w13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_bytes, src.weight,
-                                             gu_bytes, cudaMemcpyDeviceToDevice, stream));
-                    BANK_TRY(launch_unswizzle(src.scales_swizzled,
-                                              sf13 + (static_cast<std::size_t>(e) * 2 + kind) * gu_sf, intermediate,
-                                              hidden / 16, stream));
-                } else {
-                    BANK_TRY(cudaMemcpyAsync(w2 + static_cast<std::size_t>(e) * dn_bytes, src.weight, dn_bytes,
-                                             cudaMemcpyDeviceToDevice, stream));
-                    BANK_TRY(launch_unswizzle(src.scales_swizzled, sf2 + static_cast<std::size_t>(e) * dn_sf, hidden,
-                                              intermediate / 16, stream));
-                }
-            }
-        }
-    }
     BANK_TRY(cudaStreamSynchronize(stream));
 #undef BANK_TRY
     cudaFree(device_table);
     bank->view.g13 = g13;
     bank->view.g2 = g2;
-    bank->view.w13 = w13;
-    bank->view.w2 = w2;
-    bank->view.sf13 = sf13;
-    bank->view.sf2 = sf2;
     bank->view.alpha = alpha;
     bank->view.first_expert = first_expert;
     bank->view.local_experts = local_experts;
@@ -225,9 +177,6 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->chunk_hist = c.take<std::int32_t>(static_cast<std::size_t>(plan->chunks) * kExperts);
         plan->xq = c.take<std::uint8_t>(rows * (hidden / 2));
         plan->xs = c.take<std::uint8_t>(rows * (hidden / 16));
-        plan->hq = c.take<std::uint8_t>(rows * (kTop + 1) * (intermediate / 2));
-        plan->hs = c.take<std::uint8_t>(rows * (kTop + 1) * (intermediate / 16));
-        plan->mixed = c.take<std::uint16_t>(rows * (kTop + 1) * hidden);
         plan->xq_pp = c.take<std::uint8_t>(plan->pp_rows * (hidden / 2));
         plan->xs_sw = c.take<std::uint8_t>(plan->pp_rows * (hidden / 16));
         plan->hq_pp = c.take<std::uint8_t>(plan->pp_rows * (intermediate / 2));
@@ -286,8 +235,8 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
 }
 
 int p92b_plan_set_path(p92b_plan* plan, int path) {
-    if (plan == nullptr || path < 0 || path > 3) return cudaErrorInvalidValue;
-    if (path >= 2 && !plan->tc_ready) return cudaErrorNotSupported;
+    if (plan == nullptr || (path != 0 && path != 2 && path != 3)) return cudaErrorInvalidValue;
+    if (!plan->tc_ready) return cudaErrorNotSupported;
     plan->path = path;
     return cudaSuccess;
 }
@@ -344,7 +293,7 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* v) {
     v->position = plan->position;
     v->counts = plan->counts;
     v->offsets = plan->offsets;
-    v->mixed = plan->last_path == 2 ? plan->mixed_pp : plan->mixed;
+    v->mixed = plan->mixed_pp;
     v->mixed_index = plan->pp_of_flat;
     v->status = plan->status;
     v->trace = plan->mega_trace;
@@ -418,13 +367,12 @@ int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16
     // programmatic dependent launch: each kernel's prologue (and, for the down kernel, its weight
     // prefetch) overlaps the tail of the one before; P92B_NO_PDL=1 switches it off for A/B timing
     static const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
-    const bool tc = plan->path >= 2 || (plan->path == 0 && plan->tc_ready && bank->tc_ready);
-    if (tc && (!plan->tc_ready || !bank->tc_ready)) return cudaErrorNotSupported;
+    if (!plan->tc_ready || !bank->tc_ready) return cudaErrorNotSupported;
     // the single-kernel form is written for the model's expert shape; other shapes take the multi-kernel pipeline
     const bool mega_shape = plan->hidden == 2560 && plan->intermediate == 1024;
     if (plan->path == 3 && (rows > decode_mega_max_rows() || !mega_shape)) return cudaErrorInvalidValue;
-    plan->last_path = tc ? 2 : 1;
-    if (tc && plan->path != 2 && rows <= decode_mega_max_rows() && mega_shape) {
+    plan->last_path = 2;
+    if (plan->path != 2 && rows <= decode_mega_max_rows() && mega_shape) {
         // the whole block as one persistent kernel; in timing mode its time is reported as stage 0
         cudaError_t st = mark();
         if (st != cudaSuccess) return st;
@@ -445,8 +393,8 @@ int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16
         }
         return cudaSuccess;
     }
-    const int pad_align = tc ? tc_pad_align(rows) : 1;
-    const int tile_rows = tc ? tc_tile_rows(rows) : (1 << 30);
+    const int pad_align = tc_pad_align(rows);
+    const int tile_rows = tc_tile_rows(rows);
     cudaError_t st = cudaSuccess;
     if (pre_norm_weight != nullptr) {
         // the multi-kernel pipeline reads the token rows in three kernels: normalise them once into the plan's scratch
@@ -460,7 +408,7 @@ int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16
     if (st != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
     plan->last_launches += 1;
-    if (tc && rows <= route_fused_max_rows()) {
+    if (rows <= route_fused_max_rows()) {
         // top-8, permutation and token quantisation as one block (stages 1-3 of the timing table)
         st = launch_route_fused(plan, correction_bias, routed_scale, input, rows, pad_align, tile_rows, stream, pdl);
         if (st != cudaSuccess) return st;
@@ -477,35 +425,18 @@ int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16
                             pad_align, tile_rows, stream, pdl);
         if (st != cudaSuccess) return st;
         if ((st = mark()) != cudaSuccess) return st;
-        if (tc) {
-            st = launch_quantize_padded(plan, input, rows, stream, pdl);
-        } else {
-            st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * hidden / 16, 1.0F, stream);
-        }
+        st = launch_quantize_padded(plan, input, rows, stream, pdl);
         if (st != cudaSuccess) return st;
         if ((st = mark()) != cudaSuccess) return st;
         plan->last_launches += 1;
     }
-    if (tc) {
-        st = launch_experts_tc(plan, bank, rows, false, stream, pdl);
-        if (st != cudaSuccess) return st;
-        if ((st = mark()) != cudaSuccess) return st;
-        st = launch_experts_tc(plan, bank, rows, true, stream, pdl);
-        if (st != cudaSuccess) return st;
-        if ((st = mark()) != cudaSuccess) return st;
-        st = launch_combine_shared(plan->mixed_pp, plan->pp_of_flat, plan->route_weights, output, rows, hidden, stream,
-                                   pdl);
-    } else {
-        const RouteView route = route_view(plan);
-        st = launch_gate_up(plan, bank->view, route, plan->xq, plan->xs, plan->hq, plan->hs, nullptr, nullptr,
-                            plan->order, rows, stream);
-        if (st != cudaSuccess) return st;
-        if ((st = mark()) != cudaSuccess) return st;
-        st = launch_down(plan, bank->view, route, plan->hq, plan->hs, plan->mixed, nullptr, nullptr, 0, stream);
-        if (st != cudaSuccess) return st;
-        if ((st = mark()) != cudaSuccess) return st;
-        st = launch_combine_shared(plan->mixed, plan->pp_of_flat, plan->route_weights, output, rows, hidden, stream);
-    }
+    st = launch_experts_tc(plan, bank, rows, false, stream, pdl);
+    if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
+    st = launch_experts_tc(plan, bank, rows, true, stream, pdl);
+    if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
+    st = launch_combine_shared(plan->mixed_pp, plan->pp_of_flat, plan->route_weights, output, rows, hidden, stream, pdl);
     plan->last_launches += 3;
     if (st != cudaSuccess) return st;
     if (post_norm_weight != nullptr) {
@@ -660,15 +591,24 @@ int p92b_project_expert_gate_up(p92b_plan* plan, const p92b_bank* bank, const in
         up_output == nullptr || rows <= 0 || rows > plan->max_rows || !shapes_match(plan, bank)) {
         return cudaErrorInvalidValue;
     }
+    if (!plan->tc_ready || !bank->tc_ready) return cudaErrorNotSupported;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    static const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
     plan->last_launches = 0;
+    plan->last_path = 2;
+    // permutation of the caller's ids -> token rows quantised into the padded position space -> the grouped
+    // tcgen05 product with the epilogue that stores gate and up un-fused at their (row, slot) rows
     cudaError_t st = launch_permute(plan, expert_ids, rows * kTop, plan->order, plan->position, plan->counts,
-                                    plan->offsets, true, 1, 1 << 30, stream);
+                                    plan->offsets, true, tc_pad_align(rows), tc_tile_rows(rows), stream);
     if (st != cudaSuccess) return st;
-    st = launch_quantize(input, plan->xq, plan->xs, static_cast<long>(rows) * plan->hidden / 16, 1.0F, stream);
+    st = launch_quantize_padded(plan, input, rows, stream, pdl);
     if (st != cudaSuccess) return st;
-    st = launch_gate_up(plan, bank->view, route_view(plan), plan->xq, plan->xs, nullptr, nullptr, gate_output,
-                        up_output, plan->order, rows, stream);
+    TcIo io {};
+    io.gate_out = gate_output;
+    io.up_out = up_output;
+    io.out_row = plan->order;
+    io.skip_shared = true;
+    st = launch_experts_tc(plan, bank, rows, false, stream, pdl, &io);
     plan->last_launches += 2;
     return st;
 }
@@ -679,19 +619,123 @@ int p92b_project_expert_down(p92b_plan* plan, const p92b_bank* bank, const int32
         output_rows == nullptr || rows <= 0 || rows > plan->max_rows || !shapes_match(plan, bank)) {
         return cudaErrorInvalidValue;
     }
+    if (!plan->tc_ready || !bank->tc_ready) return cudaErrorNotSupported;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    static const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
     plan->last_launches = 0;
+    plan->last_path = 2;
     cudaError_t st = launch_permute(plan, expert_ids, rows * kTop, plan->order, plan->position, plan->counts,
-                                    plan->offsets, true, 1, 1 << 30, stream);
+                                    plan->offsets, true, tc_pad_align(rows), tc_tile_rows(rows), stream);
     if (st != cudaSuccess) return st;
-    // every (row, slot) intermediate row is quantised on its own (src/executor.cpp:85-91), in flat order
-    st = launch_quantize(input_rows, plan->hq, plan->hs, static_cast<long>(rows) * kTop * plan->intermediate / 16, 1.0F,
-                         stream);
+    // every (row, slot) intermediate row is quantised on its own (src/executor.cpp:85-91), to its padded position
+    st = launch_quantize_rows_to_pp(input_rows, plan->pp_of_flat, plan->hq_pp, plan->hs_sw, rows * kTop, plan->intermediate,
+                                    stream, pdl);
     if (st != cudaSuccess) return st;
-    st = launch_down(plan, bank->view, route_view(plan), plan->hq, plan->hs, output_rows, plan->order, plan->order, 1,
-                     stream);
+    TcIo io {};
+    io.down_out = output_rows;
+    io.out_row = plan->order;
+    io.skip_shared = true;
+    io.wait_upstream = true;
+    st = launch_experts_tc(plan, bank, rows, true, stream, pdl, &io);
     plan->last_launches += 2;
     return st;
+}
+
+// ---- stand-ins for the reference's grouped-projection plan and call (include/p92/kernels.h:25-53) ------------------
+
+struct p92b_grouped_plan {
+    p92b_plan* inner = nullptr;
+    int groups = 0, rows = 0, columns = 0;
+};
+
+int p92b_nvfp4_grouped_plan_create(p92b_grouped_plan** out, int groups, int rows, int columns) {
+    if (out == nullptr) return cudaErrorInvalidValue;
+    *out = nullptr;
+    // the reference's checks (cuda/nvfp4_grouped.cu:227-230) plus what the tile stream needs
+    if (groups <= 0 || groups % kTop != 0 || rows <= 0 || columns <= 0 || rows % 128 != 0 || columns % 256 != 0) {
+        return cudaErrorInvalidValue;
+    }
+    p92b_grouped_plan* g = new (std::nothrow) p92b_grouped_plan();
+    if (g == nullptr) return cudaErrorMemoryAllocation;
+    g->groups = groups;
+    g->rows = rows;
+    g->columns = columns;
+    // a gate/up plan (rows < columns: [intermediate x hidden]) keeps its operand rows on the hidden side of the
+    // scratch, a down plan ([hidden x intermediate]) on the intermediate side
+    const bool token_side = rows < columns;
+    const int st = p92b_plan_create(&g->inner, groups / kTop, token_side ? columns : rows, token_side ? rows : columns);
+    if (st != cudaSuccess) {
+        delete g;
+        return st;
+    }
+    *out = g;
+    return cudaSuccess;
+}
+
+void p92b_nvfp4_grouped_plan_destroy(p92b_grouped_plan* plan) {
+    if (plan == nullptr) return;
+    p92b_plan_destroy(plan->inner);
+    delete plan;
+}
+
+int p92b_nvfp4_grouped_plan_status(const p92b_grouped_plan* plan, const int32_t** device_status) {
+    if (plan == nullptr || device_status == nullptr) return cudaErrorInvalidValue;
+    *device_status = plan->inner->status;
+    return cudaSuccess;
+}
+
+int p92b_nvfp4_grouped_rows(p92b_grouped_plan* plan, const uint8_t* packed_input, const uint8_t* input_scales_swizzled,
+                            const p92b_expert_projection* expert_bank, const int32_t* expert_ids, uint16_t* first_output,
+                            uint16_t* second_output, int projection_kind, int batch_rows, int expert_distinct_input_rows,
+                            void* stream_) {
+    // cuda/nvfp4_grouped.cu:354-359
+    if (plan == nullptr || packed_input == nullptr || input_scales_swizzled == nullptr || expert_bank == nullptr ||
+        expert_ids == nullptr || first_output == nullptr || projection_kind < 0 || projection_kind > 2 || batch_rows <= 0 ||
+        plan->groups != batch_rows * (second_output != nullptr ? 2 * kTop : kTop)) {
+        return cudaErrorInvalidValue;
+    }
+    if (second_output != nullptr && projection_kind != 0) return cudaErrorNotSupported;   // two outputs = gate and up
+    p92b_plan* p = plan->inner;
+    const bool token_side = plan->rows < plan->columns;
+    const bool down = !token_side;
+    if ((projection_kind == 2) != down) return cudaErrorInvalidValue;     // the plan was created for the other matrix shape
+    if (!p->tc_ready) return cudaErrorNotSupported;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    static const bool pdl = std::getenv("P92B_NO_PDL") == nullptr;
+    p->last_launches = 0;
+    p->last_path = 2;
+    const int assignments = batch_rows * kTop;
+    // the reference orders its problems by (kind, expert) with ties in the original order
+    // (cuda/nvfp4_grouped.cu:117-132); the same stable order groups the rows per expert here
+    cudaError_t st = launch_permute(p, expert_ids, assignments, p->order, p->position, p->counts, p->offsets, true,
+                                    tc_pad_align(batch_rows), tc_tile_rows(batch_rows), stream);
+    if (st != cudaSuccess) return st;
+    st = launch_gather_quantized_rows(packed_input, input_scales_swizzled, p->pp_of_flat, down ? p->hq_pp : p->xq_pp,
+                                      down ? p->hs_sw : p->xs_sw, assignments, plan->columns / 2,
+                                      expert_distinct_input_rows != 0, stream, pdl);
+    if (st != cudaSuccess) return st;
+    TcIo io {};
+    io.table = expert_bank;
+    io.table_kind = projection_kind;
+    io.out_row = p->order;
+    io.skip_shared = true;
+    if (second_output != nullptr) {
+        io.gate_out = first_output;
+        io.up_out = second_output;
+    } else {
+        io.down_out = first_output;
+        io.single_matrix = !down;
+    }
+    st = launch_experts_tc(p, nullptr, batch_rows, down, stream, pdl, &io);
+    p->last_launches += 2;
+    return st;
+}
+
+int p92b_nvfp4_grouped_m1(p92b_grouped_plan* plan, const uint8_t* packed_input, const uint8_t* input_scales_swizzled,
+                          const p92b_expert_projection* expert_bank, const int32_t* expert_ids, uint16_t* first_output,
+                          uint16_t* second_output, int projection_kind, int distinct_input_rows, void* stream) {
+    return p92b_nvfp4_grouped_rows(plan, packed_input, input_scales_swizzled, expert_bank, expert_ids, first_output,
+                                   second_output, projection_kind, 1, distinct_input_rows, stream);
 }
 
 }  // extern "C"

@@ -24,6 +24,7 @@ enum : int {
     kStatusOk = 0,
     kStatusBadExpertId = 1,   // an expert id outside the bank's range was clamped
     kStatusWaitExpired = 2,   // a bounded mbarrier wait gave up
+    kStatusBadPointer = 3,    // a matrix of a caller's projection table is not 16-byte aligned
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(std::uint16_t bits) {
@@ -174,11 +175,6 @@ constexpr int kChunkScaleBytes = 2048;
 struct BankView {
     const std::uint8_t* g13;
     const std::uint8_t* g2;
-    // optional row-major copy for the SIMT kernels and the un-fused stage entry points (null if absent)
-    const std::uint8_t* w13;    // [entries][2][I][H/2]   gate rows then up rows
-    const std::uint8_t* w2;     // [entries][H][I/2]
-    const std::uint8_t* sf13;   // [entries][2][I][H/16]  linear E4M3
-    const std::uint8_t* sf2;    // [entries][H][I/16]     linear E4M3
     const float* alpha;         // [entries][3]
     int first_expert;
     int local_experts;
@@ -234,9 +230,6 @@ struct p92b_plan {
     int chunks = 0;
     std::uint8_t* xq = nullptr;           // [max_rows][H/2]
     std::uint8_t* xs = nullptr;           // [max_rows][H/16]
-    std::uint8_t* hq = nullptr;           // [9*max_rows][I/2]   position space
-    std::uint8_t* hs = nullptr;           // [9*max_rows][I/16]
-    std::uint16_t* mixed = nullptr;       // [9*max_rows][H]     position space
     std::uint16_t* stage_in = nullptr;    // [max_rows][H]  host-call staging
     std::uint16_t* stage_out = nullptr;   // [max_rows][H]
     // pipelined host calls: second pair of staging rows, copy streams and the events between the three streams
@@ -251,8 +244,8 @@ struct p92b_plan {
     std::int32_t* status = nullptr;       // [1]
     // tensor-core path: operands in the padded position space (every expert's rows start on a
     // multiple of 32 or 128), scales in the 128x4-tiled layout
-    int last_path = 1;                    // path the last forward took
-    int path = 0;                         // 0 auto, 1 SIMT kernels, 2 tcgen05 kernels, 3 fused tcgen05 decode kernel
+    int last_path = 2;                    // path the last forward took
+    int path = 0;                         // 0 auto, 2 tcgen05 kernels one launch per stage, 3 fused tcgen05 decode kernel
     bool tc_ready = false;
     std::size_t pp_rows = 0;              // rows of the padded buffers
     std::uint8_t* xq_pp = nullptr;        // [pp_rows][H/2]
@@ -362,16 +355,6 @@ cudaError_t launch_route_fused(p92b_plan* plan, const float* bias, float routed_
                                int rows, int pad_align, int tile_rows, cudaStream_t stream, bool pdl);
 cudaError_t launch_quantize(const std::uint16_t* input, std::uint8_t* output, std::uint8_t* scales,
                             long groups, float global_scale, cudaStream_t stream);
-cudaError_t launch_gate_up(const p92b_plan* plan, const BankView& bank, const RouteView& route,
-                           const std::uint8_t* xq, const std::uint8_t* xs, std::uint8_t* hq,
-                           std::uint8_t* hs, std::uint16_t* gate_out, std::uint16_t* up_out,
-                           const std::int32_t* order, int rows, cudaStream_t stream);
-cudaError_t launch_down(const p92b_plan* plan, const BankView& bank, const RouteView& route,
-                        const std::uint8_t* hq, const std::uint8_t* hs, std::uint16_t* mixed,
-                        const std::int32_t* in_rows, const std::int32_t* out_rows, int first_active,
-                        cudaStream_t stream);
-cudaError_t launch_unswizzle(const std::uint8_t* swizzled, std::uint8_t* linear, int rows, int scale_columns,
-                             cudaStream_t stream);
 // Writes the matrices of one kind (0/1/2 = gate/up/down) of all `entries` of a table of reference-format
 // projections (device copy, entry * 3 + kind) into the chunk stream, and their alpha values.
 // blocks_per_chunk 1: gate (slot 0) or up (slot 1) of a K block; 2: K blocks 2s, 2s+1 of a down matrix.
@@ -395,8 +378,20 @@ cudaError_t launch_quantize_rows_to_pp(const std::uint16_t* x, const std::int32_
                                        std::uint8_t* xs, int n, int width, cudaStream_t stream, bool pdl = false);
 // Optional redirections of the grouped kernels' outputs (null members: the plan's own buffers).
 struct TcIo {
-    std::uint16_t* down_out = nullptr;      // down product: BF16 rows [padded position][H] written here instead of mixed_pp
+    std::uint16_t* down_out = nullptr;      // single-matrix products: BF16 rows written here instead of mixed_pp
+    const std::int32_t* out_row = nullptr;  // [dense position] -> output row (null: rows sit at their padded position)
+    std::uint16_t* gate_out = nullptr;      // both set: gate and up rows stored un-fused (no SwiGLU, no re-quantisation)
+    std::uint16_t* up_out = nullptr;
+    const p92b_expert_projection* table = nullptr;   // weights read in place from this device table (expert * 3 + kind)
+    int table_kind = 0;                     // with `table`, single-matrix products: which of the three matrices
+    bool single_matrix = false;             // with `table`, token-row side: one matrix (gate or up alone), rows to down_out
+    bool skip_shared = false;               // the call has no shared expert
+    bool wait_upstream = false;             // down product: the kernel just upstream may still be waiting for ITS predecessor
+                                            // when this one starts, so the routing lists may only be read after a wait
 };
+cudaError_t launch_gather_quantized_rows(const std::uint8_t* packed, const std::uint8_t* scales_swizzled,
+                                         const std::int32_t* pp_of_flat, std::uint8_t* xq, std::uint8_t* xs, int assignments,
+                                         int k_bytes, bool distinct_rows, cudaStream_t stream, bool pdl = false);
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
                               cudaStream_t stream, bool pdl = false, const TcIo* io = nullptr);
 // Routing lists of a call in which every row goes to the bank's last entry only (the dense MLP).

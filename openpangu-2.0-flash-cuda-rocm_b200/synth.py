@@ -172,7 +172,7 @@ def fit_zipf_bias(router_weight: torch.Tensor, alpha: float, seed: int, sample_r
 
 
 def make_layer(seed: int, layer: int, bias_mode: str = "normal", zipf_alpha: float = 1.2,
-               keep_raw: bool = False, stream_copy: bool = False, batched: bool = False) -> Layer:
+               keep_raw: bool = False, batched: bool = False) -> Layer:
     """bias_mode: 'normal' (~N(0,0.01)), 'zero', or 'zipf' (fitted, see fit_zipf_bias).
     batched: draw and quantise the layer with make_raw_layer_batched (other bytes, same distributions)."""
     router_weight, bias = make_router(seed, layer, bias_std=0.0 if bias_mode == "zero" else 0.01)
@@ -181,6 +181,6 @@ def make_layer(seed: int, layer: int, bias_mode: str = "normal", zipf_alpha: flo
         bias, achieved = fit_zipf_bias(router_weight, zipf_alpha, seed + layer)
         info["zipf_share_max"] = float(achieved.max())
     raw = make_raw_layer_batched(seed, layer) if batched else make_raw_layer(seed, layer)
-    bank = ExpertBank(raw.entries(), stream_copy=stream_copy)
+    bank = ExpertBank(raw.entries())
     torch.cuda.synchronize()
     return Layer(router_weight, bias.contiguous(), bank, raw if keep_raw else None, info)

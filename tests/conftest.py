@@ -56,7 +56,7 @@ def layer0(cuda, pkg):
     pkg.load_library()
     from p92moe_b200 import synth
 
-    return synth.make_layer(seed=1234, layer=0, keep_raw=True, stream_copy=True)
+    return synth.make_layer(seed=1234, layer=0, keep_raw=True)
 
 
 @pytest.fixture(scope="session")
