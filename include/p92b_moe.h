@@ -103,6 +103,10 @@ int p92b_expert_combine_rows(const uint16_t* expert_rows, const float* route_wei
  * the reference's kernel (same summation order, same fast-math rsqrtf and division).  elements <= 24576. */
 int p92b_rmsnorm(const uint16_t* input, const uint16_t* weight, uint16_t* output, int rows, int elements, float epsilon,
                  void* stream);
+/* p92::cuda::rmsnorm_strided (include/p92/kernels.h:85-93; cuda/nvfp4_ops.cu:920-937): rows `input_stride` /
+ * `output_stride` elements apart. */
+int p92b_rmsnorm_strided(const uint16_t* input, int input_stride, const uint16_t* weight, uint16_t* output,
+                         int output_stride, int rows, int elements, float epsilon, void* stream);
 
 /* p92::cuda::add_inplace (include/p92/kernels.h:95-98; cuda/nvfp4_ops.cu:92-95). */
 int p92b_add_inplace(uint16_t* destination, const uint16_t* source, int elements, void* stream);

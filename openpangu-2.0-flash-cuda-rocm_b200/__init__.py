@@ -85,6 +85,7 @@ SIGNATURES = {
     "p92b_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "p92b_expert_combine_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "p92b_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
+    "p92b_rmsnorm_strided": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
     "p92b_add_inplace": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "p92b_moe_permute": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "p92b_moe_permute_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -449,6 +449,12 @@ int p92b_rmsnorm(const uint16_t* input, const uint16_t* weight, uint16_t* output
                           static_cast<cudaStream_t>(stream), false);
 }
 
+int p92b_rmsnorm_strided(const uint16_t* input, int input_stride, const uint16_t* weight, uint16_t* output,
+                         int output_stride, int rows, int elements, float epsilon, void* stream) {
+    return launch_rmsnorm(input, weight, output, rows, elements, input_stride, output_stride, epsilon,
+                          static_cast<cudaStream_t>(stream), false);
+}
+
 int p92b_add_inplace(uint16_t* destination, const uint16_t* source, int elements, void* stream) {
     if (destination == nullptr || source == nullptr || elements <= 0) return cudaErrorInvalidValue;
     add_kernel<<<blocks_for(elements, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(destination, source, elements);
