@@ -232,7 +232,11 @@ size_t p92b_plan_bytes(const p92b_plan* plan);
  * (src/model.cpp:1486-1573): router logits -> top-8 -> permutation -> NVFP4
  * gate/up + SwiGLU -> NVFP4 down -> weighted combine (device law,
  * cuda/nvfp4_ops.cu:124-142) -> + shared expert.  input/output: BF16 [rows][hidden].
- * rows == 1 uses the T=1 logits order, rows > 1 the T>1 order, as the reference does.
+ * rows == 1 uses the T=1 logits order, rows > 1 the T>1 order, as the reference does.  From 256 rows on the logits
+ * are a BF16 tensor-core product and only the ones that can decide the top-8 (every expert within a proven error bound
+ * of the 8th best, about nine per token) are recomputed in the reference's exact order; expert ids and route weights
+ * are still the reference's bit for bit, the `logits` view then holds approximate values except at those positions.
+ * P92B_EXACT_LOGITS=1 in the environment keeps the exact-order kernel at every size.
  *
  * For up to 8 rows the block is ONE persistent kernel with one thread block per SM whose blocks hand
  * data to one another (p92b_plan_set_path).  They must all be resident at once: do not run it while
@@ -429,6 +433,8 @@ typedef struct p92b_plan_views {
     const int32_t* mixed_index;   /* [rows*8 + rows]: row of `mixed` holding assignment (row, slot), then the shared rows */
     const int32_t* status;        /* device int: 0 ok, else the first error a kernel recorded: 1 expert id out of range (clamped), 2 a bounded wait gave up,
                                      3 a matrix of a caller's projection table is not 16-byte aligned */
+    const int32_t* router_stats;  /* [2] large-batch router (tensor-core logits + exact repair): logits recomputed in the
+                                     reference's order so far on this plan, tokens whose whole row was recomputed */
     const unsigned long long* trace; /* [trace_blocks][64] %globaltimer stamps of the last fused decode launch
                                         (written only when P92B_TRACE is set in the environment) */
     int trace_blocks;

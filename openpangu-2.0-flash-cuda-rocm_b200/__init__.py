@@ -65,6 +65,7 @@ class PlanViews(ctypes.Structure):
         ("mixed", c_void_p),
         ("mixed_index", c_void_p),
         ("status", c_void_p),
+        ("router_stats", c_void_p),
         ("trace", c_void_p),
         ("trace_blocks", c_int),
     ]
@@ -463,6 +464,7 @@ class MoePlan:
             "offsets": grab(v.offsets, (EXPERTS + 1,), torch.int32),
             "mixed_index": mixed_index,
             "status": grab(v.status, (1,), torch.int32),
+            "router_stats": grab(v.router_stats, (2,), torch.int32),
             "trace": torch.as_tensor(_DeviceSpan(v.trace, (v.trace_blocks, 64), "<i8"), device="cuda").clone(),
         }
 

@@ -191,6 +191,8 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->mega_logits = c.take<unsigned long long>(static_cast<std::size_t>(8) * kExperts);
         plan->mega_ret = c.take<unsigned long long>(static_cast<std::size_t>(8) * (kTop + 1) * 1280);
         plan->mega_trace = c.take<unsigned long long>(static_cast<std::size_t>(plan->sm_count) * 64);
+        plan->w_norms = c.take<float>(kExperts);
+        plan->router_stats = c.take<int>(2);
         plan->mega_hidden = c.take<unsigned long long>(static_cast<std::size_t>(8) * (hidden / 2));
         plan->normed = c.take<std::uint16_t>(rows * hidden);
         plan->ep_words = 16 * (kExperts + 1);
@@ -296,6 +298,7 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* v) {
     v->mixed = plan->mixed_pp;
     v->mixed_index = plan->pp_of_flat;
     v->status = plan->status;
+    v->router_stats = plan->router_stats;
     v->trace = plan->mega_trace;
     v->trace_blocks = plan->sm_count;
     return cudaSuccess;
@@ -404,10 +407,20 @@ int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16
         plan->last_launches += 1;
     }
     if ((st = mark()) != cudaSuccess) return st;
-    st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream, pdl);
-    if (st != cudaSuccess) return st;
+    // large batches: tensor-core logits with exact repair of the candidates (ids and weights still the reference's bit
+    // for bit); in the stage table its three kernels are the "router logits" stage and the top-8 stage is empty
+    bool routed = false;
+    if (rows >= router_fast_min_rows()) {
+        st = launch_router_fast(plan, input, router_weight, correction_bias, rows, routed_scale, stream, pdl);
+        if (st == cudaSuccess) routed = true;
+        else if (st != cudaErrorNotSupported) return st;
+    }
+    if (!routed) {
+        st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream, pdl);
+        if (st != cudaSuccess) return st;
+        plan->last_launches += 1;
+    }
     if ((st = mark()) != cudaSuccess) return st;
-    plan->last_launches += 1;
     if (rows <= route_fused_max_rows()) {
         // top-8, permutation and token quantisation as one block (stages 1-3 of the timing table)
         st = launch_route_fused(plan, correction_bias, routed_scale, input, rows, pad_align, tile_rows, stream, pdl);
@@ -416,11 +429,13 @@ int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16
         if ((st = mark()) != cudaSuccess) return st;
         if ((st = mark()) != cudaSuccess) return st;
     } else {
-        st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream,
-                                pdl);
-        if (st != cudaSuccess) return st;
+        if (!routed) {
+            st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream,
+                                    pdl);
+            if (st != cudaSuccess) return st;
+            plan->last_launches += 1;
+        }
         if ((st = mark()) != cudaSuccess) return st;
-        plan->last_launches += 1;
         st = launch_permute(plan, plan->ids, rows * kTop, plan->order, plan->position, plan->counts, plan->offsets, true,
                             pad_align, tile_rows, stream, pdl);
         if (st != cudaSuccess) return st;

@@ -72,13 +72,27 @@ def _check_block_against_reference(torch, pkg, orc, layer0, bias, x, out, views,
     ref_logits = torch.empty((rows, 256), dtype=torch.float32, device="cuda")
     assert orc.ref().ref_bf16_gemm_f32(x.data_ptr(), layer0.router_weight.data_ptr(), ref_logits.data_ptr(), rows, 256,
                                        2560, _stream(torch)) == 0
-    assert torch.equal(views["logits"], ref_logits)
+    if rows < 256:
+        assert torch.equal(views["logits"], ref_logits)
     ref_ids = torch.empty((rows, 8), dtype=torch.int32, device="cuda")
     ref_w = torch.empty((rows, 8), dtype=torch.float32, device="cuda")
     assert orc.ref().ref_router_top8_rows(ref_logits.data_ptr(), bias.data_ptr(), ref_ids.data_ptr(), ref_w.data_ptr(),
                                           rows, 2.5, _stream(torch)) == 0
     assert torch.equal(views["expert_ids"], ref_ids)
     assert torch.equal(views["expert_weights"], ref_w)
+    if rows >= 256:
+        # large batches: tensor-core logits, exact only where they can decide the routing.  The selected experts' logits
+        # are the reference's bit for bit; everywhere else the deviation must stay far (8x) inside the bound the repair
+        # assumes, 2^-14 * ||x|| * ||w|| (about 3e-3 here)
+        picked = ref_ids.long()
+        assert torch.equal(torch.gather(views["logits"], 1, picked), torch.gather(ref_logits, 1, picked))
+        x_norm = x.float().norm(dim=1, keepdim=True)
+        w_norm = layer0.router_weight.float().norm(dim=1)[None, :]
+        ratio = ((views["logits"] - ref_logits).abs() / (x_norm * w_norm * 2.0 ** -14)).max()
+        stats = views["router_stats"].cpu().numpy()
+        print(f"rows {rows}: max |approximate - exact| / bound = {float(ratio):.4f}; exactly recomputed logits so far "
+              f"{int(stats[0])} ({int(stats[0]) / rows:.2f} per token if one call), whole rows {int(stats[1])}")
+        assert float(ratio) <= 0.125
     ids = ref_ids.cpu().numpy()
     # router invariants of tests/moe_forward_test.cpp:143-157 on every row
     assert (np.sort(ids, axis=1)[:, 1:] != np.sort(ids, axis=1)[:, :-1]).all() and ids.min() >= 0 and ids.max() < 256
