@@ -348,9 +348,15 @@ int p92b_ep_route(p92b_plan* plan, const uint16_t* input, const uint16_t* router
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const int hidden = plan->hidden;
     plan->last_launches = 0;
-    cudaError_t st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream);
-    if (st != cudaSuccess) return st;
-    st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream);
+    // large batches: tensor-core logits with exact repair (same ids and weights); otherwise the exact-order kernels
+    cudaError_t st = rows >= router_fast_min_rows()
+                         ? launch_router_fast(plan, input, router_weight, correction_bias, rows, routed_scale, stream, false)
+                         : cudaErrorNotSupported;
+    if (st == cudaErrorNotSupported) {
+        st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream);
+        if (st != cudaSuccess) return st;
+        st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream);
+    }
     if (st != cudaSuccess) return st;
     st = launch_permute(plan, plan->ids, rows * kTop, plan->order, plan->position, plan->counts, plan->offsets, true, 1,
                         1 << 30, stream);
@@ -446,9 +452,15 @@ int p92b_ep_route_fixed(p92b_plan* plan, const uint16_t* input, const uint16_t* 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const int hidden = plan->hidden;
     plan->last_launches = 0;
-    cudaError_t st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream);
-    if (st != cudaSuccess) return st;
-    st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream);
+    // large batches: tensor-core logits with exact repair (same ids and weights); otherwise the exact-order kernels
+    cudaError_t st = rows >= router_fast_min_rows()
+                         ? launch_router_fast(plan, input, router_weight, correction_bias, rows, routed_scale, stream, false)
+                         : cudaErrorNotSupported;
+    if (st == cudaErrorNotSupported) {
+        st = launch_router_logits(input, router_weight, plan->logits, rows, kExperts, hidden, rows == 1, stream);
+        if (st != cudaSuccess) return st;
+        st = launch_router_top8(plan->logits, correction_bias, plan->ids, plan->route_weights, rows, routed_scale, stream);
+    }
     if (st != cudaSuccess) return st;
     st = launch_permute(plan, plan->ids, rows * kTop, plan->order, plan->position, plan->counts, plan->offsets, true, 1,
                         1 << 30, stream);

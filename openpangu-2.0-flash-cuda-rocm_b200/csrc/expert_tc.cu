@@ -776,6 +776,243 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
     }
 }
 
+// ---- down product for large batches: the token slab stays in shared memory ---------------------------------
+// At thousands of tokens both grouped products are bound by what one SM's copy engine takes in (about 55 GB/s
+// whatever the source), and in the tile-by-tile down kernel half of that intake is the token slab, loaded again
+// for each of the 20 row tiles of the weight.  Here an item is (128-token slab of an expert, half of the row
+// tiles): the slab's four K blocks (64 KB) and their scale slabs (8 KB) are loaded ONCE and stay resident, their
+// scale factors stay in TMEM, and only weight chunks stream through the ring - half the bytes per result.
+// Needs the whole K extent of a slab in shared memory: intermediate sizes up to 1024.
+struct DownSlab {
+    static constexpr int kN = 128;
+    static constexpr int kKBlocksMax = 4;
+    static constexpr int kBBytes = kKBlocksMax * (kN * kBlockKBytes + kSfSlab);     // 73,728
+    static constexpr int kOffBSf = kKBlocksMax * kN * kBlockKBytes;                 // scale slabs behind the boxes
+    static constexpr int kStages = 3;                                               // one chunk (two K blocks of the weight) each
+    static constexpr int kStageBytes = kChunkBytes;
+    static constexpr int kStoreBytes = 16 * 32 * 2;                                 // per epilogue warp: 16 tokens x 32 rows of BF16
+    static constexpr int kAccumBuffers = 2;
+    static constexpr int kSfbCols = kKBlocksMax * 16;                               // resident for an item
+    static constexpr int kSfaCols = 2 * 16;                                         // per chunk, two buffers
+    static constexpr int kTmemCols = 512;                                           // 2 * 128 + 64 + 2 * 32 = 384
+    static constexpr int kBarriers = 2 + 2 * kStages + 2 * kAccumBuffers;
+    static constexpr int kSmemBytes = kBBytes + kStages * kStageBytes + kEpilogueWarps * kStoreBytes + kBarriers * 8 + 16 + 1024;
+    static constexpr int kGroups = 2;                                               // row-tile halves per slab
+};
+
+__global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const __grid_constant__ CUtensorMap map_b,
+                                                                         const TcParams p) {
+    using C = DownSlab;
+    extern __shared__ std::uint8_t smem_raw[];
+    const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+    const std::uint32_t ring = base + C::kBBytes;
+    const std::uint32_t store_area = ring + C::kStages * C::kStageBytes;
+    const std::uint32_t bars = store_area + kEpilogueWarps * C::kStoreBytes;
+    const std::uint32_t b_full = bars, b_empty = bars + 8U;
+    auto weight_bar = [&](int s) { return bars + 8U * (2 + s); };
+    auto empty_bar = [&](int s) { return bars + 8U * (2 + C::kStages + s); };
+    auto accum_full = [&](int b) { return bars + 8U * (2 + 2 * C::kStages + b); };
+    auto accum_empty = [&](int b) { return bars + 8U * (2 + 2 * C::kStages + C::kAccumBuffers + b); };
+    const std::uint32_t tmem_slot = bars + 8U * C::kBarriers;
+    volatile std::uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile std::uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+    volatile std::uint32_t* abort_ptr = tmem_slot_ptr + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int k_blocks = p.k_bytes / kBlockKBytes;              // <= 4, even
+    const int chunks = k_blocks / 2;
+    const int tiles_per_group = p.m_tiles / C::kGroups;
+
+    if (threadIdx.x == 0) {
+        mbar_init(b_full, 1);
+        mbar_init(b_empty, 1);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(weight_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < C::kAccumBuffers; ++b) {
+            mbar_init(accum_full(b), 1);
+            mbar_init(accum_empty(b), kEpilogueWarps);
+        }
+        *abort_ptr = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    pdl_wait();                       // routing lists and the SwiGLU rows come from the kernels upstream
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    pdl_launch_dependents();
+    const std::uint32_t tmem_base = *tmem_slot_ptr;
+    const int total_items = p.tile_prefix[*p.route.active_count] * C::kGroups;      // tile_prefix counts 128-row slabs here
+    auto give_up = [&]() {
+        *abort_ptr = 1;
+        atomicCAS(p.status, kStatusOk, kStatusWaitExpired);
+    };
+    // item -> (slab, first row tile); decode_item wants an index over (slab, row tile)
+    auto decode = [&](int item, Item* it) {
+        const int slab = item / C::kGroups;
+        const int group = item - slab * C::kGroups;
+        const bool ok = decode_item<C::kN>(p, slab * p.m_tiles + group * tiles_per_group, it);
+        return ok;
+    };
+
+    if (warp == 0) {
+        if (elect_one()) {
+            int stage = 0;
+            std::uint32_t phase = 0, b_phase = 0;
+            for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
+                Item it;
+                if (!decode(item, &it)) continue;
+                if (!mbar_wait(b_empty, b_phase ^ 1U)) { give_up(); break; }
+                b_phase ^= 1U;
+                mbar_arrive_expect_tx(b_full, k_blocks * (C::kN * kBlockKBytes + kSfSlab));
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    tma_load_2d(base + kb * C::kN * kBlockKBytes, &map_b, b_full, kb * kBlockKBytes, it.pp0);
+                    bulk_load(base + C::kOffBSf + kb * kSfSlab,
+                              p.b_sf + (static_cast<std::size_t>(it.pp0 >> 7) * (p.k_bytes / 32) + kb * 4) * 512, kSfSlab, b_full);
+                }
+                bool ok = true;
+                for (int t = 0; t < tiles_per_group && ok; ++t) {
+                    const int m_tile = it.m_tile + t;
+                    for (int c = 0; c < chunks; ++c) {
+                        if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(); ok = false; break; }
+                        mbar_arrive_expect_tx(weight_bar(stage), kChunkBytes);
+                        bulk_load(ring + stage * C::kStageBytes,
+                                  p.bank.g2 + ((static_cast<std::size_t>(it.entry) * p.m_tiles + m_tile) * chunks + c) * kChunkBytes,
+                                  kChunkBytes, weight_bar(stage));
+                        if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
+                    }
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            int stage = 0;
+            std::uint32_t phase = 0, b_phase = 0;
+            int buffer = 0;
+            std::uint32_t accum_phase[2] = {0U, 0U};
+            constexpr std::uint32_t idesc = idesc_nvf4(kTileM, C::kN);
+            const std::uint32_t sfb_tmem = tmem_base + C::kAccumBuffers * C::kN;
+            const std::uint32_t sfa_tmem = sfb_tmem + C::kSfbCols;
+            int sfa_buffer = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_items && !*abort_ptr && ok; item += gridDim.x) {
+                Item it;
+                if (!decode(item, &it)) continue;
+                if (!mbar_wait(b_full, b_phase)) { give_up(); break; }
+                b_phase ^= 1U;
+                tc_fence_after();
+                // the slab's scale factors: 16 TMEM columns per K block, kept for the whole item
+                for (int kb = 0; kb < k_blocks; ++kb) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        tc_copy_sf(sfb_tmem + kb * 16 + k * 4, desc_scale_atom(base + C::kOffBSf + kb * kSfSlab + k * 512));
+                    }
+                }
+                for (int t = 0; t < tiles_per_group && ok; ++t) {
+                    if (!mbar_wait(accum_empty(buffer), accum_phase[buffer] ^ 1U)) { give_up(); ok = false; break; }
+                    tc_fence_after();
+                    const std::uint32_t accum = tmem_base + buffer * C::kN;
+                    for (int c = 0; c < chunks; ++c) {
+                        if (!mbar_wait(weight_bar(stage), phase)) { give_up(); ok = false; break; }
+                        tc_fence_after();
+                        const std::uint32_t st = ring + stage * C::kStageBytes;
+                        const std::uint32_t sfa = sfa_tmem + sfa_buffer * C::kSfaCols;
+#pragma unroll
+                        for (int o = 0; o < 2; ++o) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                tc_copy_sf(sfa + o * 16 + k * 4, desc_scale_atom(st + kChunkScaleOffset + o * kChunkScaleBytes + k * 512));
+                            }
+                        }
+#pragma unroll
+                        for (int o = 0; o < 2; ++o) {
+                            const int kb = 2 * c + o;
+                            const std::uint64_t a_desc = desc_k_major_sw128(st + o * kChunkBox);
+                            const std::uint64_t b_desc = desc_k_major_sw128(base + kb * C::kN * kBlockKBytes);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                mma_nvf4(accum, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa + o * 16 + k * 4,
+                                         sfb_tmem + kb * 16 + k * 4, kb > 0 || k > 0);
+                            }
+                        }
+                        tc_commit(empty_bar(stage));
+                        sfa_buffer ^= 1;
+                        if (++stage == C::kStages) { stage = 0; phase ^= 1U; }
+                    }
+                    if (!ok) break;
+                    tc_commit(accum_full(buffer));
+                    accum_phase[buffer] ^= 1U;
+                    buffer ^= 1;
+                }
+                if (!ok) break;
+                tc_commit(b_empty);           // every product that reads the slab has been issued and will have completed
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int sub = (warp - 2) >> 2;
+        int buffer = 0;
+        std::uint32_t accum_phase[2] = {0U, 0U};
+        bool ok = true;
+        for (int item = blockIdx.x; item < total_items && !*abort_ptr && ok; item += gridDim.x) {
+            Item it;
+            if (!decode(item, &it)) continue;
+            const float alpha = p.bank.alpha[it.entry * 3 + 2];
+            const int hidden = p.m_total;
+            for (int t = 0; t < tiles_per_group; ++t) {
+                if (!mbar_wait(accum_full(buffer), accum_phase[buffer])) { give_up(); ok = false; break; }
+                accum_phase[buffer] ^= 1U;
+                tc_fence_after();
+                const std::uint32_t lane_base = tmem_base + buffer * C::kN + (static_cast<std::uint32_t>(quarter * 32) << 16);
+                // A lane holds one weight row for 16 tokens; the output is token-major, so 2-byte stores would touch a
+                // 64-byte piece per instruction.  The warp turns its 32 x 16 block round through its own 1 KB of
+                // shared memory and stores 16 bytes per lane: 8 rows of one token.
+                std::uint16_t* stage_rows = reinterpret_cast<std::uint16_t*>(smem_raw + (store_area - smem_u32(smem_raw))) +
+                                            (warp - 2) * (C::kStoreBytes / 2);
+                const int first_row = (it.m_tile + t) * kTileM + quarter * 32;
+#pragma unroll 1
+                for (int c0 = sub * 16; c0 < C::kN; c0 += 16 * (kEpilogueWarps / 4)) {
+                    if (c0 >= it.valid) break;
+                    std::uint32_t d[16];
+                    tmem_load16(lane_base + c0, d);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage_rows[j * 32 + lane] = float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
+                    __syncwarp();
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int v = lane + 32 * h;                 // 64 pieces of 16 bytes: token v / 4, rows (v % 4) * 8 ..
+                        const int n = c0 + (v >> 2);
+                        if (n < it.valid) {
+                            *reinterpret_cast<uint4*>(p.out + static_cast<std::size_t>(it.pp0 + n) * hidden + first_row + (v & 3) * 8) =
+                                *reinterpret_cast<const uint4*>(stage_rows + (v >> 2) * 32 + (v & 3) * 8);
+                        }
+                    }
+                    __syncwarp();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accum_empty(buffer));
+                buffer ^= 1;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
 // Quantises the token rows into the padded position space of the tensor-core
 // kernels: row pp gets the NVFP4 bytes of its token, and the scales go straight
 // into the 128x4-tiled layout (cuda/nvfp4_ops.cu:818-841 and :869-890 in one pass).
@@ -1019,6 +1256,14 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
             if (plan->wide_rows == 128) {
                 // every expert segment starts on a multiple of 128 padded rows, so 128-row tiles stay inside it
                 p.tile_prefix = plan->tile_prefix_wide;
+                const int k_blocks = p.k_bytes / kBlockKBytes;
+                if (io == nullptr && k_blocks <= DownSlab::kKBlocksMax && k_blocks % 2 == 0 && p.m_tiles % DownSlab::kGroups == 0 &&
+                    std::getenv("P92B_NO_DOWN_SLAB") == nullptr) {
+                    // the token slab resident in shared memory, only weights streaming
+                    if (cudaError_t st = ensure_dynamic_smem<expert_down_slab_kernel>(DownSlab::kSmemBytes); st != cudaSuccess) return st;
+                    return launch_kernel(expert_down_slab_kernel, dim3(plan->sm_count), dim3(kThreadsTc), DownSlab::kSmemBytes,
+                                         stream, pdl, plan->map_h[3], p);
+                }
                 return launch_tc<1, 128>(plan, plan->map_h[3], p, stream, pdl);
             }
             return launch_tc<1, 64>(plan, plan->map_h[2], p, stream, pdl);

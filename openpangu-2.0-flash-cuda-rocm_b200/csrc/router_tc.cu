@@ -77,9 +77,17 @@ __global__ void __launch_bounds__(256) expert_norms_kernel(const std::uint16_t* 
     const int lane = threadIdx.x & 31;
     if (e >= experts) return;
     float s = 0.0F;
-    for (int c = lane; c < hidden; c += 32) {
-        const float v = bf16_bits_to_float(w[static_cast<std::size_t>(e) * hidden + c]);
-        s = fmaf(v, v, s);
+    const uint4* row = reinterpret_cast<const uint4*>(w + static_cast<std::size_t>(e) * hidden);
+#pragma unroll 4
+    for (int v = lane; v < hidden / 8; v += 32) {
+        const uint4 q = __ldg(row + v);
+        const std::uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float lo = __uint_as_float(words[k] << 16), hi = __uint_as_float(words[k] & 0xffff0000U);
+            s = fmaf(lo, lo, s);
+            s = fmaf(hi, hi, s);
+        }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffU, s, off);
@@ -195,6 +203,11 @@ __global__ void __launch_bounds__(kLogitThreads, 1) logits_tc_kernel(const __gri
     }
 }
 
+// 16-byte asynchronous copy global -> shared.
+__device__ __forceinline__ void copy16_async(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+
 // Exact logit of (token row in shared memory, router row in global memory) in the reference's T > 1 order.
 __device__ __forceinline__ float exact_logit(const std::uint16_t* __restrict__ x_row, const std::uint16_t* __restrict__ w_row,
                                              int hidden, int lane) {
@@ -208,8 +221,15 @@ __device__ __forceinline__ float exact_logit(const std::uint16_t* __restrict__ x
     return __shfl_sync(0xffffffffU, value, 0);
 }
 
-constexpr int kRepairWarps = 8;
+constexpr int kRepairWarps = 4;
+constexpr int kRepairDepth = 3;                // router rows in flight per warp (register variant)
 
+// CHUNKS = hidden / 32 > 0: the lane's columns of the token row (l, l+32, ...) stay in registers and every candidate's
+// router row is brought into shared memory by asynchronous 16-byte copies two candidates ahead (three buffers per warp:
+// the rows come from the L2 at about a microsecond each, and 171 MB of them at T=4096 make the L2-to-SM fabric the bound),
+// so a chain costs a shared-memory read, a shift and an fmaf per column instead of two 2-byte loads from the L2 that
+// the chain has to wait for.  CHUNKS = 0: any hidden size, token row in shared memory, router rows read in place.
+template <int CHUNKS>
 __global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
     const std::uint16_t* __restrict__ x, const std::uint16_t* __restrict__ w, const float* __restrict__ bias,
     const float* __restrict__ w_norms, float* __restrict__ logits, std::int32_t* __restrict__ ids,
@@ -221,19 +241,31 @@ __global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
     const int lane = threadIdx.x & 31;
     const int token = blockIdx.x * kRepairWarps + warp;
     if (token >= rows) return;
-    std::uint16_t* x_row = repair_smem + static_cast<std::size_t>(warp) * hidden;
-    float* exact_row = reinterpret_cast<float*>(repair_smem + static_cast<std::size_t>(kRepairWarps) * hidden) + warp * kExperts;
-    // the token row into shared memory (16-byte loads) and its norm
+    // per warp: [CHUNKS > 0: two router-row buffers | CHUNKS == 0: the token row], then 256 exact logits, then the candidate list
+    constexpr int kRowSlots = CHUNKS > 0 ? kRepairDepth : 1;
+    std::uint16_t* x_row = repair_smem + static_cast<std::size_t>(warp) * kRowSlots * hidden;
+    std::uint8_t* tail = reinterpret_cast<std::uint8_t*>(repair_smem + static_cast<std::size_t>(kRepairWarps) * kRowSlots * hidden);
+    float* exact_row = reinterpret_cast<float*>(tail) + warp * kExperts;
+    std::uint16_t* cand = reinterpret_cast<std::uint16_t*>(tail + kRepairWarps * kExperts * 4) + warp * kExperts;
+    float xr[CHUNKS > 0 ? CHUNKS : 1];
     float square = 0.0F;
-    for (int v = lane; v < hidden / 8; v += 32) {
-        const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(token) * hidden) + v);
-        reinterpret_cast<uint4*>(x_row)[v] = q;
-        const std::uint32_t words[4] = {q.x, q.y, q.z, q.w};
+    if constexpr (CHUNKS > 0) {
+        const std::uint16_t* xg = x + static_cast<std::size_t>(token) * hidden + lane;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float lo = __uint_as_float(words[k] << 16), hi = __uint_as_float(words[k] & 0xffff0000U);
-            square = fmaf(lo, lo, square);
-            square = fmaf(hi, hi, square);
+        for (int j = 0; j < CHUNKS; ++j) xr[j] = bf16_bits_to_float(__ldg(xg + 32 * j));
+#pragma unroll
+        for (int j = 0; j < CHUNKS; ++j) square = fmaf(xr[j], xr[j], square);
+    } else {
+        for (int v = lane; v < hidden / 8; v += 32) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(token) * hidden) + v);
+            reinterpret_cast<uint4*>(x_row)[v] = q;
+            const std::uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float lo = __uint_as_float(words[k] << 16), hi = __uint_as_float(words[k] & 0xffff0000U);
+                square = fmaf(lo, lo, square);
+                square = fmaf(hi, hi, square);
+            }
         }
     }
 #pragma unroll
@@ -297,14 +329,46 @@ __global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
     }
     // exact logits of the candidates (or of the whole row), into the logits buffer and into this warp's row
     for (int e = lane; e < kExperts; e += 32) exact_row[e] = -3.0e38F;       // non-candidates can never be selected
-    __syncwarp();
-#pragma unroll 1
+    int n_cand = 0;
+#pragma unroll
     for (int i = 0; i < 8; ++i) {
-        unsigned todo = member[i];
-        while (todo != 0U) {
-            const int src_lane = __ffs(todo) - 1;
-            todo &= todo - 1U;
-            const int e = src_lane + 32 * i;
+        if ((member[i] >> lane) & 1U) cand[n_cand + __popc(member[i] & ((1U << lane) - 1U))] = static_cast<std::uint16_t>(lane + 32 * i);
+        n_cand += __popc(member[i]);
+    }
+    __syncwarp();
+    if constexpr (CHUNKS > 0) {
+        auto fetch = [&](int k) {
+            if (k < n_cand) {
+                const uint4* src = reinterpret_cast<const uint4*>(w + static_cast<std::size_t>(cand[k]) * hidden);
+                uint4* dst = reinterpret_cast<uint4*>(x_row + static_cast<std::size_t>(k % kRepairDepth) * hidden);
+                for (int v = lane; v < hidden / 8; v += 32) copy16_async(dst + v, src + v);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");       // an empty group keeps the count in step
+        };
+#pragma unroll
+        for (int k = 0; k < kRepairDepth - 1; ++k) fetch(k);
+#pragma unroll 1
+        for (int k = 0; k < n_cand; ++k) {
+            fetch(k + kRepairDepth - 1);                        // its buffer was last read by candidate k - 1
+            asm volatile("cp.async.wait_group %0;" ::"n"(kRepairDepth - 1) : "memory");
+            __syncwarp();
+            const std::uint16_t* w_row = x_row + static_cast<std::size_t>(k % kRepairDepth) * hidden + lane;
+            float value = 0.0F;
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j) value = fmaf(xr[j], bf16_bits_to_float(w_row[32 * j]), value);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
+            if (lane == 0) {
+                const int e = cand[k];
+                exact_row[e] = value;
+                lg[e] = value;
+            }
+            __syncwarp();                                       // every lane is done with this buffer before it is refilled
+        }
+    } else {
+#pragma unroll 1
+        for (int k = 0; k < n_cand; ++k) {
+            const int e = cand[k];
             const float value = exact_logit(x_row, w + static_cast<std::size_t>(e) * hidden, hidden, lane);
             if (lane == 0) {
                 exact_row[e] = value;
@@ -392,15 +456,20 @@ cudaError_t launch_router_fast(p92b_plan* plan, const std::uint16_t* x, const st
     if (st == cudaSuccess) st = make_operand_map(&map_w, router_w, kExperts, static_cast<std::size_t>(hidden) * 2, kExpTile);
     if (st != cudaSuccess) return cudaErrorNotSupported;
     if ((st = ensure_dynamic_smem<logits_tc_kernel>(kLogitSmem)) != cudaSuccess) return st;
-    const std::size_t repair_smem = static_cast<std::size_t>(kRepairWarps) * hidden * 2 + static_cast<std::size_t>(kRepairWarps) * kExperts * 4;
-    if ((st = ensure_dynamic_smem<route_repair_kernel>(static_cast<int>(repair_smem))) != cudaSuccess) return st;
+    const bool in_registers = hidden == 2560;
+    const std::size_t repair_smem = static_cast<std::size_t>(kRepairWarps) * (in_registers ? kRepairDepth : 1) * hidden * 2 +
+                                    static_cast<std::size_t>(kRepairWarps) * kExperts * (4 + 2);
+    st = in_registers ? ensure_dynamic_smem<route_repair_kernel<80>>(static_cast<int>(repair_smem))
+                      : ensure_dynamic_smem<route_repair_kernel<0>>(static_cast<int>(repair_smem));
+    if (st != cudaSuccess) return st;
     st = launch_kernel(expert_norms_kernel, dim3(kExperts / 8), dim3(256), 0, stream, pdl, router_w, plan->w_norms, kExperts, hidden);
     if (st != cudaSuccess) return st;
     st = launch_kernel(logits_tc_kernel, dim3((rows + kTokTile - 1) / kTokTile, kExperts / kExpTile), dim3(kLogitThreads),
                        kLogitSmem, stream, pdl, map_x, map_w, plan->logits, rows, hidden, plan->status);
     if (st != cudaSuccess) return st;
-    st = launch_kernel(route_repair_kernel, dim3((rows + kRepairWarps - 1) / kRepairWarps), dim3(kRepairWarps * 32), repair_smem,
-                       stream, pdl, x, router_w, bias, static_cast<const float*>(plan->w_norms), plan->logits, plan->ids,
+    st = launch_kernel(in_registers ? route_repair_kernel<80> : route_repair_kernel<0>,
+                       dim3((rows + kRepairWarps - 1) / kRepairWarps), dim3(kRepairWarps * 32), repair_smem, stream, pdl, x,
+                       router_w, bias, static_cast<const float*>(plan->w_norms), plan->logits, plan->ids,
                        plan->route_weights, rows, hidden, routed_scale, plan->router_stats);
     plan->last_launches += 3;
     return st;
