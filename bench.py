@@ -432,6 +432,14 @@ class SingleGpu:
                          "timing": "one launch per layer call back to back on one stream: step time / calls (an event pair per "
                                    "launch would break the overlap of consecutive launches)"},
         }
+        if rows > 8:
+            # the multi-kernel pipeline: per-stage device times from event pairs inside the library
+            plan.stage_timing(True)
+            for _ in range(2 * n_layers):
+                step_one()
+            stage_ms, calls = plan.stage_times()
+            plan.stage_timing(False)
+            rec["stage_us"] = {k: v / calls * 1e3 for k, v in stage_ms.items()}
         if name == "cfg0":
             rec["target_us"] = 8.99
         if e2e:

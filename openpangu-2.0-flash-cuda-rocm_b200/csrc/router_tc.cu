@@ -441,7 +441,7 @@ __global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
 
 }  // namespace
 
-int router_fast_min_rows() { return 256; }
+int router_fast_min_rows() { return 32; }
 
 cudaError_t launch_router_fast(p92b_plan* plan, const std::uint16_t* x, const std::uint16_t* router_w, const float* bias,
                                int rows, float routed_scale, cudaStream_t stream, bool pdl) {

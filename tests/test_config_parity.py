@@ -17,6 +17,7 @@ pytestmark = pytest.mark.gpu
 
 REL_L2 = 1e-2
 MAX_ABS = 2e-2
+FAST_ROUTER_ROWS = 32        # from this batch size on the block takes tensor-core logits with exact repair
 
 
 def _stream(torch):
@@ -72,7 +73,7 @@ def _check_block_against_reference(torch, pkg, orc, layer0, bias, x, out, views,
     ref_logits = torch.empty((rows, 256), dtype=torch.float32, device="cuda")
     assert orc.ref().ref_bf16_gemm_f32(x.data_ptr(), layer0.router_weight.data_ptr(), ref_logits.data_ptr(), rows, 256,
                                        2560, _stream(torch)) == 0
-    if rows < 256:
+    if rows < FAST_ROUTER_ROWS:
         assert torch.equal(views["logits"], ref_logits)
     ref_ids = torch.empty((rows, 8), dtype=torch.int32, device="cuda")
     ref_w = torch.empty((rows, 8), dtype=torch.float32, device="cuda")
@@ -80,8 +81,8 @@ def _check_block_against_reference(torch, pkg, orc, layer0, bias, x, out, views,
                                           rows, 2.5, _stream(torch)) == 0
     assert torch.equal(views["expert_ids"], ref_ids)
     assert torch.equal(views["expert_weights"], ref_w)
-    if rows >= 256:
-        # large batches: tensor-core logits, exact only where they can decide the routing.  The selected experts' logits
+    if rows >= FAST_ROUTER_ROWS:
+        # larger batches: tensor-core logits, exact only where they can decide the routing.  The selected experts' logits
         # are the reference's bit for bit; everywhere else the deviation must stay far (8x) inside the bound the repair
         # assumes, 2^-14 * ||x|| * ||w|| (about 3e-3 here)
         picked = ref_ids.long()
