@@ -148,7 +148,7 @@ def ep_mode(workload: str, world: int) -> str:
         return "fused"
     if rows <= 512 and world * rows <= 1024:
         return "gathered"
-    return "exact"
+    return "bulk"
 
 
 def ep_rows(workload: str, world: int) -> int:
@@ -161,6 +161,9 @@ PARALLELISM = {
     "fused": "one kernel per GPU and layer, dispatch (all-gather) and combine by peer stores over NVLink inside the kernel",
     "gathered": "all-gather dispatch and direct placement of result rows by the library's own kernels (peer stores over "
                 "NVLink, polled words), grouped tcgen05 products in between; no NCCL, no host sync",
+    "bulk": "all-gather dispatch and direct placement of result rows by the library's own kernels (16-byte peer stores over "
+            "NVLink, one flag per peer and exchange), permutation over the whole batch restricted to the local experts, "
+            "grouped tcgen05 products; no NCCL, no host sync",
     "fixed": "NCCL all-to-all dispatch and combine, fixed-capacity blocks, no host sync",
     "exact": "NCCL all-to-all dispatch and combine, exact-size splits",
 }
@@ -662,13 +665,13 @@ class ExpertParallel:
         self.timer = Timer(torch, dist)
         self.windows_ok = None
 
-    def window_and_plan(self, rows):
+    def window_and_plan(self, rows, bulk=False):
         """One window and one plan serve all layers of a workload.  If the windows cannot be mapped into one
         another (no inter-process memory handles in this environment) every rank falls back to NCCL."""
         torch, dist = self.torch, self.dist
         ok, window, plan = 1, None, None
         try:
-            window = self.ep.EpWindow(self.rank, self.world, rows)
+            window = self.ep.EpWindow(self.rank, self.world, rows, bulk=bulk)
             plan = self.pkg.MoePlan(max_rows=self.world * rows)
         except Exception as exc:                                 # noqa: BLE001 - any failure means "no peer windows"
             ok = 0
@@ -688,8 +691,8 @@ class ExpertParallel:
         n_layers = min(layers_wanted, len(self.banks))
         mode = ep_mode(name, world)
         window = plan = None
-        if mode in ("fused", "gathered"):
-            window, plan = self.window_and_plan(rows)
+        if mode in ("fused", "gathered", "bulk"):
+            window, plan = self.window_and_plan(rows, bulk=mode == "bulk")
             if window is None:
                 mode = "fixed" if rows <= ep.FIXED_MAX_ROWS else "exact"
         biases = []
@@ -714,6 +717,8 @@ class ExpertParallel:
                 ep.forward_fused(window, plan, self.banks[l], self.routers[l], biases[l], x, o, rows)
             elif mode == "gathered":
                 ep.forward_gathered(window, plan, self.banks[l], self.routers[l], biases[l], x, o, rows)
+            elif mode == "bulk":
+                ep.forward_bulk(window, plan, self.banks[l], self.routers[l], biases[l], x, o, rows)
             elif mode == "fixed":
                 ep.forward_nccl_fixed(states[l], x, o, rows, 8 * rows)
             else:
@@ -728,9 +733,10 @@ class ExpertParallel:
         for _ in range(warmup):
             step()
         ms, repeats = self.timer.run(step, steps, min_seconds, sampler)
-        count_plan = plan if mode in ("fused", "gathered") else states[-1].arrivals
-        home_plan = plan if mode in ("fused", "gathered") else states[-1].home
-        if mode in ("fused", "gathered"):
+        own = mode in ("fused", "gathered", "bulk")
+        count_plan = plan if own else states[-1].arrivals
+        home_plan = plan if own else states[-1].home
+        if own:
             launches = count_plan.last_launches
         else:    # the library's kernels of route + experts + combine, counted by the three plans they run on
             launches = states[-1].home.last_launches + states[-1].arrivals.last_launches + states[-1].shared.last_launches
@@ -764,6 +770,29 @@ class ExpertParallel:
         }
         if mode == "exact":
             rec["exposed_communication"] = self.exposed_communication(states, xs, outs, rows, n_layers, ms)
+        if mode == "bulk":
+            # event pairs inside the library around the parts of the layer: the two exchange parts hold the peer stores
+            # AND the wait for the slowest peer, i.e. everything a GPU spends not computing
+            plan.stage_timing(True)
+            self.timer.barrier()
+            for _ in range(5):
+                for l in range(n_layers):
+                    forward(l, xs[l], outs[l])
+            stage_ms, calls = plan.stage_times()
+            plan.stage_timing(False)
+            names = ("router", "dispatch_exchange", "permute_and_placement", "unused", "gate_up_swiglu", "down",
+                     "return_exchange_and_combine")
+            per_call = [v / calls * 1e3 for v in stage_ms.values()]
+            stage_us = {n: self.timer.max_over_ranks(v) for n, v in zip(names, per_call) if n != "unused"}
+            exchange = stage_us["dispatch_exchange"] + stage_us["return_exchange_and_combine"]
+            rec["stage_us_max_over_ranks"] = stage_us
+            rec["exposed_communication"] = {
+                "wall_ms_per_step": ms, "exchange_us_per_layer": exchange, "compute_us_per_layer": sum(stage_us.values()) - exchange,
+                "exposed_ms": exchange * n_layers * 1e-3,
+                "definition": "per layer, max over ranks: peer stores of the dispatch + wait for every peer's rows, and peer stores of "
+                              "the results + wait for every peer's results + the slot-order combine; nothing overlaps them in this "
+                              "orchestration (stage times with a stream synchronisation per call, so they add up to a little more "
+                              "than the wall time)"}
         if e2e:
             rec["e2e"] = self.e2e(mode, window, plan, biases, forward, xs, outs, rows, n_layers)
         if window is not None:

@@ -418,6 +418,23 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
                              const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
                              float routed_scale, void* stream);
 
+/* Large batches (hundreds to thousands of tokens per GPU): the same two exchanges - all-gather of the quantised
+ * rows and ids, direct placement of the result rows - as plain 16-byte peer stores with one flag word per peer and
+ * exchange (system-scope release / bounded acquire poll) instead of tagged words, around the grouped tcgen05
+ * kernels and the large-batch router.  No collective library, no split sizes crossing to the host, no host
+ * synchronisation: the whole layer is asynchronous on `stream`.  Every GPU runs the permutation law over the ids of
+ * the whole batch restricted to its own experts (cuda/nvfp4_grouped.cu:117-132), and the home GPU combines in slot
+ * order (cuda/nvfp4_ops.cu:124-142), so ids, per-expert row order and the combine are the single-device ones.
+ * The window is created with p92b_ep_window_create_bulk (world * rows_per_gpu * 1.5 KB + rows_per_gpu * 40 KB of
+ * exchange memory), published and connected like the other windows, and serves only this call; rows may differ per
+ * GPU and per call (rows <= rows_per_gpu), the plan must hold world * rows_per_gpu rows.  Same calling rule: all
+ * GPUs make the same sequence of calls on their windows; a peer that never arrives ends the wait after about a
+ * second with status 2. */
+int p92b_ep_window_create_bulk(p92b_ep_window** out, int rank, int world, int rows_per_gpu, int hidden);
+int p92b_ep_forward_bulk(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window* window, const uint16_t* input,
+                         const uint16_t* router_weight, const float* correction_bias, uint16_t* output, int rows,
+                         float routed_scale, void* stream);
+
 /* Device views of the last p92b_moe_forward's intermediates, for tests and
  * tracing (the reference keeps the same buffers as Model::Impl members,
  * src/model.cpp:872-885).  Valid until the next call on the plan. */

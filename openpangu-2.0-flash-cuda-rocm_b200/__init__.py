@@ -105,6 +105,8 @@ SIGNATURES = {
     "p92b_ep_window_handle": (c_int, [c_void_p, c_void_p]),
     "p92b_ep_window_connect": (c_int, [c_void_p, c_void_p]),
     "p92b_ep_window_connect_local": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "p92b_ep_window_create_bulk": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_int]),
+    "p92b_ep_forward_bulk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_ep_forward_gathered": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_ep_forward_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "p92b_ep_forward_fused_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),

@@ -905,6 +905,7 @@ int p92b_ep_forward_fused(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window
         correction_bias == nullptr || output == nullptr || rows <= 0 || rows > window->rows_per_gpu) {
         return cudaErrorInvalidValue;
     }
+    if (window->bulk) return cudaErrorNotSupported;     // a large-batch window has another layout
     if (!window->connected || !window->fused_ok || !plan->tc_ready || !bank->tc_ready || plan->hidden != 2560 || plan->intermediate != 1024 ||
         bank->view.hidden != 2560 || bank->view.intermediate != 1024 || bank->view.local_experts != kExperts / window->world ||
         bank->view.first_expert != window->rank * (kExperts / window->world) ||

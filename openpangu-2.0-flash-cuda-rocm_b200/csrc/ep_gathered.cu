@@ -382,6 +382,7 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
     const int local = kExperts / world;
     // one source: its token count is the batch; several: every slot of every GPU, empty ones marked by their owner
     const int tokens = world == 1 ? rows : world * rpg;
+    if (window->bulk) return cudaErrorNotSupported;     // a large-batch window has another layout
     if (!window->connected || !plan->tc_ready || !bank->tc_ready || plan->hidden != 2560 || plan->intermediate != 1024 ||
         bank->view.hidden != 2560 || bank->view.intermediate != 1024 || bank->view.local_experts != local ||
         bank->view.first_expert != window->rank * local || plan->max_rows < tokens) {

@@ -296,6 +296,8 @@ struct p92b_ep_window {
     bool opened[16] = {};
     bool connected = false;
     bool fused_ok = false;                // small enough for the single-kernel path
+    bool bulk = false;                    // a window of the large-batch path (p92b_ep_window_create_bulk): its own layout
+    int bulk_hidden = 0;
     unsigned epoch = 0;                   // calls so far (the same number on every GPU)
     std::size_t bytes = 0;
     std::size_t gathered_base = 0;        // offset of the regions of the multi-kernel gathered path
@@ -348,10 +350,14 @@ cudaError_t launch_router_logits(const std::uint16_t* x, const std::uint16_t* w,
 cudaError_t launch_router_top8(const float* logits, const float* bias, std::int32_t* ids,
                                float* weights, int rows, float routed_scale, cudaStream_t stream,
                                bool pdl = false);
+// range_count >= 0 restricts the permutation to expert ids [range_first, range_first + range_count): other ids
+// (another GPU's experts, -1 for an empty token slot) are skipped and get position -1.  shared_rows >= 0 overrides
+// the shared expert's row count in the lists (default: assignments / 8).
 cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignments,
                            std::int32_t* order, std::int32_t* position, std::int32_t* counts,
                            std::int32_t* offsets, bool route_lists, int pad_align, int tile_rows,
-                           cudaStream_t stream, bool pdl = false);
+                           cudaStream_t stream, bool pdl = false, int range_first = 0, int range_count = -1,
+                           int shared_rows = -1);
 int route_fused_max_rows();
 cudaError_t launch_route_fused(p92b_plan* plan, const float* bias, float routed_scale, const std::uint16_t* x,
                                int rows, int pad_align, int tile_rows, cudaStream_t stream, bool pdl);

@@ -25,18 +25,31 @@ namespace {
 constexpr int kChunk = 256;          // flat indices per warp in the multi-block path
 constexpr int kWarps = 8;
 
+// Which expert ids take part.  The whole range by default; an expert-parallel GPU that holds the ids of the whole
+// batch restricts the permutation to its own experts [first, first + count) - ids outside (other GPUs' experts, and
+// -1 for an empty token slot) are then skipped, not clamped: they get no position and are not counted.
+struct IdRange {
+    int first = 0;
+    int count = kExperts;
+    int restricted = 0;
+};
+
 // Counts the experts of one chunk into hist[256] (owned by the calling warp).
 // `cached` (optional): the chunk's ids already in shared memory, cached[i - begin].
 __device__ __forceinline__ void warp_histogram(const std::int32_t* __restrict__ ids, int begin, int end,
                                                std::int32_t* hist, std::int32_t* status,
-                                               const std::int16_t* cached = nullptr) {
+                                               const std::int16_t* cached = nullptr, IdRange range = IdRange()) {
     const int lane = threadIdx.x & 31;
     for (int e = lane; e < kExperts; e += 32) hist[e] = 0;
     __syncwarp();
     for (int base = begin; base < end; base += 32) {
         const int i = base + lane;
-        const bool valid = i < end;
+        bool valid = i < end;
         int e = valid ? (cached != nullptr ? static_cast<int>(cached[i - begin]) : ids[i]) : -1;
+        if (range.restricted && (e < range.first || e >= range.first + range.count)) {
+            valid = false;
+            e = -1;
+        }
         if (valid && (e < 0 || e >= kExperts)) {
             atomicCAS(status, kStatusOk, kStatusBadExpertId);
             e = e < 0 ? 0 : kExperts - 1;
@@ -56,14 +69,22 @@ __device__ __forceinline__ void warp_scatter(const std::int32_t* __restrict__ id
                                              std::int32_t* __restrict__ row_token,
                                              const std::int32_t* offsets, const std::int32_t* pp_off,
                                              std::int32_t* __restrict__ pp_of_flat,
-                                             const std::int16_t* cached = nullptr) {
+                                             const std::int16_t* cached = nullptr, IdRange range = IdRange()) {
     const int lane = threadIdx.x & 31;
     for (int e = lane; e < kExperts; e += 32) running[e] = base[e];
     __syncwarp();
     for (int step = begin; step < end; step += 32) {
         const int i = step + lane;
-        const bool valid = i < end;
+        bool valid = i < end;
         int e = valid ? (cached != nullptr ? static_cast<int>(cached[i - begin]) : ids[i]) : -1;
+        if (range.restricted && (e < range.first || e >= range.first + range.count)) {
+            if (valid) {                      // skipped: no position
+                if (position != nullptr) position[i] = -1;
+                if (pp_of_flat != nullptr) pp_of_flat[i] = -1;
+            }
+            valid = false;
+            e = -1;
+        }
         if (valid) e = e < 0 ? 0 : (e >= kExperts ? kExperts - 1 : e);
         const unsigned peers = __match_any_sync(0xffffffffU, e);
         const int rank = __popc(peers & ((1U << lane) - 1U));
@@ -164,7 +185,7 @@ __device__ __forceinline__ void write_route_lists(int e, int count, int offset, 
 __global__ void __launch_bounds__(256) permute_small_kernel(
     const std::int32_t* __restrict__ ids, int assignments, std::int32_t* order,
     std::int32_t* position, RouteLists lists, std::int32_t* row_token, std::int32_t* pp_of_flat,
-    std::int32_t* status) {
+    std::int32_t* status, IdRange range, int shared_rows) {
     __shared__ std::int32_t hist[kWarps][kExperts];
     __shared__ std::int32_t running[kWarps][kExperts];
     __shared__ std::int32_t scan_scratch[kWarps];
@@ -182,7 +203,7 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
         cached_ids[warp][i - begin] = static_cast<std::int16_t>(e < -1 ? -1 : (e > kExperts ? kExperts : e));   // out-of-range stays out of range
     }
     __syncwarp();
-    warp_histogram(ids, begin, end, hist[warp], status, cached_ids[warp]);
+    warp_histogram(ids, begin, end, hist[warp], status, cached_ids[warp], range);
     __syncthreads();
     const int e = threadIdx.x;
     int total = 0;
@@ -195,11 +216,11 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
     const int offset = block_exclusive_scan_256(total, scan_scratch);
 #pragma unroll
     for (int wi = 0; wi < kWarps; ++wi) hist[wi][e] += offset;
-    const int rows = assignments / kTop;
+    const int rows = shared_rows >= 0 ? shared_rows : assignments / kTop;
     write_route_lists(e, total, offset, assignments, rows, lists, scan_scratch);
     __syncthreads();
     warp_scatter(ids, begin, end, hist[warp], running[warp], order, position, row_token, lists.offsets, lists.pp_off,
-                 pp_of_flat, cached_ids[warp]);
+                 pp_of_flat, cached_ids[warp], range);
     if (row_token != nullptr) {
         for (int t = threadIdx.x; t < rows; t += blockDim.x) {
             row_token[assignments + t] = t;
@@ -212,7 +233,7 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
 __global__ void __launch_bounds__(256) permute_hist_kernel(const std::int32_t* __restrict__ ids,
                                                            int assignments,
                                                            std::int32_t* __restrict__ chunk_hist,
-                                                           std::int32_t* status) {
+                                                           std::int32_t* status, IdRange range) {
     __shared__ std::int32_t hist[kWarps][kExperts];
     pdl_launch_dependents();
     pdl_wait();
@@ -221,14 +242,14 @@ __global__ void __launch_bounds__(256) permute_hist_kernel(const std::int32_t* _
     const int chunk = blockIdx.x * kWarps + warp;
     const int begin = min(assignments, chunk * kChunk);
     const int end = min(assignments, begin + kChunk);
-    warp_histogram(ids, begin, end, hist[warp], status);
+    warp_histogram(ids, begin, end, hist[warp], status, nullptr, range);
     if (begin < assignments) {
         for (int e = lane; e < kExperts; e += 32) chunk_hist[static_cast<std::size_t>(chunk) * kExperts + e] = hist[warp][e];
     }
 }
 
 __global__ void __launch_bounds__(256) permute_scan_kernel(std::int32_t* __restrict__ chunk_hist, int chunks,
-                                                           int assignments, RouteLists lists) {
+                                                           int assignments, RouteLists lists, int shared_rows) {
     __shared__ std::int32_t scan_scratch[kWarps];
     pdl_launch_dependents();
     pdl_wait();
@@ -242,13 +263,14 @@ __global__ void __launch_bounds__(256) permute_scan_kernel(std::int32_t* __restr
         total += v;
     }
     const int offset = block_exclusive_scan_256(total, scan_scratch);
-    write_route_lists(e, total, offset, assignments, assignments / kTop, lists, scan_scratch);
+    write_route_lists(e, total, offset, assignments, shared_rows >= 0 ? shared_rows : assignments / kTop, lists, scan_scratch);
 }
 
 __global__ void __launch_bounds__(256) permute_scatter_kernel(
     const std::int32_t* __restrict__ ids, int assignments, const std::int32_t* __restrict__ chunk_hist,
     const std::int32_t* __restrict__ offsets, std::int32_t* order, std::int32_t* position,
-    std::int32_t* row_token, const std::int32_t* __restrict__ pp_off, std::int32_t* pp_of_flat) {
+    std::int32_t* row_token, const std::int32_t* __restrict__ pp_off, std::int32_t* pp_of_flat, IdRange range,
+    int shared_rows) {
     __shared__ std::int32_t base[kWarps][kExperts];
     __shared__ std::int32_t running[kWarps][kExperts];
     pdl_launch_dependents();
@@ -264,9 +286,10 @@ __global__ void __launch_bounds__(256) permute_scatter_kernel(
         }
     }
     __syncwarp();
-    warp_scatter(ids, begin, end, base[warp], running[warp], order, position, row_token, offsets, pp_off, pp_of_flat);
+    warp_scatter(ids, begin, end, base[warp], running[warp], order, position, row_token, offsets, pp_off, pp_of_flat,
+                 nullptr, range);
     if (row_token != nullptr) {
-        const int rows = assignments / kTop;
+        const int rows = shared_rows >= 0 ? shared_rows : assignments / kTop;
         const int t = blockIdx.x * blockDim.x + threadIdx.x;
         if (t < rows) {
             row_token[assignments + t] = t;
@@ -430,7 +453,13 @@ cudaError_t launch_route_fused(p92b_plan* plan, const float* bias, float routed_
 cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignments,
                            std::int32_t* order, std::int32_t* position, std::int32_t* counts,
                            std::int32_t* offsets, bool route_lists, int pad_align, int tile_rows,
-                           cudaStream_t stream, bool pdl) {
+                           cudaStream_t stream, bool pdl, int range_first, int range_count, int shared_rows) {
+    IdRange range;
+    if (range_count >= 0) {
+        range.first = range_first;
+        range.count = range_count;
+        range.restricted = 1;
+    }
     if (plan == nullptr || ids == nullptr || counts == nullptr || offsets == nullptr || assignments <= 0 ||
         assignments > plan->max_rows * kTop) {
         return cudaErrorInvalidValue;
@@ -457,22 +486,23 @@ cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignm
     if (assignments <= kWarps * 1024) {
         plan->last_launches += 1;
         return launch_kernel(permute_small_kernel, dim3(1), dim3(256), 0, stream, pdl, ids, assignments, order, position,
-                             lists, row_token, pp_of_flat, plan->status);
+                             lists, row_token, pp_of_flat, plan->status, range, shared_rows);
     }
     const int chunks = (assignments + kChunk - 1) / kChunk;
     if (chunks > plan->chunks) return cudaErrorInvalidValue;
     const int blocks = (chunks + kWarps - 1) / kWarps;
     plan->last_launches += 3;
     cudaError_t st = launch_kernel(permute_hist_kernel, dim3(blocks), dim3(256), 0, stream, pdl, ids, assignments,
-                                   plan->chunk_hist, plan->status);
+                                   plan->chunk_hist, plan->status, range);
     if (st != cudaSuccess) return st;
     st = launch_kernel(permute_scan_kernel, dim3(1), dim3(256), 0, stream, pdl, plan->chunk_hist, chunks, assignments,
-                       lists);
+                       lists, shared_rows);
     if (st != cudaSuccess) return st;
     return launch_kernel(permute_scatter_kernel, dim3(blocks), dim3(256), 0, stream, pdl,
                          static_cast<const std::int32_t*>(ids), assignments,
                          static_cast<const std::int32_t*>(plan->chunk_hist), static_cast<const std::int32_t*>(offsets),
-                         order, position, row_token, static_cast<const std::int32_t*>(lists.pp_off), pp_of_flat);
+                         order, position, row_token, static_cast<const std::int32_t*>(lists.pp_off), pp_of_flat, range,
+                         shared_rows);
 }
 
 }  // namespace p92b
@@ -561,15 +591,15 @@ extern "C" int p92b_moe_permute_static(const int32_t* expert_ids, int assignment
     lists.tile_prefix_wide = nullptr;
     if (assignments <= kWarps * 1024) {
         permute_small_kernel<<<1, 256, 0, stream>>>(expert_ids, assignments, order, position, lists, nullptr, nullptr,
-                                                    status);
+                                                    status, IdRange(), -1);
         return cudaGetLastError();
     }
     const int chunks = (assignments + kChunk - 1) / kChunk;
     const int blocks = (chunks + kWarps - 1) / kWarps;
-    permute_hist_kernel<<<blocks, 256, 0, stream>>>(expert_ids, assignments, chunk_hist, status);
-    permute_scan_kernel<<<1, 256, 0, stream>>>(chunk_hist, chunks, assignments, lists);
+    permute_hist_kernel<<<blocks, 256, 0, stream>>>(expert_ids, assignments, chunk_hist, status, IdRange());
+    permute_scan_kernel<<<1, 256, 0, stream>>>(chunk_hist, chunks, assignments, lists, -1);
     permute_scatter_kernel<<<blocks, 256, 0, stream>>>(expert_ids, assignments, chunk_hist, offsets, order, position,
-                                                       nullptr, nullptr, nullptr);
+                                                       nullptr, nullptr, nullptr, IdRange(), -1);
     return cudaGetLastError();
 }
 

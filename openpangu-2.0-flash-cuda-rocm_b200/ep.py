@@ -159,10 +159,16 @@ class EpWindow:
     Collective over `group` when world > 1 (the 64-byte handles are all-gathered); one window serves all
     layers.  Every rank must make the same sequence of forward_fused calls on it."""
 
-    def __init__(self, rank: int, world: int, rows_per_gpu: int, group=None, connect: bool = True):
+    def __init__(self, rank: int, world: int, rows_per_gpu: int, group=None, connect: bool = True, bulk: bool = False,
+                 hidden: int = HIDDEN):
+        """bulk=True makes the window of the large-batch path (forward_bulk): another layout, any rows_per_gpu."""
         lib = load_library()
         handle = ctypes.c_void_p()
-        _check(lib.p92b_ep_window_create(ctypes.byref(handle), rank, world, rows_per_gpu), "ep_window_create")
+        if bulk:
+            _check(lib.p92b_ep_window_create_bulk(ctypes.byref(handle), rank, world, rows_per_gpu, hidden),
+                   "ep_window_create_bulk")
+        else:
+            _check(lib.p92b_ep_window_create(ctypes.byref(handle), rank, world, rows_per_gpu), "ep_window_create")
         self.handle, self.rank, self.world, self.rows_per_gpu = handle, rank, world, rows_per_gpu
         if not connect:
             return
@@ -224,6 +230,16 @@ def forward_gathered(window: EpWindow, plan: MoePlan, bank: ExpertBank, router_w
     _check(load_library().p92b_ep_forward_gathered(plan.handle, bank.handle, window.handle, _ptr(x), _ptr(router_weight),
                                                    _ptr(correction_bias), _ptr(out), rows, routed_scale, _stream()),
            "ep_forward_gathered")
+
+
+def forward_bulk(window: EpWindow, plan: MoePlan, bank: ExpertBank, router_weight, correction_bias, x, out, rows: int,
+                 routed_scale: float = ROUTED_SCALE) -> None:
+    """The block on this GPU's `rows` home tokens for large batches: all-gather dispatch and direct placement of the
+    result rows by the library's own kernels (16-byte peer stores, one flag per peer and exchange), no NCCL, no host
+    synchronisation.  `window` was created with bulk=True; `plan` needs max_rows >= world * rows_per_gpu."""
+    _check(load_library().p92b_ep_forward_bulk(plan.handle, bank.handle, window.handle, _ptr(x), _ptr(router_weight),
+                                               _ptr(correction_bias), _ptr(out), rows, routed_scale, _stream()),
+           "ep_forward_bulk")
 
 
 FIXED_MAX_ROWS = 64      # per-GPU batch up to which forward_auto takes the fixed-capacity exchange

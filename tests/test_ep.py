@@ -219,3 +219,50 @@ def test_gathered_path_world_one_matches_block(cuda, pkg, layer0, rows):
             assert rel <= 1e-2 and np.abs(got - exp).max() <= 2e-2, (call, rel)
     finally:
         window.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [40, 700, 2048])
+def test_bulk_path_world_one_matches_block(cuda, pkg, layer0, rows):
+    """One GPU owning all experts: rows and ids stored into its own window, flags, the permutation restricted to the
+    local range (here everything), grouped products, result rows placed through the window, combine.  Fewer rows
+    than the window holds on the second call (empty slots carry id -1 and are skipped)."""
+    torch = cuda
+    from p92moe_b200 import ep, synth
+
+    window = ep.EpWindow(0, 1, rows, bulk=True)
+    plan = pkg.MoePlan(max_rows=rows)
+    try:
+        for call, n in enumerate((rows, rows - 7, rows)):
+            x = synth.make_activations(760 + call, 0, n)
+            out = torch.full_like(x, float("nan"))
+            ep.forward_bulk(window, plan, layer0.bank, layer0.router_weight, layer0.bias, x, out, n)
+            torch.cuda.synchronize()
+            assert plan.status() == 0
+            want, ref = _single_gpu_reference(pkg, layer0, x, n)
+            v = plan.views(n)
+            assert torch.equal(v["expert_ids"], ref["expert_ids"])
+            assert torch.equal(v["expert_weights"], ref["expert_weights"])
+            assert torch.equal(v["counts"], ref["counts"])
+            # same kernels, same per-expert row order, same combine law: the same bits
+            assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    finally:
+        window.close()
+
+
+@pytest.mark.gpu
+def test_other_calls_refuse_a_bulk_window(cuda, pkg, layer0):
+    torch = cuda
+    from p92moe_b200 import ep, synth
+
+    window = ep.EpWindow(0, 1, 8, bulk=True)
+    plan = pkg.MoePlan(max_rows=8)
+    x = synth.make_activations(770, 0, 4)
+    out = torch.zeros_like(x)
+    try:
+        for call in (ep.forward_fused, ep.forward_gathered):
+            with pytest.raises(pkg.P92Error) as err:
+                call(window, plan, layer0.bank, layer0.router_weight, layer0.bias, x, out, 4)
+            assert err.value.code == 801
+    finally:
+        window.close()

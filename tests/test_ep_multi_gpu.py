@@ -100,10 +100,32 @@ def _worker(rank: int, world: int, port: int, schedule, result) -> None:
         rel = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
         worst = max(worst, rel)
         ok &= bool(np.isfinite(got).all()) and rel <= 1e-2 and float(np.abs(got - ref).max()) <= 2e-2
+    # the large-batch path: 300 home tokens per GPU, then ragged (rank r brings 300 - 11 r)
+    bulk_rows = 300
+    bulk_window = ep.EpWindow(rank, world, bulk_rows, bulk=True)
+    bulk_plan = pkg.MoePlan(max_rows=world * bulk_rows)
+    for call in range(3):
+        rows = [bulk_rows - (11 * r if call == 1 else 0) for r in range(world)]
+        xs = [synth.make_activations(1700 + 16 * call + r, 0, n) for r, n in enumerate(rows)]
+        x_all = torch.cat(xs).contiguous()
+        total = x_all.shape[0]
+        plan = pkg.MoePlan(max_rows=total)
+        want = torch.empty_like(x_all)
+        pkg.MoeBlock(layer.bank, layer.router_weight, layer.bias, plan).run_moe_rows(x_all, want, total)
+        at, n = sum(rows[:rank]), rows[rank]
+        out = torch.full_like(xs[rank], float("nan"))
+        ep.forward_bulk(bulk_window, bulk_plan, bank, layer.router_weight, layer.bias, xs[rank], out, n)
+        torch.cuda.synchronize()
+        ok &= bulk_plan.status() == 0
+        ok &= bool(torch.equal(bulk_plan.views(n)["expert_ids"], plan.views(total)["expert_ids"][at:at + n]))
+        # per expert the rows are in the single-GPU order and the combine is the single-GPU law: the same bits
+        ok &= bool(torch.equal(out.view(torch.int16), want[at:at + n].view(torch.int16)))
+        plan.close()
     dist.barrier()
     torch.cuda.synchronize()
     window.close()
     wide_window.close()
+    bulk_window.close()
     result[rank] = (bool(ok), worst)
     dist.destroy_process_group()
 
