@@ -928,6 +928,8 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"         # the version banner goes to stdout, where only the JSON line belongs
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)

@@ -38,7 +38,7 @@ constexpr int kMaxWorld = 16;
 constexpr int kFlagBytes = 512;                 // arrive_flag[16], result_flag[16], block counters
 
 struct BulkLayout {
-    std::size_t flags, ids, rows, results, total;
+    std::size_t flags, ids, rows, results, dest, total;
     int row_bytes;
     __host__ __device__ BulkLayout(int world, int rows_per_gpu, int hidden) {
         row_bytes = hidden / 2 + hidden / 16;
@@ -48,7 +48,12 @@ struct BulkLayout {
         rows = (rows + 255) / 256 * 256;
         results = rows + static_cast<std::size_t>(world) * rows_per_gpu * row_bytes;
         results = (results + 255) / 256 * 256;
-        total = results + static_cast<std::size_t>(rows_per_gpu) * kTop * hidden * 2;
+        dest = results + static_cast<std::size_t>(rows_per_gpu) * kTop * hidden * 2;      // local use: one pointer per padded row
+        dest = (dest + 255) / 256 * 256;
+        total = dest + dest_entries(world, rows_per_gpu) * sizeof(void*);
+    }
+    __host__ __device__ static std::size_t dest_entries(int world, int rows_per_gpu) {
+        return (static_cast<std::size_t>(world) * rows_per_gpu * (kTop + 1) + (kExperts + 1) * 127 + 127) / 128 * 128;
     }
 };
 
@@ -149,7 +154,9 @@ __global__ void bulk_wait_kernel(const unsigned* __restrict__ flags, int world, 
 // ---- 2. rows of this GPU's experts (and its own shared-expert rows) into the padded position space -------------
 __global__ void __launch_bounds__(256) bulk_scatter_kernel(const std::uint8_t* __restrict__ arrived, const std::int32_t* __restrict__ pp_of_flat,
                                                            int assignments, int home_first_token, int home_rows, int row_bytes,
-                                                           int k_bytes, std::uint8_t* __restrict__ xq, std::uint8_t* __restrict__ xs) {
+                                                           int k_bytes, std::uint8_t* __restrict__ xq, std::uint8_t* __restrict__ xs,
+                                                           PeerBases peers, std::size_t results_base, int rows_per_gpu,
+                                                           std::uint16_t* mixed_pp, std::uint16_t** row_dest) {
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (unit >= assignments + home_rows) return;
@@ -157,6 +164,18 @@ __global__ void __launch_bounds__(256) bulk_scatter_kernel(const std::uint8_t* _
     if (pp_signed < 0) return;                                   // another GPU's expert, or an empty slot
     const std::size_t pp = static_cast<std::size_t>(pp_signed);
     const std::size_t token = unit < assignments ? unit / kTop : home_first_token + (unit - assignments);
+    if (row_dest != nullptr && lane == 0) {
+        // where the down product stores this row: slot [token][slot] of the results in its home GPU's window, or,
+        // for a shared-expert row, its own padded position on this GPU
+        const int hidden = k_bytes * 2;
+        if (unit < assignments) {
+            const int home = static_cast<int>(token) / rows_per_gpu;
+            const std::size_t slot_row = (token - static_cast<std::size_t>(home) * rows_per_gpu) * kTop + (unit - token * kTop);
+            row_dest[pp] = reinterpret_cast<std::uint16_t*>(peers.base[home] + results_base) + slot_row * hidden;
+        } else {
+            row_dest[pp] = mixed_pp + pp * hidden;
+        }
+    }
     const std::uint8_t* src = arrived + token * row_bytes;
     uint4* to = reinterpret_cast<uint4*>(xq + pp * k_bytes);
     for (int v = lane; v < k_bytes / 16; v += 32) to[v] = reinterpret_cast<const uint4*>(src)[v];
@@ -185,6 +204,15 @@ __global__ void __launch_bounds__(256) bulk_return_kernel(const std::uint16_t* _
         }
     }
     publish_when_grid_done(peers, bulk_base, counter + 1, 1, rank, world, epoch);
+}
+
+// The down product stored its rows straight into the windows (TcIo::row_dest): this launch comes after it in the
+// stream, so those stores are complete, and only has to tell every peer.
+__global__ void bulk_publish_kernel(PeerBases peers, std::size_t bulk_base, int which, int rank, int world, unsigned epoch) {
+    const int d = threadIdx.x;
+    if (d >= world) return;
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<unsigned*>(peers.base[d] + bulk_base) + which * kMaxWorld + rank, epoch);
 }
 
 // ---- 4. combine on the home GPU: eight slots in slot order, one rounding, then the shared expert ----------------
@@ -329,19 +357,28 @@ int p92b_ep_forward_bulk(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window*
                         tc_pad_align(tokens), tc_tile_rows(tokens), stream, false, bank->view.first_expert, local, rows);
     if (st != cudaSuccess) return st;
     const int units = assignments + rows;
+    // large batches: the down product stores every row where the combine wants it, over NVLink while it computes
+    const bool direct = down_slab_applies(plan, tokens) && std::getenv("P92B_BULK_NO_DIRECT") == nullptr;
+    std::uint16_t** row_dest = direct ? reinterpret_cast<std::uint16_t**>(mine + layout.dest) : nullptr;
     bulk_scatter_kernel<<<(units + 7) / 8, 256, 0, stream>>>(mine + layout.rows, plan->pp_of_flat, assignments,
                                                              window->rank * rpg, rows, layout.row_bytes, hidden / 2, plan->xq_pp,
-                                                             plan->xs_sw);
+                                                             plan->xs_sw, peers, layout.results, rpg, plan->mixed_pp, row_dest);
     if ((st = cudaGetLastError()) != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
     if ((st = launch_experts_tc(plan, bank, tokens, false, stream, false)) != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
-    if ((st = launch_experts_tc(plan, bank, tokens, true, stream, false)) != cudaSuccess) return st;
+    TcIo io {};
+    io.row_dest = row_dest;
+    if ((st = launch_experts_tc(plan, bank, tokens, true, stream, false, direct ? &io : nullptr)) != cudaSuccess) return st;
     if ((st = mark()) != cudaSuccess) return st;
     // combine
-    bulk_return_kernel<<<(assignments + 7) / 8, 256, 0, stream>>>(plan->mixed_pp, plan->pp_of_flat, peers, 0, layout, counters,
-                                                                  assignments, window->rank, world, rpg, hidden, epoch);
+    if (direct) {
+        bulk_publish_kernel<<<1, 32, 0, stream>>>(peers, 0, 1, window->rank, world, epoch);
+    } else {
+        bulk_return_kernel<<<(assignments + 7) / 8, 256, 0, stream>>>(plan->mixed_pp, plan->pp_of_flat, peers, 0, layout, counters,
+                                                                      assignments, window->rank, world, rpg, hidden, epoch);
+    }
     bulk_wait_kernel<<<1, 32, 0, stream>>>(flags + kMaxWorld, world, epoch, plan->status);
     dim3 grid((hidden / 8 + 255) / 256, rows);
     bulk_combine_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const std::uint16_t*>(mine + layout.results),

@@ -95,6 +95,7 @@ struct TcParams {
     const p92b_expert_projection* table;   // SRC 1: device table of reference-format matrices, entry expert * 3 + kind
     int table_kind;                    // SRC 1, MODE 1: which of an expert's three matrices
     int skip_shared;                   // 1: the shared expert's items are not computed (the caller has none)
+    std::uint16_t* const* row_dest;    // slab kernel of the down product: null, or [padded position] -> destination row
 };
 
 struct Item {
@@ -790,7 +791,7 @@ struct DownSlab {
     static constexpr int kOffBSf = kKBlocksMax * kN * kBlockKBytes;                 // scale slabs behind the boxes
     static constexpr int kStages = 3;                                               // one chunk (two K blocks of the weight) each
     static constexpr int kStageBytes = kChunkBytes;
-    static constexpr int kStoreBytes = 16 * 32 * 2;                                 // per epilogue warp: 16 tokens x 32 rows of BF16
+    static constexpr int kStoreBytes = 16 * 32 * 2;                                 // per epilogue warp (a group of four shares 4 KB): 16 tokens x 32 rows of BF16
     static constexpr int kAccumBuffers = 2;
     static constexpr int kSfbCols = kKBlocksMax * 16;                               // resident for an item
     static constexpr int kSfaCols = 2 * 16;                                         // per chunk, two buffers
@@ -799,6 +800,18 @@ struct DownSlab {
     static constexpr int kSmemBytes = kBBytes + kStages * kStageBytes + kEpilogueWarps * kStoreBytes + kBarriers * 8 + 16 + 1024;
     static constexpr int kGroups = 2;                                               // row-tile halves per slab
 };
+
+// Named barriers over the 128 threads of one epilogue group (barrier 0 is __syncthreads).
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ bool group_all(bool mine, int id) {
+    std::uint32_t all;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(all)
+        : "r"(static_cast<std::uint32_t>(mine)), "r"(id)
+        : "memory");
+    return all != 0U;
+}
 
 __global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const __grid_constant__ CUtensorMap map_b,
                                                                          const TcParams p) {
@@ -962,22 +975,26 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const _
         int buffer = 0;
         std::uint32_t accum_phase[2] = {0U, 0U};
         bool ok = true;
-        for (int item = blockIdx.x; item < total_items && !*abort_ptr && ok; item += gridDim.x) {
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            if (!group_all(*abort_ptr == 0U, 1 + sub)) break;       // the four warps of a group leave together
             Item it;
             if (!decode(item, &it)) continue;
             const float alpha = p.bank.alpha[it.entry * 3 + 2];
             const int hidden = p.m_total;
             for (int t = 0; t < tiles_per_group; ++t) {
-                if (!mbar_wait(accum_full(buffer), accum_phase[buffer])) { give_up(); ok = false; break; }
+                // the four warps of a group (one per 32-lane quarter of the accumulator) move in step: they share a
+                // staging area and its barriers, so a wait that ran out in one of them ends the tile for all four
+                if (!group_all(mbar_wait(accum_full(buffer), accum_phase[buffer]), 1 + sub)) { give_up(); ok = false; break; }
                 accum_phase[buffer] ^= 1U;
                 tc_fence_after();
                 const std::uint32_t lane_base = tmem_base + buffer * C::kN + (static_cast<std::uint32_t>(quarter * 32) << 16);
                 // A lane holds one weight row for 16 tokens; the output is token-major, so 2-byte stores would touch a
-                // 64-byte piece per instruction.  The warp turns its 32 x 16 block round through its own 1 KB of
-                // shared memory and stores 16 bytes per lane: 8 rows of one token.
+                // 64-byte piece per instruction.  The group turns its 128 x 16 block round through 4 KB of shared
+                // memory and every lane stores 16 bytes: a token's 128 rows leave as one 256-byte run, which is what
+                // keeps a store that crosses NVLink (TcIo::row_dest) efficient.
                 std::uint16_t* stage_rows = reinterpret_cast<std::uint16_t*>(smem_raw + (store_area - smem_u32(smem_raw))) +
-                                            (warp - 2) * (C::kStoreBytes / 2);
-                const int first_row = (it.m_tile + t) * kTileM + quarter * 32;
+                                            sub * (4 * C::kStoreBytes / 2);
+                const int first_row = (it.m_tile + t) * kTileM;
 #pragma unroll 1
                 for (int c0 = sub * 16; c0 < C::kN; c0 += 16 * (kEpilogueWarps / 4)) {
                     if (c0 >= it.valid) break;
@@ -985,18 +1002,23 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const _
                     tmem_load16(lane_base + c0, d);
                     tmem_load_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) stage_rows[j * 32 + lane] = float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
-                    __syncwarp();
+                    for (int j = 0; j < 16; ++j) {
+                        stage_rows[j * kTileM + quarter * 32 + lane] = float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
+                    }
+                    group_sync(1 + sub);
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        const int v = lane + 32 * h;                 // 64 pieces of 16 bytes: token v / 4, rows (v % 4) * 8 ..
-                        const int n = c0 + (v >> 2);
+                        const int v = lane + 32 * h;                 // this warp: 4 tokens x 16 pieces of 16 bytes
+                        const int j = quarter * 4 + (v >> 4);
+                        const int n = c0 + j;
                         if (n < it.valid) {
-                            *reinterpret_cast<uint4*>(p.out + static_cast<std::size_t>(it.pp0 + n) * hidden + first_row + (v & 3) * 8) =
-                                *reinterpret_cast<const uint4*>(stage_rows + (v >> 2) * 32 + (v & 3) * 8);
+                            std::uint16_t* to = p.row_dest != nullptr ? p.row_dest[it.pp0 + n]
+                                                                      : p.out + static_cast<std::size_t>(it.pp0 + n) * hidden;
+                            *reinterpret_cast<uint4*>(to + first_row + (v & 15) * 8) =
+                                *reinterpret_cast<const uint4*>(stage_rows + j * kTileM + (v & 15) * 8);
                         }
                     }
-                    __syncwarp();
+                    group_sync(1 + sub);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -1166,6 +1188,16 @@ cudaError_t launch_quantize_rows_to_pp(const std::uint16_t* x, const std::int32_
                          1.0F);
 }
 
+namespace {
+bool slab_shape(const p92b_plan* plan) {
+    const int k_blocks = plan->intermediate / 2 / kBlockKBytes;
+    return plan->wide_rows == 128 && k_blocks <= DownSlab::kKBlocksMax && k_blocks % 2 == 0 &&
+           (plan->hidden / kTileM) % DownSlab::kGroups == 0 && std::getenv("P92B_NO_DOWN_SLAB") == nullptr;
+}
+}  // namespace
+
+bool down_slab_applies(const p92b_plan* plan, int rows) { return tc_tile_rows(rows) == 64 && slab_shape(plan); }
+
 cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int rows, bool down,
                               cudaStream_t stream, bool pdl, const TcIo* io) {
     const bool in_place = io != nullptr && io->table != nullptr;
@@ -1188,6 +1220,7 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
         p.table = io->table;
         p.table_kind = io->table_kind;
         p.skip_shared = io->skip_shared ? 1 : 0;
+        p.row_dest = io->row_dest;
     }
     const bool unfused = io != nullptr && io->gate_out != nullptr;
     const bool single = io != nullptr && io->single_matrix;      // one matrix of the token-row side (gate or up alone)
@@ -1249,6 +1282,7 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
             default: return launch_tc<1, 64, 1>(plan, plan->map_h[2], p, stream, pdl);
         }
     }
+    if (p.row_dest != nullptr && which != 2) return cudaErrorNotSupported;
     switch (which) {
         case 0: return launch_tc<1, 16>(plan, plan->map_h[0], p, stream, pdl);
         case 1: return launch_tc<1, 32>(plan, plan->map_h[1], p, stream, pdl);
@@ -1256,16 +1290,17 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
             if (plan->wide_rows == 128) {
                 // every expert segment starts on a multiple of 128 padded rows, so 128-row tiles stay inside it
                 p.tile_prefix = plan->tile_prefix_wide;
-                const int k_blocks = p.k_bytes / kBlockKBytes;
-                if (io == nullptr && k_blocks <= DownSlab::kKBlocksMax && k_blocks % 2 == 0 && p.m_tiles % DownSlab::kGroups == 0 &&
-                    std::getenv("P92B_NO_DOWN_SLAB") == nullptr) {
+                const bool plain = io == nullptr || (io->down_out == nullptr && io->out_row == nullptr && !io->skip_shared);
+                if (plain && slab_shape(plan)) {
                     // the token slab resident in shared memory, only weights streaming
                     if (cudaError_t st = ensure_dynamic_smem<expert_down_slab_kernel>(DownSlab::kSmemBytes); st != cudaSuccess) return st;
                     return launch_kernel(expert_down_slab_kernel, dim3(plan->sm_count), dim3(kThreadsTc), DownSlab::kSmemBytes,
                                          stream, pdl, plan->map_h[3], p);
                 }
+                if (p.row_dest != nullptr) return cudaErrorNotSupported;
                 return launch_tc<1, 128>(plan, plan->map_h[3], p, stream, pdl);
             }
+            if (p.row_dest != nullptr) return cudaErrorNotSupported;
             return launch_tc<1, 64>(plan, plan->map_h[2], p, stream, pdl);
     }
 }

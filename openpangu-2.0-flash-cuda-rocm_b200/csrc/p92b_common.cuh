@@ -401,7 +401,12 @@ struct TcIo {
     bool skip_shared = false;               // the call has no shared expert
     bool wait_upstream = false;             // down product: the kernel just upstream may still be waiting for ITS predecessor
                                             // when this one starts, so the routing lists may only be read after a wait
+    std::uint16_t* const* row_dest = nullptr;   // down product of large batches only (down_slab_applies): [padded position] ->
+                                            // where that row's `hidden` BF16 values go, this GPU's memory or a peer's
 };
+// True when launch_experts_tc(..., down = true) with the lists last built for `rows` runs the slab kernel, the one
+// that honours TcIo::row_dest.
+bool down_slab_applies(const p92b_plan* plan, int rows);
 cudaError_t launch_gather_quantized_rows(const std::uint8_t* packed, const std::uint8_t* scales_swizzled,
                                          const std::int32_t* pp_of_flat, std::uint8_t* xq, std::uint8_t* xs, int assignments,
                                          int k_bytes, bool distinct_rows, cudaStream_t stream, bool pdl = false);
