@@ -29,8 +29,7 @@
 // parity, and a GPU cannot be more than one launch ahead of any peer (it needs the peer's results of
 // launch k to finish launch k), which is what makes two buffers enough.  Every wait - on a peer's
 // word, a device-wide counter or an mbarrier - is bounded by wall time and ends in a status word.
-#include "p92b_common.cuh"
-#include "tc_ptx.cuh"
+#include "decode_pipeline.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -40,6 +39,7 @@
 namespace p92b {
 
 using namespace ptx;
+using namespace decode;
 
 namespace {
 
@@ -47,16 +47,6 @@ constexpr int kEpThreads = 192;
 constexpr int kEpMaxLocalRows = 8;                 // home tokens per GPU
 constexpr int kEpMaxTokens = 32;                   // gathered batch (all GPUs)
 constexpr int kEpMaxWorld = 16;
-constexpr int kTile = 128;
-constexpr int kKB = 128;
-constexpr int kSlab = 2048;
-constexpr int kOffA0 = 0, kOffA1 = 16384, kOffSfA0 = 32768, kOffB0 = 36864;   // SFA1 follows SFA0 by one slab
-constexpr int kStages = 4;
-constexpr int kAccumStride = 32;
-constexpr int kAccumCols = 64;
-constexpr int kSfColsPerBuffer = 64;
-constexpr int kAccumBuffers = 4;
-constexpr int kTmemCols = 512;
 constexpr int kMaxSlots = kExperts + 1;            // local experts (all 256 on a single GPU) + the shared expert
 
 // ---- window layout (identical on every GPU) --------------------------------------------------
@@ -118,24 +108,6 @@ struct Routing {
     float bias[kExperts];
 };
 
-__device__ __forceinline__ int slab_of_slot(int slot, int n_active) {
-    return (slot == 0 ? n_active - 1 : slot - 1) * kTile;
-}
-
-__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-
-__device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned target) {
-    const std::uint64_t start = global_timer_ns();
-    while (static_cast<int>(ld_acquire_gpu(counter) - target) < 0) {
-        if (global_timer_ns() - start > 1000000000ULL) return false;
-    }
-    return true;
-}
 // Device-wide rendezvous of the co-resident blocks: arrive, then wait for everyone.  Nothing the
 // kernel has written before it leaves this GPU, so device-scope fences are enough.
 __device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned target) {
@@ -151,17 +123,6 @@ __device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned targ
     }
     __syncthreads();
     return ok != 0;
-}
-
-// Tiles are handed out through one device-wide counter (same scheme as the single-GPU decode kernel):
-// the producer lane takes the numbers, one ahead, and passes each tile to the MMA lane and the epilogue
-// warps through a small queue in shared memory; a negative entry ends the queue.
-constexpr int kTileQueue = 16;
-__device__ __forceinline__ int encode_tile(int kind, int slot, int m_tile) { return (kind << 24) | (slot << 8) | m_tile; }
-__device__ __forceinline__ void decode_tile(int code, int* kind, int* slot, int* m_tile) {
-    *kind = code >> 24;
-    *slot = (code >> 8) & 0xffff;
-    *m_tile = code & 0xff;
 }
 
 template <int kN>
@@ -606,37 +567,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                         break;
                     }
                     tc_fence_after();
-                    const std::uint32_t st = base + stage * L::kStage;
-                    const std::uint32_t sfc = sf_tmem + sf_buffer * kSfColsPerBuffer;
-                    const int slabs = kind == 0 ? 3 : 4;
-                    for (int o = 0; o < slabs; ++o) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            tc_copy_sf(sfc + o * 16 + k * 4,
-                                       desc_scale_atom(st + (o < 2 ? kOffSfA0 + o * kSlab : L::kOffSfB0 + (o - 2) * kSlab) + k * 512));
-                        }
-                    }
-                    const std::uint64_t a0 = desc_k_major_sw128(st + kOffA0);
-                    const std::uint64_t a1 = desc_k_major_sw128(st + kOffA1);
-                    const std::uint64_t b0 = desc_k_major_sw128(st + kOffB0);
-                    const std::uint64_t b1 = desc_k_major_sw128(st + L::kOffB1);
-                    if (kind == 0) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            mma_nvf4(accum, a0 + 2 * k, b0 + 2 * k, idesc, sfc + k * 4, sfc + 32 + k * 4, s > 0 || k > 0);
-                            mma_nvf4(accum + kAccumStride, a1 + 2 * k, b0 + 2 * k, idesc, sfc + 16 + k * 4,
-                                     sfc + 32 + k * 4, s > 0 || k > 0);
-                        }
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            mma_nvf4(accum, a0 + 2 * k, b0 + 2 * k, idesc, sfc + k * 4, sfc + 32 + k * 4, s > 0 || k > 0);
-                        }
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            mma_nvf4(accum, a1 + 2 * k, b1 + 2 * k, idesc, sfc + 16 + k * 4, sfc + 48 + k * 4, true);
-                        }
-                    }
+                    issue_stage(kind, base + stage * L::kStage, L::kOffB1, L::kOffSfB0, sf_tmem + sf_buffer * kSfColsPerBuffer,
+                                accum, idesc, s == 0);
                     tc_commit(empty_bar(stage));
                     sf_buffer ^= 1;
                     if (++stage == kStages) { stage = 0; phase ^= 1U; }

@@ -30,35 +30,24 @@
 //
 // All blocks are co-resident (one per SM, grid = SM count); every wait on a counter, a
 // word or an mbarrier is bounded by wall time and ends in a status word, never a hang.
-#include "p92b_common.cuh"
-#include "tc_ptx.cuh"
+#include "decode_pipeline.cuh"
 
 #include <cstdlib>
 
 namespace p92b {
 
 using namespace ptx;
+using namespace decode;
 
 namespace {
 
 constexpr int kMegaThreads = 192;
 constexpr int kMegaMaxRows = 8;
 constexpr int kN = 16;                             // token columns of every MMA
-constexpr int kTile = 128;
-constexpr int kKB = 128;                           // bytes per operand row per K block
-constexpr int kSlab = 2048;
-// stage: two weight boxes, two token boxes, four scale slabs
-// (the first 36,864 bytes are one chunk of the bank's tile stream, copied as a whole)
-constexpr int kOffA0 = 0, kOffA1 = 16384, kOffSfA0 = 32768;   // SFA1 follows SFA0 by one slab
-constexpr int kOffB0 = 36864, kOffB1 = 38912, kOffSfB0 = 40960, kOffSfB1 = 43008;
+// a ring stage: the bank's chunk (decode_pipeline.cuh), then two token boxes and two token scale slabs
+constexpr int kOffB1 = 38912, kOffSfB0 = 40960, kOffSfB1 = 43008;
 constexpr int kStage = 45056;
-constexpr int kStages = 4;
 constexpr int kWeightTx = kChunkBytes;
-constexpr int kAccumStride = 32;
-constexpr int kAccumCols = 64;                     // per buffer: gate at +0, up at +32
-constexpr int kSfColsPerBuffer = 64;               // SFA0, SFA1, SFB0, SFB1 x 16 columns
-constexpr int kAccumBuffers = 4;                   // the issuer may run four tiles ahead of the epilogue
-constexpr int kTmemCols = 512;
 constexpr int kMaxActive = kMegaMaxRows * kTop + 1;
 
 struct MegaParams {
@@ -115,29 +104,6 @@ struct Routing {                   // shared-memory copy, identical in every blo
     float bias[kExperts];
 };
 
-// Every active slot owns one 128-row slab of the padded position space, in slot order; the shared
-// expert (slot 0) takes the slab after the last routed one.
-__device__ __forceinline__ int slab_of_slot(int slot, int n_active) {
-    return (slot == 0 ? n_active - 1 : slot - 1) * kTile;
-}
-
-__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-
-// Bounded wait until *counter has reached `target` (wrap-safe).
-__device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned target) {
-    const std::uint64_t start = global_timer_ns();
-    while (static_cast<int>(ld_acquire(counter) - target) < 0) {
-        if (global_timer_ns() - start > 1000000000ULL) return false;
-    }
-    return true;
-}
-
 // One arrival per block on a device-wide counter; whoever needs all blocks to have arrived waits for
 // the count itself (wait_counter).
 __device__ __forceinline__ void grid_arrive(unsigned* counter) {
@@ -147,18 +113,6 @@ __device__ __forceinline__ void grid_arrive(unsigned* counter) {
         fence_proxy_async_all();          // what the block wrote is later read by TMA in other blocks
         atomicAdd(counter, 1U);
     }
-}
-
-// Tiles are handed out through one device-wide counter.  The producer lane takes the numbers (one
-// ahead of the tile it is loading, so the atomic's latency is hidden) and passes each tile to the MMA
-// lane and the epilogue warps through a small queue in shared memory, published by the mbarrier
-// arrivals that already order the three roles.  A negative entry ends the queue.
-constexpr int kTileQueue = 16;       // the producer is never more than 9 tiles ahead of the epilogue
-__device__ __forceinline__ int encode_tile(int kind, int slot, int m_tile) { return (kind << 24) | (slot << 8) | m_tile; }
-__device__ __forceinline__ void decode_tile(int code, int* kind, int* slot, int* m_tile) {
-    *kind = code >> 24;
-    *slot = (code >> 8) & 0xffff;
-    *m_tile = code & 0xff;
 }
 
 __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -605,37 +559,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                     }
                     tc_fence_after();
                     if (sequence == 0 && s < 10) stamp(26 + s);
-                    const std::uint32_t st = base + stage * kStage;
-                    const std::uint32_t sfc = sf_tmem + sf_buffer * kSfColsPerBuffer;
-                    const int slabs = kind == 0 ? 3 : 4;            // SFA0, SFA1, SFB0 (, SFB1)
-                    for (int o = 0; o < slabs; ++o) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            tc_copy_sf(sfc + o * 16 + k * 4,
-                                       desc_scale_atom(st + (o < 2 ? kOffSfA0 + o * kSlab : kOffSfB0 + (o - 2) * kSlab) + k * 512));
-                        }
-                    }
-                    const std::uint64_t a0 = desc_k_major_sw128(st + kOffA0);
-                    const std::uint64_t a1 = desc_k_major_sw128(st + kOffA1);
-                    const std::uint64_t b0 = desc_k_major_sw128(st + kOffB0);
-                    const std::uint64_t b1 = desc_k_major_sw128(st + kOffB1);
-                    if (kind == 0) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            mma_nvf4(accum, a0 + 2 * k, b0 + 2 * k, idesc, sfc + k * 4, sfc + 32 + k * 4, s > 0 || k > 0);
-                            mma_nvf4(accum + kAccumStride, a1 + 2 * k, b0 + 2 * k, idesc, sfc + 16 + k * 4,
-                                     sfc + 32 + k * 4, s > 0 || k > 0);
-                        }
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            mma_nvf4(accum, a0 + 2 * k, b0 + 2 * k, idesc, sfc + k * 4, sfc + 32 + k * 4, s > 0 || k > 0);
-                        }
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            mma_nvf4(accum, a1 + 2 * k, b1 + 2 * k, idesc, sfc + 16 + k * 4, sfc + 48 + k * 4, true);
-                        }
-                    }
+                    issue_stage(kind, base + stage * kStage, kOffB1, kOffSfB0, sf_tmem + sf_buffer * kSfColsPerBuffer, accum,
+                                idesc, s == 0);
                     tc_commit(empty_bar(stage));
                     if (sequence == 0 && s < 10) stamp(36 + s);
                     sf_buffer ^= 1;

@@ -126,40 +126,97 @@ __global__ void __launch_bounds__(256) swizzle_kernel(const std::uint8_t* __rest
     swizzled[destination] = linear[index];
 }
 
-// cuda/nvfp4_ops.cu:97-105: bf16( g / (1 + expf(-g)) * u ), fast-math like the reference.
-__global__ void __launch_bounds__(256) swiglu_kernel(const std::uint16_t* __restrict__ gate,
-                                                     const std::uint16_t* __restrict__ up,
-                                                     std::uint16_t* __restrict__ output, int elements) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= elements) return;
-    const float value = bf16_bits_to_float(gate[i]);
-    output[i] = float_to_bf16_bits((value / (1.0F + expf(-value))) * bf16_bits_to_float(up[i]));
+// The three element-wise operators of the block's stage interface.  Each thread takes eight BF16 values through one
+// 16-byte load per operand and one 16-byte store; `vectors` is the number of such groups (0 when a pointer or a row
+// pitch is not 16-byte aligned) and the threads after them take the remaining values one each.
+struct Bf16x8 {
+    float v[8];
+    __device__ __forceinline__ explicit Bf16x8(const uint4 raw) {
+        const std::uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000U);
+        }
+    }
+};
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
+    std::uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        w[i] = static_cast<std::uint32_t>(float_to_bf16_bits(v[2 * i])) |
+               (static_cast<std::uint32_t>(float_to_bf16_bits(v[2 * i + 1])) << 16);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__host__ inline bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr) {
+    return ((reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(b) | reinterpret_cast<std::uintptr_t>(c)) & 15U) == 0U;
 }
 
-// cuda/nvfp4_ops.cu:124-142: FP32 fmaf over the slots in rank order, one rounding.
+// SwiGLU, bf16( g / (1 + expf(-g)) * u ) with the fast-math expf and division of cuda/nvfp4_ops.cu:97-105.
+__device__ __forceinline__ float silu_times(float g, float u) { return (g / (1.0F + expf(-g))) * u; }
+__global__ void __launch_bounds__(256) swiglu_kernel(const std::uint16_t* __restrict__ gate,
+                                                     const std::uint16_t* __restrict__ up,
+                                                     std::uint16_t* __restrict__ output, long elements, long vectors) {
+    const long t = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t < vectors) {
+        const Bf16x8 g(__ldg(reinterpret_cast<const uint4*>(gate) + t));
+        const Bf16x8 u(__ldg(reinterpret_cast<const uint4*>(up) + t));
+        float r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = silu_times(g.v[i], u.v[i]);
+        reinterpret_cast<uint4*>(output)[t] = pack_bf16x8(r);
+        return;
+    }
+    const long i = vectors * 8 + (t - vectors);
+    if (i < elements) output[i] = float_to_bf16_bits(silu_times(bf16_bits_to_float(gate[i]), bf16_bits_to_float(up[i])));
+}
+
+// Weighted sum of a token's expert rows: one FP32 fmaf chain per output value over the slots in slot order, one
+// rounding at the end (cuda/nvfp4_ops.cu:124-142).  grid.y = batch row; `vectors` counts 8-value groups per row.
 __global__ void __launch_bounds__(256) combine_rows_kernel(const std::uint16_t* __restrict__ expert_rows,
                                                            const float* __restrict__ route_weights,
                                                            std::uint16_t* __restrict__ output, int experts,
-                                                           int elements) {
-    const int element = blockIdx.x * blockDim.x + threadIdx.x;
-    const int row = blockIdx.y;
+                                                           int elements, int vectors) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const std::size_t route_base = static_cast<std::size_t>(blockIdx.y) * experts;
+    std::uint16_t* out_row = output + static_cast<std::size_t>(blockIdx.y) * elements;
+    if (t < vectors) {
+        float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
+        for (int slot = 0; slot < experts; ++slot) {
+            const float w = __ldg(route_weights + route_base + slot);
+            const Bf16x8 row(__ldg(reinterpret_cast<const uint4*>(expert_rows + (route_base + slot) * elements) + t));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(row.v[i], w, acc[i]);
+        }
+        reinterpret_cast<uint4*>(out_row)[t] = pack_bf16x8(acc);
+        return;
+    }
+    const int element = vectors * 8 + (t - vectors);
     if (element >= elements) return;
     float value = 0.0F;
-    const std::size_t route_base = static_cast<std::size_t>(row) * experts;
     for (int slot = 0; slot < experts; ++slot) {
         value = fmaf(bf16_bits_to_float(expert_rows[(route_base + slot) * elements + element]),
-                     route_weights[route_base + slot], value);
+                     __ldg(route_weights + route_base + slot), value);
     }
-    output[static_cast<std::size_t>(row) * elements + element] = float_to_bf16_bits(value);
+    out_row[element] = float_to_bf16_bits(value);
 }
 
-// cuda/nvfp4_ops.cu:92-95.
+// destination = bf16(destination + source), the residual add of cuda/nvfp4_ops.cu:92-95.
 __global__ void __launch_bounds__(256) add_kernel(std::uint16_t* __restrict__ destination,
-                                                  const std::uint16_t* __restrict__ source, int elements) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < elements) {
-        destination[i] = float_to_bf16_bits(bf16_bits_to_float(destination[i]) + bf16_bits_to_float(source[i]));
+                                                  const std::uint16_t* __restrict__ source, long elements, long vectors) {
+    const long t = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t < vectors) {
+        const Bf16x8 d(reinterpret_cast<const uint4*>(destination)[t]);
+        const Bf16x8 s(__ldg(reinterpret_cast<const uint4*>(source) + t));
+        float r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = d.v[i] + s.v[i];
+        reinterpret_cast<uint4*>(destination)[t] = pack_bf16x8(r);
+        return;
     }
+    const long i = vectors * 8 + (t - vectors);
+    if (i < elements) destination[i] = float_to_bf16_bits(bf16_bits_to_float(destination[i]) + bf16_bits_to_float(source[i]));
 }
 
 // RMSNorm of BF16 rows, bit-exact with the reference operator (cuda/nvfp4_ops.cu:67-90, called either side of
@@ -422,7 +479,9 @@ int p92b_nvfp4_pack_weight_batch(const uint16_t* input, uint8_t* packed, uint8_t
 
 int p92b_swiglu(const uint16_t* gate, const uint16_t* up, uint16_t* output, int elements, void* stream) {
     if (gate == nullptr || up == nullptr || output == nullptr || elements <= 0) return cudaErrorInvalidValue;
-    swiglu_kernel<<<blocks_for(elements, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(gate, up, output, elements);
+    const long vectors = aligned16(gate, up, output) ? elements / 8 : 0;
+    swiglu_kernel<<<blocks_for(vectors + (elements - vectors * 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        gate, up, output, elements, vectors);
     return cudaGetLastError();
 }
 
@@ -432,9 +491,10 @@ int p92b_expert_combine_rows(const uint16_t* expert_rows, const float* route_wei
         experts <= 0 || elements <= 0) {
         return cudaErrorInvalidValue;
     }
-    dim3 grid(blocks_for(elements, 256), batch_rows);
+    const int vectors = aligned16(expert_rows, output) && elements % 8 == 0 ? elements / 8 : 0;
+    dim3 grid(blocks_for(vectors + (elements - vectors * 8), 256), batch_rows);
     combine_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_rows, route_weights, output,
-                                                                            experts, elements);
+                                                                            experts, elements, vectors);
     return cudaGetLastError();
 }
 
@@ -457,7 +517,9 @@ int p92b_rmsnorm_strided(const uint16_t* input, int input_stride, const uint16_t
 
 int p92b_add_inplace(uint16_t* destination, const uint16_t* source, int elements, void* stream) {
     if (destination == nullptr || source == nullptr || elements <= 0) return cudaErrorInvalidValue;
-    add_kernel<<<blocks_for(elements, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(destination, source, elements);
+    const long vectors = aligned16(destination, source) ? elements / 8 : 0;
+    add_kernel<<<blocks_for(vectors + (elements - vectors * 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        destination, source, elements, vectors);
     return cudaGetLastError();
 }
 

@@ -241,6 +241,37 @@ def test_elementwise_ops_bit_exact_vs_reference_kernels(cuda, pkg, orc):
     assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
 
 
+@pytest.mark.parametrize("elements,offset", [(8 * 1024 + 5, 0), (4099, 3), (7, 0), (2560, 1)])
+def test_elementwise_ops_odd_sizes_and_unaligned_pointers(cuda, pkg, orc, elements, offset):
+    """The 16-byte lanes take whole groups of eight values from aligned pointers; everything else - the last few
+    values, or all of them when a pointer is not 16-byte aligned - goes through the element-wise lane.  Both must
+    give the reference kernels' bits (cuda/nvfp4_ops.cu:92-105,124-142)."""
+    torch = cuda
+    if not orc.have_ref():
+        pytest.skip("oracle/_ref was not built")
+    g = torch.Generator(device="cuda").manual_seed(50 + elements)
+    def rows_of(n, std):
+        return torch.empty(n + offset, dtype=torch.float32, device="cuda").normal_(0, std, generator=g).to(torch.bfloat16)[offset:]
+    gate, up = rows_of(elements, 2.0), rows_of(elements, 2.0)
+    a = torch.zeros(elements + offset, dtype=torch.bfloat16, device="cuda")[offset:]
+    b = torch.zeros(elements + offset, dtype=torch.bfloat16, device="cuda")[offset:]
+    pkg.swiglu(gate, up, a, elements)
+    assert orc.ref().ref_swiglu(gate.data_ptr(), up.data_ptr(), b.data_ptr(), elements, _stream(torch)) == 0
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    pkg.add_inplace(a, gate, elements)
+    assert orc.ref().ref_add_inplace(b.data_ptr(), gate.data_ptr(), elements, _stream(torch)) == 0
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    rows = 3
+    mixed = rows_of(rows * 8 * elements, 0.05)
+    rw = torch.rand((rows, 8), dtype=torch.float32, device="cuda", generator=g)
+    o1 = torch.zeros(rows * elements + offset, dtype=torch.bfloat16, device="cuda")[offset:]
+    o2 = torch.zeros(rows * elements + offset, dtype=torch.bfloat16, device="cuda")[offset:]
+    pkg.expert_combine_rows(mixed, rw, o1, rows, 8, elements)
+    assert orc.ref().ref_expert_combine_rows(mixed.data_ptr(), rw.data_ptr(), o2.data_ptr(), rows, 8, elements,
+                                             _stream(torch)) == 0
+    assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
+
+
 def test_elementwise_ops_vs_cpu_oracle(cuda, pkg, orc):
     torch = cuda
     g = torch.Generator(device="cuda").manual_seed(6)
