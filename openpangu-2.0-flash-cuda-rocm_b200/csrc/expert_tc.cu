@@ -108,23 +108,51 @@ struct Item {
     int dense0;    // dense (unpadded) position of the tile's first row
 };
 
+// The routing lists a block needs to turn an item number into work, copied to shared memory once per block:
+// every role decodes every item, and from global memory that is a dozen dependent loads (a binary search over
+// the tile prefix, then the expert's entries) - about 1.4 µs per item, which in the MMA lane is time the tensor
+// pipe runs dry.  Indexed by active slot.
+struct RouteTable {
+    std::int32_t prefix[kExperts + 2];      // exclusive prefix of token tiles over the active list, total at [active_count]
+    std::int32_t expert[kExperts + 1];
+    std::int32_t count[kExperts + 1];
+    std::int32_t pp_off[kExperts + 1];
+    std::int32_t offset[kExperts + 1];
+    std::int32_t active_count;
+};
+
+// All threads of the block, after the lists are known to be written; the caller synchronises the block afterwards.
+__device__ __forceinline__ void load_route_table(const TcParams& p, RouteTable* t) {
+    const int n = min(*p.route.active_count, kExperts + 1);
+    for (int a = threadIdx.x; a <= n; a += blockDim.x) {
+        t->prefix[a] = p.tile_prefix[a];
+        if (a < n) {
+            const int e = p.route.active[a];
+            t->expert[a] = e;
+            t->count[a] = p.route.counts[e];
+            t->pp_off[a] = p.pp_off[e];
+            t->offset[a] = p.route.offsets[e];
+        }
+    }
+    if (threadIdx.x == 0) t->active_count = n;
+}
+
 template <int N>
-__device__ __forceinline__ bool decode_item(const TcParams& p, int item, Item* it) {
+__device__ __forceinline__ bool decode_item(const TcParams& p, const RouteTable& t, int item, Item* it) {
     const int tt = item / p.m_tiles;
     it->m_tile = item - tt * p.m_tiles;
-    const int active_count = *p.route.active_count;
-    int lo = 0, hi = active_count;           // find a: tile_prefix[a] <= tt < tile_prefix[a+1]
+    int lo = 0, hi = t.active_count;         // find a: prefix[a] <= tt < prefix[a+1]
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (p.tile_prefix[mid] <= tt) lo = mid; else hi = mid;
+        if (t.prefix[mid] <= tt) lo = mid; else hi = mid;
     }
-    const int n_tile = tt - p.tile_prefix[lo];
-    it->expert = p.route.active[lo];
+    const int n_tile = tt - t.prefix[lo];
+    it->expert = t.expert[lo];
     it->entry = it->expert == kExperts ? p.bank.local_experts : it->expert - p.bank.first_expert;
-    it->count = p.route.counts[it->expert];
-    it->pp0 = p.pp_off[it->expert] + n_tile * N;
+    it->count = t.count[lo];
+    it->pp0 = t.pp_off[lo] + n_tile * N;
     it->valid = min(N, it->count - n_tile * N);
-    it->dense0 = p.route.offsets[it->expert] + n_tile * N;
+    it->dense0 = t.offset[lo] + n_tile * N;
     if (p.skip_shared && it->expert == kExperts) return false;
     if (p.table != nullptr) {          // weights in place: the table is indexed by the global expert id
         it->entry = it->expert;
@@ -138,11 +166,93 @@ __device__ __forceinline__ void async_copy16_tc(std::uint32_t dst_smem, const vo
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 
+// The gate/up epilogue for one chunk of 16 token columns (shared by expert_tc_kernel<0, N> and
+// expert_gu_pair_kernel).  A lane holds one weight row (row0 + lane of the intermediate dimension): gate g[j] and
+// up u[j] for token column c0 + j.  bf16(alpha * product) for both, SwiGLU rounded to BF16
+// (cuda/nvfp4_ops.cu:97-105), then the activation quantiser (cuda/nvfp4_ops.cu:818-841) along the intermediate
+// dimension, whose 16-element blocks are the two 16-lane halves of the warp:
+//   * block maximum of every column: one warp reduction per column over the half (|h| is a non-negative float, so
+//     its bit pattern orders like an unsigned integer);
+//   * the E4M3 scale and the multiplier of column c are computed ONCE, by lane c of the half, which also stores the
+//     scale byte; the other lanes fetch the multiplier with one shuffle per column;
+//   * a lane packs its 16 quantised values (one row, 16 tokens) into 64 bits, and a four-round butterfly over the
+//     half transposes the 16 x 16 nibble matrix, after which lane c holds the 16 rows of token c0 + c: one 8-byte
+//     store per lane instead of a byte store per lane pair and column.
+// The arithmetic per element is the reference's; only who computes what has changed.
+// hq_rows = packed rows of the tile's first token (p.hq + pp0 * inter / 2); hs_tile = the 128-row scale tile row of
+// that token (p.hs + (pp0 >> 7) * (inter / 64) * 512); n_base = pp0 & 127; columns from `valid` on are not stored.
+__device__ __forceinline__ void swiglu_requant_chunk(const std::uint32_t (&g)[16], const std::uint32_t (&u)[16], float alpha_g,
+                                                     float alpha_u, float quant_scale, int lane, int c0, int valid, int n_base,
+                                                     int inter, int row0, std::uint8_t* hq_rows, std::uint8_t* hs_tile) {
+    const int half = lane >> 4;                       // which 16-row block of the warp's 32 rows
+    const int c = lane & 15;                          // the column this lane owns after the reductions
+    const unsigned half_mask = half ? 0xffff0000U : 0x0000ffffU;
+    float h[16];
+    std::uint32_t amax_bits[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[j]) * alpha_g));
+        const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[j]) * alpha_u));
+        h[j] = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
+        amax_bits[j] = __reduce_max_sync(half_mask, __float_as_uint(h[j]) & 0x7fffffffU);
+    }
+    // amax of the column this lane owns: a select tree over the 16 results (register arrays take no run-time index)
+    std::uint32_t mine8[8], mine4[4], mine2[2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mine8[i] = (c & 8) ? amax_bits[8 + i] : amax_bits[i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mine4[i] = (c & 4) ? mine8[4 + i] : mine8[i];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) mine2[i] = (c & 2) ? mine4[2 + i] : mine4[i];
+    const float amax = __uint_as_float((c & 1) ? mine2[1] : mine2[0]);
+    const __nv_fp8_e4m3 scale(amax * (quant_scale / 6.0F));
+    const float decoded = static_cast<float>(scale);
+    const float my_multiplier = decoded == 0.0F ? 0.0F : quant_scale / decoded;
+    const int n_mine = c0 + c;
+    if (n_mine < valid) {
+        const int sf_col = (row0 >> 4) + half;
+        const int tn = n_base + n_mine;
+        hs_tile[static_cast<std::size_t>(sf_col >> 2) * 512 + (sf_col & 3) + (tn & 31) * 16 + (tn >> 5) * 4] = scale.__x;
+    }
+    // this lane's row: 16 E2M1 values, column j at nibble j
+    std::uint32_t w0 = 0U, w1 = 0U;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float m0 = __shfl_sync(0xffffffffU, my_multiplier, (lane & 16) | (2 * k));
+        const float m1 = __shfl_sync(0xffffffffU, my_multiplier, (lane & 16) | (2 * k + 1));
+        const std::uint32_t byte = __nv_fp4x2_e2m1(make_float2(h[2 * k] * m0, h[2 * k + 1] * m1)).__x;
+        if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
+    }
+    // transpose the half's 16 x 16 nibble matrix: afterwards nibble r of lane c is (row r, column c)
+    {
+        const bool up8 = (lane & 8) != 0;                  // distance 8: whole words change hands
+        const std::uint32_t got = __shfl_xor_sync(0xffffffffU, up8 ? w0 : w1, 8);
+        if (up8) w0 = got; else w1 = got;
+    }
+#pragma unroll
+    for (int d = 4; d >= 1; d >>= 1) {
+        const std::uint32_t low = d == 4 ? 0x0000ffffU : d == 2 ? 0x00ff00ffU : 0x0f0f0f0fU;
+        const int shift = 4 * d;
+        const bool upper = (lane & d) != 0;
+        const std::uint32_t s0 = upper ? (w0 & low) << shift : (w0 >> shift) & low;
+        const std::uint32_t s1 = upper ? (w1 & low) << shift : (w1 >> shift) & low;
+        const std::uint32_t r0 = __shfl_xor_sync(0xffffffffU, s0, d);
+        const std::uint32_t r1 = __shfl_xor_sync(0xffffffffU, s1, d);
+        w0 = (upper ? w0 & ~low : w0 & low) | r0;
+        w1 = (upper ? w1 & ~low : w1 & low) | r1;
+    }
+    if (n_mine < valid) {
+        *reinterpret_cast<uint2*>(hq_rows + static_cast<std::size_t>(n_mine) * (inter / 2) + ((row0 + 16 * half) >> 1)) =
+            make_uint2(w0, w1);
+    }
+}
+
 template <int MODE, int N, int SRC>
 __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_constant__ CUtensorMap map_b,
                                                                    const TcParams p) {
     using C = Tc<MODE, N>;
     extern __shared__ std::uint8_t smem_raw[];
+    __shared__ RouteTable route_table;
     const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     const std::uint32_t bars = base + C::kStages * C::kStageBytes;
     // per stage: weights landed, tokens landed, stage free; per accumulator buffer: full, empty
@@ -183,12 +293,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
     // the routing lists come from the kernel just upstream (gate/up) or from one further up (down):
     // only the former has to wait for its predecessor before it can look at its work list
     if (p.routing_is_upstream || SRC == 1) pdl_wait();
+    load_route_table(p, &route_table);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     pdl_launch_dependents();
     const std::uint32_t tmem_base = *tmem_slot_ptr;
-    const int total_items = p.tile_prefix[*p.route.active_count] * p.m_tiles;
+    const int total_items = route_table.prefix[route_table.active_count] * p.m_tiles;
     auto give_up = [&]() {
         *abort_ptr = 1;
         atomicCAS(p.status, kStatusOk, kStatusWaitExpired);
@@ -207,7 +318,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         bool ok = true;
         for (int item = blockIdx.x; item < total_items && !*abort_ptr && ok; item += gridDim.x) {
             Item it;
-            if (!decode_item<N>(p, item, &it)) continue;
+            if (!decode_item<N>(p, route_table, item, &it)) continue;
             const p92b_expert_projection first = p.table[it.entry * 3 + (MODE == 1 ? p.table_kind : 0)];
             const p92b_expert_projection second = MODE == 1 ? first : p.table[it.entry * 3 + 1];
             if (((reinterpret_cast<std::uintptr_t>(first.weight) | reinterpret_cast<std::uintptr_t>(second.weight) |
@@ -271,7 +382,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
             bool upstream_done = p.routing_is_upstream != 0;
             for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
                 Item it;
-                if (!decode_item<N>(p, item, &it)) continue;
+                if (!decode_item<N>(p, route_table, item, &it)) continue;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(); break; }
                     const std::uint32_t st = base + stage * C::kStageBytes;
@@ -308,7 +419,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                         int it_item = blockIdx.x, it_kb = 0;
                         for (int s = 0; s <= stage; ++s) {
                             Item held;
-                            while (!decode_item<N>(p, it_item, &held)) it_item += gridDim.x;
+                            while (!decode_item<N>(p, route_table, it_item, &held)) it_item += gridDim.x;
                             const std::uint32_t hst = base + s * C::kStageBytes;
                             mbar_arrive_expect_tx(token_bar(s), C::kTokenBytes);
                             tma_load_2d(hst + C::kOffB, &map_b, token_bar(s), it_kb * kBlockKBytes, held.pp0);
@@ -335,7 +446,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
             int sf_buffer = 0;
             for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
                 Item it;
-                if (!decode_item<N>(p, item, &it)) continue;
+                if (!decode_item<N>(p, route_table, item, &it)) continue;
                 if (!mbar_wait(accum_empty(buffer), accum_phase[buffer] ^ 1U)) { give_up(); break; }
                 tc_fence_after();
                 const std::uint32_t accum = tmem_base + buffer * C::kAccumCols;
@@ -390,7 +501,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
         std::uint32_t accum_phase[2] = {0U, 0U};
         for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
             Item it;
-            if (!decode_item<N>(p, item, &it)) continue;
+            if (!decode_item<N>(p, route_table, item, &it)) continue;
             if (!mbar_wait(accum_full(buffer), accum_phase[buffer])) { give_up(); break; }
             accum_phase[buffer] ^= 1U;
             tc_fence_after();
@@ -401,12 +512,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                 const float alpha_g = p.bank.alpha[it.entry * 3 + 0];
                 const float alpha_u = p.bank.alpha[it.entry * 3 + 1];
                 const int inter = p.m_total;
-                const int sf_col = row >> 4;
-                // scale byte of (token pp0 + n, 16-row block sf_col) in the 128x4 tiling; pp0 is a multiple of 64
-                std::uint8_t* hs_base = p.hs + (static_cast<std::size_t>(it.pp0 >> 7) * (inter / 64) + (sf_col >> 2)) * 512 +
-                                        (sf_col & 3);
-                std::uint8_t* hq_base = p.hq + static_cast<std::size_t>(it.pp0) * (inter / 2) + (row >> 1);
+                // the token tile's packed rows and its 128-row scale tile; pp0 is a multiple of N
+                std::uint8_t* hs_tile = p.hs + static_cast<std::size_t>(it.pp0 >> 7) * (inter / 64) * 512;
+                std::uint8_t* hq_rows = p.hq + static_cast<std::size_t>(it.pp0) * (inter / 2);
                 const int n_base = it.pp0 & 127;
+                const int row0 = it.m_tile * kTileM + quarter * 32;
 #pragma unroll 1
                 for (int c0 = half * 16; c0 < N; c0 += 16 * (kEpilogueWarps / 4)) {
                     if (c0 >= it.valid) break;                                    // warp uniform
@@ -414,51 +524,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_tc_kernel(const __grid_c
                     tmem_load16(lane_base + c0, g);
                     tmem_load16(lane_base + C::kAccumStride + c0, u);
                     tmem_load_wait();
-                    float h[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[j]) * alpha_g));
-                        const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[j]) * alpha_u));
-                        h[j] = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
-                    }
-                    // |h| maximum over the 16 rows of a block: h is BF16-exact, so two columns share one
-                    // bf16x2 register through the four shuffle rounds
-                    std::uint32_t packed[8];
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        packed[k] = (__float_as_uint(fabsf(h[2 * k])) >> 16) | (__float_as_uint(fabsf(h[2 * k + 1])) & 0xffff0000U);
-                    }
-#pragma unroll
-                    for (int off = 8; off > 0; off >>= 1) {
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const std::uint32_t other = __shfl_xor_sync(0xffffffffU, packed[k], off);
-                            __nv_bfloat162 a2 = *reinterpret_cast<__nv_bfloat162*>(&packed[k]);
-                            const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&other);
-                            a2 = __hmax2(a2, b2);
-                            packed[k] = *reinterpret_cast<std::uint32_t*>(&a2);
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float amax = __uint_as_float((j & 1) ? (packed[j >> 1] & 0xffff0000U) : (packed[j >> 1] << 16));
-                        const __nv_fp8_e4m3 scale(amax * (p.quant_scale / 6.0F));
-                        const float decoded = static_cast<float>(scale);
-                        const float multiplier = decoded == 0.0F ? 0.0F : p.quant_scale / decoded;
-                        const float q = h[j] * multiplier;
-                        const float q_next = __shfl_xor_sync(0xffffffffU, q, 1);
-                        const int n = c0 + j;
-                        if (n < it.valid) {
-                            if ((lane & 1) == 0) {
-                                hq_base[static_cast<std::size_t>(n) * (inter / 2)] =
-                                    static_cast<std::uint8_t>(__nv_fp4x2_e2m1(make_float2(q, q_next)).__x);
-                            }
-                            if ((lane & 15) == 0) {
-                                const int tn = n_base + n;
-                                hs_base[(tn & 31) * 16 + (tn >> 5) * 4] = scale.__x;
-                            }
-                        }
-                    }
+                    swiglu_requant_chunk(g, u, alpha_g, alpha_u, p.quant_scale, lane, c0, it.valid, n_base, inter, row0, hq_rows, hs_tile);
                 }
             } else if constexpr (MODE == 2) {
                 // gate and up rows as the reference's project_expert_gate_up returns them: bf16(alpha * product),
@@ -548,6 +614,7 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
                                                                         const TcParams p) {
     using C = GuPair;
     extern __shared__ std::uint8_t smem_raw[];
+    __shared__ RouteTable route_table;
     const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     const std::uint32_t bars = base + C::kStages * C::kStageBytes;
     auto weight_bar = [&](int s) { return bars + 8U * s; };
@@ -583,12 +650,13 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
         tmem_relinquish();
     }
     pdl_wait();                       // routing lists and token rows come from the kernels upstream
+    load_route_table(p, &route_table);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     pdl_launch_dependents();
     const std::uint32_t tmem_base = *tmem_slot_ptr;
-    const int total_items = p.tile_prefix[*p.route.active_count] * p.m_tiles;       // tile_prefix counts 128-row slabs here
+    const int total_items = route_table.prefix[route_table.active_count] * p.m_tiles;       // the prefix counts 128-row slabs here
     auto give_up = [&]() {
         *abort_ptr = 1;
         atomicCAS(p.status, kStatusOk, kStatusWaitExpired);
@@ -600,7 +668,7 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
             std::uint32_t phase = 0;
             for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
                 Item it;
-                if (!decode_item<2 * C::kN>(p, item, &it)) continue;
+                if (!decode_item<2 * C::kN>(p, route_table, item, &it)) continue;
                 const bool two = it.valid > C::kN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(); break; }
@@ -630,7 +698,7 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
             int sf_buffer = 0;
             for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
                 Item it;
-                if (!decode_item<2 * C::kN>(p, item, &it)) continue;
+                if (!decode_item<2 * C::kN>(p, route_table, item, &it)) continue;
                 const int halves = it.valid > C::kN ? 2 : 1;
                 int buffer[2];
                 bool ok = true;
@@ -690,13 +758,12 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
         std::uint32_t accum_phase = 0;
         for (int item = blockIdx.x; item < total_items && !*abort_ptr; item += gridDim.x) {
             Item it;
-            if (!decode_item<2 * C::kN>(p, item, &it)) continue;
+            if (!decode_item<2 * C::kN>(p, route_table, item, &it)) continue;
             const int halves = it.valid > C::kN ? 2 : 1;
             const float alpha_g = p.bank.alpha[it.entry * 3 + 0];
             const float alpha_u = p.bank.alpha[it.entry * 3 + 1];
             const int inter = p.m_total;
-            const int row = it.m_tile * kTileM + quarter * 32 + lane;
-            const int sf_col = row >> 4;
+            const int row0 = it.m_tile * kTileM + quarter * 32;
             bool ok = true;
             for (int hh = 0; hh < halves; ++hh) {
                 const int buffer = next_buffer;
@@ -708,63 +775,25 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
                 const int valid = hh == 0 ? min(C::kN, it.valid) : it.valid - C::kN;
                 const std::uint32_t lane_base =
                     tmem_base + buffer * C::kAccumCols + (static_cast<std::uint32_t>(quarter * 32) << 16);
-                std::uint8_t* hs_base = p.hs + (static_cast<std::size_t>(pp0 >> 7) * (inter / 64) + (sf_col >> 2)) * 512 + (sf_col & 3);
-                std::uint8_t* hq_base = p.hq + static_cast<std::size_t>(pp0) * (inter / 2) + (row >> 1);
+                std::uint8_t* hs_tile = p.hs + static_cast<std::size_t>(pp0 >> 7) * (inter / 64) * 512;
+                std::uint8_t* hq_rows = p.hq + static_cast<std::size_t>(pp0) * (inter / 2);
                 const int n_base = pp0 & 127;
-#pragma unroll 1
-                for (int c0 = sub * 16; c0 < C::kN; c0 += 16 * (C::kEpilogueWarps / 4)) {
-                    if (c0 >= valid) break;                                       // warp uniform
-                    std::uint32_t g[16], u[16];
+                // Sixteen warps, sixteen (quarter, 16-column chunk) pieces per half: a warp has exactly one.  It takes its
+                // piece into registers and gives the buffer back at once - the arithmetic that follows is several times
+                // longer than the read, and the MMA lane needs two free buffers to start the next item.
+                static_assert(C::kN == 16 * (C::kEpilogueWarps / 4), "one chunk per warp and half");
+                const int c0 = sub * 16;
+                const bool mine = c0 < valid;                                        // warp uniform
+                std::uint32_t g[16], u[16];
+                if (mine) {
                     tmem_load16(lane_base + c0, g);
                     tmem_load16(lane_base + C::kN + c0, u);
                     tmem_load_wait();
-                    float h[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[j]) * alpha_g));
-                        const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[j]) * alpha_u));
-                        h[j] = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
-                    }
-                    std::uint32_t packed[8];
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        packed[k] = (__float_as_uint(fabsf(h[2 * k])) >> 16) | (__float_as_uint(fabsf(h[2 * k + 1])) & 0xffff0000U);
-                    }
-#pragma unroll
-                    for (int off = 8; off > 0; off >>= 1) {
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const std::uint32_t other = __shfl_xor_sync(0xffffffffU, packed[k], off);
-                            __nv_bfloat162 a2 = *reinterpret_cast<__nv_bfloat162*>(&packed[k]);
-                            const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&other);
-                            a2 = __hmax2(a2, b2);
-                            packed[k] = *reinterpret_cast<std::uint32_t*>(&a2);
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float amax = __uint_as_float((j & 1) ? (packed[j >> 1] & 0xffff0000U) : (packed[j >> 1] << 16));
-                        const __nv_fp8_e4m3 scale(amax * (p.quant_scale / 6.0F));
-                        const float decoded = static_cast<float>(scale);
-                        const float multiplier = decoded == 0.0F ? 0.0F : p.quant_scale / decoded;
-                        const float q = h[j] * multiplier;
-                        const float q_next = __shfl_xor_sync(0xffffffffU, q, 1);
-                        const int n = c0 + j;
-                        if (n < valid) {
-                            if ((lane & 1) == 0) {
-                                hq_base[static_cast<std::size_t>(n) * (inter / 2)] =
-                                    static_cast<std::uint8_t>(__nv_fp4x2_e2m1(make_float2(q, q_next)).__x);
-                            }
-                            if ((lane & 15) == 0) {
-                                const int tn = n_base + n;
-                                hs_base[(tn & 31) * 16 + (tn >> 5) * 4] = scale.__x;
-                            }
-                        }
-                    }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(accum_empty(buffer));
+                if (mine) swiglu_requant_chunk(g, u, alpha_g, alpha_u, p.quant_scale, lane, c0, valid, n_base, inter, row0, hq_rows, hs_tile);
             }
             if (!ok) break;
         }
@@ -817,6 +846,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const _
                                                                          const TcParams p) {
     using C = DownSlab;
     extern __shared__ std::uint8_t smem_raw[];
+    __shared__ RouteTable route_table;
     const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     const std::uint32_t ring = base + C::kBBytes;
     const std::uint32_t store_area = ring + C::kStages * C::kStageBytes;
@@ -857,12 +887,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const _
         tmem_relinquish();
     }
     pdl_wait();                       // routing lists and the SwiGLU rows come from the kernels upstream
+    load_route_table(p, &route_table);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     pdl_launch_dependents();
     const std::uint32_t tmem_base = *tmem_slot_ptr;
-    const int total_items = p.tile_prefix[*p.route.active_count] * C::kGroups;      // tile_prefix counts 128-row slabs here
+    const int total_items = route_table.prefix[route_table.active_count] * C::kGroups;      // the prefix counts 128-row slabs here
     auto give_up = [&]() {
         *abort_ptr = 1;
         atomicCAS(p.status, kStatusOk, kStatusWaitExpired);
@@ -871,7 +902,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const _
     auto decode = [&](int item, Item* it) {
         const int slab = item / C::kGroups;
         const int group = item - slab * C::kGroups;
-        const bool ok = decode_item<C::kN>(p, slab * p.m_tiles + group * tiles_per_group, it);
+        const bool ok = decode_item<C::kN>(p, route_table, slab * p.m_tiles + group * tiles_per_group, it);
         return ok;
     };
 
@@ -995,15 +1026,28 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const _
                 std::uint16_t* stage_rows = reinterpret_cast<std::uint16_t*>(smem_raw + (store_area - smem_u32(smem_raw))) +
                                             sub * (4 * C::kStoreBytes / 2);
                 const int first_row = (it.m_tile + t) * kTileM;
-#pragma unroll 1
-                for (int c0 = sub * 16; c0 < C::kN; c0 += 16 * (kEpilogueWarps / 4)) {
+                // a warp's two chunks of 16 columns (sub * 16 and 64 + sub * 16) go into registers first and the buffer
+                // back to the MMA lane at once; staging and stores follow
+                constexpr int kChunks = C::kN / (16 * (kEpilogueWarps / 4));
+                static_assert(kChunks == 2, "two chunks per warp and tile");
+                std::uint32_t d[kChunks][16];
+#pragma unroll
+                for (int q = 0; q < kChunks; ++q) {
+                    const int c0 = sub * 16 + q * 16 * (kEpilogueWarps / 4);
+                    if (c0 < it.valid) tmem_load16(lane_base + c0, d[q]);              // group uniform
+                }
+                tmem_load_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accum_empty(buffer));
+                buffer ^= 1;
+#pragma unroll
+                for (int q = 0; q < kChunks; ++q) {
+                    const int c0 = sub * 16 + q * 16 * (kEpilogueWarps / 4);
                     if (c0 >= it.valid) break;
-                    std::uint32_t d[16];
-                    tmem_load16(lane_base + c0, d);
-                    tmem_load_wait();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        stage_rows[j * kTileM + quarter * 32 + lane] = float_to_bf16_bits(__uint_as_float(d[j]) * alpha);
+                        stage_rows[j * kTileM + quarter * 32 + lane] = float_to_bf16_bits(__uint_as_float(d[q][j]) * alpha);
                     }
                     group_sync(1 + sub);
 #pragma unroll
@@ -1020,10 +1064,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) expert_down_slab_kernel(const _
                     }
                     group_sync(1 + sub);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(accum_empty(buffer));
-                buffer ^= 1;
             }
         }
     }
