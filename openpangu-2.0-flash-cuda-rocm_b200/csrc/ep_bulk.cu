@@ -176,13 +176,37 @@ __global__ void __launch_bounds__(256) bulk_scatter_kernel(const std::uint8_t* _
             row_dest[pp] = mixed_pp + pp * hidden;
         }
     }
+    // 1,280 + 160 bytes at hidden 2560: every lane's loads are issued before its first store; the scale bytes move as
+    // 4-byte words (a row's four scales of one 64-element step are neighbours in both layouts)
     const std::uint8_t* src = arrived + token * row_bytes;
     uint4* to = reinterpret_cast<uint4*>(xq + pp * k_bytes);
-    for (int v = lane; v < k_bytes / 16; v += 32) to[v] = reinterpret_cast<const uint4*>(src)[v];
-    const int scale_columns = k_bytes / 8;
-    const int col_blocks = (scale_columns + 3) / 4;
+    const int pieces = k_bytes / 16;
+    constexpr int kMaxPerLane = 4;                              // hidden <= 4096
+    uint4 held[kMaxPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        const int v = lane + 32 * i;
+        if (v < pieces) held[i] = __ldcs(reinterpret_cast<const uint4*>(src) + v);
+    }
+    const int scale_words = k_bytes / 32;                       // K / 16 scale bytes, four to a word
+    const int col_blocks = scale_words;
     std::uint8_t* sf_to = xs + (pp >> 7) * col_blocks * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4;
-    for (int c = lane; c < scale_columns; c += 32) sf_to[(c >> 2) * 512 + (c & 3)] = src[k_bytes + c];
+    std::uint32_t scale_word[2] = {0U, 0U};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c = lane + 32 * i;
+        if (c < scale_words) scale_word[i] = __ldcs(reinterpret_cast<const std::uint32_t*>(src + k_bytes) + c);
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        const int v = lane + 32 * i;
+        if (v < pieces) to[v] = held[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c = lane + 32 * i;
+        if (c < scale_words) *reinterpret_cast<std::uint32_t*>(sf_to + static_cast<std::size_t>(c) * 512) = scale_word[i];
+    }
 }
 
 // ---- 3. result rows to their home GPUs ------------------------------------------------------------------------
@@ -265,7 +289,7 @@ int p92b_ep_window_create_bulk(p92b_ep_window** out, int rank, int world, int ro
     if (out == nullptr) return cudaErrorInvalidValue;
     *out = nullptr;
     if (world <= 0 || world > kMaxWorld || rank < 0 || rank >= world || kExperts % world != 0 || rows_per_gpu <= 0 ||
-        rows_per_gpu > (1 << 16) || hidden <= 0 || hidden % 256 != 0) {
+        rows_per_gpu > (1 << 16) || hidden <= 0 || hidden % 256 != 0 || hidden > 4096) {
         return cudaErrorInvalidValue;
     }
     p92b_ep_window* w = new (std::nothrow) p92b_ep_window();
