@@ -807,9 +807,8 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
 }
 
 // ---- down product for large batches: the token slab stays in shared memory ---------------------------------
-// At thousands of tokens both grouped products are bound by what one SM's copy engine takes in (about 55 GB/s
-// whatever the source), and in the tile-by-tile down kernel half of that intake is the token slab, loaded again
-// for each of the 20 row tiles of the weight.  Here an item is (128-token slab of an expert, half of the row
+// In the tile-by-tile down kernel half of what a block loads is the token slab, fetched again for each of the 20
+// row tiles of the weight, and a ring stage that waits for it is a stage less of weights in flight.  Here an item is (128-token slab of an expert, half of the row
 // tiles): the slab's four K blocks (64 KB) and their scale slabs (8 KB) are loaded ONCE and stay resident, their
 // scale factors stay in TMEM, and only weight chunks stream through the ring - half the bytes per result.
 // Needs the whole K extent of a slab in shared memory: intermediate sizes up to 1024.
