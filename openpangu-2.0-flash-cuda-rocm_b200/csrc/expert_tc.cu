@@ -166,6 +166,12 @@ __device__ __forceinline__ void async_copy16_tc(std::uint32_t dst_smem, const vo
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 
+// Two floats rounded to BF16 (nearest even) in one conversion: the first in the low half.
+__device__ __forceinline__ std::uint32_t bf16x2_bits(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const std::uint32_t*>(&pair);
+}
+
 // The gate/up epilogue for one chunk of 16 token columns (shared by expert_tc_kernel<0, N> and
 // expert_gu_pair_kernel).  A lane holds one weight row (row0 + lane of the intermediate dimension): gate g[j] and
 // up u[j] for token column c0 + j.  bf16(alpha * product) for both, SwiGLU rounded to BF16
@@ -189,13 +195,25 @@ __device__ __forceinline__ void swiglu_requant_chunk(const std::uint32_t (&g)[16
     const unsigned half_mask = half ? 0xffff0000U : 0x0000ffffU;
     float h[16];
     std::uint32_t amax_bits[16];
+    // the three BF16 roundings per element go through the two-wide conversion (one instruction for gate and up of a
+    // column, one for the results of two columns): same round-to-nearest-even, fewer trips through the conversion pipe
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[j]) * alpha_g));
-        const float uv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(u[j]) * alpha_u));
-        h[j] = bf16_bits_to_float(float_to_bf16_bits((gv / (1.0F + expf(-gv))) * uv));
-        amax_bits[j] = __reduce_max_sync(half_mask, __float_as_uint(h[j]) & 0x7fffffffU);
+    for (int k = 0; k < 8; ++k) {
+        float silu_times_up[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int j = 2 * k + i;
+            const std::uint32_t gu = bf16x2_bits(__uint_as_float(g[j]) * alpha_g, __uint_as_float(u[j]) * alpha_u);
+            const float gv = __uint_as_float(gu << 16);
+            const float uv = __uint_as_float(gu & 0xffff0000U);
+            silu_times_up[i] = (gv / (1.0F + expf(-gv))) * uv;
+        }
+        const std::uint32_t hh = bf16x2_bits(silu_times_up[0], silu_times_up[1]);
+        h[2 * k] = __uint_as_float(hh << 16);
+        h[2 * k + 1] = __uint_as_float(hh & 0xffff0000U);
     }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax_bits[j] = __reduce_max_sync(half_mask, __float_as_uint(h[j]) & 0x7fffffffU);
     // amax of the column this lane owns: a select tree over the 16 results (register arrays take no run-time index)
     std::uint32_t mine8[8], mine4[4], mine2[2];
 #pragma unroll
