@@ -56,6 +56,34 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
+def nvfp4_yardstick(torch):
+    """Dense NVFP4 rate of this GPU measured with a LIBRARY block-scaled FP4 GEMM (torch._scaled_mm: E2M1 operands,
+    E4M3 scales per 16 values, BF16 result; 8192^3, a burst of 20 calls after 5 warm-up calls).  A yardstick for the
+    tensor-side denominator only - nothing of the product runs through it.  None if this torch build refuses."""
+    try:
+        m = n = k = 8192
+        a = torch.randint(0, 255, (m, k // 2), dtype=torch.uint8, device="cuda").view(torch.float4_e2m1fn_x2)
+        b = torch.randint(0, 255, (n, k // 2), dtype=torch.uint8, device="cuda").view(torch.float4_e2m1fn_x2)
+        sa = torch.full((m * (k // 16),), 0x38, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+        sb = torch.full((n * (k // 16),), 0x38, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+
+        def run():
+            return torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+
+        for _ in range(5):
+            run()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(20):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        return 2.0 * m * n * k * 20 / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    except Exception:                     # noqa: BLE001 - any refusal of the library call means "no yardstick"
+        return None
+
+
 def ncu_ratios() -> dict:
     """kernel -> (traffic / algorithmic bytes, tensor pipe %) from the table kept beside the ncu summaries."""
     out = {}
@@ -521,7 +549,8 @@ class SingleGpu:
         tiles64 = int((np.ceil(counts / 64) * 64).sum() + math.ceil(rows / 64) * 64)
         pk = peaks()
         t_bytes = layer_bytes(distinct, rows) / (pk["hbm_gbs"] * 1e9)
-        nvfp4_peak = 4 * pk["bf16_tflops"]
+        yardstick = nvfp4_yardstick(torch)
+        nvfp4_peak = yardstick if yardstick else 4 * pk["bf16_tflops"]
         t_flops = rows * FLOPS_PER_TOKEN / (nvfp4_peak * 1e12)
         ratios = ncu_ratios()
         gu = ratios.get("expert_gu_pair_kernel")
@@ -540,8 +569,10 @@ class SingleGpu:
             "roofline_layer": {"t_bytes_us": t_bytes * 1e6, "t_flops_us": t_flops * 1e6,
                                "frac_of_max": max(t_bytes, t_flops) / (ms * 1e-3),
                                "nvfp4_dense_peak_tflops": nvfp4_peak,
-                               "nvfp4_peak_source": "4 x the measured dense BF16 rate of MEASURED_PEAKS.json (no block-scaled FP4 "
-                                                    "library GEMM was measured on this box); vendor figure 9000",
+                               "nvfp4_peak_source": ("measured in this run: library block-scaled FP4 GEMM (torch._scaled_mm, 8192^3, "
+                                                     "burst); vendor figure 9000") if yardstick else
+                                                    ("4 x the measured dense BF16 rate of MEASURED_PEAKS.json (the library FP4 GEMM "
+                                                     "was refused by this torch build); vendor figure 9000"),
                                "flops_per_token": FLOPS_PER_TOKEN, "tensor_pipe_pct_ncu": gu["tensor_pipe_pct"] if gu else None,
                                "tensor_pipe_capture": gu["capture"] if gu else None},
             "roofline": {"bound": "hbm", "kernel": "expert_gu_pair_kernel", "achieved": gu_gbs, "peak": pk["hbm_gbs"],
