@@ -381,7 +381,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
         for (int t = warp; t < rows; t += kMegaThreads / 32) {
             warp_top8(rt.logits + t * kExperts, rt.bias, rt.ids + t * kTop, rt.weights + t * kTop, p.routed_scale);
         }
+        if (threadIdx.x == 0) stamp(13);
         __syncthreads();
+        if (threadIdx.x == 0) stamp(14);
         // The ranking law of cuda/nvfp4_grouped.cu:117-132, position = #(smaller expert id) + #(same id,
         // smaller flat index), through one bit mask of tokens per expert (a token picks an expert at most
         // once): popcounts give the ranks, a scan over the 256 experts the offsets and the active slots.

@@ -86,27 +86,26 @@ __device__ __forceinline__ void warp_top8(const float* __restrict__ lg, const fl
                                           std::int32_t* __restrict__ ids, float* __restrict__ weights,
                                           float routed_scale) {
     const int lane = threadIdx.x & 31;
-    float raw[8];
-    float corrected[8];
-    int id[8];
+    // One 64-bit word per candidate: the high half is an order-preserving integer image of the corrected score (0 for
+    // a NaN: a comparison-based scan never picks it), the low half is ~id, so that "greater" means higher score, then
+    // lower id - the reference's total order (cuda/nvfp4_ops.cu:391-392,411-412) in one unsigned comparison.
+    unsigned long long cand[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int e = lane + 32 * i;
-        raw[i] = 1.0F / (1.0F + expf(-lg[e]));
-        corrected[i] = raw[i] + bias[e];
-        id[i] = e;
+        const float raw = 1.0F / (1.0F + expf(-lg[e]));
+        const float corrected = raw + bias[e];
+        const std::uint32_t bits = __float_as_uint(corrected);
+        const std::uint32_t key = corrected != corrected ? 0U : (bits & 0x80000000U ? ~bits : bits | 0x80000000U);
+        cand[i] = (static_cast<unsigned long long>(key) << 32) | static_cast<std::uint32_t>(~e);
     }
-    // Each lane first orders its own eight candidates (higher corrected score first, lower id on
-    // ties; a NaN orders last, as a comparison-based scan would never pick it): a 19-comparator
-    // network on registers.  A round of the selection then only looks at the head of each lane's list.
-#define P92B_ORDER(a, b)                                                                              \
-    {                                                                                                 \
-        const bool swap = corrected[b] > corrected[a] || (corrected[b] == corrected[a] && id[b] < id[a]) || \
-                          (corrected[a] != corrected[a] && corrected[b] == corrected[b]);             \
-        const float c0 = swap ? corrected[b] : corrected[a], c1 = swap ? corrected[a] : corrected[b]; \
-        const float r0 = swap ? raw[b] : raw[a], r1 = swap ? raw[a] : raw[b];                         \
-        const int i0 = swap ? id[b] : id[a], i1 = swap ? id[a] : id[b];                               \
-        corrected[a] = c0; corrected[b] = c1; raw[a] = r0; raw[b] = r1; id[a] = i0; id[b] = i1;       \
+    // Each lane first orders its own eight candidates, best first: a 19-comparator network on registers.  A round of
+    // the selection then only looks at the head of each lane's list.
+#define P92B_ORDER(a, b)                                                       \
+    {                                                                          \
+        const unsigned long long hi = cand[a] > cand[b] ? cand[a] : cand[b];   \
+        const unsigned long long lo = cand[a] > cand[b] ? cand[b] : cand[a];   \
+        cand[a] = hi; cand[b] = lo;                                            \
     }
     P92B_ORDER(0, 1) P92B_ORDER(2, 3) P92B_ORDER(4, 5) P92B_ORDER(6, 7)
     P92B_ORDER(0, 2) P92B_ORDER(1, 3) P92B_ORDER(4, 6) P92B_ORDER(5, 7)
@@ -115,36 +114,33 @@ __device__ __forceinline__ void warp_top8(const float* __restrict__ lg, const fl
     P92B_ORDER(2, 4) P92B_ORDER(3, 5)
     P92B_ORDER(1, 2) P92B_ORDER(3, 4) P92B_ORDER(5, 6)
 #undef P92B_ORDER
-    float chosen_weight = 0.0F;   // lane k keeps slot k's raw weight
-    int chosen_id = 0;
+    int chosen_id = 0;            // lane k keeps slot k's expert
     // The eight rounds stay a loop: unrolled they are a few thousand instructions, and a block that
     // runs this alone (the routing block of the fused kernels) then waits on instruction fetches.
 #pragma unroll 1
     for (int slot = 0; slot < 8; ++slot) {
-        // warp arg-max over the heads, lower id on ties: order-preserving integer image of the score
-        // (0 for a NaN or an exhausted list), one max over the warp, then the smallest id among the
-        // lanes that hold it
-        const float best = corrected[0];
-        const std::uint32_t bits = __float_as_uint(best);
-        const std::uint32_t key = best != best ? 0U : (bits & 0x80000000U ? ~bits : bits | 0x80000000U);
+        // warp arg-max over the heads: one max over the score images, one vote for who holds it; only when two lanes
+        // hold exactly the same score (or every list is down to NaNs) the lower id has to be found as well
+        const std::uint32_t key = static_cast<std::uint32_t>(cand[0] >> 32);
+        const std::uint32_t my_id = ~static_cast<std::uint32_t>(cand[0]);       // an exhausted list reads 0xffffffff
         const std::uint32_t top = __reduce_max_sync(0xffffffffU, key);
-        const int winner = static_cast<int>(__reduce_min_sync(0xffffffffU, key == top ? static_cast<std::uint32_t>(id[0]) : 0xffffffffU));
-        const float winner_raw = __shfl_sync(0xffffffffU, raw[0], winner & 31);
-        if ((winner & 31) == lane) {
+        const unsigned holders = __ballot_sync(0xffffffffU, key == top);
+        int winner;
+        if (__popc(holders) == 1) {
+            winner = static_cast<int>(__shfl_sync(0xffffffffU, my_id, __ffs(holders) - 1));
+        } else {
+            winner = static_cast<int>(__reduce_min_sync(0xffffffffU, key == top ? my_id : 0xffffffffU));
+        }
+        if ((winner & 31) == lane && static_cast<std::uint32_t>(winner) == my_id) {
 #pragma unroll
-            for (int i = 0; i < 7; ++i) {
-                corrected[i] = corrected[i + 1];
-                raw[i] = raw[i + 1];
-                id[i] = id[i + 1];
-            }
-            corrected[7] = __uint_as_float(0x7fc00000U);      // exhausted: key 0
-            id[7] = 0x7fffffff;
+            for (int i = 0; i < 7; ++i) cand[i] = cand[i + 1];
+            cand[7] = 0ULL;                                    // exhausted: image 0, id 0xffffffff
         }
-        if (lane == slot) {
-            chosen_weight = winner_raw;
-            chosen_id = winner;
-        }
+        if (lane == slot) chosen_id = winner;
     }
+    // weights: the uncorrected sigmoid of the winners (the same expression as above, so the same bits), summed in slot
+    // order and scaled by routed_scale / total (:420,425-432)
+    const float chosen_weight = lane < 8 ? 1.0F / (1.0F + expf(-lg[chosen_id & (kExperts - 1)])) : 0.0F;
     float total = 0.0F;
 #pragma unroll
     for (int slot = 0; slot < 8; ++slot) total += __shfl_sync(0xffffffffU, chosen_weight, slot);
