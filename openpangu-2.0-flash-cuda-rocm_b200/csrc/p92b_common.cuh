@@ -261,6 +261,7 @@ struct p92b_plan {
     unsigned long long* mega_logits = nullptr;  // [8][256] router logits as {value, launch number} words
     unsigned long long* mega_ret = nullptr;     // [8][9][1280] down rows as {two BF16, launch number} words
     float* w_norms = nullptr;                   // [256] norms of the router rows (large-batch router)
+    float* logit_partials = nullptr;            // [kRouterSplits][min(max_rows, kRouterSplitRows)][256] partial logits of the K splits
     int* router_stats = nullptr;                // [2] large-batch router: logits recomputed exactly so far, tokens that took a whole row
     unsigned long long* mega_hidden = nullptr;  // [8][H/2] un-normalised output rows as tagged words (fused post-norm)
     std::uint16_t* normed = nullptr;            // [max_rows][H] pre-normalised rows of the multi-kernel path
@@ -374,6 +375,8 @@ cudaError_t launch_rmsnorm(const std::uint16_t* input, const std::uint16_t* weig
 // Large-batch router (router_tc.cu): tensor-core logits + exact repair -> plan->logits, ids, route_weights.
 // cudaErrorNotSupported when the batch is too small or a pointer is not 16-byte aligned: take the exact kernels then.
 int router_fast_min_rows();
+constexpr int kRouterSplits = 8;                // K splits of the tensor-core logits for small batches
+constexpr int kRouterSplitRows = 256;           // ... used up to this many rows
 cudaError_t launch_router_fast(p92b_plan* plan, const std::uint16_t* x, const std::uint16_t* router_w, const float* bias,
                                int rows, float routed_scale, cudaStream_t stream, bool pdl);
 // tensor-core path (expert_tc.cu)

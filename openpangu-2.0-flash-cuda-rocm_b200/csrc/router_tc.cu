@@ -98,6 +98,9 @@ __global__ void __launch_bounds__(kLogitThreads, 1) logits_tc_kernel(const __gri
                                                                      const __grid_constant__ CUtensorMap map_w,
                                                                      float* __restrict__ logits, int rows, int hidden,
                                                                      std::int32_t* status) {
+    // gridDim.z > 1: block z takes a slice of the K blocks and writes its partial sums to slice z of `logits`
+    // ([gridDim.z][rows][256]); the repair kernel adds the slices (small batches: 4 blocks would otherwise walk all of
+    // K one after the other while 144 SMs idle)
     extern __shared__ std::uint8_t smem_raw[];
     __shared__ __align__(8) std::uint64_t barrier_words[2 * kLogitStages + 1];
     __shared__ std::uint32_t tmem_slot_word;
@@ -109,9 +112,13 @@ __global__ void __launch_bounds__(kLogitThreads, 1) logits_tc_kernel(const __gri
     const std::uint32_t accum_bar = bars + 8U * (2 * kLogitStages);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int k_blocks = hidden * 2 / kKBytes;
+    const int all_k_blocks = hidden * 2 / kKBytes;
+    const int per_split = (all_k_blocks + static_cast<int>(gridDim.z) - 1) / static_cast<int>(gridDim.z);
+    const int kb_first = min(all_k_blocks, static_cast<int>(blockIdx.z) * per_split);
+    const int k_blocks = min(all_k_blocks, kb_first + per_split) - kb_first;       // this block's share
     const int t0 = blockIdx.x * kTokTile;
     const int e0 = blockIdx.y * kExpTile;
+    logits += static_cast<std::size_t>(blockIdx.z) * rows * kExperts;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kLogitStages; ++s) {
@@ -147,8 +154,8 @@ __global__ void __launch_bounds__(kLogitThreads, 1) logits_tc_kernel(const __gri
                 if (!mbar_wait(empty_bar(stage), phase ^ 1U)) { give_up(); break; }
                 const std::uint32_t st = base + stage * kStageBytes;
                 mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-                tma_load_2d(st, &map_x, full_bar(stage), kb * kKBytes, t0);            // rows beyond the batch read as zero
-                tma_load_2d(st + kStageA, &map_w, full_bar(stage), kb * kKBytes, e0);
+                tma_load_2d(st, &map_x, full_bar(stage), (kb_first + kb) * kKBytes, t0);        // rows beyond the batch read as zero
+                tma_load_2d(st + kStageA, &map_w, full_bar(stage), (kb_first + kb) * kKBytes, e0);
                 if (++stage == kLogitStages) { stage = 0; phase ^= 1U; }
             }
         }
@@ -169,9 +176,9 @@ __global__ void __launch_bounds__(kLogitThreads, 1) logits_tc_kernel(const __gri
                 tc_commit(empty_bar(stage));
                 if (++stage == kLogitStages) { stage = 0; phase ^= 1U; }
             }
-            if (ok) tc_commit(accum_bar);
+            if (ok && k_blocks > 0) tc_commit(accum_bar);
         }
-    } else {
+    } else if (k_blocks > 0) {
         const int quarter = warp & 3;                       // TMEM lanes 32 * quarter ..: the token rows of this warp
         if (mbar_wait(accum_bar, 0)) {
             tc_fence_after();
@@ -229,24 +236,31 @@ constexpr int kRepairDepth = 3;                // router rows in flight per warp
 // the rows come from the L2 at about a microsecond each, and 171 MB of them at T=4096 make the L2-to-SM fabric the bound),
 // so a chain costs a shared-memory read, a shift and an fmaf per column instead of two 2-byte loads from the L2 that
 // the chain has to wait for.  CHUNKS = 0: any hidden size, token row in shared memory, router rows read in place.
-template <int CHUNKS>
-__global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
+// WPT (warps per token) = 1: a warp does everything for its token, four tokens per block - the form for thousands of
+// tokens.  WPT = 8: one token per block; the eight warps each build the candidate list (the same list) and then share
+// the candidates' exact logits out among themselves, warp 0 finishes - a few hundred tokens would otherwise leave
+// most SMs idle while every warp walks eight 2560-step chains one after the other.
+// `partials` (splits > 1): the approximate logits arrive as `splits` slices of partial sums ([splits][rows][256]).
+template <int CHUNKS, int WPT>
+__global__ void __launch_bounds__((WPT > 1 ? WPT : kRepairWarps) * 32) route_repair_kernel(
     const std::uint16_t* __restrict__ x, const std::uint16_t* __restrict__ w, const float* __restrict__ bias,
     const float* __restrict__ w_norms, float* __restrict__ logits, std::int32_t* __restrict__ ids,
-    float* __restrict__ weights, int rows, int hidden, float routed_scale, int* __restrict__ stats) {
+    float* __restrict__ weights, int rows, int hidden, float routed_scale, int* __restrict__ stats,
+    const float* __restrict__ partials, int splits) {
     extern __shared__ __align__(16) std::uint16_t repair_smem[];
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int kWarps = WPT > 1 ? WPT : kRepairWarps;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int token = blockIdx.x * kRepairWarps + warp;
-    if (token >= rows) return;
+    const int token = WPT > 1 ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) * kRepairWarps + warp;
+    if (token >= rows) return;                     // WPT > 1: the grid is exactly `rows` blocks
     // per warp: [CHUNKS > 0: two router-row buffers | CHUNKS == 0: the token row], then 256 exact logits, then the candidate list
     constexpr int kRowSlots = CHUNKS > 0 ? kRepairDepth : 1;
     std::uint16_t* x_row = repair_smem + static_cast<std::size_t>(warp) * kRowSlots * hidden;
-    std::uint8_t* tail = reinterpret_cast<std::uint8_t*>(repair_smem + static_cast<std::size_t>(kRepairWarps) * kRowSlots * hidden);
-    float* exact_row = reinterpret_cast<float*>(tail) + warp * kExperts;
-    std::uint16_t* cand = reinterpret_cast<std::uint16_t*>(tail + kRepairWarps * kExperts * 4) + warp * kExperts;
+    std::uint8_t* tail = reinterpret_cast<std::uint8_t*>(repair_smem + static_cast<std::size_t>(kWarps) * kRowSlots * hidden);
+    float* exact_row = reinterpret_cast<float*>(tail) + (WPT > 1 ? 0 : warp) * kExperts;      // WPT > 1: one row per block
+    std::uint16_t* cand = reinterpret_cast<std::uint16_t*>(tail + kWarps * kExperts * 4) + warp * kExperts;
     float xr[CHUNKS > 0 ? CHUNKS : 1];
     float square = 0.0F;
     if constexpr (CHUNKS > 0) {
@@ -276,10 +290,31 @@ __global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
     float* lg = logits + static_cast<std::size_t>(token) * kExperts;
     float approx[8], score[8];
     bool finite = true;
+    if (splits > 1) {
+        // all loads of the slices are issued before the first sum: one round trip, not one per slice
+        float part[kRouterSplits][8];
+#pragma unroll
+        for (int z = 0; z < kRouterSplits; ++z) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                part[z][i] = z < splits ? __ldg(partials + (static_cast<std::size_t>(z) * rows + token) * kExperts + lane + 32 * i) : 0.0F;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float sum = part[0][i];
+#pragma unroll
+            for (int z = 1; z < kRouterSplits; ++z) sum += part[z][i];
+            approx[i] = sum;
+            if (WPT == 1 || warp == 0) lg[lane + 32 * i] = sum;           // the logits buffer holds the approximate values
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) approx[i] = lg[lane + 32 * i];
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int e = lane + 32 * i;
-        approx[i] = lg[e];
         finite = finite && (fabsf(approx[i]) <= 3.0e38F);
         score[i] = 1.0F / (1.0F + expf(-approx[i])) + bias[e];
     }
@@ -328,7 +363,12 @@ __global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
         for (int i = 0; i < 8; ++i) member[i] = 0xffffffffU;
     }
     // exact logits of the candidates (or of the whole row), into the logits buffer and into this warp's row
-    for (int e = lane; e < kExperts; e += 32) exact_row[e] = -3.0e38F;       // non-candidates can never be selected
+    if constexpr (WPT > 1) {
+        for (int e = threadIdx.x; e < kExperts; e += WPT * 32) exact_row[e] = -3.0e38F;
+        __syncthreads();                               // before any warp stores a result into the shared row
+    } else {
+        for (int e = lane; e < kExperts; e += 32) exact_row[e] = -3.0e38F;   // non-candidates can never be selected
+    }
     int n_cand = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -336,30 +376,34 @@ __global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
         n_cand += __popc(member[i]);
     }
     __syncwarp();
+    // this warp's share of the candidates: all of them (WPT = 1) or every WPT-th, starting with its own number
+    const int first = WPT > 1 ? warp : 0;
+    constexpr int kStep = WPT > 1 ? WPT : 1;
+    const int n_mine = n_cand > first ? (n_cand - first + kStep - 1) / kStep : 0;
     if constexpr (CHUNKS > 0) {
-        auto fetch = [&](int k) {
-            if (k < n_cand) {
-                const uint4* src = reinterpret_cast<const uint4*>(w + static_cast<std::size_t>(cand[k]) * hidden);
-                uint4* dst = reinterpret_cast<uint4*>(x_row + static_cast<std::size_t>(k % kRepairDepth) * hidden);
+        auto fetch = [&](int i) {
+            if (i < n_mine) {
+                const uint4* src = reinterpret_cast<const uint4*>(w + static_cast<std::size_t>(cand[first + i * kStep]) * hidden);
+                uint4* dst = reinterpret_cast<uint4*>(x_row + static_cast<std::size_t>(i % kRepairDepth) * hidden);
                 for (int v = lane; v < hidden / 8; v += 32) copy16_async(dst + v, src + v);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");       // an empty group keeps the count in step
         };
 #pragma unroll
-        for (int k = 0; k < kRepairDepth - 1; ++k) fetch(k);
+        for (int i = 0; i < kRepairDepth - 1; ++i) fetch(i);
 #pragma unroll 1
-        for (int k = 0; k < n_cand; ++k) {
-            fetch(k + kRepairDepth - 1);                        // its buffer was last read by candidate k - 1
+        for (int i = 0; i < n_mine; ++i) {
+            fetch(i + kRepairDepth - 1);                        // its buffer was last read by candidate i - 1
             asm volatile("cp.async.wait_group %0;" ::"n"(kRepairDepth - 1) : "memory");
             __syncwarp();
-            const std::uint16_t* w_row = x_row + static_cast<std::size_t>(k % kRepairDepth) * hidden + lane;
+            const std::uint16_t* w_row = x_row + static_cast<std::size_t>(i % kRepairDepth) * hidden + lane;
             float value = 0.0F;
 #pragma unroll
             for (int j = 0; j < CHUNKS; ++j) value = fmaf(xr[j], bf16_bits_to_float(w_row[32 * j]), value);
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
             if (lane == 0) {
-                const int e = cand[k];
+                const int e = cand[first + i * kStep];
                 exact_row[e] = value;
                 lg[e] = value;
             }
@@ -367,14 +411,18 @@ __global__ void __launch_bounds__(kRepairWarps * 32) route_repair_kernel(
         }
     } else {
 #pragma unroll 1
-        for (int k = 0; k < n_cand; ++k) {
-            const int e = cand[k];
+        for (int i = 0; i < n_mine; ++i) {
+            const int e = cand[first + i * kStep];
             const float value = exact_logit(x_row, w + static_cast<std::size_t>(e) * hidden, hidden, lane);
             if (lane == 0) {
                 exact_row[e] = value;
                 lg[e] = value;
             }
         }
+    }
+    if constexpr (WPT > 1) {
+        __syncthreads();                                        // every warp's results are in the block's row
+        if (warp != 0) return;
     }
     __syncwarp();
     if (lane == 0 && stats != nullptr) {
@@ -457,20 +505,42 @@ cudaError_t launch_router_fast(p92b_plan* plan, const std::uint16_t* x, const st
     if (st != cudaSuccess) return cudaErrorNotSupported;
     if ((st = ensure_dynamic_smem<logits_tc_kernel>(kLogitSmem)) != cudaSuccess) return st;
     const bool in_registers = hidden == 2560;
-    const std::size_t repair_smem = static_cast<std::size_t>(kRepairWarps) * (in_registers ? kRepairDepth : 1) * hidden * 2 +
-                                    static_cast<std::size_t>(kRepairWarps) * kExperts * (4 + 2);
-    st = in_registers ? ensure_dynamic_smem<route_repair_kernel<80>>(static_cast<int>(repair_smem))
-                      : ensure_dynamic_smem<route_repair_kernel<0>>(static_cast<int>(repair_smem));
+    // small batches: K split over blocks of the logits kernel, and a block of eight warps per token in the repair
+    const bool small = rows <= kRouterSplitRows && plan->logit_partials != nullptr && plan->max_rows >= rows &&
+                       std::getenv("P92B_ROUTER_NO_SPLIT") == nullptr;
+    const int k_blocks = hidden * 2 / kKBytes;
+    const int per_split = small ? (k_blocks + kRouterSplits - 1) / kRouterSplits : k_blocks;
+    const int splits = (k_blocks + per_split - 1) / per_split;                    // no empty slice
+    constexpr int kWide = 8;
+    const int repair_warps = small ? kWide : kRepairWarps;
+    const std::size_t repair_smem = static_cast<std::size_t>(repair_warps) * (in_registers ? kRepairDepth : 1) * hidden * 2 +
+                                    static_cast<std::size_t>(repair_warps) * kExperts * (4 + 2);
+    if (small) {
+        st = in_registers ? ensure_dynamic_smem<route_repair_kernel<80, kWide>>(static_cast<int>(repair_smem))
+                          : ensure_dynamic_smem<route_repair_kernel<0, kWide>>(static_cast<int>(repair_smem));
+    } else {
+        st = in_registers ? ensure_dynamic_smem<route_repair_kernel<80, 1>>(static_cast<int>(repair_smem))
+                          : ensure_dynamic_smem<route_repair_kernel<0, 1>>(static_cast<int>(repair_smem));
+    }
     if (st != cudaSuccess) return st;
     st = launch_kernel(expert_norms_kernel, dim3(kExperts / 8), dim3(256), 0, stream, pdl, router_w, plan->w_norms, kExperts, hidden);
     if (st != cudaSuccess) return st;
-    st = launch_kernel(logits_tc_kernel, dim3((rows + kTokTile - 1) / kTokTile, kExperts / kExpTile), dim3(kLogitThreads),
-                       kLogitSmem, stream, pdl, map_x, map_w, plan->logits, rows, hidden, plan->status);
+    float* approx_out = splits > 1 ? plan->logit_partials : plan->logits;
+    st = launch_kernel(logits_tc_kernel, dim3((rows + kTokTile - 1) / kTokTile, kExperts / kExpTile, splits), dim3(kLogitThreads),
+                       kLogitSmem, stream, pdl, map_x, map_w, approx_out, rows, hidden, plan->status);
     if (st != cudaSuccess) return st;
-    st = launch_kernel(in_registers ? route_repair_kernel<80> : route_repair_kernel<0>,
-                       dim3((rows + kRepairWarps - 1) / kRepairWarps), dim3(kRepairWarps * 32), repair_smem, stream, pdl, x,
-                       router_w, bias, static_cast<const float*>(plan->w_norms), plan->logits, plan->ids,
-                       plan->route_weights, rows, hidden, routed_scale, plan->router_stats);
+    const float* partials = splits > 1 ? plan->logit_partials : nullptr;
+    if (small) {
+        st = launch_kernel(in_registers ? route_repair_kernel<80, kWide> : route_repair_kernel<0, kWide>, dim3(rows),
+                           dim3(kWide * 32), repair_smem, stream, pdl, x, router_w, bias,
+                           static_cast<const float*>(plan->w_norms), plan->logits, plan->ids, plan->route_weights, rows, hidden,
+                           routed_scale, plan->router_stats, partials, splits);
+    } else {
+        st = launch_kernel(in_registers ? route_repair_kernel<80, 1> : route_repair_kernel<0, 1>,
+                           dim3((rows + kRepairWarps - 1) / kRepairWarps), dim3(kRepairWarps * 32), repair_smem, stream, pdl, x,
+                           router_w, bias, static_cast<const float*>(plan->w_norms), plan->logits, plan->ids,
+                           plan->route_weights, rows, hidden, routed_scale, plan->router_stats, partials, splits);
+    }
     plan->last_launches += 3;
     return st;
 }
