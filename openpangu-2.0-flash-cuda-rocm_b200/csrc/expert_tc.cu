@@ -96,7 +96,6 @@ struct TcParams {
     int table_kind;                    // SRC 1, MODE 1: which of an expert's three matrices
     int skip_shared;                   // 1: the shared expert's items are not computed (the caller has none)
     std::uint16_t* const* row_dest;    // slab kernel of the down product: null, or [padded position] -> destination row
-    int prefetch_weights;              // paired gate/up kernel: L2 prefetch of the weights of items ahead
 };
 
 struct Item {
@@ -783,22 +782,6 @@ __global__ void __launch_bounds__(GuPair::kThreads, 1) expert_gu_pair_kernel(con
             const float alpha_u = p.bank.alpha[it.entry * 3 + 1];
             const int inter = p.m_total;
             const int row0 = it.m_tile * kTileM + quarter * 32;
-            if (p.prefetch_weights) {
-                // Ask the L2 for the weight chunks of the item two ahead (368,640 contiguous bytes, a few lines per
-                // thread, through the load/store path): about half of the kernel's weight bytes come from HBM at
-                // 1.5 - 2.5 µs, and with four stages in flight that latency, not a bandwidth, was what the ring delivered.
-                // The epilogue warps do it because they move with the items; a free-running prefetcher would ask for
-                // the whole kernel's weights at once.
-                Item next;
-                const int ahead = item + 2 * static_cast<int>(gridDim.x);
-                if (ahead < total_items && decode_item<2 * C::kN>(p, route_table, ahead, &next)) {
-                    const std::uint8_t* chunks =
-                        p.bank.g13 + (static_cast<std::size_t>(next.entry) * p.m_tiles + next.m_tile) * k_blocks * kChunkBytes;
-                    for (int line = static_cast<int>(threadIdx.x) - 64; line < k_blocks * kChunkBytes / 128; line += 32 * C::kEpilogueWarps) {
-                        prefetch_l2_line(chunks + static_cast<std::size_t>(line) * 128);
-                    }
-                }
-            }
             bool ok = true;
             for (int hh = 0; hh < halves; ++hh) {
                 const int buffer = next_buffer;
@@ -1337,7 +1320,6 @@ cudaError_t launch_experts_tc(const p92b_plan* plan, const p92b_bank* bank, int 
                     // large batches: pairs of 64-row token tiles share one weight stage (one 128-column tile was
                     // tried too: a single accumulator buffer and three stages then, 377 µs against 283 µs at T=4096)
                     p.tile_prefix = plan->tile_prefix_wide;
-                    p.prefetch_weights = std::getenv("P92B_NO_WEIGHT_PREFETCH") == nullptr ? 1 : 0;
                     if (cudaError_t st = ensure_dynamic_smem<expert_gu_pair_kernel>(GuPair::kSmemBytes); st != cudaSuccess) return st;
                     return launch_kernel(expert_gu_pair_kernel, dim3(plan->sm_count), dim3(GuPair::kThreads), GuPair::kSmemBytes,
                                          stream, pdl, plan->map_x[2], p);

@@ -166,11 +166,6 @@ __device__ __forceinline__ void bulk_load_hint(std::uint32_t dst, const void* sr
 }
 
 
-// Ask the L2 for one 128-byte line (through the load/store path: the bulk-copy engine stays free for the ring).
-__device__ __forceinline__ void prefetch_l2_line(const void* p) {
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");
-}
-
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
