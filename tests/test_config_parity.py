@@ -183,6 +183,31 @@ def test_block_of_64_and_512_rows_against_reference_kernels(cuda, pkg, orc, laye
     plan.close()
 
 
+@pytest.mark.parametrize("rows", [32, 33, 100, 255, 256, 257, 300])
+def test_router_either_side_of_the_small_batch_switch(cuda, pkg, orc, layer0, rows):
+    """The tensor-core router runs in two forms: up to 256 rows K is split over blocks and a block of eight warps
+    repairs one token; above, one warp per token.  Ids and route weights of every row must be the reference
+    kernels' bits in both (cuda/nvfp4_ops.cu:178-207,357-433), also with a bias that crowds the scores."""
+    torch = cuda
+    if not orc.have_ref():
+        pytest.skip("oracle/_ref was not built")
+    from p92moe_b200 import synth
+
+    for seed, bias in ((4300 + rows, layer0.bias), (4400 + rows, torch.zeros_like(layer0.bias))):
+        x = synth.make_activations(seed, rows, rows)
+        out = torch.empty_like(x)
+        plan = pkg.MoePlan(max_rows=rows)
+        plan.set_path(2)
+        pkg.MoeBlock(layer0.bank, layer0.router_weight, bias, plan).run_moe_rows(x, out, rows)
+        torch.cuda.synchronize()
+        views = plan.views(rows)
+        assert int(views["status"][0]) == 0
+        _, ref_ids, ref_w = _reference_rows(torch, orc, layer0, bias, x)
+        assert torch.equal(views["expert_ids"], ref_ids)
+        assert torch.equal(views["expert_weights"], ref_w)
+        plan.close()
+
+
 def test_gathered_exchange_path_300_rows_against_reference_kernels(cuda, pkg, orc, layer0):
     """The multi-kernel expert-parallel path (one GPU owning all experts): its own routing lists, the window
     round trip and the grouped products, checked against the reference chain on sampled rows."""
