@@ -13,7 +13,10 @@
 //   experts.  The grouped tcgen05 kernels on this GPU's shard and, for its home tokens, the shared expert.
 //   combine = direct placement.  Every result row is stored into its home GPU's window at [token][slot] (5 KB
 //       each, the volume of an all-to-all return); the home GPU sums the eight slots in slot order and adds its
-//       shared expert (cuda/nvfp4_ops.cu:124-142,92-95): the single-device combine law, bit for bit.
+//       shared expert (cuda/nvfp4_ops.cu:124-142,92-95): the single-device combine law, bit for bit.  At large
+//       batches the down product's own epilogue does these stores (a table of one destination pointer per padded row,
+//       TcIo::row_dest; 256-byte runs), so the return crosses NVLink while the product is still running and only a
+//       one-warp launch that publishes the flags follows; at small batches a separate kernel copies the rows.
 //
 // Synchronisation: data crosses as ordinary stores; after its stores a kernel's blocks fence at system scope and
 // count themselves, the last one publishes the call number in a flag word of every peer (release, system scope);

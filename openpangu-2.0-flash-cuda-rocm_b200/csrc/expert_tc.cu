@@ -22,6 +22,10 @@
 //           (tcgen05.ld), applies the per-tensor scale, rounds to BF16 where the reference does, and either fuses
 //           SwiGLU + re-quantisation to NVFP4 (MODE 0), stores the BF16 down rows (MODE 1) or stores BF16 gate and
 //           up rows un-fused (MODE 2, the reference's project_expert_gate_up result).
+// Every role turns an item number into work from a copy of the routing lists in shared memory (RouteTable), and an
+// epilogue warp hands its accumulator buffer back as soon as it has read its columns into registers.
+// Two more kernels in this file serve large batches with the same three roles: expert_gu_pair_kernel (one weight stage
+// against two 64-row token tiles) and expert_down_slab_kernel (a 128-token slab resident, weights streaming past).
 // Scale factors stay in the 128x4-tiled layout the reference keeps them in
 // (cuda/nvfp4_ops.cu:869-890): one 512-byte tile is exactly one tcgen05.cp atom.
 //
