@@ -108,23 +108,6 @@ struct Routing {
     float bias[kExperts];
 };
 
-// Device-wide rendezvous of the co-resident blocks: arrive, then wait for everyone.  Nothing the
-// kernel has written before it leaves this GPU, so device-scope fences are enough.
-__device__ __forceinline__ bool grid_rendezvous(unsigned* counter, unsigned target) {
-    __shared__ int ok;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        fence_proxy_async_all();
-        atomicAdd(counter, 1U);
-        ok = wait_counter(counter, target) ? 1 : 0;
-        __threadfence();
-        fence_proxy_async_all();
-    }
-    __syncthreads();
-    return ok != 0;
-}
-
 template <int kN>
 struct StageLayout {
     static constexpr int kOffB1 = kOffB0 + kN * kKB;
@@ -320,12 +303,69 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
                 st_tagged(dst + 2 * b + 1, packed.y, tag);
                 if ((b & 3) == 0) st_tagged(dst + kTokRowWords + (b >> 2), scales4, tag);
             }
+        } else if (g < rows * blocks16 + (rpg - rows)) {
+            // a token slot this GPU does not fill this time: the first word of its row says so (the complement of the
+            // launch number can be neither this launch's tag nor an older one), so that the receivers can tell a row that
+            // will not come from one that has not come yet without waiting for the ids
+            const int t = rows + (g - rows * blocks16);
+            for (int d = 0; d < world; ++d) {
+                std::uint64_t* dst = reinterpret_cast<std::uint64_t*>(p.win[d] + kWinArrive + parity * kWinArriveParity) +
+                                     static_cast<std::size_t>(p.rank * rpg + t) * kTokWords + kTokIdWords;
+                st_tagged(dst, 0U, ~tag);
+            }
         }
         if (block == 0) {
             for (int i = threadIdx.x; i <= kExperts + 1; i += kEpThreads) done_next[i] = 0;
         }
     }
     if (threadIdx.x == 0) stamp(1);
+
+    // ------------------------------------------------- the batch's rows: tagged words -> the layouts the TMA reads
+    // The rows left their GPUs in P0, long before the ids (which need the logits of all blocks and the top-8): the
+    // blocks that do not route turn them into the untagged row and scale layouts now, each its share, and count
+    // themselves in; the wait for that count sits just before the tiles, by when everybody has long arrived.
+    const int tokens = world * rpg;
+    const std::uint64_t* arrive = reinterpret_cast<const std::uint64_t*>(my_win + kWinArrive + parity * kWinArriveParity);
+    if (!abort_word && (block >= world || grid <= world)) {
+        std::uint8_t* xq_dense = my_win + kWinXq + parity * kWinXqParity;
+        std::uint8_t* xs_dense = my_win + kWinXs + parity * kWinXsParity;
+        const int per_token = kTokRowWords + kTokScaleWords;
+        const int copiers = grid > world ? grid - world : grid;
+        const int me = grid > world ? block - world : block;
+        for (int i = me * kEpThreads + threadIdx.x; i < tokens * per_token; i += copiers * kEpThreads) {
+            const int g = i / per_token;
+            const int w = i - g * per_token;
+            const std::uint64_t* row_words = arrive + static_cast<std::size_t>(g) * kTokWords + kTokIdWords;
+            // the slot's first word: this launch's tag (a row) or its complement (no row this time)
+            uint2 head = ld_tagged(row_words);
+            if (head.y != tag && head.y != ~tag) {
+                const std::uint64_t start = global_timer_ns();
+                do {
+                    if (poll_expired(start)) break;
+                    head = ld_tagged(row_words);
+                } while (head.y != tag && head.y != ~tag);
+            }
+            if (head.y == ~tag) continue;
+            std::uint32_t word = 0;
+            if (head.y != tag || !poll_tagged(row_words + w, tag, &word)) {
+                give_up(kStatusWaitExpired);
+                break;
+            }
+            if (w < kTokRowWords) {
+                reinterpret_cast<std::uint32_t*>(xq_dense + g * kXqRow)[w] = word;
+            } else {
+                *reinterpret_cast<std::uint32_t*>(xs_dense + (w - kTokRowWords) * 512 + g * 16) = word;
+            }
+        }
+    }
+    // (one arrival per block; what the block wrote is later read by TMA in other blocks)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        fence_proxy_async_all();
+        atomicAdd(p.sync, 1U);
+    }
+    if (threadIdx.x == 0) stamp(2);
 
     // ------------------------------------------------- routing of the home tokens: block d tells GPU d
     if (!abort_word && block < world) {
@@ -384,8 +424,6 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
 
     // ------------------------------------------------- arrivals: ids (every block), rows (one word per thread)
     const int local = p.bank.local_experts;
-    const int tokens = world * rpg;
-    const std::uint64_t* arrive = reinterpret_cast<const std::uint64_t*>(my_win + kWinArrive + parity * kWinArriveParity);
     for (int i = threadIdx.x; i < kMaxSlots; i += kEpThreads) rt.expert_mask[i] = 0;
     __syncthreads();
     if (!abort_word) {
@@ -408,25 +446,6 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     }
     __syncthreads();
     if (!abort_word) {
-        // this thread's share of the batch: tagged word -> the untagged row and scale layouts
-        std::uint8_t* xq_dense = my_win + kWinXq + parity * kWinXqParity;
-        std::uint8_t* xs_dense = my_win + kWinXs + parity * kWinXsParity;
-        const int per_token = kTokRowWords + kTokScaleWords;
-        for (int i = block * kEpThreads + threadIdx.x; i < tokens * per_token; i += grid * kEpThreads) {
-            const int g = i / per_token;
-            const int w = i - g * per_token;
-            if (rt.ids[g * kTop] < 0) continue;                      // slot not filled this time
-            std::uint32_t word = 0;
-            if (!poll_tagged(arrive + static_cast<std::size_t>(g) * kTokWords + kTokIdWords + w, tag, &word)) {
-                give_up(kStatusWaitExpired);
-                break;
-            }
-            if (w < kTokRowWords) {
-                reinterpret_cast<std::uint32_t*>(xq_dense + g * kXqRow)[w] = word;
-            } else {
-                *reinterpret_cast<std::uint32_t*>(xs_dense + (w - kTokRowWords) * 512 + g * 16) = word;
-            }
-        }
         // routing lists of this GPU's experts (every block, in shared memory)
         if (warp == 0) {
             int found = 0;
@@ -452,8 +471,17 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
         }
     }
     if (threadIdx.x == 0) stamp(5);
-    // the untagged batch is complete on this GPU once every block has written its share
-    if (!grid_rendezvous(p.sync, (p.epoch + 1U) * static_cast<unsigned>(grid))) give_up(kStatusWaitExpired);
+    // the untagged batch is complete on this GPU once every block has counted itself in (after P0, above)
+    {
+        __shared__ int batch_ready;
+        if (threadIdx.x == 0) {
+            batch_ready = wait_counter(p.sync, (p.epoch + 1U) * static_cast<unsigned>(grid)) ? 1 : 0;
+            __threadfence();
+            fence_proxy_async_all();
+        }
+        __syncthreads();
+        if (!batch_ready) give_up(kStatusWaitExpired);
+    }
     if (threadIdx.x == 0) stamp(6);
 
     // ------------------------------------------------------------ gate/up and down tiles
