@@ -156,15 +156,21 @@ __global__ void bulk_wait_kernel(const unsigned* __restrict__ flags, int world, 
 
 // ---- 2. rows of this GPU's experts (and its own shared-expert rows) into the padded position space -------------
 __global__ void __launch_bounds__(256) bulk_scatter_kernel(const std::uint8_t* __restrict__ arrived, const std::int32_t* __restrict__ pp_of_flat,
+                                                           const std::int32_t* __restrict__ order, const std::int32_t* __restrict__ counts,
+                                                           const std::int32_t* __restrict__ offsets,
                                                            int assignments, int home_first_token, int home_rows, int row_bytes,
                                                            int k_bytes, std::uint8_t* __restrict__ xq, std::uint8_t* __restrict__ xs,
                                                            PeerBases peers, std::size_t results_base, int rows_per_gpu,
                                                            std::uint16_t* mixed_pp, std::uint16_t** row_dest) {
+    // A fixed grid walks the rows this GPU computes: the sorted positions of its experts' assignments (order[] maps a
+    // position back to the flat index; with 2..8 GPUs these are a half to an eighth of the batch, and a block per
+    // eight flat indices would mostly launch blocks that leave at once), then its own shared-expert rows.
     const int lane = threadIdx.x & 31;
-    const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (unit >= assignments + home_rows) return;
+    const int local_total = offsets[kExperts - 1] + counts[kExperts - 1];
+    for (int work = blockIdx.x * 8 + (threadIdx.x >> 5); work < local_total + home_rows; work += gridDim.x * 8) {
+    const int unit = work < local_total ? order[work] : assignments + (work - local_total);
     const int pp_signed = pp_of_flat[unit];
-    if (pp_signed < 0) return;                                   // another GPU's expert, or an empty slot
+    if (pp_signed < 0) continue;                                 // (cannot happen for a listed position)
     const std::size_t pp = static_cast<std::size_t>(pp_signed);
     const std::size_t token = unit < assignments ? unit / kTop : home_first_token + (unit - assignments);
     if (row_dest != nullptr && lane == 0) {
@@ -209,6 +215,7 @@ __global__ void __launch_bounds__(256) bulk_scatter_kernel(const std::uint8_t* _
     for (int i = 0; i < 2; ++i) {
         const int c = lane + 32 * i;
         if (c < scale_words) *reinterpret_cast<std::uint32_t*>(sf_to + static_cast<std::size_t>(c) * 512) = scale_word[i];
+    }
     }
 }
 
@@ -387,7 +394,9 @@ int p92b_ep_forward_bulk(p92b_plan* plan, const p92b_bank* bank, p92b_ep_window*
     // large batches: the down product stores every row where the combine wants it, over NVLink while it computes
     const bool direct = down_slab_applies(plan, tokens) && std::getenv("P92B_BULK_NO_DIRECT") == nullptr;
     std::uint16_t** row_dest = direct ? reinterpret_cast<std::uint16_t**>(mine + layout.dest) : nullptr;
-    bulk_scatter_kernel<<<(units + 7) / 8, 256, 0, stream>>>(mine + layout.rows, plan->pp_of_flat, assignments,
+    (void)units;
+    bulk_scatter_kernel<<<plan->sm_count * 4, 256, 0, stream>>>(mine + layout.rows, plan->pp_of_flat, plan->order, plan->counts,
+                                                                plan->offsets, assignments,
                                                              window->rank * rpg, rows, layout.row_bytes, hidden / 2, plan->xq_pp,
                                                              plan->xs_sw, peers, layout.results, rpg, plan->mixed_pp, row_dest);
     if ((st = cudaGetLastError()) != cudaSuccess) return st;
