@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 
 REL_L2 = 1e-2
 MAX_ABS = 2e-2
-FAST_ROUTER_ROWS = 32        # from this batch size on the block takes tensor-core logits with exact repair
+FAST_ROUTER_ROWS = 9         # from this batch size on the block takes tensor-core logits with exact repair
 
 
 def _stream(torch):
@@ -183,7 +183,7 @@ def test_block_of_64_and_512_rows_against_reference_kernels(cuda, pkg, orc, laye
     plan.close()
 
 
-@pytest.mark.parametrize("rows", [32, 33, 100, 255, 256, 257, 300])
+@pytest.mark.parametrize("rows", [9, 10, 17, 31, 32, 33, 100, 255, 256, 257, 300])
 def test_router_either_side_of_the_small_batch_switch(cuda, pkg, orc, layer0, rows):
     """The tensor-core router runs in two forms: up to 256 rows K is split over blocks and a block of eight warps
     repairs one token; above, one warp per token.  Ids and route weights of every row must be the reference
