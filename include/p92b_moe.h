@@ -232,7 +232,7 @@ size_t p92b_plan_bytes(const p92b_plan* plan);
  * (src/model.cpp:1486-1573): router logits -> top-8 -> permutation -> NVFP4
  * gate/up + SwiGLU -> NVFP4 down -> weighted combine (device law,
  * cuda/nvfp4_ops.cu:124-142) -> + shared expert.  input/output: BF16 [rows][hidden].
- * rows == 1 uses the T=1 logits order, rows > 1 the T>1 order, as the reference does.  From 256 rows on the logits
+ * rows == 1 uses the T=1 logits order, rows > 1 the T>1 order, as the reference does.  From 9 rows on the logits
  * are a BF16 tensor-core product and only the ones that can decide the top-8 (every expert within a proven error bound
  * of the 8th best, about nine per token) are recomputed in the reference's exact order; expert ids and route weights
  * are still the reference's bit for bit, the `logits` view then holds approximate values except at those positions.
