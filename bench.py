@@ -448,8 +448,8 @@ class SingleGpu:
         bytes_call = layer_bytes(d_mean, rows)
         pk = peaks()
         gbs = bytes_call / (us_per_call * 1e-6) / 1e9
-        kernel = "moe_decode_kernel" if rows <= 8 else "expert_tc_kernel (gate/up + down of a %d-launch chain)" % launches_per_call
-        ratio = ncu_ratios().get("moe_decode_kernel") if rows <= 8 else None
+        kernel = "moe_decode_kernel" if rows <= 16 else "expert_tc_kernel (gate/up + down of a %d-launch chain)" % launches_per_call
+        ratio = ncu_ratios().get("moe_decode_kernel") if rows <= 16 else None
         rec = {
             "ms_per_step": ms, "value": rows / (ms * 1e-3), "unit": "tokens/s", "steps": steps * inner, "repeats": repeats,
             "us_per_layer_call": us_per_call, "gpu_launches": launches_per_call * calls_per_step * steps * inner * repeats,

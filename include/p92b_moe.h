@@ -238,7 +238,7 @@ size_t p92b_plan_bytes(const p92b_plan* plan);
  * are still the reference's bit for bit, the `logits` view then holds approximate values except at those positions.
  * P92B_EXACT_LOGITS=1 in the environment keeps the exact-order kernel at every size.
  *
- * For up to 8 rows the block is ONE persistent kernel with one thread block per SM whose blocks hand
+ * For up to 16 rows the block is ONE persistent kernel with one thread block per SM whose blocks hand
  * data to one another (p92b_plan_set_path).  They must all be resident at once: do not run it while
  * kernels on other streams keep SMs occupied for long.  Every wait inside is bounded: if the blocks cannot
  * make progress within about a second the call ends with 2 in the plan's status word (p92b_plan_get_views)
@@ -250,7 +250,7 @@ int p92b_moe_forward(p92b_plan* plan, const p92b_bank* bank, const uint16_t* inp
 /* The block with the two RMSNorms the engine runs either side of it (src/model.cpp:211-218 decode, :1210-1217
  * prefill rows): output = rmsnorm(block(rmsnorm(input, pre_norm_weight)), post_norm_weight), each norm the reference's
  * operator bit for bit (p92b_rmsnorm), so the routing equals the reference's on the same `mixed_` rows.  Either weight
- * may be NULL (that norm is skipped); norm_epsilon is the engine's kNormEpsilon (src/model.cpp:57).  For up to 8 rows
+ * may be NULL (that norm is skipped); norm_epsilon is the engine's kNormEpsilon (src/model.cpp:57).  For up to 16 rows
  * both norms run inside the one persistent kernel - the pre-norm where it stages the token rows, the post-norm behind
  * its combine - so the engine saves two launches per layer; larger batches run p92b_rmsnorm around the pipeline. */
 int p92b_moe_forward_normed(p92b_plan* plan, const p92b_bank* bank, const uint16_t* input, const uint16_t* pre_norm_weight,
@@ -469,8 +469,8 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* views);
 int p92b_plan_stage_timing(p92b_plan* plan, int enable);
 int p92b_plan_stage_times(const p92b_plan* plan, float* host_ms, int* host_calls);
 
-/* Kernel family for the block: 0 automatic (3 for up to 8 rows, else 2), 2 tcgen05 block-scaled MMA kernels
- * (TMA + TMEM), one launch per stage, at any size, 3 the whole block as one persistent tcgen05 kernel (up to 8
+/* Kernel family for the block: 0 automatic (3 for up to 16 rows, else 2), 2 tcgen05 block-scaled MMA kernels
+ * (TMA + TMEM), one launch per stage, at any size, 3 the whole block as one persistent tcgen05 kernel (up to 16
  * rows).  The environment variable P92B_PATH sets the default of new plans.  Both implement the same
  * arithmetic contract. */
 int p92b_plan_set_path(p92b_plan* plan, int path);

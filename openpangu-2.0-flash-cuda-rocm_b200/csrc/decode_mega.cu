@@ -1,4 +1,4 @@
-// The whole MoE block for up to 8 tokens (decode, MTP verify) as ONE persistent kernel.
+// The whole MoE block for up to 16 tokens (decode, MTP verify, small decode batches) as ONE persistent kernel.
 //
 // At these sizes the block is a 120 MB weight stream (≈19 µs at HBM speed) wrapped in a
 // few microseconds of routing, so kernel boundaries - five dependent launches - cost
@@ -42,13 +42,13 @@ using namespace decode;
 namespace {
 
 constexpr int kMegaThreads = 192;
-constexpr int kMegaMaxRows = 8;
+constexpr int kMegaMaxRows = 16;                   // = kN: the token side of every MMA holds them all; the kernel is built
+                                                   // for 8 (the decode sizes, leaner loops) and for 16 rows
 constexpr int kN = 16;                             // token columns of every MMA
 // a ring stage: the bank's chunk (decode_pipeline.cuh), then two token boxes and two token scale slabs
 constexpr int kOffB1 = 38912, kOffSfB0 = 40960, kOffSfB1 = 43008;
 constexpr int kStage = 45056;
 constexpr int kWeightTx = kChunkBytes;
-constexpr int kMaxActive = kMegaMaxRows * kTop + 1;
 
 struct MegaParams {
     BankView bank;
@@ -87,20 +87,22 @@ struct MegaParams {
     int inter;
 };
 
-struct Routing {                   // shared-memory copy, identical in every block
-    std::int32_t ids[kMegaMaxRows * kTop];
-    float weights[kMegaMaxRows * kTop];
-    std::int32_t rank[kMegaMaxRows * kTop];          // earlier assignments with the same expert
-    std::int32_t less[kMegaMaxRows * kTop];          // assignments with a smaller expert id
-    std::int32_t slot_a[kMegaMaxRows * kTop];        // active slot of the assignment's expert (1-based)
+template <int R>
+struct Routing {                   // shared-memory copy, identical in every block; R = the build's row limit
+    static constexpr int kMaxActive = R * kTop + 1;
+    std::int32_t ids[R * kTop];
+    float weights[R * kTop];
+    std::int32_t rank[R * kTop];          // earlier assignments with the same expert
+    std::int32_t less[R * kTop];          // assignments with a smaller expert id
+    std::int32_t slot_a[R * kTop];        // active slot of the assignment's expert (1-based)
     std::int32_t active[kMaxActive];                 // expert of an active slot; slot 0 is the shared expert
     std::int32_t slot_rows[kMaxActive];              // rows of an active slot
-    std::int32_t pp_tok[kMaxActive][kMegaMaxRows];   // padded position of (active slot, token), -1 if not routed
+    std::int32_t pp_tok[kMaxActive][R];   // padded position of (active slot, token), -1 if not routed
     std::int32_t n_active;
     std::uint32_t expert_mask[kExperts];             // tokens routed to each expert
     std::int32_t before[kExperts];                   // assignments with a smaller expert id
     std::int32_t slot_of[kExperts];                  // active slot an expert has (if any token picked it)
-    float logits[kMegaMaxRows * kExperts];
+    float logits[R * kExperts];
     float bias[kExperts];
 };
 
@@ -115,19 +117,21 @@ __device__ __forceinline__ void grid_arrive(unsigned* counter) {
     }
 }
 
+template <int R>
 __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                       const __grid_constant__ CUtensorMap map_h,
                                                                       const MegaParams p) {
     extern __shared__ std::uint8_t smem_raw[];
-    __shared__ Routing rt;
+    __shared__ Routing<R> rt;
+    constexpr int kMaxActive = Routing<R>::kMaxActive;
     __shared__ __align__(8) std::uint64_t barrier_words[3 * kStages + 2 * kAccumBuffers];
     __shared__ std::uint32_t tmem_slot_word;
     __shared__ volatile std::uint32_t abort_word;
     __shared__ volatile int tile_queue[kTileQueue];
     __shared__ volatile int first_tile_word;
     __shared__ volatile int rows_ready_word;
-    __shared__ float norm_partial[kMegaMaxRows][8];
-    __shared__ float norm_inverse[kMegaMaxRows];
+    __shared__ float norm_partial[R][8];
+    __shared__ float norm_inverse[R];
 
     const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
     const std::uint32_t bars = smem_u32(barrier_words);
@@ -337,7 +341,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     {
         // logits come from all blocks of this launch: each word is polled until it carries this launch's
         // number.  All of a thread's words are requested before the first is looked at.
-        constexpr int kPerThread = (kMegaMaxRows * kExperts + kMegaThreads - 1) / kMegaThreads;
+        constexpr int kPerThread = (R * kExperts + kMegaThreads - 1) / kMegaThreads;
         uint2 word[kPerThread];
         const std::uint64_t poll_start = global_timer_ns();
         while (true) {
@@ -372,7 +376,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
             fence_proxy_async_all();      // ordinary stores of other blocks -> this block's TMA loads
             rows_ready_word = arrived ? 1 : 0;
         }
-        for (int i = threadIdx.x; i < kMaxActive * kMegaMaxRows; i += kMegaThreads) (&rt.pp_tok[0][0])[i] = -1;
+        for (int i = threadIdx.x; i < kMaxActive * R; i += kMegaThreads) (&rt.pp_tok[0][0])[i] = -1;
         for (int i = threadIdx.x; i < kExperts; i += kMegaThreads) rt.expert_mask[i] = 0U;
         __syncthreads();
     }
@@ -623,7 +627,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                 tmem_load16(lane_base + kAccumStride, u);
                 tmem_load_wait();
 #pragma unroll
-                for (int n = 0; n < kMegaMaxRows; ++n) {
+                for (int n = 0; n < R; ++n) {
                     const int pp_signed = n < rows ? rt.pp_tok[slot][n] : -1;        // warp uniform
                     if (pp_signed < 0) continue;
                     const float gv = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(g[n]) * alpha_g));
@@ -668,7 +672,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                 // combine expects it (slot 8 = the shared expert)
                 int n = 0;
 #pragma unroll
-                for (int t = 0; t < kMegaMaxRows; ++t) {
+                for (int t = 0; t < R; ++t) {
                     if (t >= rows || rt.pp_tok[slot][t] < 0) continue;             // warp uniform
                     int k = kTop;
                     if (slot != 0) {
@@ -678,7 +682,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
                     }
                     std::uint32_t value = 0;
 #pragma unroll
-                    for (int c = 0; c < kMegaMaxRows; ++c) value = c == n ? d[c] : value;   // d[n] without dynamic indexing
+                    for (int c = 0; c < R; ++c) value = c == n ? d[c] : value;   // d[n] without dynamic indexing
                     value = float_to_bf16_bits(__uint_as_float(value) * alpha);
                     p.mixed[static_cast<std::size_t>(pp0 + n) * hidden + row] = static_cast<std::uint16_t>(value);
                     const std::uint32_t next = __shfl_down_sync(0xffffffffU, value, 1);
@@ -785,7 +789,11 @@ cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std
         plan->intermediate != 1024) {
         return cudaErrorNotSupported;
     }
-    if (cudaError_t st = ensure_dynamic_smem<moe_decode_kernel>(kMegaSmem); st != cudaSuccess) return st;
+    const bool wide = rows > 8;
+    if (cudaError_t st = wide ? ensure_dynamic_smem<moe_decode_kernel<16>>(kMegaSmem) : ensure_dynamic_smem<moe_decode_kernel<8>>(kMegaSmem);
+        st != cudaSuccess) {
+        return st;
+    }
     MegaParams p {};
     p.bank = bank->view;
     p.x = x;
@@ -822,8 +830,10 @@ cudaError_t launch_decode_mega(p92b_plan* plan, const p92b_bank* bank, const std
     p.hidden = plan->hidden;
     p.inter = plan->intermediate;
     plan->last_launches += 1;
-    return launch_kernel(moe_decode_kernel, dim3(plan->sm_count), dim3(kMegaThreads), kMegaSmem, stream, pdl,
-                         plan->map_x_tok, plan->map_h[0], p);
+    return wide ? launch_kernel(moe_decode_kernel<16>, dim3(plan->sm_count), dim3(kMegaThreads), kMegaSmem, stream, pdl,
+                                plan->map_x_tok, plan->map_h[0], p)
+                : launch_kernel(moe_decode_kernel<8>, dim3(plan->sm_count), dim3(kMegaThreads), kMegaSmem, stream, pdl,
+                                plan->map_x_tok, plan->map_h[0], p);
 }
 
 }  // namespace p92b

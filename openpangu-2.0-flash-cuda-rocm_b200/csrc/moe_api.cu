@@ -188,13 +188,13 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->gu_done = c.take<std::int32_t>(2 * 264);
         plan->ep_gu_done = c.take<std::int32_t>(2 * 264);
         plan->ep_logits = c.take<unsigned long long>(static_cast<std::size_t>(8) * kExperts);
-        plan->mega_logits = c.take<unsigned long long>(static_cast<std::size_t>(8) * kExperts);
-        plan->mega_ret = c.take<unsigned long long>(static_cast<std::size_t>(8) * (kTop + 1) * 1280);
+        plan->mega_logits = c.take<unsigned long long>(static_cast<std::size_t>(16) * kExperts);
+        plan->mega_ret = c.take<unsigned long long>(static_cast<std::size_t>(16) * (kTop + 1) * 1280);
         plan->mega_trace = c.take<unsigned long long>(static_cast<std::size_t>(plan->sm_count) * 64);
         plan->w_norms = c.take<float>(kExperts);
         plan->router_stats = c.take<int>(2);
         plan->logit_partials = c.take<float>(static_cast<std::size_t>(kRouterSplits) * std::min(max_rows, kRouterSplitRows) * kExperts);
-        plan->mega_hidden = c.take<unsigned long long>(static_cast<std::size_t>(8) * (hidden / 2));
+        plan->mega_hidden = c.take<unsigned long long>(static_cast<std::size_t>(16) * (hidden / 2));
         plan->normed = c.take<std::uint16_t>(rows * hidden);
         plan->ep_words = 16 * (kExperts + 1);
         plan->ep_src_base = c.take<std::int32_t>(plan->ep_words);

@@ -297,17 +297,17 @@ def _oracle_forward(orc, pkg, host, x_bits, **kw):
 
 
 PATHS = [pytest.param(2, id="tcgen05"), pytest.param(3, id="fused-decode")]
-FUSED_MAX_ROWS = 8      # path 3 is the single persistent decode kernel, up to 8 tokens
+FUSED_MAX_ROWS = 16     # path 3 is the single persistent decode kernel, up to 16 tokens
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("rows", [1, 2, 4, 5, 8, 17])
+@pytest.mark.parametrize("rows", [1, 2, 4, 5, 8, 9, 13, 16, 17])
 def test_moe_forward_against_cpu_oracle(cuda, pkg, orc, layer0, layer0_host, rows, path):
     torch = cuda
     from p92moe_b200 import synth
 
     if path == 3 and rows > FUSED_MAX_ROWS:
-        pytest.skip("fused decode kernel serves up to 8 tokens")
+        pytest.skip("fused decode kernel serves up to 16 tokens")
     x = synth.make_activations(42, rows, rows)
     out = torch.full_like(x, float("nan"))
     plan = pkg.MoePlan(max_rows=max(rows, 4))
@@ -350,7 +350,7 @@ def test_moe_forward_against_cpu_oracle(cuda, pkg, orc, layer0, layer0_host, row
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("rows", [1, 3, 4, 8, 33, 70, 200])
+@pytest.mark.parametrize("rows", [1, 3, 4, 8, 11, 16, 33, 70, 200])
 def test_moe_forward_against_reference_kernels(cuda, pkg, orc, layer0, rows, path):
     torch = cuda
     if not orc.have_ref():
@@ -358,7 +358,7 @@ def test_moe_forward_against_reference_kernels(cuda, pkg, orc, layer0, rows, pat
     from p92moe_b200 import synth
 
     if path == 3 and rows > FUSED_MAX_ROWS:
-        pytest.skip("fused decode kernel serves up to 8 tokens")
+        pytest.skip("fused decode kernel serves up to 16 tokens")
     x = synth.make_activations(43, rows, rows)
     out = torch.empty_like(x)
     plan = pkg.MoePlan(max_rows=rows)
