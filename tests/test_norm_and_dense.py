@@ -67,7 +67,7 @@ def test_rmsnorm_operator_bit_exact_with_reference_kernel(cuda, pkg, orc, rows, 
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("rows", [1, 3, 4, 8, 33])
+@pytest.mark.parametrize("rows", [1, 3, 4, 8, 9, 16, 33])
 @pytest.mark.parametrize("which", ["both", "pre", "post"])
 def test_block_with_fused_norms_against_reference_chain(cuda, pkg, orc, layer0, rows, which):
     """rmsnorm(pre_mlp_norm) -> run_moe_rows -> rmsnorm(post_mlp_norm) in one call: the pre-normalised rows must be
