@@ -801,21 +801,27 @@ class ExpertParallel:
         }
         if mode == "exact":
             rec["exposed_communication"] = self.exposed_communication(states, xs, outs, rows, n_layers, ms)
-        if mode == "bulk":
-            # event pairs inside the library around the parts of the layer: the two exchange parts hold the peer stores
+        if mode in ("bulk", "gathered"):
+            # event pairs inside the library around the parts of the layer: the exchange parts hold the peer stores
             # AND the wait for the slowest peer, i.e. everything a GPU spends not computing
             plan.stage_timing(True)
             self.timer.barrier()
-            for _ in range(5):
+            for _ in range(5 if mode == "bulk" else 2):
                 for l in range(n_layers):
                     forward(l, xs[l], outs[l])
             stage_ms, calls = plan.stage_times()
             plan.stage_timing(False)
-            names = ("router", "dispatch_exchange", "permute_and_placement", "unused", "gate_up_swiglu", "down",
-                     "return_exchange_and_combine")
+            if mode == "bulk":
+                names = ("router", "dispatch_exchange", "permute_and_placement", "unused", "gate_up_swiglu", "down",
+                         "return_exchange_and_combine")
+            else:
+                names = ("router", "dispatch_exchange", "routing_lists_after_all_ids", "placement_after_all_rows",
+                         "gate_up_swiglu", "down", "return_exchange_and_combine")
             per_call = [v / calls * 1e3 for v in stage_ms.values()]
             stage_us = {n: self.timer.max_over_ranks(v) for n, v in zip(names, per_call) if n != "unused"}
             exchange = stage_us["dispatch_exchange"] + stage_us["return_exchange_and_combine"]
+            if mode == "gathered":
+                exchange += stage_us["routing_lists_after_all_ids"]
             rec["stage_us_max_over_ranks"] = stage_us
             rec["exposed_communication"] = {
                 "wall_ms_per_step": ms, "exchange_us_per_layer": exchange, "compute_us_per_layer": sum(stage_us.values()) - exchange,

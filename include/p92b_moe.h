@@ -464,7 +464,10 @@ int p92b_plan_get_views(const p92b_plan* plan, p92b_plan_views* views);
  * the call and accumulates the elapsed times; off by default and free when off.
  * Stages: 0 router logits, 1 top-8, 2 permutation, 3 activation quantise, 4 gate/up + SwiGLU,
  * 5 down, 6 combine + shared add.  host_ms[7] receives the sums since enabling, host_calls the
- * number of forwards accumulated. */
+ * number of forwards accumulated.  The multi-kernel expert-parallel calls honour it too, with their own meaning of the
+ * seven slots: p92b_ep_forward_bulk 0 router, 1 dispatch (stores + wait for every peer's rows), 2 permutation +
+ * placement, 3 unused, 4 gate/up, 5 down, 6 return + combine; p92b_ep_forward_gathered 0 router, 1 push, 2 routing
+ * lists (waits for all ids), 3 placement (waits for all rows), 4 gate/up, 5 down, 6 return + combine. */
 #define P92B_STAGES 7
 int p92b_plan_stage_timing(p92b_plan* plan, int enable);
 int p92b_plan_stage_times(const p92b_plan* plan, float* host_ms, int* host_calls);

@@ -403,6 +403,15 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
     const std::uint64_t* my_arrive = reinterpret_cast<const std::uint64_t*>(window->local + arrive_offset);
     const std::uint64_t* my_ret = reinterpret_cast<const std::uint64_t*>(window->local + ret_offset);
     plan->last_launches = 0;
+    // optional stage timing (p92b_plan_stage_timing): 0 router, 1 push (quantise + stores to every window), 2 routing lists
+    // (waits for the ids of the whole batch), 3 placement (waits for the rows), 4 gate/up, 5 down, 6 return + combine
+    // (waits for every peer's result rows)
+    int stage = 0;
+    auto mark = [&]() -> cudaError_t {
+        if (!plan->timing) return cudaSuccess;
+        return cudaEventRecord(plan->stage_events[stage++], stream);
+    };
+    if (cudaError_t m = mark(); m != cudaSuccess) return m;
 
     // router of the home tokens (ids into plan->ids, weights stay in plan->route_weights for the combine)
     // (tensor-core logits with exact repair from 9 rows on: same ids and weights, 20 against 38 µs at 64 to 512 rows)
@@ -416,11 +425,13 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
         plan->last_launches += 2;
     }
     if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
     const int push_threads = std::max(rows * (hidden / 16), rpg * kTop);
     st = launch_kernel(epg_push_kernel, dim3((push_threads + 255) / 256), dim3(256), 0, stream, pdl, input,
                        static_cast<const std::int32_t*>(plan->ids), peers, arrive_offset, window->rank, world, rows, rpg,
                        hidden, 1.0F, tag);
     if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
     // routing lists of this GPU's experts (+ its shared-expert rows) from the ids of the whole batch; a token picks
     // an expert at most once, so no expert has more rows than there are tokens
     const int tile_rows = tc_tile_rows(tokens);
@@ -431,6 +442,7 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
                        bank->view.first_expert, local, rows, tile_rows, tag, plan->counts, plan->pp_off, plan->active,
                        plan->active_count, plan->tile_prefix, plan->pp_of_flat, plan->status);
     if (st != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
     plan->wide_rows = 0;
     const int units = assignments + rows;
     st = launch_kernel(epg_scatter_kernel, dim3((units + 7) / 8), dim3(256), 0, stream, pdl, my_arrive,
@@ -439,8 +451,11 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
     if (st != cudaSuccess) return st;
     // every kernel of the chain waits for its predecessor before it finishes, so the lists two launches up are
     // complete when the down product looks at them
+    if ((st = mark()) != cudaSuccess) return st;
     if ((st = launch_experts_tc(plan, bank, tokens, false, stream, pdl)) != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
     if ((st = launch_experts_tc(plan, bank, tokens, true, stream, pdl)) != cudaSuccess) return st;
+    if ((st = mark()) != cudaSuccess) return st;
     st = launch_kernel(epg_return_kernel, dim3((assignments + 7) / 8), dim3(256), 0, stream, pdl,
                        static_cast<const std::uint16_t*>(plan->mixed_pp), static_cast<const std::int32_t*>(plan->pp_of_flat),
                        peers, ret_offset, assignments, rpg, hidden, tag);
@@ -450,6 +465,17 @@ int p92b_ep_forward_gathered(p92b_plan* plan, const p92b_bank* bank, p92b_ep_win
                        static_cast<const std::int32_t*>(plan->pp_off), output, rows, hidden, tag, plan->status);
     plan->last_launches += 7;           // behind the router's two or three
     plan->last_path = 2;
+    if (st != cudaSuccess) return st;
+    if (plan->timing) {
+        if ((st = mark()) != cudaSuccess) return st;
+        if ((st = cudaStreamSynchronize(stream)) != cudaSuccess) return st;
+        for (int i = 0; i < P92B_STAGES; ++i) {
+            float ms = 0.0F;
+            if ((st = cudaEventElapsedTime(&ms, plan->stage_events[i], plan->stage_events[i + 1])) != cudaSuccess) return st;
+            plan->stage_ms[i] += ms;
+        }
+        plan->timed_calls += 1;
+    }
     return st;
 }
 
