@@ -174,9 +174,9 @@ def ep_mode(workload: str, world: int) -> str:
     rows = ep_rows(workload, world)
     if rows <= 8 and world * rows <= 32:
         return "fused"
-    if rows <= 512 and world * rows <= 1024:
-        return "gathered"
-    return "bulk"
+    if rows <= 128 and world * rows <= 1024:
+        return "gathered"          # measured on the 512-token workload: 6.42 ms against 7.03 ms (bulk) at 128 rows per GPU,
+    return "bulk"                  # 9.42 ms against 9.06 ms (bulk) at 256
 
 
 def ep_rows(workload: str, world: int) -> int:
