@@ -251,20 +251,22 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
         if (rows == 1) {
             // T = 1 order: 256 partial chains (thread t: columns t, t+256, ...), a shuffle-down tree
             // per 32 of them, then a tree over the eight results (cuda/nvfp4_ops.cu:38-51,161-176)
-            for (int q = warp; q < my_experts; q += kMegaThreads / 32) {
+            // The block's (router row, group of 32 chains) pairs are dealt to its six warps - one warp per row would walk
+            // eight dependent rounds while four warps idle - and a warp per row then adds the eight group sums.
+            for (int job = warp; job < my_experts * 8; job += kMegaThreads / 32) {
+                const int q = job >> 3, v = job & 7;
                 const std::uint16_t* wr = w_rows + q * hidden;
-                float value = 0.0F;
-#pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    float partial = 0.0F;
-                    for (int c = lane + 32 * v; c < hidden; c += 256) {
-                        partial = fmaf(bf16_bits_to_float(x_rows[c]), bf16_bits_to_float(wr[c]), partial);
-                    }
-#pragma unroll
-                    for (int off = 16; off > 0; off >>= 1) partial += __shfl_down_sync(0xffffffffU, partial, off);
-                    const float warp_sum = __shfl_sync(0xffffffffU, partial, 0);
-                    if (lane == v) value = warp_sum;
+                float partial = 0.0F;
+                for (int c = lane + 32 * v; c < hidden; c += 256) {
+                    partial = fmaf(bf16_bits_to_float(x_rows[c]), bf16_bits_to_float(wr[c]), partial);
                 }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) partial += __shfl_down_sync(0xffffffffU, partial, off);
+                if (lane == 0) norm_partial[q][v] = partial;
+            }
+            __syncthreads();
+            for (int q = warp; q < my_experts; q += kMegaThreads / 32) {
+                float value = lane < 8 ? norm_partial[q][lane] : 0.0F;
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) value += __shfl_down_sync(0xffffffffU, value, off);
                 if (lane == 0) {
