@@ -26,7 +26,7 @@ def test_shim_compiles_against_the_reference_header():
     assert result.returncode == 0, result.stderr
 
 
-def test_shim_defines_every_moe_entry_point_the_survey_lists():
+def test_shim_defines_every_moe_entry_point_of_the_reference_header():
     text = open(SHIM).read()
     for name in ("nvfp4_grouped_plan_create", "nvfp4_grouped_plan_destroy", "nvfp4_grouped_m1", "nvfp4_grouped_rows",
                  "bf16_gemv_f32", "bf16_gemm_f32", "router_top8", "router_top8_rows", "nvfp4_quantize",
