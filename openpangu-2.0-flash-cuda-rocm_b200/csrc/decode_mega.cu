@@ -117,6 +117,11 @@ __device__ __forceinline__ void grid_arrive(unsigned* counter) {
     }
 }
 
+// 16-byte asynchronous copy global -> shared (through the load/store unit).
+__device__ __forceinline__ void async_copy16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+
 template <int R>
 __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                       const __grid_constant__ CUtensorMap map_h,
@@ -179,11 +184,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     std::uint16_t* w_rows = reinterpret_cast<std::uint16_t*>(smem_raw + (base - smem_u32(smem_raw)));
     std::uint16_t* x_rows = w_rows + 2 * hidden;
     const int vec_per_row = hidden / 8;
+    // (asynchronous 16-byte copies: the token rows below are requested behind them without waiting for these, so the
+    // block pays one round trip to the L2 for both, not two)
     for (int i = threadIdx.x; i < my_experts * vec_per_row; i += kMegaThreads) {
         const int r = i / vec_per_row;
         const int c = i - r * vec_per_row;
-        reinterpret_cast<uint4*>(w_rows + r * hidden)[c] =
-            __ldg(reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
+        async_copy16(reinterpret_cast<uint4*>(w_rows + r * hidden) + c,
+                     reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
     }
     for (int e = threadIdx.x; e < kExperts; e += kMegaThreads) rt.bias[e] = __ldg(p.bias + e);
     pdl_wait();                       // the token rows come from the kernel before this one
@@ -193,9 +200,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     for (int i = threadIdx.x; i < rows * vec_per_row; i += kMegaThreads) {
         const int r = i / vec_per_row;
         const int c = i - r * vec_per_row;
-        reinterpret_cast<uint4*>(x_rows + r * hidden)[c] =
-            __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r) * hidden) + c);
+        async_copy16(reinterpret_cast<uint4*>(x_rows + r * hidden) + c,
+                     reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r) * hidden) + c);
     }
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
