@@ -183,8 +183,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     for (int i = threadIdx.x; i < my_experts * vec_per_row; i += kEpThreads) {
         const int r = i / vec_per_row;
         const int c = i - r * vec_per_row;
-        reinterpret_cast<uint4*>(w_rows + r * hidden)[c] =
-            __ldg(reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
+        async_copy16(reinterpret_cast<uint4*>(w_rows + r * hidden) + c,
+                     reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
     }
     for (int e = threadIdx.x; e < kExperts; e += kEpThreads) rt.bias[e] = __ldg(p.bias + e);
     pdl_wait();
@@ -194,9 +194,10 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
     for (int i = threadIdx.x; i < rows * vec_per_row; i += kEpThreads) {
         const int r = i / vec_per_row;
         const int c = i - r * vec_per_row;
-        reinterpret_cast<uint4*>(x_rows + r * hidden)[c] =
-            __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r) * hidden) + c);
+        async_copy16(reinterpret_cast<uint4*>(x_rows + r * hidden) + c,
+                     reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r) * hidden) + c);
     }
+    async_copies_wait();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

@@ -117,11 +117,6 @@ __device__ __forceinline__ void grid_arrive(unsigned* counter) {
     }
 }
 
-// 16-byte asynchronous copy global -> shared (through the load/store unit).
-__device__ __forceinline__ void async_copy16(void* dst_smem, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-
 template <int R>
 __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                       const __grid_constant__ CUtensorMap map_h,
@@ -203,7 +198,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
         async_copy16(reinterpret_cast<uint4*>(x_rows + r * hidden) + c,
                      reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r) * hidden) + c);
     }
-    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+    async_copies_wait();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

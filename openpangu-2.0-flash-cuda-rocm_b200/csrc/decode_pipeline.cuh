@@ -40,6 +40,15 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+// 16-byte asynchronous copy global -> shared (through the load/store unit); the kernels' prologues bring the router
+// rows and the token rows in with these so that the second request does not wait for the first answer.
+__device__ __forceinline__ void async_copy16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void async_copies_wait() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
 // Bounded wait (one second of wall time) until *counter has reached `target`; wrap-safe.
 __device__ __forceinline__ bool wait_counter(const unsigned* counter, unsigned target) {
     const std::uint64_t start = global_timer_ns();
