@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) moe_decode_ep_kernel(const __gr
         async_copy16(reinterpret_cast<uint4*>(w_rows + r * hidden) + c,
                      reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
     }
-    for (int e = threadIdx.x; e < kExperts; e += kEpThreads) rt.bias[e] = __ldg(p.bias + e);
+    for (int e = threadIdx.x; e < kExperts; e += kEpThreads) async_copy4(&rt.bias[e], p.bias + e);
     pdl_wait();
     pdl_launch_dependents();
     // the first tile number is asked for now and used after the routing, the atomic's latency in between

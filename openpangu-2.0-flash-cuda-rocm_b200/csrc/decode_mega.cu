@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
         async_copy16(reinterpret_cast<uint4*>(w_rows + r * hidden) + c,
                      reinterpret_cast<const uint4*>(p.router_w + static_cast<std::size_t>(block + r * grid) * hidden) + c);
     }
-    for (int e = threadIdx.x; e < kExperts; e += kMegaThreads) rt.bias[e] = __ldg(p.bias + e);
+    for (int e = threadIdx.x; e < kExperts; e += kMegaThreads) async_copy4(&rt.bias[e], p.bias + e);
     pdl_wait();                       // the token rows come from the kernel before this one
     pdl_launch_dependents();
     // the first tile number is asked for now and used after the routing, the atomic's latency in between
