@@ -190,14 +190,15 @@ __global__ void __launch_bounds__(kMegaThreads, 1) moe_decode_kernel(const __gri
     for (int e = threadIdx.x; e < kExperts; e += kMegaThreads) async_copy4(&rt.bias[e], p.bias + e);
     pdl_wait();                       // the token rows come from the kernel before this one
     pdl_launch_dependents();
-    // the first tile number is asked for now and used after the routing, the atomic's latency in between
-    if (threadIdx.x == 0) first_tile_word = static_cast<int>(atomicAdd(tile_counter, 1U));
     for (int i = threadIdx.x; i < rows * vec_per_row; i += kMegaThreads) {
         const int r = i / vec_per_row;
         const int c = i - r * vec_per_row;
         async_copy16(reinterpret_cast<uint4*>(x_rows + r * hidden) + c,
                      reinterpret_cast<const uint4*>(p.x + static_cast<std::size_t>(r) * hidden) + c);
     }
+    // the first tile number is asked for now and used after the routing, the atomic's latency in between; behind the
+    // copies, because the store of its result makes the warp wait for the answer
+    if (threadIdx.x == 0) first_tile_word = static_cast<int>(atomicAdd(tile_counter, 1U));
     async_copies_wait();
     tc_fence_before();
     __syncthreads();
