@@ -191,7 +191,7 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->mega_logits = c.take<unsigned long long>(static_cast<std::size_t>(16) * kExperts);
         plan->mega_ret = c.take<unsigned long long>(static_cast<std::size_t>(16) * (kTop + 1) * 1280);
         plan->mega_trace = c.take<unsigned long long>(static_cast<std::size_t>(plan->sm_count) * 64);
-        plan->w_norms = c.take<float>(kExperts);
+        plan->w_norms = c.take<float>(2 * kExperts);
         plan->router_stats = c.take<int>(2);
         plan->logit_partials = c.take<float>(static_cast<std::size_t>(kRouterSplits) * std::min(max_rows, kRouterSplitRows) * kExperts);
         plan->mega_hidden = c.take<unsigned long long>(static_cast<std::size_t>(16) * (hidden / 2));

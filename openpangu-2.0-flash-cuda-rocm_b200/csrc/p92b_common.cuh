@@ -260,7 +260,8 @@ struct p92b_plan {
     unsigned long long* ep_logits = nullptr;    // [8][256] its router logits as tagged words
     unsigned long long* mega_logits = nullptr;  // [8][256] router logits as {value, launch number} words
     unsigned long long* mega_ret = nullptr;     // [8][9][1280] down rows as {two BF16, launch number} words
-    float* w_norms = nullptr;                   // [256] norms of the router rows (large-batch router)
+    float* w_norms = nullptr;                   // [2][256] norms of the router rows (tensor-core router), alternating by call
+    int norms_parity = 0;
     float* logit_partials = nullptr;            // [kRouterSplits][min(max_rows, kRouterSplitRows)][256] partial logits of the K splits
     int* router_stats = nullptr;                // [2] large-batch router: logits recomputed exactly so far, tokens that took a whole row
     unsigned long long* mega_hidden = nullptr;  // [8][H/2] un-normalised output rows as tagged words (fused post-norm)

@@ -70,12 +70,17 @@ __host__ __device__ constexpr std::uint32_t idesc_bf16(int m, int n) {
 
 __global__ void __launch_bounds__(256) expert_norms_kernel(const std::uint16_t* __restrict__ w, float* __restrict__ norms,
                                                            int experts, int hidden) {
+    // Nothing here reads the upstream kernel's output, so the work comes first and overlaps that kernel's tail; the wait
+    // comes last (the kernels behind this one rely on the chain: a kernel that finished without waiting would let them
+    // start before the token rows are written).  `norms` alternates between two buffers from call to call, so a repair
+    // kernel of the call before cannot still be reading what this one writes.
     pdl_launch_dependents();
-    pdl_wait();       // nothing here reads the upstream kernel's output, but the kernels behind this one rely on the chain:
-                      // a kernel that finished without waiting would let them start before the token rows are written
     const int e = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
-    if (e >= experts) return;
+    if (e >= experts) {
+        pdl_wait();
+        return;
+    }
     float s = 0.0F;
     const uint4* row = reinterpret_cast<const uint4*>(w + static_cast<std::size_t>(e) * hidden);
 #pragma unroll 4
@@ -92,6 +97,7 @@ __global__ void __launch_bounds__(256) expert_norms_kernel(const std::uint16_t* 
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffU, s, off);
     if (lane == 0) norms[e] = sqrtf(s) * 1.0001F;             // rounded up a little: it feeds a bound
+    pdl_wait();
 }
 
 __global__ void __launch_bounds__(kLogitThreads, 1) logits_tc_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -525,7 +531,8 @@ cudaError_t launch_router_fast(p92b_plan* plan, const std::uint16_t* x, const st
                           : ensure_dynamic_smem<route_repair_kernel<0, 1>>(static_cast<int>(repair_smem));
     }
     if (st != cudaSuccess) return st;
-    st = launch_kernel(expert_norms_kernel, dim3(kExperts / 8), dim3(256), 0, stream, pdl, router_w, plan->w_norms, kExperts, hidden);
+    float* norms = plan->w_norms + (plan->norms_parity ^= 1) * kExperts;
+    st = launch_kernel(expert_norms_kernel, dim3(kExperts / 8), dim3(256), 0, stream, pdl, router_w, norms, kExperts, hidden);
     if (st != cudaSuccess) return st;
     float* approx_out = splits > 1 ? plan->logit_partials : plan->logits;
     st = launch_kernel(logits_tc_kernel, dim3((rows + kTokTile - 1) / kTokTile, kExperts / kExpTile, splits), dim3(kLogitThreads),
@@ -535,12 +542,12 @@ cudaError_t launch_router_fast(p92b_plan* plan, const std::uint16_t* x, const st
     if (small) {
         st = launch_kernel(in_registers ? route_repair_kernel<80, kWide> : route_repair_kernel<0, kWide>, dim3(rows),
                            dim3(kWide * 32), repair_smem, stream, pdl, x, router_w, bias,
-                           static_cast<const float*>(plan->w_norms), plan->logits, plan->ids, plan->route_weights, rows, hidden,
+                           static_cast<const float*>(norms), plan->logits, plan->ids, plan->route_weights, rows, hidden,
                            routed_scale, plan->router_stats, partials, splits);
     } else {
         st = launch_kernel(in_registers ? route_repair_kernel<80, 1> : route_repair_kernel<0, 1>,
                            dim3((rows + kRepairWarps - 1) / kRepairWarps), dim3(kRepairWarps * 32), repair_smem, stream, pdl, x,
-                           router_w, bias, static_cast<const float*>(plan->w_norms), plan->logits, plan->ids,
+                           router_w, bias, static_cast<const float*>(norms), plan->logits, plan->ids,
                            plan->route_weights, rows, hidden, routed_scale, plan->router_stats, partials, splits);
     }
     plan->last_launches += 3;
