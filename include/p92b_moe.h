@@ -142,7 +142,8 @@ int p92b_moe_permute(p92b_plan* plan, const int32_t* expert_ids, int assignments
  *     cudaGetSymbolAddress with that device current) and remembers it; make that first call
  *     before starting any stream capture on that device;
  *   - all calls on a device share the one array, which still holds the previous call's contents:
- *     the entry point clears the status word itself and overwrites every histogram it reads, but
+ *     the entry point clears the status word and its scan's block counter itself and overwrites
+ *     every histogram it reads, but
  *     two calls whose kernels overlap on the GPU (different streams) race and must be serialised
  *     by the caller;
  *   - outputs as p92b_moe_permute: order/position may be NULL, counts[256], offsets[257]. */

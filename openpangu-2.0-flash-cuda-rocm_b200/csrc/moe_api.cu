@@ -175,6 +175,7 @@ int p92b_plan_create(p92b_plan** out, int max_rows, int hidden, int intermediate
         plan->tile_prefix_wide = c.take<std::int32_t>(kExperts + 2);
         plan->pp_of_flat = c.take<std::int32_t>(rows * (kTop + 1));
         plan->chunk_hist = c.take<std::int32_t>(static_cast<std::size_t>(plan->chunks) * kExperts);
+        plan->scan_blocks_done = c.take<unsigned>(1);
         plan->xq = c.take<std::uint8_t>(rows * (hidden / 2));
         plan->xs = c.take<std::uint8_t>(rows * (hidden / 16));
         plan->xq_pp = c.take<std::uint8_t>(plan->pp_rows * (hidden / 2));

@@ -223,6 +223,7 @@ struct p92b_plan {
     int wide_rows = 0;                    // token tile tile_prefix_wide was last built for (0: not built)
     std::int32_t* pp_of_flat = nullptr;   // [9*max_rows] padded position of (row, slot), shared rows last
     std::int32_t* chunk_hist = nullptr;   // [chunks][256]
+    unsigned* scan_blocks_done = nullptr; // [1] blocks of the permutation's scan kernel that have finished (zero between calls)
     int chunks = 0;
     std::uint8_t* xq = nullptr;           // [max_rows][H/2]
     std::uint8_t* xs = nullptr;           // [max_rows][H/16]

@@ -248,31 +248,37 @@ __global__ void __launch_bounds__(256) permute_hist_kernel(const std::int32_t* _
     }
 }
 
-// Exclusive prefix over the chunks, per expert, then the lists.  1024 threads: expert e = thread % 256 has four
-// threads, each owning a quarter of the chunks (a sum pass, the quarter bases through shared memory, then the pass
-// that writes the prefixes); at 131,072 assignments one thread per expert walking 512 chunks took 60 µs.
+// Exclusive prefix over the chunks, per expert, then the lists.  gridDim.x blocks of 1024 threads share the experts
+// (256 / gridDim.x each); an expert has 1024 / that many threads, each owning a slice of the chunks: a sum pass, the
+// slice bases through shared memory, then the pass that writes the prefixes.  The block that finishes last (a counter,
+// reset by that block for the next call) adds the scan over the 256 expert totals and writes the lists.  One thread
+// per expert walking 512 chunks took 60 µs at 131,072 assignments, one block with four threads per expert 22 µs.
 constexpr int kScanThreads = 1024;
-constexpr int kScanSegments = kScanThreads / kExperts;
+constexpr int kScanBlocksLarge = 8;
 __global__ void __launch_bounds__(kScanThreads) permute_scan_kernel(std::int32_t* __restrict__ chunk_hist, int chunks,
-                                                                    int assignments, RouteLists lists, int shared_rows) {
+                                                                    int assignments, RouteLists lists, int shared_rows,
+                                                                    unsigned* __restrict__ blocks_done) {
     __shared__ std::int32_t scan_scratch[kWarps];
-    __shared__ std::int32_t segment_total[kScanSegments][kExperts];
+    __shared__ std::int32_t segment_total[kScanThreads];
+    __shared__ int is_last;
     pdl_launch_dependents();
     pdl_wait();
-    const int e = threadIdx.x % kExperts;
-    const int segment = threadIdx.x / kExperts;
-    const int per_segment = (chunks + kScanSegments - 1) / kScanSegments;
+    const int experts_here = kExperts / static_cast<int>(gridDim.x);          // 256 or 32
+    const int segments = kScanThreads / experts_here;                        // 4 or 32
+    const int e_local = threadIdx.x % experts_here;
+    const int segment = threadIdx.x / experts_here;
+    const int e = static_cast<int>(blockIdx.x) * experts_here + e_local;
+    const int per_segment = (chunks + segments - 1) / segments;
     const int first = min(chunks, segment * per_segment);
     const int last = min(chunks, first + per_segment);
     int sum = 0;
 #pragma unroll 16
     for (int c = first; c < last; ++c) sum += chunk_hist[static_cast<std::size_t>(c) * kExperts + e];
-    segment_total[segment][e] = sum;
+    segment_total[segment * experts_here + e_local] = sum;
     __syncthreads();
     int running = 0, total = 0;
-#pragma unroll
-    for (int s = 0; s < kScanSegments; ++s) {
-        const int v = segment_total[s][e];
+    for (int s = 0; s < segments; ++s) {
+        const int v = segment_total[s * experts_here + e_local];
         if (s < segment) running += v;
         total += v;
     }
@@ -283,9 +289,23 @@ __global__ void __launch_bounds__(kScanThreads) permute_scan_kernel(std::int32_t
         chunk_hist[at] = running;
         running += v;
     }
-    if (segment != 0) return;                    // whole warps leave; the block-wide barriers below count the rest
-    const int offset = block_exclusive_scan_256(total, scan_scratch);
-    write_route_lists(e, total, offset, assignments, shared_rows >= 0 ? shared_rows : assignments / kTop, lists, scan_scratch);
+    if (segment == 0) lists.counts[e] = total;
+    // the last block to get here sees every block's totals
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned before = atomicAdd(blocks_done, 1U);
+        is_last = before + 1U == gridDim.x ? 1 : 0;
+        if (is_last) *blocks_done = 0U;
+    }
+    __syncthreads();
+    if (!is_last || threadIdx.x >= kExperts) return;   // whole warps leave; the block-wide barriers below count the rest
+    __threadfence();
+    const int expert = threadIdx.x;
+    const int expert_total = __ldcg(lists.counts + expert);
+    const int offset = block_exclusive_scan_256(expert_total, scan_scratch);
+    write_route_lists(expert, expert_total, offset, assignments, shared_rows >= 0 ? shared_rows : assignments / kTop, lists,
+                      scan_scratch);
 }
 
 __global__ void __launch_bounds__(256) permute_scatter_kernel(
@@ -518,8 +538,8 @@ cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignm
     cudaError_t st = launch_kernel(permute_hist_kernel, dim3(blocks), dim3(256), 0, stream, pdl, ids, assignments,
                                    plan->chunk_hist, plan->status, range);
     if (st != cudaSuccess) return st;
-    st = launch_kernel(permute_scan_kernel, dim3(1), dim3(kScanThreads), 0, stream, pdl, plan->chunk_hist, chunks, assignments,
-                       lists, shared_rows);
+    st = launch_kernel(permute_scan_kernel, dim3(chunks >= 64 ? kScanBlocksLarge : 1), dim3(kScanThreads), 0, stream, pdl,
+                       plan->chunk_hist, chunks, assignments, lists, shared_rows, plan->scan_blocks_done);
     if (st != cudaSuccess) return st;
     return launch_kernel(permute_scatter_kernel, dim3(blocks), dim3(256), 0, stream, pdl,
                          static_cast<const std::int32_t*>(ids), assignments,
@@ -544,7 +564,7 @@ cudaError_t launch_permute(p92b_plan* plan, const std::int32_t* ids, int assignm
 // In host code the array's name is only a stand-in for the symbol, not a device
 // address, so the address is fetched once per device with cudaGetSymbolAddress
 // (that device current) and handed to the kernels as an ordinary pointer.
-// Layout: [chunks][256] int32 chunk histograms, then the status word.
+// Layout: [chunks][256] int32 chunk histograms, then the status word and the scan kernel's block counter.
 //
 // The address cache below is filled on first use per device.  Two host threads that make their
 // first call on the same device at the same time both look the address up and both store the
@@ -600,9 +620,9 @@ extern "C" int p92b_moe_permute_static(const int32_t* expert_ids, int assignment
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     std::int32_t* chunk_hist = scratch;
     std::int32_t* status = scratch + kStaticChunks * kExperts;
-    // the array still holds the previous call's words: the status word must start at zero,
+    // the array still holds the previous call's words: the status word and the block counter must start at zero,
     // the histograms are fully rewritten by permute_hist_kernel before anything reads them
-    st = cudaMemsetAsync(status, 0, sizeof(std::int32_t), stream);
+    st = cudaMemsetAsync(status, 0, 2 * sizeof(std::int32_t), stream);       // the status word and the scan's block counter
     if (st != cudaSuccess) return st;
     RouteLists lists {};
     lists.counts = counts;
@@ -620,7 +640,8 @@ extern "C" int p92b_moe_permute_static(const int32_t* expert_ids, int assignment
     const int chunks = (assignments + kChunk - 1) / kChunk;
     const int blocks = (chunks + kWarps - 1) / kWarps;
     permute_hist_kernel<<<blocks, 256, 0, stream>>>(expert_ids, assignments, chunk_hist, status, IdRange());
-    permute_scan_kernel<<<1, p92b::kScanThreads, 0, stream>>>(chunk_hist, chunks, assignments, lists, -1);
+    permute_scan_kernel<<<chunks >= 64 ? p92b::kScanBlocksLarge : 1, p92b::kScanThreads, 0, stream>>>(
+        chunk_hist, chunks, assignments, lists, -1, reinterpret_cast<unsigned*>(status + 1));
     permute_scatter_kernel<<<blocks, 256, 0, stream>>>(expert_ids, assignments, chunk_hist, offsets, order, position,
                                                        nullptr, nullptr, nullptr, IdRange(), -1);
     return cudaGetLastError();
