@@ -1115,26 +1115,35 @@ __global__ void __launch_bounds__(256) quantize_padded_kernel(const std::uint16_
     const int col_blocks = (blocks + 3) / 4;
     constexpr int kMaxPerLane = 8;                   // hidden <= 4096
     uint2 packed[kMaxPerLane];
-    std::uint8_t scale_bits[kMaxPerLane];
+    std::uint32_t scale_word[kMaxPerLane];           // lanes 0, 4, 8, ...: the scales of four neighbouring blocks
+    // the nine destinations of the row, fetched before the row itself so that the stores wait for nothing
+    const int place_index = lane < kTop ? token * kTop + lane : rows * kTop + token;
+    const int my_pp = lane <= kTop ? __ldg(pp_of_flat + place_index) : 0;
 #pragma unroll
     for (int j = 0; j < kMaxPerLane; ++j) {
         const int b = lane + 32 * j;
-        if (b >= blocks) break;
-        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(token) * hidden + b * 16);
-        const uint4 lo = __ldg(src);
-        const uint4 hi = __ldg(src + 1);
-        const std::uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        float v[16];
+        std::uint8_t scale_bits = 0;
+        if (b < blocks) {                            // blocks is a multiple of 4: a quad of lanes is in or out together
+            const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<std::size_t>(token) * hidden + b * 16);
+            const uint4 lo = __ldg(src);
+            const uint4 hi = __ldg(src + 1);
+            const std::uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            float v[16];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            v[2 * i] = __uint_as_float(words[i] << 16);
-            v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+            for (int i = 0; i < 8; ++i) {
+                v[2 * i] = __uint_as_float(words[i] << 16);
+                v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000U);
+            }
+            packed[j] = quantize_block16(v, global_scale, &scale_bits);
         }
-        packed[j] = quantize_block16(v, global_scale, &scale_bits[j]);
+        std::uint32_t word = scale_bits;
+        word |= __shfl_down_sync(0xffffffffU, word, 1) << 8;
+        word |= __shfl_down_sync(0xffffffffU, word, 2) << 16;
+        scale_word[j] = word;
     }
+#pragma unroll 1
     for (int place = 0; place <= kTop; ++place) {
-        const int index = place < kTop ? token * kTop + place : rows * kTop + token;
-        const std::size_t pp = static_cast<std::size_t>(pp_of_flat[index]);
+        const std::size_t pp = static_cast<std::size_t>(__shfl_sync(0xffffffffU, my_pp, place));
         std::uint8_t* row_q = xq + pp * (hidden / 2);
         std::uint8_t* row_s = xs + (pp >> 7) * col_blocks * 512 + (pp & 31) * 16 + ((pp >> 5) & 3) * 4;
 #pragma unroll
@@ -1142,7 +1151,7 @@ __global__ void __launch_bounds__(256) quantize_padded_kernel(const std::uint16_
             const int b = lane + 32 * j;
             if (b >= blocks) break;
             *reinterpret_cast<uint2*>(row_q + b * 8) = packed[j];
-            row_s[(b >> 2) * 512 + (b & 3)] = scale_bits[j];
+            if ((lane & 3) == 0) *reinterpret_cast<std::uint32_t*>(row_s + (b >> 2) * 512) = scale_word[j];
         }
     }
 }
