@@ -60,14 +60,27 @@ __device__ __forceinline__ void warp_histogram(const std::int32_t* __restrict__ 
     }
 }
 
-// Scatters one chunk.  base[e] = first position of this chunk's rows of expert e;
-// running[256] is warp-private scratch.
+// A warp's ids once into shared memory, all loads in flight together, clamped to -1 .. 256 so that they fit 16 bits
+// and an id out of range stays out of range.
+__device__ __forceinline__ void load_chunk_ids(const std::int32_t* __restrict__ ids, int begin, int end,
+                                               std::int16_t* cached) {
+    for (int i = begin + (threadIdx.x & 31); i < end; i += 32) {
+        const int e = ids[i];
+        cached[i - begin] = static_cast<std::int16_t>(e < -1 ? -1 : (e > kExperts ? kExperts : e));
+    }
+    __syncwarp();
+}
+
+// Scatters one chunk.  base[e] = first position of this chunk's rows of expert e; running[256] is warp-private
+// scratch; pp_delta[e] (shared memory, read only with pp_of_flat) = padded offset - offset of expert e.  The steps
+// of a chunk depend on one another through running[], so whatever a step reads has to be in shared memory or in
+// registers already: a global load per step is a round trip to the L2 per step.
 __device__ __forceinline__ void warp_scatter(const std::int32_t* __restrict__ ids, int begin, int end,
                                              const std::int32_t* base, std::int32_t* running,
                                              std::int32_t* __restrict__ order,
                                              std::int32_t* __restrict__ position,
                                              std::int32_t* __restrict__ row_token,
-                                             const std::int32_t* offsets, const std::int32_t* pp_off,
+                                             const std::int32_t* pp_delta,
                                              std::int32_t* __restrict__ pp_of_flat,
                                              const std::int16_t* cached = nullptr, IdRange range = IdRange()) {
     const int lane = threadIdx.x & 31;
@@ -94,7 +107,7 @@ __device__ __forceinline__ void warp_scatter(const std::int32_t* __restrict__ id
             if (order != nullptr) order[pos] = i;
             if (position != nullptr) position[i] = pos;
             if (row_token != nullptr) row_token[pos] = i / kTop;
-            if (pp_of_flat != nullptr) pp_of_flat[i] = pp_off[e] + pos - offsets[e];
+            if (pp_of_flat != nullptr) pp_of_flat[i] = pp_delta[e] + pos;
         }
         __syncwarp();
         if (valid && rank == 0) running[e] += __popc(peers);
@@ -189,6 +202,7 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
     __shared__ std::int32_t hist[kWarps][kExperts];
     __shared__ std::int32_t running[kWarps][kExperts];
     __shared__ std::int32_t scan_scratch[kWarps];
+    __shared__ std::int32_t pp_delta[kExperts];
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5;
@@ -198,11 +212,7 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
     // the warp's ids once into shared memory, all loads in flight together: the two passes below are chains of
     // dependent 32-wide steps and would otherwise pay a global-memory round trip per step
     __shared__ std::int16_t cached_ids[kWarps][1024];
-    for (int i = begin + (threadIdx.x & 31); i < end; i += 32) {
-        const int e = ids[i];
-        cached_ids[warp][i - begin] = static_cast<std::int16_t>(e < -1 ? -1 : (e > kExperts ? kExperts : e));   // out-of-range stays out of range
-    }
-    __syncwarp();
+    load_chunk_ids(ids, begin, end, cached_ids[warp]);
     warp_histogram(ids, begin, end, hist[warp], status, cached_ids[warp], range);
     __syncthreads();
     const int e = threadIdx.x;
@@ -218,9 +228,10 @@ __global__ void __launch_bounds__(256) permute_small_kernel(
     for (int wi = 0; wi < kWarps; ++wi) hist[wi][e] += offset;
     const int rows = shared_rows >= 0 ? shared_rows : assignments / kTop;
     write_route_lists(e, total, offset, assignments, rows, lists, scan_scratch);
+    pp_delta[e] = (pp_of_flat != nullptr && lists.pp_off != nullptr) ? lists.pp_off[e] - offset : 0;       // write_route_lists stored both just above
     __syncthreads();
-    warp_scatter(ids, begin, end, hist[warp], running[warp], order, position, row_token, lists.offsets, lists.pp_off,
-                 pp_of_flat, cached_ids[warp], range);
+    warp_scatter(ids, begin, end, hist[warp], running[warp], order, position, row_token, pp_delta, pp_of_flat,
+                 cached_ids[warp], range);
     if (row_token != nullptr) {
         for (int t = threadIdx.x; t < rows; t += blockDim.x) {
             row_token[assignments + t] = t;
@@ -235,6 +246,7 @@ __global__ void __launch_bounds__(256) permute_hist_kernel(const std::int32_t* _
                                                            std::int32_t* __restrict__ chunk_hist,
                                                            std::int32_t* status, IdRange range) {
     __shared__ std::int32_t hist[kWarps][kExperts];
+    __shared__ std::int16_t cached_ids[kWarps][kChunk];
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5;
@@ -242,7 +254,8 @@ __global__ void __launch_bounds__(256) permute_hist_kernel(const std::int32_t* _
     const int chunk = blockIdx.x * kWarps + warp;
     const int begin = min(assignments, chunk * kChunk);
     const int end = min(assignments, begin + kChunk);
-    warp_histogram(ids, begin, end, hist[warp], status, nullptr, range);
+    load_chunk_ids(ids, begin, end, cached_ids[warp]);
+    warp_histogram(ids, begin, end, hist[warp], status, cached_ids[warp], range);
     if (begin < assignments) {
         for (int e = lane; e < kExperts; e += 32) chunk_hist[static_cast<std::size_t>(chunk) * kExperts + e] = hist[warp][e];
     }
@@ -315,6 +328,8 @@ __global__ void __launch_bounds__(256) permute_scatter_kernel(
     int shared_rows) {
     __shared__ std::int32_t base[kWarps][kExperts];
     __shared__ std::int32_t running[kWarps][kExperts];
+    __shared__ std::int32_t pp_delta[kExperts];
+    __shared__ std::int16_t cached_ids[kWarps][kChunk];
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5;
@@ -322,14 +337,16 @@ __global__ void __launch_bounds__(256) permute_scatter_kernel(
     const int chunk = blockIdx.x * kWarps + warp;
     const int begin = min(assignments, chunk * kChunk);
     const int end = min(assignments, begin + kChunk);
+    load_chunk_ids(ids, begin, end, cached_ids[warp]);
+    pp_delta[threadIdx.x] = pp_of_flat != nullptr ? pp_off[threadIdx.x] - offsets[threadIdx.x] : 0;
     if (begin < assignments) {
         for (int e = lane; e < kExperts; e += 32) {
             base[warp][e] = offsets[e] + chunk_hist[static_cast<std::size_t>(chunk) * kExperts + e];
         }
     }
-    __syncwarp();
-    warp_scatter(ids, begin, end, base[warp], running[warp], order, position, row_token, offsets, pp_off, pp_of_flat,
-                 nullptr, range);
+    __syncthreads();
+    warp_scatter(ids, begin, end, base[warp], running[warp], order, position, row_token, pp_delta, pp_of_flat,
+                 cached_ids[warp], range);
     if (row_token != nullptr) {
         const int rows = shared_rows >= 0 ? shared_rows : assignments / kTop;
         const int t = blockIdx.x * blockDim.x + threadIdx.x;
